@@ -1,0 +1,175 @@
+// Embedding lookup, rotation tables and row-wise RMS norms (with the residual
+// sum folded in).  One templated kernel per operation serves the bfloat16 and
+// the 32-bit path; statistics, the residual stream and the rotation angles are
+// 32-bit (angles are formed in 64-bit and rounded once).
+//
+// Reference formulas: embedding * sqrt(H) src/models/gemma3.zig:1017-1046;
+// RMS norm with eps inside the root src/backend/kernels/cuda/rms_norm.zig:22-29;
+// rotation angle src/backend/kernels/cuda/rope.zig:9-37 (here without the
+// approximate sin/cos).
+#include "common.cuh"
+
+// ------------------------------------------------------------------ embedding
+template <typename TW>
+__global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
+                             float* __restrict__ out, int H, int V, float scale) {
+    const int t = blockIdx.x;
+    int tok = tokens[t];
+    if (tok < 0 || tok >= V) tok = 0;   // callers validate ids; never read outside the table
+    const TW* row = table + (size_t)tok * H;
+    float* o = out + (size_t)t * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_f32(row[i]) * scale;
+}
+
+AGV_API int agv_embed(const int* tokens, const void* table, int table_dtype, float* out, int T,
+                      int H, int V, float scale, cudaStream_t stream) {
+    AGV_REQUIRE(T >= 0 && H > 0 && V > 0, "embed: bad sizes T=%d H=%d V=%d", T, H, V);
+    if (T == 0) return 0;
+    const int threads = H >= 1024 ? 256 : 128;
+    if (table_dtype == AGV_F32)
+        embed_kernel<float><<<T, threads, 0, stream>>>(tokens, (const float*)table, out, H, V, scale);
+    else if (table_dtype == AGV_BF16)
+        embed_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>(tokens, (const __nv_bfloat16*)table,
+                                                               out, H, V, scale);
+    else
+        return agv_fail(-1, "embed: unknown dtype %d", table_dtype);
+    AGV_LAUNCH_OK("embed_kernel");
+    return 0;
+}
+
+// ------------------------------------------------------------ rotation tables
+__global__ void rope_table_kernel(const int* __restrict__ positions, float* __restrict__ cosv,
+                                  float* __restrict__ sinv, int T, int half, double log_theta,
+                                  double inv_factor, int rotary_dim) {
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= T * half) return;
+    const int t = idx / half, i = idx % half;
+    const double freq = exp(-log_theta * (2.0 * i) / (double)rotary_dim);
+    const double a = (double)positions[t] * inv_factor * freq;
+    double s, c;
+    sincos(a, &s, &c);
+    cosv[idx] = (float)c;
+    sinv[idx] = (float)s;
+}
+
+// cos, sin: [T, rotary_dim/2] for angle = (p / factor) * theta^(-2i/rotary_dim).
+AGV_API int agv_rope_table(const int* positions, float* cosv, float* sinv, int T, int rotary_dim,
+                           double theta, double factor, cudaStream_t stream) {
+    AGV_REQUIRE(rotary_dim > 0 && rotary_dim % 2 == 0, "rope_table: rotary_dim %d must be even",
+                rotary_dim);
+    AGV_REQUIRE(theta > 0 && factor > 0, "rope_table: theta and factor must be positive");
+    if (T == 0) return 0;
+    const int half = rotary_dim / 2, n = T * half;
+    rope_table_kernel<<<(n + 127) / 128, 128, 0, stream>>>(positions, cosv, sinv, T, half,
+                                                           log(theta), 1.0 / factor, rotary_dim);
+    AGV_LAUNCH_OK("rope_table_kernel");
+    return 0;
+}
+
+// ----------------------------------------------------------------- RMS norms
+// One block per row.  With y == nullptr: x = norm(h[rows[r]]; w_next).
+// Otherwise: b = sum over splits of y; if w_post: b = norm(b; w_post);
+// h += b; if w_next: x = norm(h; w_next).
+template <typename TY, typename TX>
+__global__ void norm_residual_kernel(float* __restrict__ h, const TY* __restrict__ y, int n_splits,
+                                     size_t split_stride, const float* __restrict__ w_post,
+                                     const float* __restrict__ w_next, TX* __restrict__ x,
+                                     const int* __restrict__ rows, int H, float eps_post,
+                                     float eps_next, int add_residual) {
+    extern __shared__ float row[];
+    __shared__ float red[33];
+    const int r = blockIdx.x;
+    const size_t src = (size_t)(rows ? rows[r] : r) * H;
+    const size_t dst = (size_t)r * H;
+    if (y) {
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < H; i += blockDim.x) {
+            float v = 0.f;
+            for (int s = 0; s < n_splits; ++s) v += to_f32(y[s * split_stride + src + i]);
+            row[i] = v;
+            ss += v * v;
+        }
+        float rs = 1.f;
+        if (w_post) {
+            ss = block_sum(ss, red);
+            rs = 1.0f / sqrtf(ss / (float)H + eps_post);
+        }
+        float ss2 = 0.f;
+        for (int i = threadIdx.x; i < H; i += blockDim.x) {
+            float v = row[i];
+            if (w_post) v = v * rs * w_post[i];
+            if (add_residual) {
+                v += h[src + i];
+                h[src + i] = v;
+            }
+            row[i] = v;
+            ss2 += v * v;
+        }
+        if (w_next) {
+            ss2 = block_sum(ss2, red);
+            const float r2 = 1.0f / sqrtf(ss2 / (float)H + eps_next);
+            for (int i = threadIdx.x; i < H; i += blockDim.x)
+                x[dst + i] = from_f32<TX>(row[i] * r2 * w_next[i]);
+        } else if (x) {
+            for (int i = threadIdx.x; i < H; i += blockDim.x) x[dst + i] = from_f32<TX>(row[i]);
+        }
+    } else {
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < H; i += blockDim.x) {
+            const float v = h[src + i];
+            row[i] = v;
+            ss += v * v;
+        }
+        ss = block_sum(ss, red);
+        const float r2 = 1.0f / sqrtf(ss / (float)H + eps_next);
+        for (int i = threadIdx.x; i < H; i += blockDim.x)
+            x[dst + i] = from_f32<TX>(row[i] * r2 * w_next[i]);
+    }
+}
+
+template <typename TY, typename TX>
+static int launch_norm(float* h, const void* y, int n_splits, size_t split_stride,
+                       const float* w_post, const float* w_next, void* x, const int* rows, int R,
+                       int H, float eps_post, float eps_next, int add_residual,
+                       cudaStream_t stream) {
+    const size_t smem = (size_t)H * sizeof(float);
+    auto kern = norm_residual_kernel<TY, TX>;
+    if (smem > 48 * 1024) {
+        AGV_REQUIRE(smem <= 200 * 1024, "norm: row width %d needs %zu bytes of shared memory, "
+                    "more than the 200 KB this kernel may take", H, smem);
+        AGV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem));
+    }
+    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    kern<<<R, threads, smem, stream>>>(h, (const TY*)y, n_splits, split_stride, w_post, w_next,
+                                       (TX*)x, rows, H, eps_post, eps_next, add_residual);
+    AGV_LAUNCH_OK("norm_residual_kernel");
+    return 0;
+}
+
+// h: [*, H] 32-bit residual stream.  y: [n_splits, R, H] branch output (y_dtype)
+// or null.  x: [R, H] output (x_dtype) or null.  rows: optional gather of h rows
+// (only with y == null).  See norm_residual_kernel for the arithmetic.
+AGV_API int agv_norm_residual(float* h, const void* y, int y_dtype, int n_splits,
+                              long long split_stride, const float* w_post, const float* w_next,
+                              void* x, int x_dtype, const int* rows, int R, int H, float eps_post,
+                              float eps_next, int add_residual, cudaStream_t stream) {
+    AGV_REQUIRE(R >= 0 && H > 0, "norm: bad sizes R=%d H=%d", R, H);
+    AGV_REQUIRE(y || (w_next && x && h), "norm: without a branch input, h, w_next and x are needed");
+    AGV_REQUIRE(!y || n_splits >= 1, "norm: n_splits must be >= 1");
+    AGV_REQUIRE(!(y && rows), "norm: row gather is only for the plain norm");
+    AGV_REQUIRE(!add_residual || h, "norm: the residual sum needs h");
+    AGV_REQUIRE(!w_next || x, "norm: w_next given without an output");
+    if (R == 0) return 0;
+#define AGV_NORM_CASE(TY, TX)                                                                   \
+    return launch_norm<TY, TX>(h, y, n_splits, (size_t)split_stride, w_post, w_next, x, rows, R, \
+                               H, eps_post, eps_next, add_residual, stream)
+    const int yd = y ? y_dtype : AGV_F32;
+    const int xd = x ? x_dtype : AGV_F32;
+    if (yd == AGV_F32 && xd == AGV_F32) AGV_NORM_CASE(float, float);
+    if (yd == AGV_F32 && xd == AGV_BF16) AGV_NORM_CASE(float, __nv_bfloat16);
+    if (yd == AGV_BF16 && xd == AGV_BF16) AGV_NORM_CASE(__nv_bfloat16, __nv_bfloat16);
+    if (yd == AGV_BF16 && xd == AGV_F32) AGV_NORM_CASE(__nv_bfloat16, float);
+#undef AGV_NORM_CASE
+    return agv_fail(-1, "norm: unknown dtypes y=%d x=%d", y_dtype, x_dtype);
+}

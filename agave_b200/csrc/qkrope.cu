@@ -1,0 +1,122 @@
+// Per-head RMS norm of q and k, rotation, and the write of k and v into the
+// paged cache, in one pass over the fused projection output.
+//
+// One warp per (token, head).  Reference order: norm before rotation
+// (src/models/gemma3.zig:724-748), split-half pairs (i, i + rotary_dim/2)
+// (src/backend/kernels/cuda/rope.zig:9-37), k stored after norm and rotation,
+// v as projected (src/backend/kernels/cpu/sdpa.zig:18-21).
+//
+// Cache addressing: position p of a sequence lives in ring row p % cap of its
+// slot; the row's page comes from the slot's page table.  A token whose row a
+// later token of the same step overwrites (p < len_after - cap) is not stored.
+#include "common.cuh"
+
+constexpr int QK_WARPS = 4;
+constexpr int QK_MAX_HD = 1024;
+
+struct CacheWrite {
+    void* k_pool;              // [n_pages, page, n_kv, hd] of this layer
+    void* v_pool;
+    const int* page_table;     // [n_slots, max_pages]
+    const int* slots;          // [B]; negative: padding entry, nothing is stored
+    const int* lens;           // [B] length after this step
+    const int* seq_index;      // [T] token -> batch entry
+    int max_pages, page, cap;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(QK_WARPS * 32)
+qk_norm_rope_store_kernel(T* __restrict__ qkv, long long row_stride, int n_tokens, int nh, int nkv,
+                          int hd, const float* __restrict__ wq, const float* __restrict__ wk,
+                          float eps, const float* __restrict__ cosv,
+                          const float* __restrict__ sinv, int rotary_half,
+                          const int* __restrict__ positions, CacheWrite cw) {
+    extern __shared__ float smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int heads = nh + 2 * nkv;
+    const long long item = (long long)blockIdx.x * QK_WARPS + warp;
+    if (item >= (long long)n_tokens * heads) return;
+    const int t = (int)(item / heads), head = (int)(item % heads);
+    float* buf = smem + warp * hd;
+    T* src = qkv + (size_t)t * row_stride + (size_t)head * hd;
+    const bool is_q = head < nh, is_k = !is_q && head < nh + nkv;
+    const float* w = is_q ? wq : (is_k ? wk : nullptr);
+
+    float ss = 0.f;
+    for (int e = lane; e < hd; e += 32) {
+        const float v = to_f32(src[e]);
+        buf[e] = v;
+        ss += v * v;
+    }
+    if (!is_q && !is_k) {
+        // v head: stored as projected
+    } else {
+        if (w) {
+            ss = warp_sum(ss);
+            const float r = 1.0f / sqrtf(ss / (float)hd + eps);
+            for (int e = lane; e < hd; e += 32) buf[e] = buf[e] * r * w[e];
+        }
+        __syncwarp();
+        if (cosv) {
+            const float* c = cosv + (size_t)t * rotary_half;
+            const float* s = sinv + (size_t)t * rotary_half;
+            for (int e = lane; e < rotary_half; e += 32) {
+                const float re = buf[e], im = buf[e + rotary_half];
+                buf[e] = re * c[e] - im * s[e];
+                buf[e + rotary_half] = re * s[e] + im * c[e];
+            }
+        }
+        __syncwarp();
+        for (int e = lane; e < hd; e += 32) src[e] = from_f32<T>(buf[e]);
+    }
+    if (is_q || !cw.k_pool) return;
+    const int b = cw.seq_index[t];
+    const int slot = cw.slots[b];
+    if (slot < 0) return;
+    const int p = positions[t];
+    if (p < cw.lens[b] - cw.cap) return;
+    const int row = p % cw.cap;
+    const int page = cw.page_table[(size_t)slot * cw.max_pages + row / cw.page];
+    const int g = is_k ? head - nh : head - nh - nkv;
+    T* pool = (T*)(is_k ? cw.k_pool : cw.v_pool);
+    T* dst = pool + (((size_t)page * cw.page + row % cw.page) * nkv + g) * hd;
+    for (int e = lane; e < hd; e += 32) dst[e] = from_f32<T>(buf[e]);
+}
+
+// qkv: [T, nh + 2 nkv, hd] (row stride in elements), rewritten in place: q and k
+// heads normed (if wq / wk given) and rotated (if cos / sin given).  k and v
+// are also written to the layer's cache pools unless k_pool is null.
+AGV_API int agv_qk_norm_rope_store(void* qkv, int dtype, long long row_stride, int n_tokens, int nh,
+                                   int nkv, int hd, const float* wq, const float* wk, float eps,
+                                   const float* cosv, const float* sinv, int rotary_dim,
+                                   const int* positions, void* k_pool, void* v_pool,
+                                   const int* page_table, const int* slots, const int* lens,
+                                   const int* seq_index, int max_pages, int page, int cap,
+                                   cudaStream_t stream) {
+    AGV_REQUIRE(n_tokens >= 0 && nh > 0 && nkv > 0 && hd > 0, "qk_norm_rope: bad sizes");
+    AGV_REQUIRE(hd <= QK_MAX_HD, "qk_norm_rope: head_dim %d exceeds %d", hd, QK_MAX_HD);
+    AGV_REQUIRE(rotary_dim % 2 == 0 && rotary_dim <= hd, "qk_norm_rope: rotary_dim %d must be even "
+                "and at most head_dim %d", rotary_dim, hd);
+    AGV_REQUIRE(row_stride >= (long long)(nh + 2 * nkv) * hd, "qk_norm_rope: row stride too short");
+    AGV_REQUIRE(!k_pool || (v_pool && page_table && slots && lens && seq_index && page > 0 &&
+                            cap > 0 && max_pages > 0), "qk_norm_rope: incomplete cache arguments");
+    AGV_REQUIRE(!cosv || (sinv && positions), "qk_norm_rope: cos without sin or positions");
+    if (n_tokens == 0) return 0;
+    CacheWrite cw{k_pool, v_pool, page_table, slots, lens, seq_index, max_pages, page, cap};
+    const long long items = (long long)n_tokens * (nh + 2 * nkv);
+    const unsigned grid = (unsigned)((items + QK_WARPS - 1) / QK_WARPS);
+    const size_t smem = (size_t)QK_WARPS * hd * sizeof(float);
+    const int half = cosv ? rotary_dim / 2 : 0;
+    if (dtype == AGV_F32)
+        qk_norm_rope_store_kernel<float><<<grid, QK_WARPS * 32, smem, stream>>>(
+            (float*)qkv, row_stride, n_tokens, nh, nkv, hd, wq, wk, eps, cosv, sinv, half,
+            positions, cw);
+    else if (dtype == AGV_BF16)
+        qk_norm_rope_store_kernel<__nv_bfloat16><<<grid, QK_WARPS * 32, smem, stream>>>(
+            (__nv_bfloat16*)qkv, row_stride, n_tokens, nh, nkv, hd, wq, wk, eps, cosv, sinv, half,
+            positions, cw);
+    else
+        return agv_fail(-1, "qk_norm_rope: unknown dtype %d", dtype);
+    AGV_LAUNCH_OK("qk_norm_rope_store_kernel");
+    return 0;
+}

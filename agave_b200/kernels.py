@@ -1,0 +1,299 @@
+"""Python face of the CUDA library: one function per exported kernel launcher.
+
+Each function takes torch CUDA tensors, checks what the C side cannot see
+(device, dtype, contiguity), and launches on torch's current stream, so the
+calls can be recorded into a CUDA graph.  There is no fallback: without the
+compiled library, or on a tensor that is not on a CUDA device, the call raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+from typing import Optional
+
+import torch
+
+from .csrc import build as _build
+
+F32, BF16 = 0, 1
+ACT = {"gelu_tanh": 0, "silu": 1}
+
+_lib = None
+_lock = threading.Lock()
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def library() -> ctypes.CDLL:
+    """The loaded CUDA library (compiled on first use)."""
+    global _lib
+    if _lib is None:
+        with _lock:
+            if _lib is None:
+                path = _build.library_path()
+                try:
+                    lib = ctypes.CDLL(path)
+                except OSError as e:
+                    raise KernelError(f"the CUDA library {path} could not be loaded: {e}") from None
+                lib.agv_last_error.restype = ctypes.c_char_p
+                _lib = lib
+    return _lib
+
+
+def _check(rc: int) -> None:
+    if rc != 0:
+        raise KernelError(library().agv_last_error().decode("utf-8", "replace"))
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.float32:
+        return F32
+    if dt == torch.bfloat16:
+        return BF16
+    raise KernelError(f"dtype {dt} has no kernels (float32 and bfloat16 do)")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    if t is None:
+        return ctypes.c_void_p(0)
+    if not t.is_cuda:
+        raise KernelError("a tensor handed to a CUDA kernel is not on a CUDA device")
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _dense(t: torch.Tensor, what: str) -> None:
+    if not t.is_contiguous():
+        raise KernelError(f"{what} must be contiguous")
+
+
+def _i32(t: Optional[torch.Tensor], what: str) -> None:
+    if t is not None and t.dtype != torch.int32:
+        raise KernelError(f"{what} must be int32, got {t.dtype}")
+
+
+def _f32(t: Optional[torch.Tensor], what: str) -> None:
+    if t is not None and t.dtype != torch.float32:
+        raise KernelError(f"{what} must be float32, got {t.dtype}")
+
+
+def device_arch() -> int:
+    rc = library().agv_device_arch()
+    if rc < 0:
+        _check(rc)
+    return rc
+
+
+# ------------------------------------------------------------------ embedding
+def embed(tokens: torch.Tensor, table: torch.Tensor, scale: float, out: torch.Tensor) -> None:
+    """out[t, :] = table[tokens[t], :] * scale, 32-bit."""
+    _i32(tokens, "tokens"); _f32(out, "out"); _dense(table, "table"); _dense(out, "out")
+    T, (V, H) = tokens.numel(), table.shape
+    assert out.shape == (T, H)
+    _check(library().agv_embed(_ptr(tokens), _ptr(table), dtype_code(table.dtype), _ptr(out),
+                               T, H, V, ctypes.c_float(scale), _stream()))
+
+
+def rope_table(positions: torch.Tensor, rotary_dim: int, theta: float, factor: float,
+               cos: torch.Tensor, sin: torch.Tensor) -> None:
+    """cos, sin [T, rotary_dim/2] of (p / factor) * theta^(-2i/rotary_dim)."""
+    _i32(positions, "positions"); _f32(cos, "cos"); _f32(sin, "sin")
+    T = positions.numel()
+    assert cos.shape == (T, rotary_dim // 2) and sin.shape == cos.shape
+    _check(library().agv_rope_table(_ptr(positions), _ptr(cos), _ptr(sin), T, rotary_dim,
+                                    ctypes.c_double(theta), ctypes.c_double(factor), _stream()))
+
+
+# ---------------------------------------------------------------------- norms
+def norm_residual(h: Optional[torch.Tensor], y: Optional[torch.Tensor],
+                  w_post: Optional[torch.Tensor], w_next: Optional[torch.Tensor],
+                  x: Optional[torch.Tensor], eps_post: float = 0.0, eps_next: float = 0.0,
+                  rows: Optional[torch.Tensor] = None, add_residual: bool = True) -> None:
+    """The norm family in one launch.
+
+    y None:  x = norm(h[rows]; w_next)               (rows optional)
+    else:    b = y (summed over a leading split axis if y is 3-D);
+             b = norm(b; w_post) if w_post; h += b if add_residual;
+             x = norm(h or b; w_next) if w_next, else x = b if x is given.
+    h is the 32-bit residual stream [R, H]; w_* are 32-bit and already hold
+    1 + w where the norm is zero-centred.
+    """
+    _f32(h, "h"); _f32(w_post, "w_post"); _f32(w_next, "w_next"); _i32(rows, "rows")
+    n_splits, split_stride, y_code = 1, 0, F32
+    if y is not None:
+        _dense(y, "y")
+        y_code = dtype_code(y.dtype)
+        if y.dim() == 3:
+            n_splits, R, H = y.shape
+            split_stride = R * H
+        else:
+            R, H = y.shape
+    else:
+        H = h.shape[-1]
+        R = rows.numel() if rows is not None else h.shape[0]
+    if h is not None:
+        _dense(h, "h")
+    x_code = F32
+    if x is not None:
+        _dense(x, "x")
+        x_code = dtype_code(x.dtype)
+        assert x.shape == (R, H), (x.shape, R, H)
+    _check(library().agv_norm_residual(
+        _ptr(h), _ptr(y), y_code, n_splits, ctypes.c_longlong(split_stride), _ptr(w_post),
+        _ptr(w_next), _ptr(x), x_code, _ptr(rows), R, H, ctypes.c_float(eps_post),
+        ctypes.c_float(eps_next), 1 if (add_residual and y is not None) else 0, _stream()))
+
+
+# ------------------------------------------------------------ matrix products
+def linear_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
+                w2: Optional[torch.Tensor] = None, activation: str = "gelu_tanh") -> None:
+    """out = x w^T, or act(x w^T) * (x w2^T); FFMA kernel (the 32-bit path)."""
+    M, K = x.shape
+    N = w.shape[0]
+    assert w.shape == (N, K) and out.shape == (M, N)
+    assert x.stride(1) == 1 and out.stride(1) == 1
+    _dense(w, "w")
+    if w2 is not None:
+        _dense(w2, "w2")
+        assert w2.shape == w.shape and w2.dtype == w.dtype
+    if x.dtype != w.dtype:
+        raise KernelError(f"linear: input {x.dtype} and weight {w.dtype} differ")
+    _check(library().agv_linear_simt(
+        _ptr(x), _ptr(w), _ptr(w2), _ptr(out), M, N, K, ctypes.c_longlong(x.stride(0)),
+        ctypes.c_longlong(out.stride(0)), dtype_code(x.dtype), dtype_code(out.dtype),
+        ACT[activation], _stream()))
+
+
+# ------------------------------------------------------------------ attention
+def qk_norm_rope_store(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
+                       wq: Optional[torch.Tensor], wk: Optional[torch.Tensor], eps: float,
+                       cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rotary_dim: int,
+                       positions: Optional[torch.Tensor],
+                       k_pool: Optional[torch.Tensor] = None, v_pool: Optional[torch.Tensor] = None,
+                       page_table: Optional[torch.Tensor] = None,
+                       slots: Optional[torch.Tensor] = None, lens: Optional[torch.Tensor] = None,
+                       seq_index: Optional[torch.Tensor] = None, page: int = 0,
+                       cap: int = 0) -> None:
+    """In place on qkv [T, (nh + 2 nkv) * hd]: per-head norm of q and k, rotation,
+    and (if pools are given) the store of k and v rows into the paged cache."""
+    T = qkv.shape[0]
+    assert qkv.stride(1) == 1
+    _f32(wq, "wq"); _f32(wk, "wk"); _f32(cos, "cos"); _f32(sin, "sin")
+    for t, n in ((positions, "positions"), (page_table, "page_table"), (slots, "slots"),
+                 (lens, "lens"), (seq_index, "seq_index")):
+        _i32(t, n)
+    if k_pool is not None:
+        _dense(k_pool, "k_pool"); _dense(v_pool, "v_pool")
+        assert k_pool.dtype == qkv.dtype and v_pool.dtype == qkv.dtype
+    max_pages = page_table.shape[1] if page_table is not None else 0
+    _check(library().agv_qk_norm_rope_store(
+        _ptr(qkv), dtype_code(qkv.dtype), ctypes.c_longlong(qkv.stride(0)), T, n_heads,
+        n_kv_heads, head_dim, _ptr(wq), _ptr(wk), ctypes.c_float(eps), _ptr(cos), _ptr(sin),
+        rotary_dim, _ptr(positions), _ptr(k_pool), _ptr(v_pool), _ptr(page_table), _ptr(slots),
+        _ptr(lens), _ptr(seq_index), max_pages, page, cap, _stream()))
+
+
+def attention_prefill_simt(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor,
+                           positions: torch.Tensor, seq_index: torch.Tensor,
+                           cu_seqlens: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
+                           scale: float, window: int) -> None:
+    """Prompts that start at 0; q [T, nh*hd], k, v [T, nkv*hd] row-strided views."""
+    T = q.shape[0]
+    assert q.stride(1) == 1 and k.stride(1) == 1 and v.stride(1) == 1
+    assert k.stride(0) == v.stride(0)
+    _dense(out, "out")
+    _i32(positions, "positions"); _i32(seq_index, "seq_index"); _i32(cu_seqlens, "cu_seqlens")
+    _check(library().agv_attention_prefill_simt(
+        _ptr(q), ctypes.c_longlong(q.stride(0)), _ptr(k), _ptr(v),
+        ctypes.c_longlong(k.stride(0)), _ptr(out), dtype_code(q.dtype), _ptr(positions),
+        _ptr(seq_index), _ptr(cu_seqlens), T, n_heads, n_kv_heads, head_dim,
+        ctypes.c_float(scale), window, _stream()))
+
+
+def attention_paged_simt(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor,
+                         v_pool: torch.Tensor, page_table: torch.Tensor, slots: torch.Tensor,
+                         positions: torch.Tensor, seq_index: torch.Tensor, page: int, cap: int,
+                         n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
+                         window: int) -> None:
+    """Queries against the paged cache; their own keys are already stored."""
+    T = q.shape[0]
+    assert q.stride(1) == 1
+    _dense(out, "out"); _dense(k_pool, "k_pool"); _dense(v_pool, "v_pool")
+    for t, n in ((positions, "positions"), (page_table, "page_table"), (slots, "slots"),
+                 (seq_index, "seq_index")):
+        _i32(t, n)
+    assert k_pool.dtype == q.dtype
+    _check(library().agv_attention_paged_simt(
+        _ptr(q), ctypes.c_longlong(q.stride(0)), _ptr(out), dtype_code(q.dtype), _ptr(k_pool),
+        _ptr(v_pool), _ptr(page_table), _ptr(slots), _ptr(positions), _ptr(seq_index),
+        page_table.shape[1], page, cap, T, n_heads, n_kv_heads, head_dim,
+        ctypes.c_float(scale), window, _stream()))
+
+
+# ------------------------------------------------------------------- sampling
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    _f32(logits, "logits"); _i32(out, "out")
+    B, V = logits.shape
+    assert logits.stride(1) == 1
+    _check(library().agv_argmax(_ptr(logits), ctypes.c_longlong(logits.stride(0)), B, V,
+                                _ptr(out), _stream()))
+
+
+def history_append(tokens: torch.Tensor, slots: torch.Tensor, hist: torch.Tensor,
+                   hist_len: torch.Tensor) -> None:
+    """hist[slot, hist_len[slot]++] = token for every entry with a slot."""
+    for t, n in ((tokens, "tokens"), (slots, "slots"), (hist, "hist"), (hist_len, "hist_len")):
+        _i32(t, n)
+    _dense(hist, "hist")
+    _check(library().agv_history_append(_ptr(tokens), _ptr(slots), _ptr(hist), _ptr(hist_len),
+                                        hist.shape[1], slots.numel(), _stream()))
+
+
+def repeat_penalty(logits: torch.Tensor, slots: torch.Tensor, hist: torch.Tensor,
+                   hist_len: torch.Tensor, penalty: float) -> None:
+    """Penalise, in place, every id in each row's slot history, once per occurrence."""
+    _f32(logits, "logits")
+    for t, n in ((slots, "slots"), (hist, "hist"), (hist_len, "hist_len")):
+        _i32(t, n)
+    B, V = logits.shape
+    _dense(hist, "hist")
+    _check(library().agv_repeat_penalty(_ptr(logits), ctypes.c_longlong(logits.stride(0)), B, V,
+                                        _ptr(slots), _ptr(hist), _ptr(hist_len), hist.shape[1],
+                                        ctypes.c_float(penalty), _stream()))
+
+
+def sample(logits: torch.Tensor, out: torch.Tensor, temperature: float, top_k: int, top_p: float,
+           seed: int, seq_ids: torch.Tensor, steps: torch.Tensor) -> None:
+    _f32(logits, "logits"); _i32(out, "out"); _i32(steps, "steps")
+    if seq_ids.dtype != torch.int64:
+        raise KernelError("seq_ids must be int64")
+    B, V = logits.shape
+    assert logits.stride(1) == 1
+    _check(library().agv_sample(_ptr(logits), ctypes.c_longlong(logits.stride(0)), B, V,
+                                _ptr(out), ctypes.c_float(temperature), int(top_k),
+                                ctypes.c_float(top_p), ctypes.c_ulonglong(seed & (2**64 - 1)),
+                                _ptr(seq_ids), _ptr(steps), _stream()))
+
+
+# ------------------------------------------------------------------ dispatch
+def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
+           w2: Optional[torch.Tensor] = None, activation: str = "gelu_tanh") -> None:
+    """out = x w^T (or the gated pair).  The kernel is chosen from the dtype and
+    the weight's shape only."""
+    linear_simt(x, w, out, w2, activation)
+
+
+def attention_prefill(q, k, v, out, ctx, n_heads, n_kv_heads, head_dim, scale, window) -> None:
+    attention_prefill_simt(q, k, v, out, ctx.positions, ctx.seq_index, ctx.cu_seqlens, n_heads,
+                           n_kv_heads, head_dim, scale, window)
+
+
+def attention_decode(q, out, view, ctx, n_heads, n_kv_heads, head_dim, scale, window) -> None:
+    attention_paged_simt(q, out, view.k_pool, view.v_pool, view.page_table, ctx.slots,
+                         ctx.positions, ctx.seq_index, view.page, view.cap, n_heads, n_kv_heads,
+                         head_dim, scale, window)

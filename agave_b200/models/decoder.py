@@ -1,0 +1,141 @@
+"""The generic decoder: embedding, blocks run in the order the spec lists,
+final norm, head.  It is built from a ``ModelSpec`` through the part
+registries and knows no architecture by name.
+
+Internal tensor names (what ``decoder_param_specs`` lists and ``load`` takes):
+``embed.weight``, ``blocks.{i}.<block-local name>``, ``final_norm.weight`` and,
+unless the head is tied to the embedding, ``lm_head.weight``.  An
+architecture maps these to the names its checkpoints use.
+
+Flow of one step (src/models/gemma3.zig:331-368 for one token, :413-442 for a
+prompt chunk): embedding times the spec's scale into a 32-bit stream, the
+blocks, the final norm on the rows whose logits are wanted, the head in
+32-bit output.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from .. import kernels
+from ..config.base import ModelSpec
+from ..parts.base import ParamSpec, norm_class
+from ..parts.block import Block
+from ..parts.linear import Linear
+
+
+def decoder_param_specs(spec: ModelSpec) -> Dict[str, ParamSpec]:
+    out: Dict[str, ParamSpec] = {
+        "embed.weight": ParamSpec((spec.vocab_size, spec.hidden_size), "embedding")}
+    for i, b in enumerate(spec.blocks):
+        for k, v in Block.param_specs(b, spec.hidden_size).items():
+            out[f"blocks.{i}.{k}"] = v
+    N = norm_class(spec.final_norm.kind)
+    for k, v in N.param_specs(spec.final_norm, spec.hidden_size).items():
+        out[f"final_norm.{k}"] = v
+    if not spec.tie_embeddings:
+        out["lm_head.weight"] = ParamSpec((spec.vocab_size, spec.hidden_size), "matrix")
+    return out
+
+
+class DecoderModel:
+    def __init__(self, spec: ModelSpec, dtype: torch.dtype, device: torch.device):
+        if dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError(f"compute dtype {dtype} is not supported (float32, bfloat16)")
+        self.spec, self.dtype, self.device = spec, dtype, device
+        self.blocks: List[Block] = [Block(b, spec.hidden_size, dtype, device)
+                                    for b in spec.blocks]
+        self.final_norm = norm_class(spec.final_norm.kind)(spec.final_norm, spec.hidden_size,
+                                                           dtype, device)
+        self.embed_table: Optional[torch.Tensor] = None
+        self.head: Optional[Linear] = None
+        for call in spec.schedule:
+            if not 0 <= call.block < len(self.blocks):
+                raise ValueError(f"the run order names block {call.block}, which does not exist")
+        writers = {}
+        for call in spec.schedule:
+            if call.writes_cache:
+                if call.cache in writers:
+                    raise ValueError(f"cache entry {call.cache} is written by two calls")
+                writers[call.cache] = call.block
+        for call in spec.schedule:
+            if not call.writes_cache and call.cache not in writers:
+                raise ValueError(f"cache entry {call.cache} is read but never written")
+        self._writers = writers
+
+    # ----------------------------------------------------------------- cache
+    def cache_requests(self) -> List[object]:
+        """What each cache entry must hold, in entry order (None: nothing)."""
+        n = self.spec.n_cache_entries()
+        out: List[object] = [None] * n
+        for entry, block in self._writers.items():
+            out[entry] = self.blocks[block].mixer.cache_request()
+        return out
+
+    # --------------------------------------------------------------- weights
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        return decoder_param_specs(self.spec)
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        """Take tensors under their internal names (any device, as stored)."""
+        dt, dev = self.dtype, self.device
+        self.embed_table = tensors["embed.weight"].to(device=dev, dtype=dt).contiguous()
+        for i, b in enumerate(self.blocks):
+            p = f"blocks.{i}."
+            b.load({k[len(p):]: v for k, v in tensors.items() if k.startswith(p)}, dt, dev)
+        self.final_norm.load({"weight": tensors["final_norm.weight"]}, dev)
+        if self.spec.tie_embeddings:
+            self.head = Linear(self.embed_table)
+        else:
+            self.head = Linear(tensors["lm_head.weight"].to(device=dev, dtype=dt).contiguous())
+
+    def weight_bytes(self) -> int:
+        seen, n = set(), 0
+        def visit(o):
+            nonlocal n
+            if isinstance(o, torch.Tensor):
+                if o.data_ptr() not in seen:
+                    seen.add(o.data_ptr())
+                    n += o.numel() * o.element_size()
+            elif isinstance(o, (list, tuple)):
+                for i in o:
+                    visit(i)
+            elif hasattr(o, "__dict__") and not isinstance(o, (type, torch.dtype, torch.device)):
+                if id(o) in seen:
+                    return
+                seen.add(id(o))
+                for v in vars(o).values():
+                    visit(v)
+        visit(self.blocks); visit(self.final_norm); visit(self.embed_table); visit(self.head)
+        return n
+
+    # --------------------------------------------------------------- forward
+    def hidden_states(self, ctx) -> torch.Tensor:
+        """The 32-bit stream [T, H] after the last block (before the final norm)."""
+        spec = self.spec
+        T = ctx.n_tokens
+        h = ctx.new(T, spec.hidden_size, dtype=torch.float32)
+        kernels.embed(ctx.tokens, self.embed_table, spec.embed_scale, h)
+        sched = spec.schedule
+        if not sched:
+            return h
+        x = ctx.new(T, spec.hidden_size)
+        self.blocks[sched[0].block].pre_mixer_norm.forward(h, x)
+        for i, call in enumerate(sched):
+            nxt = self.blocks[sched[i + 1].block].pre_mixer_norm if i + 1 < len(sched) else None
+            x = self.blocks[call.block].forward(h, x, ctx, call.cache, call.writes_cache, nxt)
+        return h
+
+    def logits(self, h: torch.Tensor, rows: torch.Tensor, ctx,
+               out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """32-bit logits [len(rows), V] of the stream rows ``rows`` (int32)."""
+        R = rows.numel()
+        x = ctx.new(R, self.spec.hidden_size)
+        self.final_norm.forward(h, x, rows=rows)
+        if out is None:
+            out = ctx.new(R, self.spec.vocab_size, dtype=torch.float32)
+        return self.head(x, out=out)
+
+    def forward(self, ctx, rows: torch.Tensor) -> torch.Tensor:
+        return self.logits(self.hidden_states(ctx), rows, ctx)

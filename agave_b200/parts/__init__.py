@@ -1,0 +1,14 @@
+from .base import (KVRequest, ParamSpec, StateRequest, feed_forward_class, mixer_class,
+                   norm_class, position_class, register_feed_forward, register_mixer,
+                   register_norm, register_position)
+from .norm import RMSNorm
+from .rope import RotaryEmbedding
+from .attention import AttentionMixer
+from .feedforward import GatedFeedForward
+from .block import Block
+from .linear import GatedLinear, Linear
+
+__all__ = ["KVRequest", "ParamSpec", "StateRequest", "feed_forward_class", "mixer_class",
+           "norm_class", "position_class", "register_feed_forward", "register_mixer",
+           "register_norm", "register_position", "RMSNorm", "RotaryEmbedding",
+           "AttentionMixer", "GatedFeedForward", "Block", "GatedLinear", "Linear"]

@@ -1,0 +1,44 @@
+"""Projections: a weight [out, in] and the kernel choice for it.
+
+The 32-bit path always runs the FFMA kernel.  The bfloat16 path runs the
+tcgen05 kernel when the shape qualifies and otherwise the FFMA kernel on
+bfloat16 data; the choice depends only on the weight's shape, never on the
+batch, so a token's result does not depend on its company.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import kernels
+
+
+class Linear:
+    def __init__(self, weight: torch.Tensor):
+        assert weight.dim() == 2 and weight.is_contiguous()
+        self.weight = weight
+        self.out_features, self.in_features = weight.shape
+
+    def __call__(self, x: torch.Tensor, out: Optional[torch.Tensor] = None,
+                 out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        if out is None:
+            out = torch.empty((x.shape[0], self.out_features), dtype=out_dtype or x.dtype,
+                              device=x.device)
+        kernels.linear(x, self.weight, out)
+        return out
+
+
+class GatedLinear:
+    """act(x wg^T) * (x wu^T) in one kernel."""
+
+    def __init__(self, w_gate: torch.Tensor, w_up: torch.Tensor, activation: str):
+        assert w_gate.shape == w_up.shape
+        self.w_gate, self.w_up, self.activation = w_gate, w_up, activation
+        self.out_features, self.in_features = w_gate.shape
+
+    def __call__(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if out is None:
+            out = torch.empty((x.shape[0], self.out_features), dtype=x.dtype, device=x.device)
+        kernels.linear(x, self.w_gate, out, w2=self.w_up, activation=self.activation)
+        return out

@@ -1,0 +1,170 @@
+"""The engine against the plain implementation on the GPU, in 32-bit and in
+bfloat16: whole requests, the last 32 tokens one by one, batches of unequal
+lengths one after another (slots reused), long decoding, first tokens, and
+greedy generation through the entry point."""
+import pytest
+import torch
+
+from util import TINY, TOL, close, model_folder, plain_logits, random_tokens
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = ["float32", "bfloat16"]
+_ENGINES = {}
+
+
+def engine_for(name, dtype, max_tokens=4096):
+    key = (name, dtype, max_tokens)
+    if key not in _ENGINES:
+        from agave_b200.engine.api import Engine
+        # weights are stored in 32-bit for the 32-bit runs and in bfloat16 for the others,
+        # so the plain implementation reads exactly the values the engine uses
+        store = torch.float32 if dtype == "float32" else torch.bfloat16
+        _ENGINES[key] = (Engine(model_folder(name, store), dtype=dtype, max_tokens=max_tokens),
+                         model_folder(name, store))
+    return _ENGINES[key]
+
+
+def vocab(name):
+    return TINY[name][0]["vocab_size"]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_whole_requests_alone(name, dtype):
+    eng, folder = engine_for(name, dtype)
+    for n, seed in ((1, 1), (5, 2), (33, 3), (100, 4)):
+        toks = random_tokens(n, vocab(name), seed)
+        s = eng.acquire()
+        got = eng.step([(s, toks)], [list(range(n))])
+        eng.release(s)
+        close(got, plain_logits(folder, toks), TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_last_32_tokens_one_by_one(name, dtype):
+    eng, folder = engine_for(name, dtype)
+    n = 75
+    toks = random_tokens(n, vocab(name), 11)
+    ref = plain_logits(folder, toks)
+    s = eng.acquire()
+    head = n - 32
+    got = [eng.step([(s, toks[:head])], [list(range(head))])]
+    for i in range(head, n):
+        got.append(eng.step([(s, [toks[i]])], [[0]]))
+    eng.release(s)
+    got = torch.cat(got)
+    close(got, ref, TOL[dtype])
+    # the first decoded token and the prompt's end, separately: the usual places of a fault
+    close(got[head - 1:head + 1], ref[head - 1:head + 1], TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_unequal_batches_one_after_another(name, dtype):
+    """Prompts of unequal lengths in one step, then one token each; shorter
+    requests end earlier; a second batch reuses the slots."""
+    eng, folder = engine_for(name, dtype)
+    V = vocab(name)
+    free_before = eng.runner.cache.book.slots.n_free
+    for round_, lengths in enumerate([(5, 11, 17), (3, 9, 20, 33)]):
+        decode = {0: 4, 1: 9, 2: 2, 3: 12}
+        seqs = [random_tokens(L + decode[i], V, 100 * round_ + i) for i, L in enumerate(lengths)]
+        refs = [plain_logits(folder, s) for s in seqs]
+        slots = [eng.acquire() for _ in seqs]
+        got = [[] for _ in seqs]
+        out = eng.step([(slots[i], seqs[i][:L]) for i, L in enumerate(lengths)],
+                       [list(range(L)) for L in lengths])
+        o = 0
+        for i, L in enumerate(lengths):
+            got[i].append(out[o:o + L]); o += L
+        live = list(range(len(seqs)))
+        pos = {i: L for i, L in enumerate(lengths)}
+        while live:
+            out = eng.step([(slots[i], [seqs[i][pos[i]]]) for i in live], [[0]] * len(live))
+            for j, i in enumerate(live):
+                got[i].append(out[j:j + 1])
+                pos[i] += 1
+            for i in [i for i in live if pos[i] == len(seqs[i])]:
+                eng.release(slots[i])
+                live.remove(i)
+        for i in range(len(seqs)):
+            close(torch.cat(got[i]), refs[i], TOL[dtype])
+    assert eng.runner.cache.book.slots.n_free == free_before
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding_past_windows_and_pages(dtype):
+    """Decoding far beyond the window and across several cache pages."""
+    eng, folder = engine_for("B", dtype)
+    n = 210
+    toks = random_tokens(n, vocab("B"), 21)
+    ref = plain_logits(folder, toks)
+    s = eng.acquire()
+    got = [eng.step([(s, toks[:3])], [[0, 1, 2]])]
+    for i in range(3, n):
+        got.append(eng.step([(s, [toks[i]])], [[0]]))
+    eng.release(s)
+    close(torch.cat(got), ref, TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_padding_and_company_change_nothing(dtype):
+    """A sequence's logits with and without other sequences in the batch."""
+    eng, folder = engine_for("A", dtype)
+    V = vocab("A")
+    a = random_tokens(19, V, 31)
+    others = [random_tokens(n, V, 40 + n) for n in (2, 30)]
+    s = eng.acquire()
+    alone = [eng.step([(s, a[:12])], [list(range(12))])]
+    for i in range(12, 19):
+        alone.append(eng.step([(s, [a[i]])], [[0]]))
+    eng.release(s)
+    slots = [eng.acquire() for _ in range(3)]
+    seqs = [others[0], a, others[1]]
+    starts = [1, 12, 20]
+    out = eng.step([(slots[i], seqs[i][:starts[i]]) for i in range(3)],
+                   [[], list(range(12)), []])
+    mixed = [out]
+    for k in range(7):
+        ent = [(slots[i], [seqs[i][starts[i] + k]]) for i in range(3)
+               if starts[i] + k < len(seqs[i])]
+        idx = [i for i in range(3) if starts[i] + k < len(seqs[i])]
+        out = eng.step(ent, [[0] if i == 1 else [] for i in idx])
+        mixed.append(out)
+    for sl in slots:
+        eng.release(sl)
+    alone, mixed = torch.cat(alone), torch.cat(mixed)
+    tol = 1e-5 if dtype == "float32" else 2e-2
+    close(mixed, alone, tol)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_through_the_entry_point(name, dtype):
+    from plain import gemma3_plain as P
+    eng, folder = engine_for(name, dtype)
+    cfg, w = P.read_config(folder), P.read_weights(folder)
+    lengths = (5, 11, 17) if name == "A" else (3, 9, 20, 33)
+    n_new = 8 if name == "A" else 12
+    prompts = [random_tokens(L, vocab(name), 60 + L) for L in lengths]
+    got = eng.generate(prompts, max_new_tokens=n_new, stop_token_ids=[])
+    assert [len(g) for g in got] == [n_new] * len(prompts)
+    for p, g in zip(prompts, got):
+        # teacher-forced check: each chosen token is the plain arg max given the
+        # engine's own prefix, or as good as it within the dtype's tolerance
+        ref = P.forward_logits(cfg, w, p + g)
+        for k, t in enumerate(g):
+            row = ref[len(p) - 1 + k]
+            best = int(row.argmax())
+            if t != best:
+                margin = (row[best] - row[t]).item()
+                assert margin <= 2 * TOL[dtype] * row.abs().max().item(), (k, t, best, margin)
+    # stop tokens: the sequence ends before the stop token and nothing follows
+    stop = got[0][3]
+    again = eng.generate(prompts[:1], max_new_tokens=n_new, stop_token_ids=[stop])
+    assert again[0] == got[0][:got[0].index(stop)]
+    # one batch after another through the same engine gives the same tokens
+    eng2_out = eng.generate(prompts + prompts, max_new_tokens=n_new, stop_token_ids=[])
+    assert eng2_out[:len(prompts)] == got and eng2_out[len(prompts):] == got
