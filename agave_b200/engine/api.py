@@ -69,6 +69,7 @@ class _DecodeGraph:
         self.next_host = torch.zeros(B, dtype=torch.int32, pin_memory=True)
         self.logits: Optional[torch.Tensor] = None
         self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.kernels_per_step = 0
         self._record(engine, params, seed)
 
     def _body(self, engine: "Engine", params: SamplingParams, seed: int) -> None:
@@ -94,8 +95,10 @@ class _DecodeGraph:
         self.dev.copy_(self.host)
         torch.cuda.synchronize()
         g = torch.cuda.CUDAGraph()
+        n0 = kernels.launch_count()
         with torch.cuda.graph(g):
             self._body(engine, params, seed)
+        self.kernels_per_step = kernels.launch_count() - n0
         self.graph = g
 
     def run(self, engine: "Engine", params: SamplingParams, seed: int) -> None:

@@ -63,8 +63,19 @@ def _ptr(t: Optional[torch.Tensor]):
     return ctypes.c_void_p(t.data_ptr())
 
 
+_launches = 0
+
+
 def _stream():
+    # called exactly once per kernel launch: the count is what bench.py reports
+    global _launches
+    _launches += 1
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def launch_count() -> int:
+    """Kernels of this library launched (or recorded into a graph) so far."""
+    return _launches
 
 
 def _dense(t: torch.Tensor, what: str) -> None:

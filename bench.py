@@ -1,0 +1,293 @@
+#!/usr/bin/env python3
+"""Measures decoding and prefill of Gemma 3 1B layer sizes on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl ours|reference]
+
+Prints ONE JSON line.  ``value`` is decoded tokens per second of K decode
+steps at batch 8 (context 8,192, prompts of unequal lengths 128..2,048,
+random bfloat16 weights), timed on the device with CUDA events; ``e2e`` is the
+same through ``Engine.generate`` with host token ids in and out every step.
+``prefill`` is one 2,048-token prompt; ``roofline`` relates the decode step to
+the bytes it has to read; ``points`` holds decoding at batch 1 and 64.
+A step's inputs (2 GB of weights) are larger than the 126 MB L2, so every
+timed iteration reads them from HBM; this is said in ``config``.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# Gemma 3 1B layer sizes (random weights, seed 2, N(0, 0.02) bfloat16)
+CONFIG_1B = {
+    "architectures": ["Gemma3ForCausalLM"], "model_type": "gemma3_text",
+    "num_hidden_layers": 26, "hidden_size": 1152, "num_attention_heads": 4,
+    "num_key_value_heads": 1, "head_dim": 256, "query_pre_attn_scalar": 256,
+    "intermediate_size": 6912, "vocab_size": 262144, "sliding_window": 512,
+    "sliding_window_pattern": 6, "rope_local_base_freq": 10000.0, "rope_theta": 1000000.0,
+    "rope_scaling": None, "rms_norm_eps": 1e-6, "tie_word_embeddings": True,
+    "max_position_embeddings": 32768, "hidden_activation": "gelu_pytorch_tanh",
+    "bos_token_id": 2, "eos_token_id": 1,
+}
+CONTEXT = 8192
+PREFILL_TOKENS = 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                p = json.load(f)
+            return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+                    "source": "measured"}
+        except Exception:
+            pass
+    return {**FALLBACK_PEAKS, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.samples, self.proc = [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        mhz = sorted(int(s[0]) for s in self.samples if s and s[0].isdigit())
+        mx = [int(s[1]) for s in self.samples if len(s) > 1 and s[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({names[i] for s in self.samples if len(s) >= 6
+                          for i in range(4) if s[2 + i].lower().startswith("active")})
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
+                "samples": len(mhz)}
+
+
+def layer_kinds(cfg):
+    P = cfg["sliding_window_pattern"]
+    return [(P > 0 and (l + 1) % P != 0) for l in range(cfg["num_hidden_layers"])]
+
+
+def decode_bytes(cfg, lens):
+    """Bytes one decode step must read: every weight once, and the live cache."""
+    H, ff, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    nh, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    L = cfg["num_hidden_layers"]
+    per_layer = (H * (nh + 2 * nkv) * hd + nh * hd * H + 3 * H * ff) * 2 + (4 * H + 2 * hd) * 4
+    weights = L * per_layer + V * H * 2 + H * 4
+    kv = 0
+    W = cfg["sliding_window"]
+    for local in layer_kinds(cfg):
+        for n in lens:
+            kv += (min(n, W) if local else n) * nkv * hd * 2 * 2
+    return weights + kv
+
+
+def prefill_flops(cfg, T, rows):
+    H, ff, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    nh, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    W = cfg["sliding_window"]
+    lin = 2 * T * (H * (nh + 2 * nkv) * hd + nh * hd * H + 3 * H * ff)
+    total = 0
+    for local in layer_kinds(cfg):
+        vis = sum(min(t + 1, W) if local else t + 1 for t in range(T))
+        total += lin + 4 * nh * hd * vis
+    return total + 2 * rows * H * V
+
+
+def run_reference(args):
+    print(json.dumps({
+        "impl": "reference",
+        "unavailable": "maci0/agave is a Zig program (build.zig); pip reports 'Neither setup.py "
+                       "nor pyproject.toml found' and no zig toolchain is installed, so it "
+                       "cannot be built or run here"}))
+    return 0
+
+
+def timed_decode(engine, torch, kernels, batch, steps, warmup, seed):
+    """K decode steps at one batch size, device-timed; returns (ms/step, lens, launches/step)."""
+    import numpy as np
+    g = torch.Generator().manual_seed(seed)
+    V = engine.spec.vocab_size
+    lens = torch.linspace(128, 2048, batch).round().int().tolist() if batch > 1 else [1088]
+    prompts = [torch.randint(3, V, (n,), generator=g).tolist() for n in lens]
+    slots = [engine.acquire() for _ in prompts]
+    # prompts in chunks of sequences, to bound the prompt step's activations
+    for i in range(0, batch, 8):
+        engine.step([(slots[j], prompts[j]) for j in range(i, min(batch, i + 8))],
+                    [[] for _ in range(i, min(batch, i + 8))])
+    from agave_b200.engine.api import _bucket
+    from agave_b200.sampling import SamplingParams
+    params = SamplingParams()
+    graph = engine._graph_for(_bucket(batch), params, 0)
+    B = graph.size
+    book = engine.runner.cache.book
+    total = warmup + steps
+    for s in slots:
+        engine.runner.cache.reserve(s, book.length[s] + total)
+    engine.runner.cache.flush()
+    staged = torch.zeros((total, graph.host.numel()), dtype=torch.int32)
+    toks = torch.randint(3, V, (total, batch), generator=g, dtype=torch.int32)
+    for k in range(total):
+        a = staged[k].numpy()
+        a[:batch] = toks[k].numpy()
+        cur = np.array([book.length[s] + k for s in slots], dtype=np.int32)
+        a[B:B + batch] = cur
+        a[2 * B:3 * B] = np.arange(B)
+        o = 3 * B
+        a[o:o + B + 1] = np.arange(B + 1)
+        a[o + B + 1:o + 2 * B + 1] = -1
+        a[o + B + 1:o + B + 1 + batch] = np.array(slots, dtype=np.int32)
+        a[o + 2 * B + 1:o + 2 * B + 1 + batch] = cur + 1
+    staged_dev = staged.to(engine.device)
+    torch.cuda.synchronize()
+    per_step = graph.kernels_per_step
+    for k in range(warmup):
+        graph.dev.copy_(staged_dev[k])
+        graph.graph.replay()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for k in range(warmup, total):
+        graph.dev.copy_(staged_dev[k])
+        graph.graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    final_lens = [book.length[s] + total for s in slots]
+    for s in slots:
+        engine.release(s)
+    return ms, final_lens, per_step
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=0,
+                    help="run fewer layers than the configuration has (0 = all)")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    if args.gpus != 1:
+        print("bench.py: this library runs on one GPU; --gpus must be 1")
+        return 2
+    args.warmup = max(3, args.warmup)
+
+    import torch
+    from agave_b200 import kernels
+    from agave_b200.engine.api import Engine
+
+    cfg = dict(CONFIG_1B)
+    full_layers = cfg["num_hidden_layers"]
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    pk = peaks()
+    engine = Engine.from_config(cfg, seed=2, std=0.02, norm_std=0.1, dtype="bfloat16",
+                                max_tokens=64 * CONTEXT, ctx_size=CONTEXT, max_batch=64)
+    V = engine.spec.vocab_size
+    g = torch.Generator().manual_seed(5)
+
+    # ---- prefill: one prompt of 2,048 tokens, logits of its last token ----
+    prompt = torch.randint(3, V, (PREFILL_TOKENS,), generator=g).tolist()
+    pre_ms = []
+    for it in range(3 + 5):
+        s = engine.acquire()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        engine.step([(s, prompt)], [[PREFILL_TOKENS - 1]])
+        e1.record()
+        torch.cuda.synchronize()
+        engine.release(s)
+        if it >= 3:
+            pre_ms.append(e0.elapsed_time(e1))
+    pre_ms = sorted(pre_ms)[len(pre_ms) // 2]
+    pflops = prefill_flops(cfg, PREFILL_TOKENS, 1)
+    prefill = {"value": round(PREFILL_TOKENS / pre_ms * 1e3, 1), "tokens": PREFILL_TOKENS,
+               "ms": round(pre_ms, 3),
+               "frac": round(pflops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+
+    # ---- decode at batch 8 (headline), with clocks sampled meanwhile ----
+    clocks = ClockSampler()
+    clocks.start()
+    ms8, lens8, launches = timed_decode(engine, torch, kernels, 8, args.steps, args.warmup, 8)
+    clock_rec = clocks.stop()
+    value = 8 / ms8 * 1e3
+    nbytes = decode_bytes(cfg, lens8)
+    achieved = nbytes / (ms8 * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"],
+                "unit": "GB/s", "frac": round(achieved / pk["hbm_gbs"], 4),
+                "of": pk["source"], "bytes_per_step": nbytes}
+
+    # ---- the other batch sizes ----
+    ms1, _, _ = timed_decode(engine, torch, kernels, 1, args.steps, args.warmup, 1)
+    ms64, _, _ = timed_decode(engine, torch, kernels, 64, max(8, args.steps // 2), args.warmup, 64)
+    points = {"decode_b1": round(1 / ms1 * 1e3, 1), "decode_b64": round(64 / ms64 * 1e3, 1)}
+
+    # ---- end to end through the Python entry point ----
+    lens = torch.linspace(128, 2048, 8).round().int().tolist()
+    prompts = [torch.randint(3, V, (n,), generator=g).tolist() for n in lens]
+    n_new = args.steps + 1
+    engine.generate(prompts, max_new_tokens=4, stop_token_ids=[])           # warm-up
+    engine.generate(prompts, max_new_tokens=n_new, stop_token_ids=[])
+    st = engine.stats
+    e2e_val = st["decode_tokens"] / st["decode_seconds"]
+    graph = next(iter(engine._graphs.values()))
+    e2e = {"value": round(e2e_val, 1), "unit": "tokens/s",
+           "h2d_bytes_per_step": int(graph.host.numel() * 4),
+           "d2h_bytes_per_step": int(graph.next_host.numel() * 4)}
+
+    out = {
+        "metric": "Gemma3-1B bf16 decode tokens/s at batch 8 (context 8192)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(ms8, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {
+            "model": "gemma3-1b-shapes-random", "layers": cfg["num_hidden_layers"],
+            "layers_full": full_layers, "hidden": cfg["hidden_size"],
+            "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+            "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"],
+            "vocab": cfg["vocab_size"], "sliding_window": cfg["sliding_window"],
+            "local_per_global": cfg["sliding_window_pattern"] - 1, "global_batch": 8,
+            "seq_len": CONTEXT, "prompt_lens": "128..2048 unequal", "seed": 2,
+            "parallelism": "single-gpu", "cache": "paged bf16",
+            "l2": "inputs larger than L2 (2 GB weights per step)"},
+        "prefill": prefill, "roofline": roofline, "points": points, "e2e": e2e,
+        "gpu_launches": int(launches * args.steps), "clocks": clock_rec,
+    }
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
