@@ -1,0 +1,469 @@
+// bfloat16 matrix products on the fifth-generation tensor cores:
+//     out[T, N] = x[T, K] * w[N, K]^T          (plain, or K split into partial sums)
+//     out[T, N] = act(x wg^T) * (x wu^T)       (gated)
+//
+// The weight is the M operand: one CTA owns 128 weight rows and a tile of BN
+// tokens (BN = 16 ... 256), so the same kernel serves decoding (a few tokens,
+// the weight streamed once from HBM) and prompts (256 tokens per tile).  TMA
+// brings [128 x 64] weight boxes and [BN x 64] activation boxes into a ring of
+// shared-memory stages (128-byte swizzle, K-major); one thread issues
+// tcgen05.mma (M 128, N BN, K 16) into a 32-bit accumulator in tensor memory;
+// four warps read the accumulator back with tcgen05.ld and write the result,
+// applying the gate's activation in the gated form (two accumulators side by
+// side).  Every output element is one dot product accumulated over K in
+// ascending order, so a token's result does not depend on its tile mates.
+//
+// Warp roles: warp 0 loads, warp 1 allocates tensor memory and issues the
+// products, warps 2-5 are the epilogue (warp w reads TMEM lanes 32 (w % 4) ...).
+// Every wait on an mbarrier is bounded; when a wait gives up the kernel records
+// a code in a status word, stops issuing work, drains what it started, frees
+// its tensor memory and returns.
+//
+// Reference: the engine this replaces computes the same products as one dot
+// product per output row with f32 accumulation, bf16 weights converted in the
+// loop (src/backend/kernels/cuda/gemv_bf16.zig:6-24), once per token for
+// prompts (src/backend/cuda.zig:1569-1570).
+#include "common.cuh"
+#include <cuda.h>
+#include <map>
+#include <mutex>
+#include <tuple>
+
+namespace {
+
+constexpr int TILE_M = 128;        // weight rows per CTA
+constexpr int TILE_K = 64;         // 64 bf16 = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int GEMM_THREADS = 192;
+constexpr unsigned WAIT_LIMIT = 1u << 22;
+
+__device__ int g_gemm_status = 0;   // 0 ok; else (role << 8) | stage of the first wait that gave up
+
+// ------------------------------------------------------------------ PTX pieces
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+                 "r"(bytes)
+                 : "memory");
+}
+// Bounded wait; false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    for (unsigned i = 0; i < WAIT_LIMIT; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y,
+                                            uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%2, %3}], [%4];" ::"r"(smem_u32(dst)),
+        "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                     smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                            uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// 32 lanes x 16 consecutive 32-bit columns: thread t gets lane (base + t).
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes
+// (64 bf16), stored with the 128-byte swizzle: 8-row groups lie 1024 bytes
+// apart (stride byte offset), version 1, layout type 2.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+    d |= (uint64_t)1 << 16;                    // leading byte offset (unused with swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;          // stride byte offset
+    d |= (uint64_t)1 << 46;                    // descriptor version
+    d |= (uint64_t)2 << 61;                    // 128-byte swizzle
+    return d;
+}
+// kind::f16 instruction descriptor: bf16 x bf16 -> f32, both operands K-major.
+__host__ __device__ constexpr uint32_t umma_idesc(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) |
+           ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ float gelu_tanh_fast(float t) {
+    const float u = 0.7978845608028654f * (t + 0.044715f * t * t * t);
+    return 0.5f * t * (1.0f + tanhf(u));
+}
+__device__ __forceinline__ float silu_fast(float t) { return t / (1.0f + __expf(-t)); }
+
+template <int BN, bool GATED>
+struct Tile {
+    static constexpr int A_BYTES = TILE_M * TILE_K * 2;                 // 16 KB
+    static constexpr int B_BYTES = BN * TILE_K * 2;
+    static constexpr int STAGE_BYTES = A_BYTES * (GATED ? 2 : 1) + B_BYTES;
+    static constexpr int BUDGET = GATED ? 196 * 1024 : (BN >= 256 ? 196 * 1024 : 108 * 1024);
+    static constexpr int STAGES_RAW = BUDGET / STAGE_BYTES;
+    static constexpr int STAGES = STAGES_RAW > 8 ? 8 : (STAGES_RAW < 2 ? 2 : STAGES_RAW);
+    static constexpr int TMEM_COLS_RAW = GATED ? 2 * BN : BN;
+    static constexpr int TMEM_COLS = TMEM_COLS_RAW < 32 ? 32 : TMEM_COLS_RAW;
+    static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+// out element types
+template <typename TO> __device__ __forceinline__ void store_out(TO* p, float v);
+template <> __device__ __forceinline__ void store_out<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat16* p, float v) {
+    *p = __float2bfloat16_rn(v);
+}
+
+template <int BN, bool GATED, typename TO>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
+                    const __grid_constant__ CUtensorMap map_w2,
+                    const __grid_constant__ CUtensorMap map_x, TO* __restrict__ out, int T, int N,
+                    int K, long long ldc, long long split_stride, int kb_per_split, int act) {
+    using TL = Tile<BN, GATED>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = (uint64_t*)(smem + TL::STAGES * TL::STAGE_BYTES);
+    uint64_t* empty = full + TL::STAGES;
+    uint64_t* acc_full = empty + TL::STAGES;
+    uint32_t* tmem_slot = (uint32_t*)(acc_full + 1);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.x * TILE_M;          // first weight row (output feature)
+    const int n0 = blockIdx.y * BN;              // first token
+    const int kb_total = (K + TILE_K - 1) / TILE_K;
+    const int kb_begin = blockIdx.z * kb_per_split;
+    const int kb_end = min(kb_total, kb_begin + kb_per_split);
+    const int n_kb = kb_end - kb_begin;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TL::STAGES; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        mbar_init(acc_full, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         smem_u32(tmem_slot)),
+                     "r"((uint32_t)TL::TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ------------------------------------------------------------ loader
+        int issued = 0;
+        for (int i = 0; i < n_kb; ++i) {
+            const int s = i % TL::STAGES;
+            const uint32_t ph = (i / TL::STAGES) & 1;
+            if (*abort_flag) break;
+            if (!mbar_wait(&empty[s], ph ^ 1)) {
+                atomicCAS(&g_gemm_status, 0, (1 << 8) | s);
+                *abort_flag = 1;
+                break;
+            }
+            uint8_t* st = smem + s * TL::STAGE_BYTES;
+            mbar_expect_tx(&full[s], TL::STAGE_BYTES);
+            const int kx = (kb_begin + i) * TILE_K;
+            tma_load_2d(st, &map_w, kx, m0, &full[s]);
+            if (GATED) tma_load_2d(st + TL::A_BYTES, &map_w2, kx, m0, &full[s]);
+            tma_load_2d(st + TL::A_BYTES * (GATED ? 2 : 1), &map_x, kx, n0, &full[s]);
+            ++issued;
+        }
+        if (*abort_flag) {
+            // let the copies already issued land before the shared memory is given up
+            const int first = issued > TL::STAGES ? issued - TL::STAGES : 0;
+            for (int i = first; i < issued; ++i)
+                mbar_wait(&full[i % TL::STAGES], (i / TL::STAGES) & 1);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ------------------------------------------------------------ products
+        constexpr uint32_t idesc = umma_idesc(TILE_M, BN);
+        bool ok = true;
+        for (int i = 0; i < n_kb && ok; ++i) {
+            const int s = i % TL::STAGES;
+            const uint32_t ph = (i / TL::STAGES) & 1;
+            if (*abort_flag) { ok = false; break; }
+            if (!mbar_wait(&full[s], ph)) {
+                atomicCAS(&g_gemm_status, 0, (2 << 8) | s);
+                *abort_flag = 1;
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            const uint32_t a_addr = smem_u32(smem + s * TL::STAGE_BYTES);
+            const uint32_t b_addr = a_addr + TL::A_BYTES * (GATED ? 2 : 1);
+#pragma unroll
+            for (int k = 0; k < TILE_K / UMMA_K; ++k) {
+                const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
+                const uint64_t bd = umma_desc(b_addr + k * UMMA_K * 2);
+                tc_mma_bf16(tmem_base, umma_desc(a_addr + k * UMMA_K * 2), bd, idesc, acc);
+                if (GATED)
+                    tc_mma_bf16(tmem_base + BN, umma_desc(a_addr + TL::A_BYTES + k * UMMA_K * 2),
+                                bd, idesc, acc);
+            }
+            tc_commit(&empty[s]);          // the stage is free once these products have read it
+        }
+        tc_commit(acc_full);               // arrives when every product above is done
+    } else if (warp >= 2) {
+        // ------------------------------------------------------------ epilogue
+        const int quarter = warp & 3;
+        const int f = m0 + quarter * 32 + lane;           // this thread's output feature
+        bool ok = mbar_wait(acc_full, 0);
+        if (!ok) {
+            atomicCAS(&g_gemm_status, 0, (3 << 8));
+            *abort_flag = 1;
+        }
+        tc_fence_after();
+        if (ok && !*abort_flag && n_kb > 0) {
+            const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+            TO* obase = out + (size_t)blockIdx.z * split_stride;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 16) {
+                uint32_t r[16], u[16];
+                tc_ld16(lane_base + c, r);
+                if (GATED) tc_ld16(lane_base + BN + c, u);
+                tc_wait_ld();
+                if (f < N) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int n = n0 + c + j;
+                        if (n < T) {
+                            float v = __uint_as_float(r[j]);
+                            if (GATED) {
+                                v = (act == 1 ? silu_fast(v) : gelu_tanh_fast(v)) *
+                                    __uint_as_float(u[j]);
+                            }
+                            store_out<TO>(obase + (size_t)n * ldc + f, v);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                     "r"((uint32_t)TL::TMEM_COLS)
+                     : "memory");
+    }
+}
+
+// ---------------------------------------------------------------- tensor maps
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
+                cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    });
+    return fn;
+}
+
+// A [rows, K] bf16 matrix with row stride ld (elements), read in boxes of
+// [box_rows x 64]; cached by its geometry (weights are asked for every step).
+int make_map(CUtensorMap* out, const void* ptr, long long rows, long long K, long long ld,
+             int box_rows) {
+    typedef std::tuple<const void*, long long, long long, long long, int> Key;
+    static std::map<Key, CUtensorMap> cache;
+    static std::mutex mu;
+    Key key(ptr, rows, K, ld, box_rows);
+    {
+        std::lock_guard<std::mutex> g(mu);
+        auto it = cache.find(key);
+        if (it != cache.end()) {
+            *out = it->second;
+            return 0;
+        }
+    }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return agv_fail(-4, "linear: the driver does not export cuTensorMapEncodeTiled");
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)TILE_K, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides,
+                    box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return agv_fail(-4, "linear: cuTensorMapEncodeTiled failed with code %d (rows %lld, K %lld, "
+                        "ld %lld)", (int)r, rows, K, ld);
+    std::lock_guard<std::mutex> g(mu);
+    if (cache.size() > 8192) cache.clear();
+    cache[key] = *out;
+    return 0;
+}
+
+template <int BN, bool GATED, typename TO>
+int launch(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx, void* out, int T,
+           int N, int K, long long ldc, long long split_stride, int splits, int kb_per_split,
+           int act, cudaStream_t stream) {
+    using TL = Tile<BN, GATED>;
+    auto kern = gemm_tcgen05_kernel<BN, GATED, TO>;
+    static bool configured = false;
+    if (!configured) {
+        AGV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         TL::SMEM));
+        configured = true;
+    }
+    dim3 grid((N + TILE_M - 1) / TILE_M, (T + BN - 1) / BN, splits);
+    AGV_REQUIRE(grid.y <= 65535, "linear: %d tokens exceed the grid limit", T);
+    kern<<<grid, GEMM_THREADS, TL::SMEM, stream>>>(mw, mw2, mx, (TO*)out, T, N, K, ldc,
+                                                   split_stride, kb_per_split, act);
+    AGV_LAUNCH_OK("gemm_tcgen05_kernel");
+    return 0;
+}
+
+template <bool GATED, typename TO>
+int launch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx,
+              void* out, int T, int N, int K, long long ldc, long long split_stride, int splits,
+              int kb_per_split, int act, cudaStream_t stream) {
+#define AGV_BN_CASE(B)                                                                          \
+    case B:                                                                                      \
+        return launch<B, GATED, TO>(mw, mw2, mx, out, T, N, K, ldc, split_stride, splits,        \
+                                    kb_per_split, act, stream)
+    switch (bn) {
+        AGV_BN_CASE(16);
+        AGV_BN_CASE(32);
+        AGV_BN_CASE(64);
+        AGV_BN_CASE(128);
+        case 256:
+            if constexpr (!GATED)
+                return launch<256, false, TO>(mw, mw2, mx, out, T, N, K, ldc, split_stride, splits,
+                                              kb_per_split, act, stream);
+    }
+#undef AGV_BN_CASE
+    return agv_fail(-1, "linear: no kernel for a token tile of %d", bn);
+}
+
+}  // namespace
+
+// Whether the tensor-core kernel takes this shape: K and the row strides must
+// be multiples of 8 elements (a TMA row stride is a multiple of 16 bytes) and
+// the pointers 16-byte aligned.
+AGV_API int agv_linear_tc_supported(int N, int K, long long lda) {
+    return (N > 0 && K > 0 && K % 8 == 0 && lda % 8 == 0) ? 1 : 0;
+}
+
+// x: [T, K] bf16, row stride lda; w (and w2 for the gated form): [N, K] bf16
+// dense; out: [T, N] (bf16 or f32, row stride ldc).  splits > 1 (plain form,
+// f32 out only): out is [splits, T, N] partial sums over K ranges, to be added
+// by the consumer.  token_tile 0 lets the launcher choose.
+AGV_API int agv_linear_tc(const void* x, const void* w, const void* w2, void* out, int T, int N,
+                          int K, long long lda, long long ldc, int out_dtype, int act, int splits,
+                          int token_tile, cudaStream_t stream) {
+    AGV_REQUIRE(T >= 0 && N > 0 && K > 0, "linear: bad sizes T=%d N=%d K=%d", T, N, K);
+    AGV_REQUIRE(K % 8 == 0 && lda % 8 == 0, "linear: the tensor-core kernel needs K (%d) and the "
+                "row stride (%lld) to be multiples of 8", K, lda);
+    AGV_REQUIRE(agv_aligned(x, 16) && agv_aligned(w, 16) && (!w2 || agv_aligned(w2, 16)),
+                "linear: operands must be 16-byte aligned");
+    AGV_REQUIRE(lda >= K && ldc >= N, "linear: row strides shorter than rows");
+    AGV_REQUIRE(splits >= 1, "linear: splits must be >= 1");
+    AGV_REQUIRE(splits == 1 || (!w2 && out_dtype == AGV_F32),
+                "linear: partial sums need the plain form and a 32-bit output");
+    if (T == 0) return 0;
+    int bn = token_tile;
+    if (bn == 0) bn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : (T <= 128 || w2) ? 128 : 256;
+    const int kb_total = (K + TILE_K - 1) / TILE_K;
+    if (splits > kb_total) splits = kb_total;
+    const int kb_per = (kb_total + splits - 1) / splits;
+    splits = (kb_total + kb_per - 1) / kb_per;       // no empty split
+    CUtensorMap mw, mw2, mx;
+    if (int rc = make_map(&mw, w, N, K, K, TILE_M)) return rc;
+    if (w2) {
+        if (int rc = make_map(&mw2, w2, N, K, K, TILE_M)) return rc;
+    } else {
+        mw2 = mw;
+    }
+    if (int rc = make_map(&mx, x, T, K, lda, bn)) return rc;
+    const long long split_stride = (long long)T * ldc;
+    if (w2) {
+        AGV_REQUIRE(out_dtype == AGV_BF16, "linear: the gated form writes bfloat16");
+        return launch_bn<true, __nv_bfloat16>(bn, mw, mw2, mx, out, T, N, K, ldc, 0, 1, kb_total,
+                                              act, stream);
+    }
+    if (out_dtype == AGV_BF16)
+        return launch_bn<false, __nv_bfloat16>(bn, mw, mw2, mx, out, T, N, K, ldc, 0, 1, kb_total,
+                                               act, stream);
+    if (out_dtype == AGV_F32)
+        return launch_bn<false, float>(bn, mw, mw2, mx, out, T, N, K, ldc, split_stride, splits,
+                                       kb_per, act, stream);
+    return agv_fail(-1, "linear: unknown output dtype %d", out_dtype);
+}
+
+// The number of partial sums agv_linear_tc will really write for these sizes.
+AGV_API int agv_linear_tc_splits(int K, int splits) {
+    const int kb_total = (K + TILE_K - 1) / TILE_K;
+    if (splits > kb_total) splits = kb_total;
+    if (splits < 1) splits = 1;
+    const int kb_per = (kb_total + splits - 1) / splits;
+    return (kb_total + kb_per - 1) / kb_per;
+}
+
+// Reads and clears the status word of the tensor-core kernels: 0, or
+// (role << 8 | stage) of the first bounded wait that gave up.
+AGV_API int agv_linear_tc_status() {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_gemm_status, sizeof(int)) != cudaSuccess) return -1;
+    if (v != 0) cudaMemcpyToSymbol(g_gemm_status, &zero, sizeof(int));
+    return v;
+}

@@ -291,12 +291,60 @@ def sample(logits: torch.Tensor, out: torch.Tensor, temperature: float, top_k: i
                                 _ptr(seq_ids), _ptr(steps), _stream()))
 
 
+def linear_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
+              w2: Optional[torch.Tensor] = None, activation: str = "gelu_tanh",
+              splits: int = 1, token_tile: int = 0) -> None:
+    """bfloat16 product on the tensor cores (tcgen05 + TMA).
+
+    out [T, N] in bfloat16 or 32-bit; with splits > 1, out is [splits, T, N] 32-bit
+    partial sums over ranges of K (use ``linear_tc_splits`` for the real count).
+    """
+    T, K = x.shape
+    N = w.shape[0]
+    assert w.shape == (N, K) and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+    assert x.stride(1) == 1
+    _dense(w, "w")
+    if w2 is not None:
+        _dense(w2, "w2")
+        assert w2.shape == w.shape and w2.dtype == w.dtype
+    if splits > 1:
+        assert out.dim() == 3 and out.shape[1:] == (T, N) and out.is_contiguous()
+        ldc = N
+    else:
+        assert out.shape == (T, N) and out.stride(1) == 1
+        ldc = out.stride(0)
+    _check(library().agv_linear_tc(
+        _ptr(x), _ptr(w), _ptr(w2), _ptr(out), T, N, K, ctypes.c_longlong(x.stride(0)),
+        ctypes.c_longlong(ldc), dtype_code(out.dtype), ACT[activation], splits, token_tile,
+        _stream()))
+
+
+def linear_tc_splits(K: int, splits: int) -> int:
+    return library().agv_linear_tc_splits(K, splits)
+
+
+def linear_tc_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and
+            w.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and
+            w.data_ptr() % 16 == 0)
+
+
+def linear_tc_status() -> int:
+    """0, or the code of the first bounded wait of a tensor-core kernel that gave
+    up since the last call (this call synchronises the device)."""
+    torch.cuda.synchronize()
+    return library().agv_linear_tc_status()
+
+
 # ------------------------------------------------------------------ dispatch
 def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
            w2: Optional[torch.Tensor] = None, activation: str = "gelu_tanh") -> None:
     """out = x w^T (or the gated pair).  The kernel is chosen from the dtype and
-    the weight's shape only."""
-    linear_simt(x, w, out, w2, activation)
+    the weight's shape only, never from the number of rows of x."""
+    if linear_tc_supported(x, w) and (w2 is None or out.dtype == torch.bfloat16):
+        linear_tc(x, w, out, w2, activation)
+    else:
+        linear_simt(x, w, out, w2, activation)
 
 
 def attention_prefill(q, k, v, out, ctx, n_heads, n_kv_heads, head_dim, scale, window) -> None:

@@ -1,0 +1,373 @@
+"""Each kernel alone against a plain PyTorch 32-bit statement of the same
+operation, at sizes other than the engine's (odd widths, head sizes in steps
+of 16, vocabularies that are no power of two)."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def rnd(*shape, dtype=torch.float32, seed=0, scale=1.0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+def rel_err(got, ref):
+    got, ref = got.double().cpu(), ref.double().cpu()
+    return ((got - ref).abs().max() / ref.abs().max().clamp_min(1e-30)).item()
+
+
+# ------------------------------------------------------------------- products
+@pytest.mark.parametrize("T,N,K", [(1, 96, 64), (5, 200, 96), (16, 128, 1152), (33, 384, 224),
+                                   (64, 1000, 136), (130, 260, 72), (300, 520, 264)])
+def test_linear_tensor_cores_plain(T, N, K):
+    from agave_b200 import kernels
+    x, w = rnd(T, K, dtype=torch.bfloat16, seed=1), rnd(N, K, dtype=torch.bfloat16, seed=2)
+    ref = x.float() @ w.float().T
+    for out_dtype in (torch.bfloat16, torch.float32):
+        out = torch.full((T, N), float("nan"), dtype=out_dtype, device=DEV)
+        kernels.linear_tc(x, w, out)
+        assert kernels.linear_tc_status() == 0
+        tol = 1e-5 if out_dtype == torch.float32 else 5e-3
+        assert rel_err(out, ref) < tol, (T, N, K, out_dtype)
+
+
+@pytest.mark.parametrize("tile", [16, 32, 64, 128, 256])
+def test_linear_tensor_cores_every_token_tile(tile):
+    from agave_b200 import kernels
+    T, N, K = 70, 300, 200
+    x, w = rnd(T, K, dtype=torch.bfloat16, seed=3), rnd(N, K, dtype=torch.bfloat16, seed=4)
+    out = torch.full((T, N), float("nan"), dtype=torch.float32, device=DEV)
+    kernels.linear_tc(x, w, out, token_tile=tile)
+    assert kernels.linear_tc_status() == 0
+    assert rel_err(out, x.float() @ w.float().T) < 1e-5
+
+
+def test_linear_tensor_cores_row_strided_input_and_output():
+    from agave_b200 import kernels
+    T, N, K = 9, 160, 128
+    big = rnd(T, K + 64, dtype=torch.bfloat16, seed=5)
+    x = big[:, 32:32 + K]            # row stride K + 64, first element 64 bytes in
+    w = rnd(N, K, dtype=torch.bfloat16, seed=6)
+    outbig = torch.zeros((T, N + 24), dtype=torch.bfloat16, device=DEV)
+    kernels.linear_tc(x, w, outbig[:, :N])
+    assert kernels.linear_tc_status() == 0
+    assert rel_err(outbig[:, :N], x.float() @ w.float().T) < 5e-3
+    assert (outbig[:, N:] == 0).all()
+
+
+@pytest.mark.parametrize("T,N,K,act", [(3, 224, 96, "gelu_tanh"), (40, 130, 320, "silu"),
+                                       (150, 256, 64, "gelu_tanh")])
+def test_linear_tensor_cores_gated(T, N, K, act):
+    from agave_b200 import kernels
+    x = rnd(T, K, dtype=torch.bfloat16, seed=7)
+    wg, wu = rnd(N, K, dtype=torch.bfloat16, seed=8, scale=0.3), rnd(N, K, dtype=torch.bfloat16, seed=9, scale=0.3)
+    g, u = x.float() @ wg.float().T, x.float() @ wu.float().T
+    a = torch.nn.functional.gelu(g, approximate="tanh") if act == "gelu_tanh" \
+        else torch.nn.functional.silu(g)
+    out = torch.full((T, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    kernels.linear_tc(x, wg, out, w2=wu, activation=act)
+    assert kernels.linear_tc_status() == 0
+    assert rel_err(out, a * u) < 6e-3
+
+
+@pytest.mark.parametrize("splits", [2, 3, 7])
+def test_linear_tensor_cores_partial_sums(splits):
+    from agave_b200 import kernels
+    T, N, K = 6, 200, 6912 // 4
+    x, w = rnd(T, K, dtype=torch.bfloat16, seed=10), rnd(N, K, dtype=torch.bfloat16, seed=11)
+    s = kernels.linear_tc_splits(K, splits)
+    out = torch.full((s, T, N), float("nan"), dtype=torch.float32, device=DEV)
+    kernels.linear_tc(x, w, out, splits=splits)
+    assert kernels.linear_tc_status() == 0
+    assert rel_err(out.sum(0), x.float() @ w.float().T) < 1e-5
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_linear_simt_plain_and_gated(dtype):
+    from agave_b200 import kernels
+    T, N, K = 37, 131, 67          # nothing a multiple of anything
+    x, w, w2 = rnd(T, K, dtype=dtype, seed=1), rnd(N, K, dtype=dtype, seed=2), rnd(N, K, dtype=dtype, seed=3)
+    out = torch.empty((T, N), dtype=dtype, device=DEV)
+    kernels.linear_simt(x, w, out)
+    tol = 1e-5 if dtype == torch.float32 else 6e-3
+    assert rel_err(out, x.float() @ w.float().T) < tol
+    kernels.linear_simt(x, w, out, w2=w2, activation="gelu_tanh")
+    ref = torch.nn.functional.gelu(x.float() @ w.float().T, approximate="tanh") * (x.float() @ w2.float().T)
+    assert rel_err(out, ref) < tol
+    if dtype == torch.float32:
+        # true 32-bit: no reduced-precision matrix mode hides in the product
+        big = rnd(8, 4096, seed=4) + 1.0
+        wb = rnd(8, 4096, seed=5) + 1.0
+        o = torch.empty((8, 8), dtype=torch.float32, device=DEV)
+        kernels.linear_simt(big, wb, o)
+        assert rel_err(o, big.double() @ wb.double().T) < 2e-6
+
+
+# ---------------------------------------------------------------------- norms
+@pytest.mark.parametrize("H", [48, 1000, 5376])
+def test_norm_family(H):
+    from agave_b200 import kernels
+    R = 7
+    h = rnd(R, H, seed=1)
+    y = rnd(R, H, dtype=torch.bfloat16, seed=2)
+    wp, wn = rnd(H, seed=3) * 0.2 + 1, rnd(H, seed=4) * 0.2 + 1
+    eps_p, eps_n = 1e-5, 1e-6
+
+    def norm(v, w, eps):
+        return v * torch.rsqrt((v * v).mean(-1, keepdim=True) + eps) * w
+
+    # plain norm with a row gather
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32, device=DEV)
+    x = torch.empty((3, H), dtype=torch.float32, device=DEV)
+    kernels.norm_residual(h, None, None, wn, x, eps_next=eps_n, rows=rows)
+    assert rel_err(x, norm(h[rows.long()], wn, eps_n)) < 1e-6
+    # h += post(y); x = next(h)
+    h2 = h.clone()
+    xb = torch.empty((R, H), dtype=torch.bfloat16, device=DEV)
+    kernels.norm_residual(h2, y, wp, wn, xb, eps_post=eps_p, eps_next=eps_n)
+    href = h + norm(y.float(), wp, eps_p)
+    assert rel_err(h2, href) < 1e-6
+    assert rel_err(xb, norm(href, wn, eps_n)) < 5e-3
+    # partial sums as the branch, no post norm, no next norm
+    parts = rnd(3, R, H, seed=5)
+    h3 = h.clone()
+    kernels.norm_residual(h3, parts, None, None, None)
+    assert rel_err(h3, h + parts.sum(0)) < 1e-6
+
+
+# ------------------------------------------------------ embedding and rotation
+def test_embed_and_rope_table():
+    from agave_b200 import kernels
+    V, H = 1003, 72
+    table = rnd(V, H, dtype=torch.bfloat16, seed=1)
+    toks = torch.tensor([0, 1002, 17, 17], dtype=torch.int32, device=DEV)
+    out = torch.empty((4, H), dtype=torch.float32, device=DEV)
+    kernels.embed(toks, table, math.sqrt(H), out)
+    assert torch.equal(out, table[toks.long()].float() * torch.tensor(math.sqrt(H), dtype=torch.float32))
+    pos = torch.tensor([0, 1, 4095, 8191], dtype=torch.int32, device=DEV)
+    rd = 48
+    cos = torch.empty((4, rd // 2), dtype=torch.float32, device=DEV)
+    sin = torch.empty_like(cos)
+    kernels.rope_table(pos, rd, 5e5, 8.0, cos, sin)
+    i = torch.arange(rd // 2, dtype=torch.float64)
+    ang = (pos.cpu().double() / 8.0)[:, None] * torch.exp(-math.log(5e5) * 2 * i / rd)[None, :]
+    assert (cos.cpu().double() - torch.cos(ang)).abs().max() < 1e-7
+    assert (sin.cpu().double() - torch.sin(ang)).abs().max() < 1e-7
+
+
+# ------------------------------------------- q/k norm, rotation and cache store
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd,rd", [(3, 1, 16, 16), (6, 2, 48, 32), (4, 4, 80, 80)])
+def test_qk_norm_rope_store(dtype, nh, nkv, hd, rd):
+    from agave_b200 import kernels
+    T, PAGE, cap = 11, 4, 8            # a ring of 8 rows in pages of 4
+    qkv = rnd(T, (nh + 2 * nkv) * hd, dtype=dtype, seed=1)
+    orig = qkv.clone().float()
+    wq, wk = rnd(hd, seed=2) * 0.1 + 1, rnd(hd, seed=3) * 0.1 + 1
+    # two sequences: tokens 0..6 are positions 0..6 of entry 0, tokens 7..10 positions 0..3 of entry 1
+    positions = torch.tensor(list(range(7)) + list(range(4)), dtype=torch.int32, device=DEV)
+    seq_index = torch.tensor([0] * 7 + [1] * 4, dtype=torch.int32, device=DEV)
+    slots = torch.tensor([2, 0], dtype=torch.int32, device=DEV)
+    lens = torch.tensor([7, 4], dtype=torch.int32, device=DEV)
+    table = torch.tensor([[5, 1], [0, 0], [3, 4]], dtype=torch.int32, device=DEV)
+    k_pool = torch.zeros((6, PAGE, nkv, hd), dtype=dtype, device=DEV)
+    v_pool = torch.zeros_like(k_pool)
+    cos = torch.empty((T, rd // 2), dtype=torch.float32, device=DEV)
+    sin = torch.empty_like(cos)
+    kernels.rope_table(positions, rd, 10000.0, 1.0, cos, sin)
+    kernels.qk_norm_rope_store(qkv, nh, nkv, hd, wq, wk, 1e-6, cos, sin, rd, positions, k_pool,
+                               v_pool, table, slots, lens, seq_index, PAGE, cap)
+    x = orig.reshape(T, nh + 2 * nkv, hd)
+
+    def ref_head(v, w):
+        v = v * torch.rsqrt((v * v).mean(-1, keepdim=True) + 1e-6) * w
+        half = rd // 2
+        c, s = cos[:, None, :], sin[:, None, :]
+        out = v.clone()
+        out[..., :half] = v[..., :half] * c - v[..., half:rd] * s
+        out[..., half:rd] = v[..., :half] * s + v[..., half:rd] * c
+        return out
+
+    q_ref, k_ref, v_ref = ref_head(x[:, :nh], wq), ref_head(x[:, nh:nh + nkv], wk), x[:, nh + nkv:]
+    got = qkv.float().reshape(T, nh + 2 * nkv, hd)
+    tol = 1e-5 if dtype == torch.float32 else 8e-3
+    assert rel_err(got[:, :nh], q_ref) < tol and rel_err(got[:, nh:nh + nkv], k_ref) < tol
+    for t in range(T):
+        b, p = int(seq_index[t]), int(positions[t])
+        row = p % cap
+        page = int(table[int(slots[b]), row // PAGE])
+        assert rel_err(k_pool[page, row % PAGE].float(), k_ref[t]) < tol
+        assert rel_err(v_pool[page, row % PAGE].float(), v_ref[t]) < tol
+    # pages nobody owns stay untouched
+    assert (k_pool[2] == 0).all() and (k_pool[1, 3] == 0).all()
+
+
+# ------------------------------------------------------------------ attention
+def ref_attention(q, k, v, scale, window):
+    """q [Tq, nh, hd] at positions pos (last Tq of the keys), k/v [Tk, nkv, hd]."""
+    Tq, nh, hd = q.shape
+    Tk, nkv = k.shape[0], k.shape[1]
+    out = torch.zeros(Tq, nh, hd, dtype=torch.float64)
+    for i in range(Tq):
+        p = Tk - Tq + i
+        lo = max(0, p - window + 1) if window else 0
+        for h in range(nh):
+            g = h // (nh // nkv)
+            s = (k[lo:p + 1, g].double() @ q[i, h].double()) * scale
+            a = torch.softmax(s, 0)
+            out[i, h] = a @ v[lo:p + 1, g].double()
+    return out.reshape(Tq, nh * hd)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd,window", [(4, 1, 16, 5), (6, 2, 48, 0), (2, 2, 128, 9)])
+def test_attention_prefill_ragged(dtype, nh, nkv, hd, window):
+    from agave_b200 import kernels
+    lens = [13, 1, 30]
+    T = sum(lens)
+    qkv = rnd(T, (nh + 2 * nkv) * hd, dtype=dtype, seed=1)
+    q, k, v = qkv[:, :nh * hd], qkv[:, nh * hd:(nh + nkv) * hd], qkv[:, (nh + nkv) * hd:]
+    out = torch.empty((T, nh * hd), dtype=dtype, device=DEV)
+    positions = torch.tensor(sum([list(range(n)) for n in lens], []), dtype=torch.int32, device=DEV)
+    seq_index = torch.tensor(sum([[i] * n for i, n in enumerate(lens)], []), dtype=torch.int32, device=DEV)
+    cu = torch.tensor([0, 13, 14, 44], dtype=torch.int32, device=DEV)
+    scale = 0.17
+    kernels.attention_prefill_simt(q, k, v, out, positions, seq_index, cu, nh, nkv, hd, scale, window)
+    o = 0
+    tol = 1e-5 if dtype == torch.float32 else 8e-3
+    for n in lens:
+        qs = q[o:o + n].float().cpu().reshape(n, nh, hd)
+        ks = k[o:o + n].float().cpu().reshape(n, nkv, hd)
+        vs = v[o:o + n].float().cpu().reshape(n, nkv, hd)
+        assert rel_err(out[o:o + n], ref_attention(qs, ks, vs, scale, window)) < tol
+        o += n
+
+
+def test_attention_finds_a_far_key_and_respects_the_window_edge():
+    """One key among hundreds is made to dominate: without a window the query
+    must return that key's value; with a window that just excludes it, it must not."""
+    from agave_b200 import kernels
+    nh = nkv = 1
+    hd, n, far = 32, 300, 3
+    k = rnd(n, hd, seed=1, scale=0.1)
+    v = rnd(n, hd, seed=2)
+    q = rnd(n, hd, seed=3, scale=0.1)
+    k[far] = 0; k[far, 0] = 40.0
+    q[-1] = 0; q[-1, 0] = 40.0
+    qkv = torch.cat([q, k, v], dim=1).contiguous()
+    positions = torch.arange(n, dtype=torch.int32, device=DEV)
+    seq_index = torch.zeros(n, dtype=torch.int32, device=DEV)
+    cu = torch.tensor([0, n], dtype=torch.int32, device=DEV)
+    out = torch.empty((n, hd), dtype=torch.float32, device=DEV)
+    args = (qkv[:, :hd], qkv[:, hd:2 * hd], qkv[:, 2 * hd:], out, positions, seq_index, cu, 1, 1, hd, 1.0)
+    kernels.attention_prefill_simt(*args, 0)
+    assert rel_err(out[-1], v[far]) < 1e-4
+    kernels.attention_prefill_simt(*args, n - far)          # window reaches exactly key `far`
+    assert rel_err(out[-1], v[far]) < 1e-4
+    kernels.attention_prefill_simt(*args, n - far - 1)      # one shorter: the key is outside
+    assert (out[-1] - v[far]).abs().max() > 0.1
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd,window", [(4, 1, 16, 0), (6, 2, 48, 7), (8, 2, 64, 0)])
+def test_attention_over_the_paged_cache(dtype, nh, nkv, hd, window):
+    from agave_b200 import kernels
+    PAGE = 4
+    lens = [9, 1, 22]                      # lengths after this step; queries are the last tokens
+    cap = 24 if not window else 8          # the window ring is shorter than the sequences
+    max_pages = cap // PAGE
+    n_pages = 40
+    k_pool = rnd(n_pages, PAGE, nkv, hd, dtype=dtype, seed=1)
+    v_pool = rnd(n_pages, PAGE, nkv, hd, dtype=dtype, seed=2)
+    perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(3)).int()
+    table = perm[:4 * max_pages].reshape(4, max_pages).contiguous().to(DEV)
+    slots = torch.tensor([3, -1, 1, 0], dtype=torch.int32, device=DEV)   # entry 1 is padding
+    lens_t = [9, 0, 1, 22]
+    q = rnd(4, nh * hd, dtype=dtype, seed=4)
+    positions = torch.tensor([8, 0, 0, 21], dtype=torch.int32, device=DEV)
+    seq_index = torch.arange(4, dtype=torch.int32, device=DEV)
+    out = torch.full((4, nh * hd), float("nan"), dtype=dtype, device=DEV)
+    kernels.attention_paged_simt(q, out, k_pool, v_pool, table, slots, positions, seq_index, PAGE,
+                                 cap, nh, nkv, hd, 0.2, window)
+    tol = 1e-5 if dtype == torch.float32 else 8e-3
+    assert (out[1] == 0).all()
+    for b in (0, 2, 3):
+        n, slot = lens_t[b], int(slots[b])
+        lo = max(0, n - window) if window else 0
+        ks, vs = [], []
+        for j in range(lo, n):
+            row = j % cap
+            page = int(table[slot, row // PAGE])
+            ks.append(k_pool[page, row % PAGE].float().cpu())
+            vs.append(v_pool[page, row % PAGE].float().cpu())
+        ks, vs = torch.stack(ks), torch.stack(vs)
+        qs = q[b].float().cpu().reshape(1, nh, hd)
+        ref = ref_attention(qs, ks, vs, 0.2, 0)
+        assert rel_err(out[b:b + 1], ref) < tol, b
+
+
+# ------------------------------------------------------------------- sampling
+@pytest.mark.parametrize("V", [257, 5000, 262144 + 64])
+def test_argmax_first_index_on_ties(V):
+    from agave_b200 import kernels
+    logits = rnd(3, V, seed=1)
+    logits[0, 100] = 50.0; logits[0, 200] = 50.0
+    logits[1, V - 1] = 60.0
+    logits[2, 0] = 70.0
+    out = torch.empty(3, dtype=torch.int32, device=DEV)
+    kernels.argmax(logits, out)
+    assert out.tolist() == [100, V - 1, 0]
+
+
+def test_sampling_matches_the_filtered_distribution():
+    import sys, os
+    from agave_b200 import kernels
+    from plain import gemma3_plain as P
+    V, n = 1000, 4000
+    base = rnd(V, seed=5) * 2.0
+    temperature, top_k, top_p = 0.8, 50, 0.9
+    wts = P.filtered_weights(base.cpu(), temperature, top_k, top_p)
+    probs = (wts / wts.sum()).double()
+    logits = base[None, :].expand(n, V).contiguous()
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    seq = torch.arange(n, dtype=torch.int64, device=DEV)
+    steps = torch.zeros(n, dtype=torch.int32, device=DEV)
+    kernels.sample(logits, out, temperature, top_k, top_p, 1234, seq, steps)
+    counts = torch.bincount(out.cpu().long(), minlength=V).double()
+    assert counts[probs == 0].sum() == 0              # nothing outside the kept set
+    kept = probs > 0
+    assert int(kept.sum()) <= top_k
+    # chi-square-like bound on the kept set
+    exp = probs[kept] * n
+    chi = (((counts[kept] - exp) ** 2) / exp.clamp_min(1e-9)).sum().item()
+    assert chi < 3 * int(kept.sum()) + 30, chi
+    # same seed, same draw; other seed, other draws; batch position does not matter
+    out2 = torch.empty_like(out)
+    kernels.sample(logits, out2, temperature, top_k, top_p, 1234, seq, steps)
+    assert torch.equal(out, out2)
+    kernels.sample(logits, out2, temperature, top_k, top_p, 99, seq, steps)
+    assert not torch.equal(out, out2)
+    perm = torch.randperm(n, device=DEV)
+    kernels.sample(logits, out2, temperature, top_k, top_p, 1234, seq[perm].contiguous(), steps)
+    assert torch.equal(out2, out[perm])
+
+
+def test_repeat_penalty_per_occurrence_and_history():
+    from agave_b200 import kernels
+    V = 300
+    logits = torch.ones((2, V), device=DEV)
+    logits[:, 7] = -2.0
+    hist = torch.zeros((4, 16), dtype=torch.int32, device=DEV)
+    hist_len = torch.zeros(4, dtype=torch.int32, device=DEV)
+    slots = torch.tensor([2, -1], dtype=torch.int32, device=DEV)
+    for tok in (5, 7, 5):
+        kernels.history_append(torch.tensor([tok, 9], dtype=torch.int32, device=DEV), slots, hist, hist_len)
+    assert hist_len.tolist() == [0, 0, 3, 0] and hist[2, :3].tolist() == [5, 7, 5]
+    kernels.repeat_penalty(logits, slots, hist, hist_len, 2.0)
+    assert logits[0, 5].item() == 0.25 and logits[0, 7].item() == -4.0
+    assert logits[0, 6].item() == 1.0 and (logits[1] == torch.where(torch.arange(V, device=DEV) == 7, -2.0, 1.0)).all()
