@@ -1,0 +1,317 @@
+// Decode attention over the paged cache, split along the keys.
+//
+// One CTA takes one sequence, one group of query heads that share a kv head,
+// and one chunk of CH consecutive key positions.  It copies the chunk's key and
+// value rows into shared memory with cp.async (every row in flight at once, so
+// the cost is one trip to HBM, not one per key), computes the scores of the
+// group's heads, their softmax weights relative to the chunk's own maximum, and
+// the weighted sum of the values; it writes that partial result (sum, maximum,
+// normaliser) to scratch memory.  A second kernel merges the chunks of each
+// (sequence, head).  Chunks past a sequence's end exit at once, so the grid can
+// be sized for the longest sequence the cache allows and the launch replayed
+// from a CUDA graph.  Scores, softmax and sums are 32-bit.
+//
+// Reference: one block per head, scores of all positions in shared memory,
+// softmax by the first 32 threads (src/backend/kernels/cuda/sdpa.zig:16-104);
+// score = (q . k) * scale, kv head = h / (nh / nkv)
+// (src/backend/kernels/cpu/sdpa.zig:36-37,58); window start sl - W
+// (src/models/gemma4.zig:1153-1155).  No value row is skipped for a small weight.
+#include "common.cuh"
+
+namespace {
+
+constexpr int AD_THREADS = 128;
+constexpr int AD_GC = 4;              // query heads of a group handled together
+constexpr int AD_MAX_HD = 512;
+constexpr int AD_MAX_SMEM = 160 * 1024;
+
+template <typename T> struct Vec16;   // 16-byte vector of T
+template <> struct Vec16<float> { static constexpr int N = 4; };
+template <> struct Vec16<__nv_bfloat16> { static constexpr int N = 8; };
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+    asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
+}
+
+__device__ __forceinline__ void load_vec(const float* p, float (&v)[4]) {
+    const float4 t = *reinterpret_cast<const float4*>(p);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+__device__ __forceinline__ void load_vec(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 t = *reinterpret_cast<const uint4*>(p);
+    const unsigned w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        v[2 * i] = __uint_as_float(w[i] << 16);
+        v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+
+__device__ __forceinline__ float2 load_pair(const float* p) {
+    return *reinterpret_cast<const float2*>(p);
+}
+__device__ __forceinline__ float2 load_pair(const __nv_bfloat16* p) {
+    const unsigned w = *reinterpret_cast<const unsigned*>(p);
+    return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
+
+struct DecodeArgs {
+    const void* q;             // [B, nh, hd] rows of stride q_stride
+    long long q_stride;
+    const void* k_pool;        // [n_pages, page, nkv, hd] of this layer
+    const void* v_pool;
+    const int* page_table;     // [n_slots, max_pages]
+    const int* slots;          // [B]; negative = padding entry
+    const int* positions;      // [B] position of the query (its key is stored already)
+    float* part_acc;           // [B, nh, S, hd]
+    float* part_ml;            // [B, nh, S, 2]
+    int max_pages, page, cap, nh, nkv, hd, window, n_splits, chunk;
+    float scale;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(AD_THREADS)
+attention_decode_split_kernel(DecodeArgs a) {
+    constexpr int VEC = Vec16<T>::N;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int b = blockIdx.z, split = blockIdx.x;
+    const int G = a.nh / a.nkv;
+    const int chunks_per_group = (G + AD_GC - 1) / AD_GC;
+    const int g = blockIdx.y / chunks_per_group;              // kv head
+    const int h0 = g * G + (blockIdx.y % chunks_per_group) * AD_GC;   // first query head
+    const int gc = min(AD_GC, g * G + G - h0);                // heads handled here
+    const int slot = a.slots[b];
+    if (slot < 0) return;
+    const int p = a.positions[b];
+    const int lo = a.window > 0 ? max(0, p - a.window + 1) : 0;
+    const int j0 = lo + split * a.chunk;
+    if (j0 > p) return;
+    const int n = min(a.chunk, p - j0 + 1);                   // keys of this chunk
+    const int hd = a.hd, CH = a.chunk;
+
+    T* Ks = reinterpret_cast<T*>(smem_raw);
+    T* Vs = Ks + (size_t)CH * hd;
+    float* qs = reinterpret_cast<float*>(Vs + (size_t)CH * hd);   // [AD_GC][hd]
+    float* sc = qs + AD_GC * hd;                                  // [AD_GC][CH]
+    float* stat = sc + AD_GC * CH;                                // [AD_GC][2]
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // ---- keys and values of the chunk into shared memory, all copies in flight
+    const int vec_per_row = hd / VEC;
+    const int* table = a.page_table + (size_t)slot * a.max_pages;
+    for (int i = tid; i < n * vec_per_row; i += AD_THREADS) {
+        const int r = i / vec_per_row, c = (i % vec_per_row) * VEC;
+        const int row = (j0 + r) % a.cap;
+        const int page = table[row / a.page];
+        const size_t off = (((size_t)page * a.page + row % a.page) * a.nkv + g) * hd + c;
+        cp_async16(Ks + (size_t)r * hd + c, (const T*)a.k_pool + off);
+        cp_async16(Vs + (size_t)r * hd + c, (const T*)a.v_pool + off);
+    }
+    // ---- the group's queries, 32-bit
+    for (int i = tid; i < gc * hd; i += AD_THREADS) {
+        const int hh = i / hd, e = i % hd;
+        qs[hh * hd + e] =
+            to_f32(((const T*)a.q)[(size_t)b * a.q_stride + (size_t)(h0 + hh) * hd + e]);
+    }
+    cp_async_wait_all();
+    __syncthreads();
+    // ---- scores: one warp per key, lanes across the head dimension
+    for (int r = warp; r < n; r += AD_THREADS / 32) {
+        float s[AD_GC] = {0.f, 0.f, 0.f, 0.f};
+        for (int e = lane * VEC; e < hd; e += 32 * VEC) {
+            float kv[VEC];
+            load_vec(Ks + (size_t)r * hd + e, kv);
+#pragma unroll
+            for (int hh = 0; hh < AD_GC; ++hh) {
+                if (hh < gc) {
+#pragma unroll
+                    for (int i = 0; i < VEC; i += 4) {
+                        const float4 qv = *reinterpret_cast<const float4*>(qs + hh * hd + e + i);
+                        s[hh] = fmaf(qv.x, kv[i], s[hh]);
+                        s[hh] = fmaf(qv.y, kv[i + 1], s[hh]);
+                        s[hh] = fmaf(qv.z, kv[i + 2], s[hh]);
+                        s[hh] = fmaf(qv.w, kv[i + 3], s[hh]);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int hh = 0; hh < AD_GC; ++hh) {
+            const float t = warp_sum(s[hh]) * a.scale;
+            if (lane == 0 && hh < gc) sc[hh * CH + r] = t;
+        }
+    }
+    __syncthreads();
+    // ---- softmax weights relative to the chunk's maximum: warp hh takes head hh
+    for (int hh = warp; hh < gc; hh += AD_THREADS / 32) {
+        float m = -INFINITY;
+        for (int r = lane; r < n; r += 32) m = fmaxf(m, sc[hh * CH + r]);
+        m = warp_max(m);
+        float l = 0.f;
+        for (int r = lane; r < n; r += 32) {
+            const float w = expf(sc[hh * CH + r] - m);
+            sc[hh * CH + r] = w;
+            l += w;
+        }
+        l = warp_sum(l);
+        if (lane == 0) {
+            stat[hh * 2] = m;
+            stat[hh * 2 + 1] = l;
+        }
+    }
+    __syncthreads();
+    // ---- weighted sum of the values: each thread owns pairs of output dimensions
+    for (int d = tid * 2; d < hd; d += AD_THREADS * 2) {
+        float acc[AD_GC][2] = {};
+        for (int r = 0; r < n; ++r) {
+            const float2 vv = load_pair(Vs + (size_t)r * hd + d);
+            const float v0 = vv.x, v1 = vv.y;
+#pragma unroll
+            for (int hh = 0; hh < AD_GC; ++hh) {
+                if (hh < gc) {
+                    const float w = sc[hh * CH + r];
+                    acc[hh][0] = fmaf(w, v0, acc[hh][0]);
+                    acc[hh][1] = fmaf(w, v1, acc[hh][1]);
+                }
+            }
+        }
+#pragma unroll
+        for (int hh = 0; hh < AD_GC; ++hh) {
+            if (hh < gc) {
+                float* dst = a.part_acc +
+                             (((size_t)b * a.nh + h0 + hh) * a.n_splits + split) * hd + d;
+                dst[0] = acc[hh][0];
+                dst[1] = acc[hh][1];
+            }
+        }
+    }
+    if (tid < gc) {
+        float* dst = a.part_ml + (((size_t)b * a.nh + h0 + tid) * a.n_splits + split) * 2;
+        dst[0] = stat[tid * 2];
+        dst[1] = stat[tid * 2 + 1];
+    }
+}
+
+// Merges the chunks of one (sequence, head): out = sum_s e^{m_s - M} acc_s /
+// sum_s e^{m_s - M} l_s, in chunk order.
+template <typename T>
+__global__ void __launch_bounds__(AD_THREADS)
+attention_decode_merge_kernel(const float* __restrict__ part_acc,
+                              const float* __restrict__ part_ml, T* __restrict__ out,
+                              const int* __restrict__ slots, const int* __restrict__ positions,
+                              int nh, int hd, int window, int n_splits, int chunk) {
+    const int b = blockIdx.x / nh, h = blockIdx.x % nh;
+    T* o = out + ((size_t)b * nh + h) * hd;
+    if (slots[b] < 0) {
+        for (int d = threadIdx.x; d < hd; d += AD_THREADS) o[d] = from_f32<T>(0.f);
+        return;
+    }
+    const int p = positions[b];
+    const int lo = window > 0 ? max(0, p - window + 1) : 0;
+    const int used = min(n_splits, (p - lo) / chunk + 1);
+    const float* ml = part_ml + ((size_t)b * nh + h) * n_splits * 2;
+    const float* acc = part_acc + ((size_t)b * nh + h) * n_splits * hd;
+    float M = -INFINITY;
+    for (int s = 0; s < used; ++s) M = fmaxf(M, ml[2 * s]);
+    float L = 0.f;
+    for (int s = 0; s < used; ++s) L += expf(ml[2 * s] - M) * ml[2 * s + 1];
+    const float inv = 1.0f / L;
+    for (int d = threadIdx.x; d < hd; d += AD_THREADS) {
+        float v = 0.f;
+        for (int s = 0; s < used; ++s) v = fmaf(expf(ml[2 * s] - M), acc[(size_t)s * hd + d], v);
+        o[d] = from_f32<T>(v * inv);
+    }
+}
+
+int pick_chunk(int hd, int elem) {
+    int ch = 64;
+    while (ch > 8 && (size_t)2 * ch * hd * elem > 128 * 1024) ch /= 2;
+    return ch;
+}
+
+size_t split_smem(int hd, int ch, int elem) {
+    return (size_t)2 * ch * hd * elem + (size_t)AD_GC * hd * 4 + (size_t)AD_GC * ch * 4 +
+           AD_GC * 2 * 4;
+}
+
+}  // namespace
+
+// How the decode attention cuts a key range of at most max_keys positions:
+// chunk length and number of chunks.  The scratch it needs is
+// B * nh * n_splits * (hd + 2) floats.
+AGV_API int agv_attention_decode_plan(int hd, int dtype, int max_keys, int* chunk,
+                                      int* n_splits) {
+    AGV_REQUIRE(hd > 0 && max_keys > 0, "attention_decode_plan: bad sizes");
+    const int ch = pick_chunk(hd, dtype == AGV_F32 ? 4 : 2);
+    *chunk = ch;
+    *n_splits = (max_keys + ch - 1) / ch;
+    return 0;
+}
+
+// One query token per batch entry against the paged cache (its own key is
+// stored already).  q: [B, nh * hd] with row stride q_stride; out: [B, nh * hd]
+// dense.  max_keys bounds the number of keys any entry sees in this launch
+// (min(window, greatest length)); part_acc / part_ml are scratch of the sizes
+// agv_attention_decode_plan implies.  A negative slot yields zeros.
+AGV_API int agv_attention_decode(const void* q, long long q_stride, void* out, int dtype,
+                                 const void* k_pool, const void* v_pool, const int* page_table,
+                                 const int* slots, const int* positions, int max_pages, int page,
+                                 int cap, int B, int nh, int nkv, int hd, float scale, int window,
+                                 int max_keys, float* part_acc, float* part_ml,
+                                 cudaStream_t stream) {
+    AGV_REQUIRE(B >= 0 && nh > 0 && nkv > 0 && hd > 0, "attention_decode: bad sizes");
+    AGV_REQUIRE(nh % nkv == 0, "attention_decode: %d heads are not a multiple of %d kv heads", nh,
+                nkv);
+    const int elem = dtype == AGV_F32 ? 4 : 2;
+    AGV_REQUIRE(dtype == AGV_F32 || dtype == AGV_BF16, "attention_decode: unknown dtype %d", dtype);
+    AGV_REQUIRE(hd % 16 == 0 && hd <= AD_MAX_HD, "attention_decode: head_dim %d must be a multiple "
+                "of 16 and at most %d", hd, AD_MAX_HD);
+    AGV_REQUIRE(page > 0 && cap > 0 && max_pages > 0 && max_keys > 0,
+                "attention_decode: bad cache geometry");
+    AGV_REQUIRE(window >= 0 && (window == 0 || window <= cap),
+                "attention_decode: window %d exceeds the ring of %d rows", window, cap);
+    AGV_REQUIRE(agv_aligned(k_pool, 16) && agv_aligned(v_pool, 16),
+                "attention_decode: cache pools must be 16-byte aligned");
+    AGV_REQUIRE(B <= 65535, "attention_decode: batch %d exceeds the grid limit", B);
+    if (B == 0) return 0;
+    const int ch = pick_chunk(hd, elem);
+    const int n_splits = (max_keys + ch - 1) / ch;
+    const size_t smem = split_smem(hd, ch, elem);
+    AGV_REQUIRE(smem <= (size_t)AD_MAX_SMEM, "attention_decode: %zu bytes of shared memory needed",
+                smem);
+    DecodeArgs a{q, q_stride, k_pool, v_pool, page_table, slots, positions, part_acc, part_ml,
+                 max_pages, page, cap, nh, nkv, hd, window, n_splits, ch, scale};
+    const int G = nh / nkv;
+    dim3 grid(n_splits, nkv * ((G + AD_GC - 1) / AD_GC), B);
+    if (dtype == AGV_F32) {
+        auto kern = attention_decode_split_kernel<float>;
+        static bool configured = false;
+        if (!configured) {
+            AGV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             AD_MAX_SMEM));
+            configured = true;
+        }
+        kern<<<grid, AD_THREADS, smem, stream>>>(a);
+        AGV_LAUNCH_OK("attention_decode_split_kernel");
+        attention_decode_merge_kernel<float><<<B * nh, AD_THREADS, 0, stream>>>(
+            part_acc, part_ml, (float*)out, slots, positions, nh, hd, window, n_splits, ch);
+    } else {
+        auto kern = attention_decode_split_kernel<__nv_bfloat16>;
+        static bool configured = false;
+        if (!configured) {
+            AGV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             AD_MAX_SMEM));
+            configured = true;
+        }
+        kern<<<grid, AD_THREADS, smem, stream>>>(a);
+        AGV_LAUNCH_OK("attention_decode_split_kernel");
+        attention_decode_merge_kernel<__nv_bfloat16><<<B * nh, AD_THREADS, 0, stream>>>(
+            part_acc, part_ml, (__nv_bfloat16*)out, slots, positions, nh, hd, window, n_splits, ch);
+    }
+    AGV_LAUNCH_OK("attention_decode_merge_kernel");
+    return 0;
+}

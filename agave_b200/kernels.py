@@ -352,7 +352,54 @@ def attention_prefill(q, k, v, out, ctx, n_heads, n_kv_heads, head_dim, scale, w
                            n_kv_heads, head_dim, scale, window)
 
 
+def attention_decode_plan(head_dim: int, dtype: torch.dtype, max_keys: int):
+    """(chunk length, number of chunks) the split decode attention uses."""
+    chunk, n = ctypes.c_int(0), ctypes.c_int(0)
+    _check(library().agv_attention_decode_plan(head_dim, dtype_code(dtype), max_keys,
+                                               ctypes.byref(chunk), ctypes.byref(n)))
+    return chunk.value, n.value
+
+
+def attention_decode_split(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor,
+                           v_pool: torch.Tensor, page_table: torch.Tensor, slots: torch.Tensor,
+                           positions: torch.Tensor, page: int, cap: int, n_heads: int,
+                           n_kv_heads: int, head_dim: int, scale: float, window: int,
+                           max_keys: int, part_acc: Optional[torch.Tensor] = None,
+                           part_ml: Optional[torch.Tensor] = None) -> None:
+    """One query per batch entry against the paged cache, keys split into chunks
+    whose partial results go through scratch memory (allocated here if not given)."""
+    B = q.shape[0]
+    assert q.stride(1) == 1
+    _dense(out, "out"); _dense(k_pool, "k_pool"); _dense(v_pool, "v_pool")
+    for t, n in ((positions, "positions"), (page_table, "page_table"), (slots, "slots")):
+        _i32(t, n)
+    assert k_pool.dtype == q.dtype and out.dtype == q.dtype
+    _, n_splits = attention_decode_plan(head_dim, q.dtype, max_keys)
+    if part_acc is None:
+        part_acc = torch.empty((B, n_heads, n_splits, head_dim), dtype=torch.float32,
+                               device=q.device)
+        part_ml = torch.empty((B, n_heads, n_splits, 2), dtype=torch.float32, device=q.device)
+    assert part_acc.numel() >= B * n_heads * n_splits * head_dim
+    assert part_ml.numel() >= B * n_heads * n_splits * 2
+    _f32(part_acc, "part_acc"); _f32(part_ml, "part_ml")
+    global _launches
+    _launches += 1                      # this launcher starts two kernels
+    _check(library().agv_attention_decode(
+        _ptr(q), ctypes.c_longlong(q.stride(0)), _ptr(out), dtype_code(q.dtype), _ptr(k_pool),
+        _ptr(v_pool), _ptr(page_table), _ptr(slots), _ptr(positions), page_table.shape[1], page,
+        cap, B, n_heads, n_kv_heads, head_dim, ctypes.c_float(scale), window, max_keys,
+        _ptr(part_acc), _ptr(part_ml), _stream()))
+
+
 def attention_decode(q, out, view, ctx, n_heads, n_kv_heads, head_dim, scale, window) -> None:
-    attention_paged_simt(q, out, view.k_pool, view.v_pool, view.page_table, ctx.slots,
-                         ctx.positions, ctx.seq_index, view.page, view.cap, n_heads, n_kv_heads,
-                         head_dim, scale, window)
+    """Decode attention of one layer: the split kernel for head sizes in steps of
+    16 up to 512, else the one-warp-per-head kernel."""
+    if head_dim % 16 == 0 and head_dim <= 512:
+        max_keys = min(window, ctx.max_len) if window else ctx.max_len
+        attention_decode_split(q, out, view.k_pool, view.v_pool, view.page_table, ctx.slots,
+                               ctx.positions, view.page, view.cap, n_heads, n_kv_heads, head_dim,
+                               scale, window, max(1, max_keys))
+    else:
+        attention_paged_simt(q, out, view.k_pool, view.v_pool, view.page_table, ctx.slots,
+                             ctx.positions, ctx.seq_index, view.page, view.cap, n_heads,
+                             n_kv_heads, head_dim, scale, window)

@@ -296,6 +296,13 @@ def test_attention_over_the_paged_cache(dtype, nh, nkv, hd, window):
                                  cap, nh, nkv, hd, 0.2, window)
     tol = 1e-5 if dtype == torch.float32 else 8e-3
     assert (out[1] == 0).all()
+    # the split kernel on the same cache: same result, whatever bound on the keys is given
+    for max_keys in (22, 200):
+        out2 = torch.full_like(out, float("nan"))
+        kernels.attention_decode_split(q, out2, k_pool, v_pool, table, slots, positions, PAGE, cap,
+                                       nh, nkv, hd, 0.2, window, window or max_keys)
+        assert (out2[1] == 0).all()
+        assert rel_err(out2, out) < tol
     for b in (0, 2, 3):
         n, slot = lens_t[b], int(slots[b])
         lo = max(0, n - window) if window else 0
@@ -371,3 +378,41 @@ def test_repeat_penalty_per_occurrence_and_history():
     kernels.repeat_penalty(logits, slots, hist, hist_len, 2.0)
     assert logits[0, 5].item() == 0.25 and logits[0, 7].item() == -4.0
     assert logits[0, 6].item() == 1.0 and (logits[1] == torch.where(torch.arange(V, device=DEV) == 7, -2.0, 1.0)).all()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd", [(4, 1, 256), (16, 2, 128), (5, 5, 80), (12, 2, 512)])
+def test_attention_decode_split_long_sequences(dtype, nh, nkv, hd):
+    """Several chunks per sequence, groups wider than the kernel's head tile,
+    a far key that must win, and a window edge in the middle of a chunk."""
+    from agave_b200 import kernels
+    PAGE = 64
+    lens = [700, 65, 1]
+    max_pages = 12
+    n_pages = 3 * max_pages
+    k_pool = rnd(n_pages, PAGE, nkv, hd, dtype=dtype, seed=1, scale=0.3)
+    v_pool = rnd(n_pages, PAGE, nkv, hd, dtype=dtype, seed=2)
+    perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(3)).int()
+    table = perm.reshape(3, max_pages).contiguous().to(DEV)
+    slots = torch.tensor([1, 2, 0], dtype=torch.int32, device=DEV)
+    q = rnd(3, nh * hd, dtype=dtype, seed=4, scale=0.3)
+    # sequence 0: key 5 dominates head 0
+    page5 = int(table[1, 0])
+    k_pool[page5, 5, 0] = 0; k_pool[page5, 5, 0, 0] = 30.0
+    q[0, :hd] = 0; q[0, 0] = 30.0
+    positions = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=DEV)
+    seq_index = torch.arange(3, dtype=torch.int32, device=DEV)
+    tol = 2e-5 if dtype == torch.float32 else 8e-3
+    for window in (0, 100, 695):
+        cap = max_pages * PAGE
+        ref = torch.empty((3, nh * hd), dtype=dtype, device=DEV)
+        kernels.attention_paged_simt(q, ref, k_pool, v_pool, table, slots, positions, seq_index,
+                                     PAGE, cap, nh, nkv, hd, 1.0, window)
+        out = torch.full_like(ref, float("nan"))
+        kernels.attention_decode_split(q, out, k_pool, v_pool, table, slots, positions, PAGE, cap,
+                                       nh, nkv, hd, 1.0, window, window or 768)
+        assert rel_err(out, ref) < tol, window
+        if window in (0, 695):
+            assert rel_err(out[0, :hd], v_pool[page5, 5, 0]) < 2e-2     # the far key is seen
+        else:
+            assert (out[0, :hd].float() - v_pool[page5, 5, 0].float()).abs().max() > 0.1
