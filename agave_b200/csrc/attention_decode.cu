@@ -315,3 +315,53 @@ AGV_API int agv_attention_decode(const void* q, long long q_stride, void* out, i
     AGV_LAUNCH_OK("attention_decode_merge_kernel");
     return 0;
 }
+
+// ------------------------------------------------------- no-allocation variant
+// See agave_b200_no_alloc.h.  The scratch of the split kernels sits in this
+// file-scope device array.  In host code the array's name is only a stand-in:
+// its device address comes from cudaGetSymbolAddress, looked up once per device.
+#include "agave_b200_no_alloc.h"
+#include <mutex>
+
+static __device__ __align__(256) float g_static_scratch[AGV_NO_ALLOC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int NO_ALLOC_MAX_DEVICES = 64;
+float* g_static_scratch_addr[NO_ALLOC_MAX_DEVICES] = {};
+std::mutex g_static_scratch_mu;
+}  // namespace
+
+AGV_API int agv_attention_decode_static(const void* q, long long q_stride, void* out, int dtype,
+                                        const void* k_pool, const void* v_pool,
+                                        const int* page_table, const int* slots,
+                                        const int* positions, int max_pages, int page, int cap,
+                                        int B, int nh, int nkv, int hd, float scale, int window,
+                                        int max_keys, cudaStream_t stream) {
+    AGV_REQUIRE(B >= 0 && nh > 0 && hd > 0 && max_keys > 0, "attention_decode_static: bad sizes");
+    int chunk = 0, n_splits = 0;
+    if (int rc = agv_attention_decode_plan(hd, dtype, max_keys, &chunk, &n_splits)) return rc;
+    const long long acc_floats = (long long)B * nh * n_splits * hd;
+    const long long need = acc_floats + (long long)B * nh * n_splits * 2;
+    AGV_REQUIRE(need <= (long long)AGV_NO_ALLOC_SCRATCH_FLOATS,
+                "attention_decode_static: B=%d heads=%d chunks=%d head_dim=%d need %lld scratch "
+                "values, the built-in array holds %d; use agv_attention_decode with your own "
+                "scratch, or a smaller batch or max_keys",
+                B, nh, n_splits, hd, need, (int)AGV_NO_ALLOC_SCRATCH_FLOATS);
+    int dev = 0;
+    AGV_CUDA_OK(cudaGetDevice(&dev));
+    AGV_REQUIRE(dev >= 0 && dev < NO_ALLOC_MAX_DEVICES, "attention_decode_static: device %d", dev);
+    float* base = nullptr;
+    {
+        std::lock_guard<std::mutex> g(g_static_scratch_mu);
+        if (!g_static_scratch_addr[dev]) {
+            float* p = nullptr;
+            AGV_CUDA_OK(cudaGetSymbolAddress((void**)&p, g_static_scratch));
+            g_static_scratch_addr[dev] = p;
+        }
+        base = g_static_scratch_addr[dev];
+    }
+    // partial sums first, then the (maximum, normaliser) pairs; both start 16-byte aligned
+    return agv_attention_decode(q, q_stride, out, dtype, k_pool, v_pool, page_table, slots,
+                                positions, max_pages, page, cap, B, nh, nkv, hd, scale, window,
+                                max_keys, base, base + acc_floats, stream);
+}
