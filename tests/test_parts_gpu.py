@@ -1,0 +1,314 @@
+"""Each part alone against the plain functions, and the generality of the
+assembly: a toy mixer with state of its own, another arrangement, activation
+and norm flavour, a block called twice and a layer that reads another layer's
+cache.  The toy parts live here and are registered from here; no file of the
+library changes for them."""
+import dataclasses
+import json
+import math
+import os
+import tempfile
+
+import pytest
+import torch
+
+from plain import gemma3_plain as P
+from util import TINY_B, TOL, close, random_tokens
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda:0")
+
+
+def _ctx(engine, entries):
+    """A step context for (slot, tokens) entries, as the step function builds it."""
+    return engine.runner.context(entries)
+
+
+# ------------------------------------------------------------ parts, one by one
+def test_rms_norm_part_zero_centred_and_plain():
+    from agave_b200.config import NormSpec
+    from agave_b200.parts import RMSNorm
+    H = 200
+    h = torch.randn(9, H, device=DEV)
+    w = torch.randn(H) * 0.3
+    for zc in (True, False):
+        n = RMSNorm(NormSpec(eps=1e-5, zero_centered=zc), H, torch.float32, DEV)
+        n.load({"weight": w}, DEV)
+        out = torch.empty_like(h)
+        n.forward(h, out)
+        ref = P.rms_norm(h.cpu().double(), w.double(), 1e-5, add_one=zc)
+        close(out, ref, 1e-6)
+
+
+def test_rotary_part_tables():
+    from agave_b200.config import RotarySpec
+    from agave_b200.parts import RotaryEmbedding
+
+    class Ctx:
+        rope_tables = {}
+        n_tokens = 5
+        positions = torch.tensor([0, 1, 2, 700, 4000], dtype=torch.int32, device=DEV)
+        def new(self, *shape, dtype=None):
+            return torch.empty(shape, dtype=dtype, device=DEV)
+
+    r = RotaryEmbedding(RotarySpec(theta=5e5, factor=4.0, rotary_dim=24), head_dim=32)
+    cos, sin = r.tables(Ctx())
+    ang = P.rope_angles(Ctx.positions.cpu(), 24, 5e5, 4.0)
+    close(cos, torch.cos(ang), 1e-6)
+    close(sin, torch.sin(ang), 1e-6)
+    assert r.tables(Ctx())[0] is cos            # made once per step and shared
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_attention_and_feed_forward_parts_alone(dtype):
+    """The mixer and the feed-forward of one layer, outside any model."""
+    from agave_b200.cache import Cache
+    from agave_b200.config import Gemma3Config
+    from agave_b200.engine.batch import PREFILL, StepContext
+    from agave_b200.parts import AttentionMixer, GatedFeedForward
+    tdt = torch.float32 if dtype == "float32" else torch.bfloat16
+    cfg = Gemma3Config.from_dict(TINY_B)
+    spec = cfg.to_model_spec()
+    block = spec.blocks[0]                      # a sliding layer
+    H = spec.hidden_size
+    g = torch.Generator().manual_seed(0)
+    mixer = AttentionMixer(block.mixer, H, tdt, DEV)
+    tensors = {n: (torch.randn(s.shape, generator=g) * (0.1 if s.role == "norm" else 0.05)).to(tdt)
+               for n, s in AttentionMixer.param_specs(block.mixer, H).items()}
+    mixer.load(tensors, tdt, DEV)
+    ffn = GatedFeedForward(block.feed_forward, H, tdt, DEV)
+    ften = {n: (torch.randn(s.shape, generator=g) * 0.05).to(tdt)
+            for n, s in GatedFeedForward.param_specs(block.feed_forward, H).items()}
+    ffn.load(ften, tdt, DEV)
+    cache = Cache([mixer.cache_request()], 256, 256, 2, tdt, DEV)
+    slot = cache.acquire()
+    T = 40
+    cache.reserve(slot, T)
+    cache.flush()
+    ar = torch.arange(T, dtype=torch.int32, device=DEV)
+    ctx = StepContext(mode=PREFILL, n_tokens=T, batch=1, tokens=ar, positions=ar,
+                      seq_index=torch.zeros(T, dtype=torch.int32, device=DEV),
+                      cu_seqlens=torch.tensor([0, T], dtype=torch.int32, device=DEV),
+                      slots=torch.tensor([slot], dtype=torch.int32, device=DEV),
+                      lens=torch.tensor([T], dtype=torch.int32, device=DEV), max_len=T, max_new=T,
+                      cache=cache, dtype=tdt, device=DEV)
+    x = (torch.randn(T, H, generator=g) * 0.5).to(tdt).to(DEV)
+    y = mixer.forward(x, ctx, 0, True)
+    # the same with the plain functions
+    w = {"layers.0.self_attn." + n: t.double() for n, t in tensors.items()}
+    pcfg = dict(TINY_B)
+    ref = P.attention_block(pcfg, w, 0, x.cpu().double(), torch.arange(T))
+    close(y, ref, 1e-4 if dtype == "float32" else 2e-2)
+    d = ffn.forward(x, ctx)
+    ref = P.geglu(x.cpu().double(), ften["gate_proj.weight"].double(),
+                  ften["up_proj.weight"].double(), ften["down_proj.weight"].double())
+    close(d, ref, 1e-4 if dtype == "float32" else 2e-2)
+
+
+# ------------------------------------------------- a toy mixer with its own state
+class PrefixSumSpec:
+    kind = "toy_prefix_sum"
+
+    def __init__(self, width):
+        self.width = width
+
+
+class PrefixSumMixer:
+    """y_t = W (x_1 + ... + x_t): the running sum is per-sequence state of fixed
+    size, kept in the cache's state storage."""
+
+    def __init__(self, spec, hidden_size, dtype, device):
+        self.hidden_size, self.dtype, self.device = hidden_size, dtype, device
+        self.w = None
+
+    @classmethod
+    def param_specs(cls, spec, hidden_size):
+        from agave_b200.parts import ParamSpec
+        return {"mix.weight": ParamSpec((hidden_size, hidden_size))}
+
+    def cache_request(self):
+        from agave_b200.parts import StateRequest
+        return StateRequest(self.hidden_size)
+
+    def load(self, tensors, dtype, device):
+        self.w = tensors["mix.weight"].to(device=device, dtype=torch.float32)
+
+    def forward(self, x, ctx, cache_entry, writes_cache):
+        state = ctx.cache.state_view(cache_entry).state
+        cu = ctx.cu_seqlens.cpu().tolist()
+        slots = ctx.slots.cpu().tolist()
+        out = torch.zeros(x.shape, dtype=torch.float32, device=x.device)
+        for b, slot in enumerate(slots):
+            if slot < 0:
+                continue
+            rows = slice(cu[b], cu[b + 1])
+            c = torch.cumsum(x[rows].float(), dim=0) + state[slot]
+            if writes_cache:
+                state[slot] = c[-1]
+            out[rows] = c @ self.w.T
+        return out.to(x.dtype)
+
+
+class ToyConfig:
+    """hidden, vocab, layers, intermediate: a decoder of prefix-sum mixers in the
+    "pre" arrangement with SiLU feed-forwards and ordinary (not zero-centred) norms."""
+
+    def __init__(self, raw):
+        self.raw = raw
+
+    @classmethod
+    def from_dict(cls, raw):
+        return cls(raw)
+
+    def to_model_spec(self):
+        from agave_b200.config import (BlockSpec, GatedFeedForwardSpec, ModelSpec, NormSpec,
+                                       default_schedule)
+        r = self.raw
+        norm = NormSpec(eps=r["eps"], zero_centered=False)
+        blocks = tuple(BlockSpec(mixer=PrefixSumSpec(r["hidden"]),
+                                 feed_forward=GatedFeedForwardSpec(intermediate_size=r["inter"],
+                                                                   activation="silu"),
+                                 norm=norm, arrangement="pre") for _ in range(r["layers"]))
+        return ModelSpec(hidden_size=r["hidden"], vocab_size=r["vocab"], embed_scale=1.5,
+                         blocks=blocks, schedule=default_schedule(len(blocks)), final_norm=norm,
+                         tie_embeddings=True, max_positions=512)
+
+
+class ToyNames:
+    prefixes = ("toy.",)
+
+    def checkpoint_name(self, internal, prefix):
+        return prefix + internal
+
+
+def toy_plain(raw, w, tokens):
+    h = w["toy.embed.weight"][torch.tensor(tokens)] * 1.5
+    for l in range(raw["layers"]):
+        p = f"toy.blocks.{l}."
+        x = P.rms_norm(h, w[p + "pre_mixer_norm.weight"], raw["eps"], add_one=False)
+        h = h + torch.cumsum(x, 0) @ w[p + "mixer.mix.weight"].T
+        x = P.rms_norm(h, w[p + "pre_ffn_norm.weight"], raw["eps"], add_one=False)
+        gte = x @ w[p + "ffn.gate_proj.weight"].T
+        d = (gte * torch.sigmoid(gte) * (x @ w[p + "ffn.up_proj.weight"].T)) \
+            @ w[p + "ffn.down_proj.weight"].T
+        h = h + d
+    return P.rms_norm(h, w["toy.final_norm.weight"], raw["eps"], add_one=False) \
+        @ w["toy.embed.weight"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_mixer_with_state_registers_builds_and_steps(dtype):
+    from safetensors.torch import load_file
+    from agave_b200.config import register_architecture
+    from agave_b200.engine.api import Engine
+    from agave_b200.parts import register_mixer
+    from agave_b200.weights import write_model_folder
+    register_mixer("toy_prefix_sum", PrefixSumMixer)
+    register_architecture("ToyPrefixSumLM", ToyConfig, lambda c: ToyNames())
+    raw = {"architectures": ["ToyPrefixSumLM"], "hidden": 72, "vocab": 300, "layers": 3,
+           "inter": 104, "eps": 1e-5}
+    store = torch.float32 if dtype == "float32" else torch.bfloat16
+    with tempfile.TemporaryDirectory() as d:
+        write_model_folder(d, raw, seed=3, std=0.05, norm_std=0.1, dtype=store)
+        w = {k: v.double() for k, v in load_file(os.path.join(d, "model.safetensors")).items()}
+        eng = Engine(d, dtype=dtype, max_tokens=1024, max_batch=4)
+    seqs = [random_tokens(n, 300, 70 + n) for n in (14, 6, 9)]
+    refs = [toy_plain(raw, w, s) for s in seqs]
+    # two batches, so that the state of a reused slot must have been zeroed
+    for order in ([0, 1], [2, 1, 0]):
+        slots = {i: eng.acquire() for i in order}
+        starts = {i: max(1, len(seqs[i]) - 4) for i in order}
+        out = eng.step([(slots[i], seqs[i][:starts[i]]) for i in order],
+                       [list(range(starts[i])) for i in order])
+        got = {i: [] for i in order}
+        o = 0
+        for i in order:
+            got[i].append(out[o:o + starts[i]]); o += starts[i]
+        for k in range(4):
+            live = [i for i in order if starts[i] + k < len(seqs[i])]
+            out = eng.step([(slots[i], [seqs[i][starts[i] + k]]) for i in live],
+                           [[0]] * len(live))
+            for j, i in enumerate(live):
+                got[i].append(out[j:j + 1])
+        for i in order:
+            close(torch.cat(got[i]), refs[i], 1e-4 if dtype == "float32" else 3e-2)
+            eng.release(slots[i])
+
+
+# ------------------------- the run order is data: a block twice, a shared cache
+class LoopedGemmaConfig:
+    def __init__(self, inner, order):
+        self.inner, self.order = inner, order
+
+    @classmethod
+    def from_dict(cls, raw):
+        from agave_b200.config import Gemma3Config
+        return cls(Gemma3Config.from_dict(raw), raw["run_order"])
+
+    def to_model_spec(self):
+        from agave_b200.config import LayerCall
+        spec = self.inner.to_model_spec()
+        return dataclasses.replace(spec, schedule=tuple(
+            LayerCall(block=b, cache=c, writes_cache=w) for b, c, w in self.order))
+
+    def to_dict(self):
+        return self.inner.to_dict()
+
+
+def looped_plain(cfg, w, tokens, order):
+    T = len(tokens)
+    pos = torch.arange(T)
+    nh, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    eps = cfg["rms_norm_eps"]
+    h = P.embed(tokens, w["embed_tokens.weight"], cfg["hidden_size"])
+    kept = {}
+    for l, cache, writes in order:
+        p = f"layers.{l}."
+        x = P.rms_norm(h, w[p + "input_layernorm.weight"], eps)
+        local = P.layer_is_local(cfg, l)
+        theta = cfg["rope_local_base_freq"] if local else cfg["rope_theta"]
+        ang = P.rope_angles(pos, hd, theta, 1.0 if local else P.rope_factor(cfg))
+        q = P.apply_rope(P.rms_norm((x @ w[p + "self_attn.q_proj.weight"].T).reshape(T, nh, hd),
+                                    w[p + "self_attn.q_norm.weight"], eps), ang)
+        if writes:
+            k = P.apply_rope(P.rms_norm((x @ w[p + "self_attn.k_proj.weight"].T).reshape(T, nkv, hd),
+                                        w[p + "self_attn.k_norm.weight"], eps), ang)
+            v = (x @ w[p + "self_attn.v_proj.weight"].T).reshape(T, nkv, hd)
+            kept[cache] = (k, v)
+        k, v = kept[cache]
+        o = P.attention(q, k, v, 1.0 / math.sqrt(cfg["query_pre_attn_scalar"]),
+                        cfg["sliding_window"] if local else None)
+        y = o @ w[p + "self_attn.o_proj.weight"].T
+        h = h + P.rms_norm(y, w[p + "post_attention_layernorm.weight"], eps)
+        d = P.geglu(P.rms_norm(h, w[p + "pre_feedforward_layernorm.weight"], eps),
+                    w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"],
+                    w[p + "mlp.down_proj.weight"])
+        h = h + P.rms_norm(d, w[p + "post_feedforward_layernorm.weight"], eps)
+    return P.rms_norm(h, w["norm.weight"], eps) @ w["embed_tokens.weight"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_block_called_twice_and_a_layer_reading_anothers_cache(dtype):
+    from agave_b200.config import register_architecture
+    from agave_b200.engine.api import Engine
+    from agave_b200.models.gemma3 import Gemma3WeightNames
+    from agave_b200.weights import write_model_folder
+    register_architecture("LoopedGemma3", LoopedGemmaConfig, lambda c: Gemma3WeightNames())
+    raw = dict(TINY_B)
+    raw["architectures"] = ["LoopedGemma3"]
+    raw["num_hidden_layers"] = 3            # layers 0, 1 sliding; 2 global
+    # block 0 runs twice with caches of its own; the last call reads block 2's cache
+    raw["run_order"] = [[0, 0, True], [2, 1, True], [0, 2, True], [1, 3, True], [2, 1, False]]
+    store = torch.float32 if dtype == "float32" else torch.bfloat16
+    with tempfile.TemporaryDirectory() as d:
+        write_model_folder(d, raw, seed=9, std=0.03, norm_std=0.2, dtype=store)
+        cfg, w = P.read_config(d), P.read_weights(d)
+        eng = Engine(d, dtype=dtype, max_tokens=1024, max_batch=2)
+    toks = random_tokens(41, 384, 5)
+    ref = looped_plain(cfg, w, toks, [tuple(o) for o in raw["run_order"]])
+    s = eng.acquire()
+    got = [eng.step([(s, toks[:30])], [list(range(30))])]
+    for i in range(30, 41):
+        got.append(eng.step([(s, [toks[i]])], [[0]]))
+    eng.release(s)
+    close(torch.cat(got), ref, TOL[dtype])
