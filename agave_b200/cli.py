@@ -185,8 +185,10 @@ def main(argv: Optional[List[str]] = None) -> int:
                     prompts.append(ids)
         except ValueError:
             return _fail("--tokens takes comma-separated integers")
-    elif args.prompt is not None or not sys.stdin.isatty():
+    elif not args.model_info and (args.prompt is not None or not sys.stdin.isatty()):
         text = args.prompt if args.prompt is not None else sys.stdin.read().strip()
+        if not text:
+            return _fail("no prompt: give text, --tokens, or pipe text in (there is no REPL here)")
         if tok is None:
             return _fail(f"{args.model} has no tokenizer.json: give the prompt as --tokens")
         chat = ""
