@@ -24,6 +24,8 @@ def replay(folder, dtype, steps, max_tokens=1024):
     assert r.returncode == 0, r.stderr[-2000:]
     done = [l for l in r.stdout.splitlines() if l.startswith("done ")]
     assert done == [f"done {s['step']}" for s in steps]
+    import atexit, shutil
+    atexit.register(shutil.rmtree, out, ignore_errors=True)
     return out
 
 

@@ -35,6 +35,16 @@ TINY = {"A": (TINY_A, 0, 0.02, 0.1), "B": (TINY_B, 1, 0.03, 0.2)}
 _FOLDERS = {}
 
 
+def _cleanup():
+    import shutil
+    for d in _FOLDERS.values():
+        shutil.rmtree(d, ignore_errors=True)
+
+
+import atexit
+atexit.register(_cleanup)
+
+
 def model_folder(name: str, dtype=torch.float32, std_scale: float = 1.0) -> str:
     """A temporary model folder for tiny configuration ``name`` (made once per run)."""
     key = (name, dtype, std_scale)
