@@ -29,10 +29,15 @@
  *   - The first call on a device looks up the array's device address
  *     (cudaGetSymbolAddress, with that device current).  Make that first call
  *     before any stream capture begins on that device.
+ *   - B times the number of head groups (nkv * ceil(nh / nkv / 4)) must not exceed
+ *     AGV_NO_ALLOC_COUNTERS; the call is refused otherwise.
  *   - All calls share the one array and it keeps what the last call left.  The
- *     kernels write every value they later read, so nothing has to be cleared;
- *     but two calls that overlap on the GPU (different streams, no ordering
- *     between them) race on it.  Order them, e.g. by using one stream.
+ *     kernels write every value they later read, so nothing has to be cleared.
+ *     The only thing that must start at zero is a small table of arrival
+ *     counters beside the array: it is zero when the library is loaded and every
+ *     call puts it back to zero before it ends.  Two calls that overlap on the
+ *     GPU (different streams, no ordering between them) race on both.  Order
+ *     them, e.g. by using one stream.
  */
 #ifndef AGAVE_B200_NO_ALLOC_H
 #define AGAVE_B200_NO_ALLOC_H
@@ -44,6 +49,7 @@ extern "C" {
 #endif
 
 #define AGV_NO_ALLOC_SCRATCH_FLOATS (4 * 1024 * 1024)
+#define AGV_NO_ALLOC_COUNTERS 65536
 
 /* dtype: 0 = float32, 1 = bfloat16 (of q, out and the cache pools).
  * Returns 0, or a negative code with a message in agv_last_error(). */

@@ -6,10 +6,13 @@
 // the cost is one trip to HBM, not one per key), computes the scores of the
 // group's heads, their softmax weights relative to the chunk's own maximum, and
 // the weighted sum of the values; it writes that partial result (sum, maximum,
-// normaliser) to scratch memory.  A second kernel merges the chunks of each
-// (sequence, head).  Chunks past a sequence's end exit at once, so the grid can
-// be sized for the longest sequence the cache allows and the launch replayed
-// from a CUDA graph.  Scores, softmax and sums are 32-bit.
+// normaliser) to scratch memory and counts itself in; the CTA that arrives last
+// for a (sequence, head group) merges the chunks in chunk order and writes the
+// output (a sequence with a single chunk is written directly).  Chunks past a
+// sequence's end exit at once, so the grid can be sized for the longest
+// sequence the cache allows and the launch replayed from a CUDA graph.  Scores,
+// softmax and sums are 32-bit.  The arrival counters must be zero before a
+// launch; every launch leaves them zero.
 //
 // Reference: one block per head, scores of all positions in shared memory,
 // softmax by the first 32 threads (src/backend/kernels/cuda/sdpa.zig:16-104);
@@ -62,6 +65,7 @@ __device__ __forceinline__ float2 load_pair(const __nv_bfloat16* p) {
 struct DecodeArgs {
     const void* q;             // [B, nh, hd] rows of stride q_stride
     long long q_stride;
+    void* out;                 // [B, nh * hd]
     const void* k_pool;        // [n_pages, page, nkv, hd] of this layer
     const void* v_pool;
     const int* page_table;     // [n_slots, max_pages]
@@ -69,6 +73,7 @@ struct DecodeArgs {
     const int* positions;      // [B] position of the query (its key is stored already)
     float* part_acc;           // [B, nh, S, hd]
     float* part_ml;            // [B, nh, S, 2]
+    int* counters;             // [B * gridDim.y], zero before and after a launch
     int max_pages, page, cap, nh, nkv, hd, window, n_splits, chunk;
     float scale;
 };
@@ -78,44 +83,56 @@ __global__ void __launch_bounds__(AD_THREADS)
 attention_decode_split_kernel(DecodeArgs a) {
     constexpr int VEC = Vec16<T>::N;
     extern __shared__ __align__(16) unsigned char smem_raw[];
+    __shared__ int s_last;
     const int b = blockIdx.z, split = blockIdx.x;
     const int G = a.nh / a.nkv;
     const int chunks_per_group = (G + AD_GC - 1) / AD_GC;
     const int g = blockIdx.y / chunks_per_group;              // kv head
     const int h0 = g * G + (blockIdx.y % chunks_per_group) * AD_GC;   // first query head
     const int gc = min(AD_GC, g * G + G - h0);                // heads handled here
+    const int hd = a.hd, CH = a.chunk;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    T* outp = (T*)a.out + ((size_t)b * a.nh + h0) * hd;
     const int slot = a.slots[b];
-    if (slot < 0) return;
+    if (slot < 0) {
+        if (split == 0)
+            for (int i = tid; i < gc * hd; i += AD_THREADS) outp[i] = from_f32<T>(0.f);
+        return;
+    }
     const int p = a.positions[b];
     const int lo = a.window > 0 ? max(0, p - a.window + 1) : 0;
     const int j0 = lo + split * a.chunk;
     if (j0 > p) return;
     const int n = min(a.chunk, p - j0 + 1);                   // keys of this chunk
-    const int hd = a.hd, CH = a.chunk;
+    const int used = (p - lo) / a.chunk + 1;                  // chunks this sequence has
 
     T* Ks = reinterpret_cast<T*>(smem_raw);
     T* Vs = Ks + (size_t)CH * hd;
     float* qs = reinterpret_cast<float*>(Vs + (size_t)CH * hd);   // [AD_GC][hd]
     float* sc = qs + AD_GC * hd;                                  // [AD_GC][CH]
     float* stat = sc + AD_GC * CH;                                // [AD_GC][2]
+    int* rowoff = reinterpret_cast<int*>(stat + AD_GC * 2);       // [CH] row index in the pool
 
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    // ---- keys and values of the chunk into shared memory, all copies in flight
-    const int vec_per_row = hd / VEC;
+    // ---- where each key row of the chunk lives (one page-table read per row)
     const int* table = a.page_table + (size_t)slot * a.max_pages;
-    for (int i = tid; i < n * vec_per_row; i += AD_THREADS) {
-        const int r = i / vec_per_row, c = (i % vec_per_row) * VEC;
+    for (int r = tid; r < n; r += AD_THREADS) {
         const int row = (j0 + r) % a.cap;
-        const int page = table[row / a.page];
-        const size_t off = (((size_t)page * a.page + row % a.page) * a.nkv + g) * hd + c;
-        cp_async16(Ks + (size_t)r * hd + c, (const T*)a.k_pool + off);
-        cp_async16(Vs + (size_t)r * hd + c, (const T*)a.v_pool + off);
+        rowoff[r] = table[row / a.page] * a.page + row % a.page;
     }
     // ---- the group's queries, 32-bit
     for (int i = tid; i < gc * hd; i += AD_THREADS) {
         const int hh = i / hd, e = i % hd;
         qs[hh * hd + e] =
             to_f32(((const T*)a.q)[(size_t)b * a.q_stride + (size_t)(h0 + hh) * hd + e]);
+    }
+    __syncthreads();
+    // ---- keys and values of the chunk into shared memory, all copies in flight
+    const int vec_per_row = hd / VEC;
+    for (int i = tid; i < n * vec_per_row; i += AD_THREADS) {
+        const int r = i / vec_per_row, c = (i % vec_per_row) * VEC;
+        const size_t off = ((size_t)rowoff[r] * a.nkv + g) * hd + c;
+        cp_async16(Ks + (size_t)r * hd + c, (const T*)a.k_pool + off);
+        cp_async16(Vs + (size_t)r * hd + c, (const T*)a.v_pool + off);
     }
     cp_async_wait_all();
     __syncthreads();
@@ -169,61 +186,74 @@ attention_decode_split_kernel(DecodeArgs a) {
         float acc[AD_GC][2] = {};
         for (int r = 0; r < n; ++r) {
             const float2 vv = load_pair(Vs + (size_t)r * hd + d);
-            const float v0 = vv.x, v1 = vv.y;
 #pragma unroll
             for (int hh = 0; hh < AD_GC; ++hh) {
                 if (hh < gc) {
                     const float w = sc[hh * CH + r];
-                    acc[hh][0] = fmaf(w, v0, acc[hh][0]);
-                    acc[hh][1] = fmaf(w, v1, acc[hh][1]);
+                    acc[hh][0] = fmaf(w, vv.x, acc[hh][0]);
+                    acc[hh][1] = fmaf(w, vv.y, acc[hh][1]);
                 }
             }
         }
 #pragma unroll
         for (int hh = 0; hh < AD_GC; ++hh) {
             if (hh < gc) {
-                float* dst = a.part_acc +
-                             (((size_t)b * a.nh + h0 + hh) * a.n_splits + split) * hd + d;
-                dst[0] = acc[hh][0];
-                dst[1] = acc[hh][1];
+                if (used == 1) {
+                    const float inv = 1.0f / stat[hh * 2 + 1];
+                    outp[hh * hd + d] = from_f32<T>(acc[hh][0] * inv);
+                    outp[hh * hd + d + 1] = from_f32<T>(acc[hh][1] * inv);
+                } else {
+                    float* dst = a.part_acc +
+                                 (((size_t)b * a.nh + h0 + hh) * a.n_splits + split) * hd + d;
+                    dst[0] = acc[hh][0];
+                    dst[1] = acc[hh][1];
+                }
             }
         }
     }
+    if (used == 1) return;
     if (tid < gc) {
         float* dst = a.part_ml + (((size_t)b * a.nh + h0 + tid) * a.n_splits + split) * 2;
         dst[0] = stat[tid * 2];
         dst[1] = stat[tid * 2 + 1];
     }
-}
-
-// Merges the chunks of one (sequence, head): out = sum_s e^{m_s - M} acc_s /
-// sum_s e^{m_s - M} l_s, in chunk order.
-template <typename T>
-__global__ void __launch_bounds__(AD_THREADS)
-attention_decode_merge_kernel(const float* __restrict__ part_acc,
-                              const float* __restrict__ part_ml, T* __restrict__ out,
-                              const int* __restrict__ slots, const int* __restrict__ positions,
-                              int nh, int hd, int window, int n_splits, int chunk) {
-    const int b = blockIdx.x / nh, h = blockIdx.x % nh;
-    T* o = out + ((size_t)b * nh + h) * hd;
-    if (slots[b] < 0) {
-        for (int d = threadIdx.x; d < hd; d += AD_THREADS) o[d] = from_f32<T>(0.f);
-        return;
+    // ---- count this chunk in; the last CTA of the (sequence, head group) merges
+    __threadfence();
+    __syncthreads();
+    int* counter = a.counters + (size_t)b * gridDim.y + blockIdx.y;
+    if (tid == 0) {
+        const int seen = atomicAdd(counter, 1);
+        s_last = (seen == used - 1);
     }
-    const int p = positions[b];
-    const int lo = window > 0 ? max(0, p - window + 1) : 0;
-    const int used = min(n_splits, (p - lo) / chunk + 1);
-    const float* ml = part_ml + ((size_t)b * nh + h) * n_splits * 2;
-    const float* acc = part_acc + ((size_t)b * nh + h) * n_splits * hd;
-    float M = -INFINITY;
-    for (int s = 0; s < used; ++s) M = fmaxf(M, ml[2 * s]);
-    float L = 0.f;
-    for (int s = 0; s < used; ++s) L += expf(ml[2 * s] - M) * ml[2 * s + 1];
-    const float inv = 1.0f / L;
-    for (int d = threadIdx.x; d < hd; d += AD_THREADS) {
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    if (tid == 0) *counter = 0;                         // ready for the next launch
+    // out = sum_s e^{m_s - M} acc_s / sum_s e^{m_s - M} l_s, in chunk order
+    for (int hh = warp; hh < gc; hh += AD_THREADS / 32) {
+        const float* ml = a.part_ml + ((size_t)b * a.nh + h0 + hh) * a.n_splits * 2;
+        float M = -INFINITY;
+        for (int sp = lane; sp < used; sp += 32) M = fmaxf(M, __ldcg(ml + 2 * sp));
+        M = warp_max(M);
+        float L = 0.f;
+        for (int sp = lane; sp < used; sp += 32)
+            L += expf(__ldcg(ml + 2 * sp) - M) * __ldcg(ml + 2 * sp + 1);
+        L = warp_sum(L);
+        if (lane == 0) {
+            stat[hh * 2] = M;
+            stat[hh * 2 + 1] = L;
+        }
+    }
+    __syncthreads();
+    for (int i = tid; i < gc * hd; i += AD_THREADS) {
+        const int hh = i / hd, d = i % hd;
+        const float* acc = a.part_acc + ((size_t)b * a.nh + h0 + hh) * a.n_splits * hd + d;
+        const float* ml = a.part_ml + ((size_t)b * a.nh + h0 + hh) * a.n_splits * 2;
+        const float M = stat[hh * 2];
         float v = 0.f;
-        for (int s = 0; s < used; ++s) v = fmaf(expf(ml[2 * s] - M), acc[(size_t)s * hd + d], v);
-        o[d] = from_f32<T>(v * inv);
+        for (int sp = 0; sp < used; ++sp)
+            v = fmaf(expf(__ldcg(ml + 2 * sp) - M), __ldcg(acc + (size_t)sp * hd), v);
+        outp[hh * hd + d] = from_f32<T>(v / stat[hh * 2 + 1]);
     }
 }
 
@@ -235,14 +265,14 @@ int pick_chunk(int hd, int elem) {
 
 size_t split_smem(int hd, int ch, int elem) {
     return (size_t)2 * ch * hd * elem + (size_t)AD_GC * hd * 4 + (size_t)AD_GC * ch * 4 +
-           AD_GC * 2 * 4;
+           AD_GC * 2 * 4 + (size_t)ch * 4;
 }
 
 }  // namespace
 
 // How the decode attention cuts a key range of at most max_keys positions:
 // chunk length and number of chunks.  The scratch it needs is
-// B * nh * n_splits * (hd + 2) floats.
+// B * nh * n_splits * (hd + 2) floats, and B * nkv * ceil(nh / nkv / 4) counters.
 AGV_API int agv_attention_decode_plan(int hd, int dtype, int max_keys, int* chunk,
                                       int* n_splits) {
     AGV_REQUIRE(hd > 0 && max_keys > 0, "attention_decode_plan: bad sizes");
@@ -256,12 +286,14 @@ AGV_API int agv_attention_decode_plan(int hd, int dtype, int max_keys, int* chun
 // stored already).  q: [B, nh * hd] with row stride q_stride; out: [B, nh * hd]
 // dense.  max_keys bounds the number of keys any entry sees in this launch
 // (min(window, greatest length)); part_acc / part_ml are scratch of the sizes
-// agv_attention_decode_plan implies.  A negative slot yields zeros.
+// agv_attention_decode_plan implies; counters are B * nkv * ceil(nh / nkv / 4)
+// ints that are zero before the call (the call leaves them zero).  A negative
+// slot yields zeros.
 AGV_API int agv_attention_decode(const void* q, long long q_stride, void* out, int dtype,
                                  const void* k_pool, const void* v_pool, const int* page_table,
                                  const int* slots, const int* positions, int max_pages, int page,
                                  int cap, int B, int nh, int nkv, int hd, float scale, int window,
-                                 int max_keys, float* part_acc, float* part_ml,
+                                 int max_keys, float* part_acc, float* part_ml, int* counters,
                                  cudaStream_t stream) {
     AGV_REQUIRE(B >= 0 && nh > 0 && nkv > 0 && hd > 0, "attention_decode: bad sizes");
     AGV_REQUIRE(nh % nkv == 0, "attention_decode: %d heads are not a multiple of %d kv heads", nh,
@@ -277,14 +309,15 @@ AGV_API int agv_attention_decode(const void* q, long long q_stride, void* out, i
     AGV_REQUIRE(agv_aligned(k_pool, 16) && agv_aligned(v_pool, 16),
                 "attention_decode: cache pools must be 16-byte aligned");
     AGV_REQUIRE(B <= 65535, "attention_decode: batch %d exceeds the grid limit", B);
+    AGV_REQUIRE(part_acc && part_ml && counters, "attention_decode: scratch pointers are null");
     if (B == 0) return 0;
     const int ch = pick_chunk(hd, elem);
     const int n_splits = (max_keys + ch - 1) / ch;
     const size_t smem = split_smem(hd, ch, elem);
     AGV_REQUIRE(smem <= (size_t)AD_MAX_SMEM, "attention_decode: %zu bytes of shared memory needed",
                 smem);
-    DecodeArgs a{q, q_stride, k_pool, v_pool, page_table, slots, positions, part_acc, part_ml,
-                 max_pages, page, cap, nh, nkv, hd, window, n_splits, ch, scale};
+    DecodeArgs a{q, q_stride, out, k_pool, v_pool, page_table, slots, positions, part_acc, part_ml,
+                 counters, max_pages, page, cap, nh, nkv, hd, window, n_splits, ch, scale};
     const int G = nh / nkv;
     dim3 grid(n_splits, nkv * ((G + AD_GC - 1) / AD_GC), B);
     if (dtype == AGV_F32) {
@@ -296,9 +329,6 @@ AGV_API int agv_attention_decode(const void* q, long long q_stride, void* out, i
             configured = true;
         }
         kern<<<grid, AD_THREADS, smem, stream>>>(a);
-        AGV_LAUNCH_OK("attention_decode_split_kernel");
-        attention_decode_merge_kernel<float><<<B * nh, AD_THREADS, 0, stream>>>(
-            part_acc, part_ml, (float*)out, slots, positions, nh, hd, window, n_splits, ch);
     } else {
         auto kern = attention_decode_split_kernel<__nv_bfloat16>;
         static bool configured = false;
@@ -308,11 +338,8 @@ AGV_API int agv_attention_decode(const void* q, long long q_stride, void* out, i
             configured = true;
         }
         kern<<<grid, AD_THREADS, smem, stream>>>(a);
-        AGV_LAUNCH_OK("attention_decode_split_kernel");
-        attention_decode_merge_kernel<__nv_bfloat16><<<B * nh, AD_THREADS, 0, stream>>>(
-            part_acc, part_ml, (__nv_bfloat16*)out, slots, positions, nh, hd, window, n_splits, ch);
     }
-    AGV_LAUNCH_OK("attention_decode_merge_kernel");
+    AGV_LAUNCH_OK("attention_decode_split_kernel");
     return 0;
 }
 
@@ -324,10 +351,14 @@ AGV_API int agv_attention_decode(const void* q, long long q_stride, void* out, i
 #include <mutex>
 
 static __device__ __align__(256) float g_static_scratch[AGV_NO_ALLOC_SCRATCH_FLOATS];
+// Arrival counters of the split kernel: zero when the library is loaded, and every
+// launch returns them to zero.
+static __device__ __align__(256) int g_static_counters[AGV_NO_ALLOC_COUNTERS];
 
 namespace {
 constexpr int NO_ALLOC_MAX_DEVICES = 64;
 float* g_static_scratch_addr[NO_ALLOC_MAX_DEVICES] = {};
+int* g_static_counters_addr[NO_ALLOC_MAX_DEVICES] = {};
 std::mutex g_static_scratch_mu;
 }  // namespace
 
@@ -347,21 +378,30 @@ AGV_API int agv_attention_decode_static(const void* q, long long q_stride, void*
                 "values, the built-in array holds %d; use agv_attention_decode with your own "
                 "scratch, or a smaller batch or max_keys",
                 B, nh, n_splits, hd, need, (int)AGV_NO_ALLOC_SCRATCH_FLOATS);
+    const int groups = nkv > 0 ? nkv * ((nh / nkv + AD_GC - 1) / AD_GC) : 0;
+    AGV_REQUIRE((long long)B * groups <= (long long)AGV_NO_ALLOC_COUNTERS,
+                "attention_decode_static: B=%d times %d head groups exceed the %d built-in counters",
+                B, groups, (int)AGV_NO_ALLOC_COUNTERS);
     int dev = 0;
     AGV_CUDA_OK(cudaGetDevice(&dev));
     AGV_REQUIRE(dev >= 0 && dev < NO_ALLOC_MAX_DEVICES, "attention_decode_static: device %d", dev);
     float* base = nullptr;
+    int* counters = nullptr;
     {
         std::lock_guard<std::mutex> g(g_static_scratch_mu);
         if (!g_static_scratch_addr[dev]) {
             float* p = nullptr;
+            int* c = nullptr;
             AGV_CUDA_OK(cudaGetSymbolAddress((void**)&p, g_static_scratch));
+            AGV_CUDA_OK(cudaGetSymbolAddress((void**)&c, g_static_counters));
             g_static_scratch_addr[dev] = p;
+            g_static_counters_addr[dev] = c;
         }
         base = g_static_scratch_addr[dev];
+        counters = g_static_counters_addr[dev];
     }
     // partial sums first, then the (maximum, normaliser) pairs; both start 16-byte aligned
     return agv_attention_decode(q, q_stride, out, dtype, k_pool, v_pool, page_table, slots,
                                 positions, max_pages, page, cap, B, nh, nkv, hd, scale, window,
-                                max_keys, base, base + acc_floats, stream);
+                                max_keys, base, base + acc_floats, counters, stream);
 }

@@ -26,7 +26,9 @@ struct CacheWrite {
 
 template <typename T>
 __global__ void __launch_bounds__(QK_WARPS * 32)
-qk_norm_rope_store_kernel(T* __restrict__ qkv, long long row_stride, int n_tokens, int nh, int nkv,
+qk_norm_rope_store_kernel(T* __restrict__ qkv, long long row_stride,
+                          const float* __restrict__ part, int n_splits, long long split_stride,
+                          int n_tokens, int nh, int nkv,
                           int hd, const float* __restrict__ wq, const float* __restrict__ wk,
                           float eps, const float* __restrict__ cosv,
                           const float* __restrict__ sinv, int rotary_half,
@@ -43,13 +45,28 @@ qk_norm_rope_store_kernel(T* __restrict__ qkv, long long row_stride, int n_token
     const float* w = is_q ? wq : (is_k ? wk : nullptr);
 
     float ss = 0.f;
-    for (int e = lane; e < hd; e += 32) {
-        const float v = to_f32(src[e]);
-        buf[e] = v;
-        ss += v * v;
+    if (part) {
+        // the projection arrives as 32-bit partial sums over ranges of K
+        const float* ps = part + (size_t)t * (size_t)(heads * hd) + (size_t)head * hd;
+        for (int e = lane; e < hd; e += 32) {
+            float v = 0.f;
+            for (int sp = 0; sp < n_splits; ++sp) v += ps[(size_t)sp * split_stride + e];
+            buf[e] = v;
+            ss += v * v;
+        }
+    } else {
+        for (int e = lane; e < hd; e += 32) {
+            const float v = to_f32(src[e]);
+            buf[e] = v;
+            ss += v * v;
+        }
     }
     if (!is_q && !is_k) {
         // v head: stored as projected
+        if (part) {
+            __syncwarp();
+            for (int e = lane; e < hd; e += 32) src[e] = from_f32<T>(buf[e]);
+        }
     } else {
         if (w) {
             ss = warp_sum(ss);
@@ -85,8 +102,11 @@ qk_norm_rope_store_kernel(T* __restrict__ qkv, long long row_stride, int n_token
 
 // qkv: [T, nh + 2 nkv, hd] (row stride in elements), rewritten in place: q and k
 // heads normed (if wq / wk given) and rotated (if cos / sin given).  k and v
-// are also written to the layer's cache pools unless k_pool is null.
-AGV_API int agv_qk_norm_rope_store(void* qkv, int dtype, long long row_stride, int n_tokens, int nh,
+// are also written to the layer's cache pools unless k_pool is null.  With
+// part != null the input is read from part [n_splits, T, (nh + 2 nkv) * hd]
+// (32-bit partial sums, dense) instead, and qkv only receives the result.
+AGV_API int agv_qk_norm_rope_store(void* qkv, int dtype, long long row_stride, const float* part,
+                                   int n_splits, int n_tokens, int nh,
                                    int nkv, int hd, const float* wq, const float* wk, float eps,
                                    const float* cosv, const float* sinv, int rotary_dim,
                                    const int* positions, void* k_pool, void* v_pool,
@@ -101,7 +121,9 @@ AGV_API int agv_qk_norm_rope_store(void* qkv, int dtype, long long row_stride, i
     AGV_REQUIRE(!k_pool || (v_pool && page_table && slots && lens && seq_index && page > 0 &&
                             cap > 0 && max_pages > 0), "qk_norm_rope: incomplete cache arguments");
     AGV_REQUIRE(!cosv || (sinv && positions), "qk_norm_rope: cos without sin or positions");
+    AGV_REQUIRE(!part || n_splits >= 1, "qk_norm_rope: partial sums need n_splits >= 1");
     if (n_tokens == 0) return 0;
+    const long long split_stride = (long long)n_tokens * (nh + 2 * nkv) * hd;
     CacheWrite cw{k_pool, v_pool, page_table, slots, lens, seq_index, max_pages, page, cap};
     const long long items = (long long)n_tokens * (nh + 2 * nkv);
     const unsigned grid = (unsigned)((items + QK_WARPS - 1) / QK_WARPS);
@@ -109,12 +131,12 @@ AGV_API int agv_qk_norm_rope_store(void* qkv, int dtype, long long row_stride, i
     const int half = cosv ? rotary_dim / 2 : 0;
     if (dtype == AGV_F32)
         qk_norm_rope_store_kernel<float><<<grid, QK_WARPS * 32, smem, stream>>>(
-            (float*)qkv, row_stride, n_tokens, nh, nkv, hd, wq, wk, eps, cosv, sinv, half,
-            positions, cw);
+            (float*)qkv, row_stride, part, n_splits, split_stride, n_tokens, nh, nkv, hd, wq, wk,
+            eps, cosv, sinv, half, positions, cw);
     else if (dtype == AGV_BF16)
         qk_norm_rope_store_kernel<__nv_bfloat16><<<grid, QK_WARPS * 32, smem, stream>>>(
-            (__nv_bfloat16*)qkv, row_stride, n_tokens, nh, nkv, hd, wq, wk, eps, cosv, sinv, half,
-            positions, cw);
+            (__nv_bfloat16*)qkv, row_stride, part, n_splits, split_stride, n_tokens, nh, nkv, hd,
+            wq, wk, eps, cosv, sinv, half, positions, cw);
     else
         return agv_fail(-1, "qk_norm_rope: unknown dtype %d", dtype);
     AGV_LAUNCH_OK("qk_norm_rope_store_kernel");

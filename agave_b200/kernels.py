@@ -189,10 +189,18 @@ def qk_norm_rope_store(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_di
                        page_table: Optional[torch.Tensor] = None,
                        slots: Optional[torch.Tensor] = None, lens: Optional[torch.Tensor] = None,
                        seq_index: Optional[torch.Tensor] = None, page: int = 0,
-                       cap: int = 0) -> None:
+                       cap: int = 0, partial: Optional[torch.Tensor] = None) -> None:
     """In place on qkv [T, (nh + 2 nkv) * hd]: per-head norm of q and k, rotation,
-    and (if pools are given) the store of k and v rows into the paged cache."""
+    and (if pools are given) the store of k and v rows into the paged cache.
+    ``partial`` [S, T, (nh + 2 nkv) * hd] (32-bit partial sums of the projection)
+    replaces qkv as the input; qkv then only receives the result."""
     T = qkv.shape[0]
+    n_splits = 0
+    if partial is not None:
+        _f32(partial, "partial"); _dense(partial, "partial")
+        assert partial.dim() == 3 and partial.shape[1] == T
+        assert partial.shape[2] == (n_heads + 2 * n_kv_heads) * head_dim
+        n_splits = partial.shape[0]
     assert qkv.stride(1) == 1
     _f32(wq, "wq"); _f32(wk, "wk"); _f32(cos, "cos"); _f32(sin, "sin")
     for t, n in ((positions, "positions"), (page_table, "page_table"), (slots, "slots"),
@@ -203,8 +211,8 @@ def qk_norm_rope_store(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_di
         assert k_pool.dtype == qkv.dtype and v_pool.dtype == qkv.dtype
     max_pages = page_table.shape[1] if page_table is not None else 0
     _check(library().agv_qk_norm_rope_store(
-        _ptr(qkv), dtype_code(qkv.dtype), ctypes.c_longlong(qkv.stride(0)), T, n_heads,
-        n_kv_heads, head_dim, _ptr(wq), _ptr(wk), ctypes.c_float(eps), _ptr(cos), _ptr(sin),
+        _ptr(qkv), dtype_code(qkv.dtype), ctypes.c_longlong(qkv.stride(0)), _ptr(partial),
+        n_splits, T, n_heads, n_kv_heads, head_dim, _ptr(wq), _ptr(wk), ctypes.c_float(eps), _ptr(cos), _ptr(sin),
         rotary_dim, _ptr(positions), _ptr(k_pool), _ptr(v_pool), _ptr(page_table), _ptr(slots),
         _ptr(lens), _ptr(seq_index), max_pages, page, cap, _stream()))
 
@@ -347,6 +355,38 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
         linear_simt(x, w, out, w2, activation)
 
 
+N_SMS = 148
+
+
+def plan_splits(T: int, N: int, K: int) -> int:
+    """How many ranges of K a product is cut into so that about one CTA per SM
+    is busy when the weight has few row tiles (decoding through narrow layers)."""
+    tile = 16 if T <= 16 else 32 if T <= 32 else 64 if T <= 64 else 128 if T <= 128 else 256
+    ctas = ((N + 127) // 128) * ((T + tile - 1) // tile)
+    kb = (K + 63) // 64
+    if ctas >= 100 or kb < 2:
+        return 1
+    return linear_tc_splits(K, min(kb, (N_SMS + ctas - 1) // ctas))
+
+
+def linear_partial(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """x w^T for a consumer that adds partial sums itself: returns [S, T, N] in
+    32-bit on the tensor-core path (S >= 1 ranges of K), else [T, N] in x's dtype."""
+    T, K = x.shape
+    N = w.shape[0]
+    if linear_tc_supported(x, w):
+        s = plan_splits(T, N, K)
+        out = torch.empty((s, T, N), dtype=torch.float32, device=x.device)
+        if s > 1:
+            linear_tc(x, w, out, splits=s)
+        else:
+            linear_tc(x, w, out[0])
+        return out
+    out = torch.empty((T, N), dtype=x.dtype, device=x.device)
+    linear_simt(x, w, out)
+    return out
+
+
 def attention_prefill(q, k, v, out, ctx, n_heads, n_kv_heads, head_dim, scale, window) -> None:
     attention_prefill_simt(q, k, v, out, ctx.positions, ctx.seq_index, ctx.cu_seqlens, n_heads,
                            n_kv_heads, head_dim, scale, window)
@@ -358,6 +398,18 @@ def attention_decode_plan(head_dim: int, dtype: torch.dtype, max_keys: int):
     _check(library().agv_attention_decode_plan(head_dim, dtype_code(dtype), max_keys,
                                                ctypes.byref(chunk), ctypes.byref(n)))
     return chunk.value, n.value
+
+
+_counters = {}
+
+
+def _decode_counters(device: torch.device, n: int) -> torch.Tensor:
+    """Arrival counters of the split decode attention: zero between launches (the
+    kernel resets what it counted), so one buffer per device serves every layer."""
+    t = _counters.get(device)
+    if t is None or t.numel() < n:
+        t = _counters[device] = torch.zeros(max(n, 65536), dtype=torch.int32, device=device)
+    return t
 
 
 def attention_decode_split(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor,
@@ -382,13 +434,12 @@ def attention_decode_split(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Ten
     assert part_acc.numel() >= B * n_heads * n_splits * head_dim
     assert part_ml.numel() >= B * n_heads * n_splits * 2
     _f32(part_acc, "part_acc"); _f32(part_ml, "part_ml")
-    global _launches
-    _launches += 1                      # this launcher starts two kernels
+    counters = _decode_counters(q.device, B * n_heads)
     _check(library().agv_attention_decode(
         _ptr(q), ctypes.c_longlong(q.stride(0)), _ptr(out), dtype_code(q.dtype), _ptr(k_pool),
         _ptr(v_pool), _ptr(page_table), _ptr(slots), _ptr(positions), page_table.shape[1], page,
         cap, B, n_heads, n_kv_heads, head_dim, ctypes.c_float(scale), window, max_keys,
-        _ptr(part_acc), _ptr(part_ml), _stream()))
+        _ptr(part_acc), _ptr(part_ml), _ptr(counters), _stream()))
 
 
 def attention_decode(q, out, view, ctx, n_heads, n_kv_heads, head_dim, scale, window) -> None:

@@ -5,6 +5,8 @@ Interface of a mixer part (what a block needs):
   ``cache_request() -> KVRequest | StateRequest | None``
   ``load(tensors, dtype, device)``
   ``forward(x [T, hidden], ctx, cache_entry, writes_cache) -> y [T, hidden]``
+  (y may also be ``[S, T, hidden]`` 32-bit partial sums; the norm that follows
+  adds them)
 
 Order of operations (src/models/gemma3.zig:714-820): q, k, v projections (one
 fused product here), per-head RMS norm of q and k, rotation, store of k and v,
@@ -78,7 +80,11 @@ class AttentionMixer:
         s = self.spec
         nh, nkv, hd = s.n_heads, s.n_kv_heads, s.head_dim
         T = x.shape[0]
-        qkv = self.qkv(x)
+        proj = self.qkv.partial(x)
+        if proj.dim() == 3:
+            part, qkv = proj, ctx.new(T, (nh + 2 * nkv) * hd)
+        else:
+            part, qkv = None, proj
         cos = sin = None
         rotary_dim = 0
         if self.position is not None:
@@ -90,10 +96,10 @@ class AttentionMixer:
             kernels.qk_norm_rope_store(
                 qkv, nh, nkv, hd, self.q_norm_weight, self.k_norm_weight, eps, cos, sin,
                 rotary_dim, ctx.positions, view.k_pool, view.v_pool, view.page_table, ctx.slots,
-                ctx.lens, ctx.seq_index, view.page, view.cap)
+                ctx.lens, ctx.seq_index, view.page, view.cap, partial=part)
         else:
             kernels.qk_norm_rope_store(qkv, nh, nkv, hd, self.q_norm_weight, self.k_norm_weight,
-                                       eps, cos, sin, rotary_dim, ctx.positions)
+                                       eps, cos, sin, rotary_dim, ctx.positions, partial=part)
         q = qkv[:, :nh * hd]
         out = ctx.new(T, nh * hd)
         window = s.window or 0
@@ -107,7 +113,7 @@ class AttentionMixer:
             kernels.attention_prefill(q, k, v, out, ctx, nh, nkv, hd, s.scale, window)
         else:
             kernels.attention_decode(q, out, view, ctx, nh, nkv, hd, s.scale, window)
-        return self.out(out)
+        return self.out.partial(out)
 
 
 register_mixer("attention", AttentionMixer)

@@ -5,7 +5,8 @@ epilogue of the gate/up kernel.
 Interface of a feed-forward part:
   ``param_specs(spec, hidden) -> {local name: ParamSpec}``      (class method)
   ``load(tensors, dtype, device)``
-  ``forward(x [T, hidden], ctx) -> y [T, hidden]``
+  ``forward(x [T, hidden], ctx) -> y [T, hidden]`` (or ``[S, T, hidden]`` 32-bit
+  partial sums, which the norm that follows adds)
 """
 from __future__ import annotations
 
@@ -43,7 +44,7 @@ class GatedFeedForward:
         self.down = Linear(mat("down_proj.weight"))
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
-        return self.down(self.gate_up(x))
+        return self.down.partial(self.gate_up(x))
 
 
 register_feed_forward("gated_dense", GatedFeedForward)

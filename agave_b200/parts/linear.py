@@ -28,6 +28,12 @@ class Linear:
         kernels.linear(x, self.weight, out)
         return out
 
+    def partial(self, x: torch.Tensor) -> torch.Tensor:
+        """x w^T for a consumer that sums over a leading axis itself: [S, T, N]
+        32-bit partial sums over ranges of K on the tensor-core path (S may be
+        1), else the plain [T, N] result."""
+        return kernels.linear_partial(x, self.weight)
+
 
 class GatedLinear:
     """act(x wg^T) * (x wu^T) in one kernel."""

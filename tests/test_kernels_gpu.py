@@ -205,6 +205,16 @@ def test_qk_norm_rope_store(dtype, nh, nkv, hd, rd):
         assert rel_err(v_pool[page, row % PAGE].float(), v_ref[t]) < tol
     # pages nobody owns stay untouched
     assert (k_pool[2] == 0).all() and (k_pool[1, 3] == 0).all()
+    # the same input given as 32-bit partial sums over three ranges of K
+    parts = torch.randn(3, T, (nh + 2 * nkv) * hd, device=DEV)
+    parts[2] = orig - parts[0] - parts[1]
+    qkv2 = torch.full_like(qkv, float("nan"))
+    k2, v2 = torch.zeros_like(k_pool), torch.zeros_like(v_pool)
+    kernels.qk_norm_rope_store(qkv2, nh, nkv, hd, wq, wk, 1e-6, cos, sin, rd, positions, k2, v2,
+                               table, slots, lens, seq_index, PAGE, cap, partial=parts)
+    assert rel_err(qkv2, qkv) < (2e-5 if dtype == torch.float32 else 8e-3)
+    assert rel_err(k2, k_pool) < (2e-5 if dtype == torch.float32 else 8e-3)
+    assert rel_err(v2, v_pool) < (2e-5 if dtype == torch.float32 else 8e-3)
 
 
 # ------------------------------------------------------------------ attention
