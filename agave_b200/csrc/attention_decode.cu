@@ -229,15 +229,23 @@ attention_decode_split_kernel(DecodeArgs a) {
     if (!s_last) return;
     __threadfence();
     if (tid == 0) *counter = 0;                         // ready for the next launch
-    // out = sum_s e^{m_s - M} acc_s / sum_s e^{m_s - M} l_s, in chunk order
+    // out = sum_s e^{m_s - M} acc_s / sum_s e^{m_s - M} l_s, in chunk order.  The
+    // weights go to shared memory first (the key buffer is free now), then every
+    // thread walks the chunks with several independent loads in flight.
+    float* wts = reinterpret_cast<float*>(smem_raw);            // [gc][used]
+    const int wcap = (int)(((size_t)2 * CH * hd * sizeof(T)) / (AD_GC * sizeof(float)));
+    const bool cached = used <= wcap;
     for (int hh = warp; hh < gc; hh += AD_THREADS / 32) {
         const float* ml = a.part_ml + ((size_t)b * a.nh + h0 + hh) * a.n_splits * 2;
         float M = -INFINITY;
         for (int sp = lane; sp < used; sp += 32) M = fmaxf(M, __ldcg(ml + 2 * sp));
         M = warp_max(M);
         float L = 0.f;
-        for (int sp = lane; sp < used; sp += 32)
-            L += expf(__ldcg(ml + 2 * sp) - M) * __ldcg(ml + 2 * sp + 1);
+        for (int sp = lane; sp < used; sp += 32) {
+            const float w = expf(__ldcg(ml + 2 * sp) - M);
+            if (cached) wts[hh * used + sp] = w;
+            L += w * __ldcg(ml + 2 * sp + 1);
+        }
         L = warp_sum(L);
         if (lane == 0) {
             stat[hh * 2] = M;
@@ -245,15 +253,38 @@ attention_decode_split_kernel(DecodeArgs a) {
         }
     }
     __syncthreads();
-    for (int i = tid; i < gc * hd; i += AD_THREADS) {
-        const int hh = i / hd, d = i % hd;
-        const float* acc = a.part_acc + ((size_t)b * a.nh + h0 + hh) * a.n_splits * hd + d;
-        const float* ml = a.part_ml + ((size_t)b * a.nh + h0 + hh) * a.n_splits * 2;
-        const float M = stat[hh * 2];
-        float v = 0.f;
-        for (int sp = 0; sp < used; ++sp)
-            v = fmaf(expf(__ldcg(ml + 2 * sp) - M), __ldcg(acc + (size_t)sp * hd), v);
-        outp[hh * hd + d] = from_f32<T>(v / stat[hh * 2 + 1]);
+    constexpr int EP = 8;               // outputs a thread accumulates at a time
+    for (int base = 0; base < gc * hd; base += AD_THREADS * EP) {
+        const float* accp[EP];
+        const float* wp[EP];
+        float v[EP], Mh[EP];
+        bool on[EP];
+#pragma unroll
+        for (int k = 0; k < EP; ++k) {
+            const int i = base + tid + k * AD_THREADS;
+            on[k] = i < gc * hd;
+            const int hh = on[k] ? i / hd : 0, d = on[k] ? i % hd : 0;
+            accp[k] = a.part_acc + ((size_t)b * a.nh + h0 + hh) * a.n_splits * hd + d;
+            wp[k] = cached ? wts + hh * used
+                           : a.part_ml + ((size_t)b * a.nh + h0 + hh) * a.n_splits * 2;
+            Mh[k] = stat[hh * 2];
+            v[k] = 0.f;
+        }
+#pragma unroll 2
+        for (int sp = 0; sp < used; ++sp) {
+#pragma unroll
+            for (int k = 0; k < EP; ++k) {
+                if (on[k]) {
+                    const float w = cached ? wp[k][sp] : expf(__ldcg(wp[k] + 2 * sp) - Mh[k]);
+                    v[k] = fmaf(w, __ldcg(accp[k] + (size_t)sp * hd), v[k]);
+                }
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < EP; ++k) {
+            const int i = base + tid + k * AD_THREADS;
+            if (on[k]) outp[i] = from_f32<T>(v[k] / stat[(i / hd) * 2 + 1]);
+        }
     }
 }
 

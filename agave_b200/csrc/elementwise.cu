@@ -127,11 +127,109 @@ __global__ void norm_residual_kernel(float* __restrict__ h, const TY* __restrict
     }
 }
 
+// The same arithmetic for rows of at most EPT * blockDim.x values, with every
+// operand a thread needs (branch partial sums, stream, both weights) loaded up
+// front into registers: the loads of one row overlap instead of queueing behind
+// the reductions.  This is the variant decode steps run.
+template <typename TY, typename TX, int EPT>
+__global__ void __launch_bounds__(1024)
+norm_residual_small_kernel(float* __restrict__ h, const TY* __restrict__ y, int n_splits,
+                           size_t split_stride, const float* __restrict__ w_post,
+                           const float* __restrict__ w_next, TX* __restrict__ x,
+                           const int* __restrict__ rows, int H, float eps_post, float eps_next,
+                           int add_residual) {
+    __shared__ float red[33];
+    const int r = blockIdx.x;
+    const size_t src = (size_t)(rows ? rows[r] : r) * H;
+    const size_t dst = (size_t)r * H;
+    float v[EPT], hv[EPT], wp[EPT], wn[EPT];
+#pragma unroll
+    for (int k = 0; k < EPT; ++k) {
+        const int i = threadIdx.x + k * blockDim.x;
+        const bool in = i < H;
+        v[k] = 0.f;
+        hv[k] = (in && (add_residual || !y)) ? h[src + i] : 0.f;
+        wp[k] = (in && w_post) ? w_post[i] : 1.f;
+        wn[k] = (in && w_next) ? w_next[i] : 1.f;
+    }
+    if (y) {
+        for (int s0 = 0; s0 < n_splits; s0 += 4) {
+            float t[4][EPT];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+                for (int k = 0; k < EPT; ++k) {
+                    const int i = threadIdx.x + k * blockDim.x;
+                    t[u][k] = (i < H && s0 + u < n_splits)
+                                  ? to_f32(y[(size_t)(s0 + u) * split_stride + src + i]) : 0.f;
+                }
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+                for (int k = 0; k < EPT; ++k) v[k] += t[u][k];
+        }
+        if (w_post) {
+            float ss = 0.f;
+#pragma unroll
+            for (int k = 0; k < EPT; ++k) ss += v[k] * v[k];
+            ss = block_sum(ss, red);
+            const float rs = 1.0f / sqrtf(ss / (float)H + eps_post);
+#pragma unroll
+            for (int k = 0; k < EPT; ++k) v[k] = v[k] * rs * wp[k];
+        }
+        if (add_residual) {
+#pragma unroll
+            for (int k = 0; k < EPT; ++k) {
+                const int i = threadIdx.x + k * blockDim.x;
+                v[k] += hv[k];
+                if (i < H) h[src + i] = v[k];
+            }
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < EPT; ++k) v[k] = hv[k];
+    }
+    if (w_next) {
+        float ss = 0.f;
+#pragma unroll
+        for (int k = 0; k < EPT; ++k) ss += v[k] * v[k];      // lanes beyond H hold 0
+        ss = block_sum(ss, red);
+        const float r2 = 1.0f / sqrtf(ss / (float)H + eps_next);
+#pragma unroll
+        for (int k = 0; k < EPT; ++k) {
+            const int i = threadIdx.x + k * blockDim.x;
+            if (i < H) x[dst + i] = from_f32<TX>(v[k] * r2 * wn[k]);
+        }
+    } else if (x) {
+#pragma unroll
+        for (int k = 0; k < EPT; ++k) {
+            const int i = threadIdx.x + k * blockDim.x;
+            if (i < H) x[dst + i] = from_f32<TX>(v[k]);
+        }
+    }
+}
+
 template <typename TY, typename TX>
 static int launch_norm(float* h, const void* y, int n_splits, size_t split_stride,
                        const float* w_post, const float* w_next, void* x, const int* rows, int R,
                        int H, float eps_post, float eps_next, int add_residual,
                        cudaStream_t stream) {
+    // few rows (decode, final norm): the register-resident kernel, one row per CTA
+    if (R <= 256 && H <= 8 * 1024) {
+        const int threads = H <= 256 ? 128 : H <= 1024 ? 512 : 1024;
+        const int ept = (H + threads - 1) / threads;
+#define AGV_SMALL(E)                                                                            \
+    norm_residual_small_kernel<TY, TX, E><<<R, threads, 0, stream>>>(                           \
+        h, (const TY*)y, n_splits, split_stride, w_post, w_next, (TX*)x, rows, H, eps_post,     \
+        eps_next, add_residual)
+        if (ept <= 1) AGV_SMALL(1);
+        else if (ept <= 2) AGV_SMALL(2);
+        else if (ept <= 4) AGV_SMALL(4);
+        else AGV_SMALL(8);
+#undef AGV_SMALL
+        AGV_LAUNCH_OK("norm_residual_small_kernel");
+        return 0;
+    }
     const size_t smem = (size_t)H * sizeof(float);
     auto kern = norm_residual_kernel<TY, TX>;
     if (smem > 48 * 1024) {

@@ -48,11 +48,27 @@ qk_norm_rope_store_kernel(T* __restrict__ qkv, long long row_stride,
     if (part) {
         // the projection arrives as 32-bit partial sums over ranges of K
         const float* ps = part + (size_t)t * (size_t)(heads * hd) + (size_t)head * hd;
-        for (int e = lane; e < hd; e += 32) {
-            float v = 0.f;
-            for (int sp = 0; sp < n_splits; ++sp) v += ps[(size_t)sp * split_stride + e];
-            buf[e] = v;
-            ss += v * v;
+        // eight elements per lane at a time, all their loads independent; the
+        // ranges of K are added in order
+        for (int e0 = 0; e0 < hd; e0 += 256) {
+            float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll 2
+            for (int sp = 0; sp < n_splits; ++sp) {
+                const float* row = ps + (size_t)sp * split_stride;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int e = e0 + lane + 32 * i;
+                    if (e < hd) v[i] += row[e];
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int e = e0 + lane + 32 * i;
+                if (e < hd) {
+                    buf[e] = v[i];
+                    ss += v[i] * v[i];
+                }
+            }
         }
     } else {
         for (int e = lane; e < hd; e += 32) {

@@ -387,9 +387,32 @@ def linear_partial(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def attention_prefill_mma(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor,
+                          cu_seqlens: torch.Tensor, max_len: int, n_heads: int, n_kv_heads: int,
+                          head_dim: int, scale: float, window: int) -> None:
+    """Prompts that start at 0 on the tensor cores (bfloat16, head sizes in steps
+    of 8 up to 256); q, k, v are row-strided views, out is dense."""
+    assert q.dtype == torch.bfloat16 and k.dtype == q.dtype and v.dtype == q.dtype
+    assert q.stride(1) == 1 and k.stride(1) == 1 and v.stride(1) == 1
+    assert k.stride(0) == v.stride(0)
+    _dense(out, "out"); _i32(cu_seqlens, "cu_seqlens")
+    _check(library().agv_attention_prefill_mma(
+        _ptr(q), ctypes.c_longlong(q.stride(0)), _ptr(k), _ptr(v),
+        ctypes.c_longlong(k.stride(0)), _ptr(out), _ptr(cu_seqlens), cu_seqlens.numel() - 1,
+        max_len, n_heads, n_kv_heads, head_dim, ctypes.c_float(scale), window, _stream()))
+
+
 def attention_prefill(q, k, v, out, ctx, n_heads, n_kv_heads, head_dim, scale, window) -> None:
-    attention_prefill_simt(q, k, v, out, ctx.positions, ctx.seq_index, ctx.cu_seqlens, n_heads,
-                           n_kv_heads, head_dim, scale, window)
+    """Prompt attention of one layer: the tensor-core kernel for bfloat16 and head
+    sizes in steps of 8 up to 256, else the one-warp-per-(token, head) kernel."""
+    if (q.dtype == torch.bfloat16 and head_dim % 8 == 0 and head_dim <= 256 and
+            q.stride(0) % 8 == 0 and k.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and
+            k.data_ptr() % 16 == 0 and v.data_ptr() % 16 == 0):
+        attention_prefill_mma(q, k, v, out, ctx.cu_seqlens, ctx.max_new, n_heads, n_kv_heads,
+                              head_dim, scale, window)
+    else:
+        attention_prefill_simt(q, k, v, out, ctx.positions, ctx.seq_index, ctx.cu_seqlens,
+                               n_heads, n_kv_heads, head_dim, scale, window)
 
 
 def attention_decode_plan(head_dim: int, dtype: torch.dtype, max_keys: int):

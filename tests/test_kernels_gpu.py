@@ -426,3 +426,51 @@ def test_attention_decode_split_long_sequences(dtype, nh, nkv, hd):
             assert rel_err(out[0, :hd], v_pool[page5, 5, 0]) < 2e-2     # the far key is seen
         else:
             assert (out[0, :hd].float() - v_pool[page5, 5, 0].float()).abs().max() > 0.1
+
+
+@pytest.mark.parametrize("nh,nkv,hd,window", [(4, 1, 256, 0), (4, 1, 256, 100), (6, 2, 128, 70),
+                                              (3, 3, 64, 0), (4, 2, 16, 5), (2, 1, 40, 33),
+                                              (2, 1, 200, 64)])
+def test_attention_prefill_tensor_cores(nh, nkv, hd, window):
+    """The mma kernel against the one-warp kernel and a 64-bit statement, ragged
+    batch whose lengths straddle the 64-row tiles."""
+    from agave_b200 import kernels
+    lens = [1, 63, 64, 65, 200, 130]
+    T = sum(lens)
+    qkv = rnd(T, (nh + 2 * nkv) * hd, dtype=torch.bfloat16, seed=1, scale=0.5)
+    q, k, v = qkv[:, :nh * hd], qkv[:, nh * hd:(nh + nkv) * hd], qkv[:, (nh + nkv) * hd:]
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=DEV)
+    positions = torch.tensor(sum([list(range(n)) for n in lens], []), dtype=torch.int32, device=DEV)
+    seq_index = torch.tensor(sum([[i] * n for i, n in enumerate(lens)], []), dtype=torch.int32, device=DEV)
+    ref = torch.empty((T, nh * hd), dtype=torch.bfloat16, device=DEV)
+    kernels.attention_prefill_simt(q, k, v, ref, positions, seq_index, cu, nh, nkv, hd, 0.3, window)
+    out = torch.full_like(ref, float("nan"))
+    kernels.attention_prefill_mma(q, k, v, out, cu, max(lens), nh, nkv, hd, 0.3, window)
+    assert torch.isfinite(out.float()).all()
+    assert rel_err(out, ref) < 1.2e-2
+    o = sum(lens[:4])
+    n = lens[4]
+    exact = ref_attention(q[o:o + n].float().cpu().reshape(n, nh, hd),
+                          k[o:o + n].float().cpu().reshape(n, nkv, hd),
+                          v[o:o + n].float().cpu().reshape(n, nkv, hd), 0.3, window)
+    assert rel_err(out[o:o + n], exact) < 1.2e-2
+
+
+def test_attention_prefill_tensor_cores_far_key_and_window_edge():
+    from agave_b200 import kernels
+    hd, n, far = 256, 300, 3
+    k = rnd(n, hd, dtype=torch.bfloat16, seed=1, scale=0.1)
+    v = rnd(n, hd, dtype=torch.bfloat16, seed=2)
+    q = rnd(n, hd, dtype=torch.bfloat16, seed=3, scale=0.1)
+    k[far] = 0; k[far, 0] = 40.0
+    q[-1] = 0; q[-1, 0] = 40.0
+    qkv = torch.cat([q, k, v], dim=1).contiguous()
+    cu = torch.tensor([0, n], dtype=torch.int32, device=DEV)
+    out = torch.empty((n, hd), dtype=torch.bfloat16, device=DEV)
+    args = (qkv[:, :hd], qkv[:, hd:2 * hd], qkv[:, 2 * hd:], out, cu, n, 1, 1, hd, 1.0)
+    kernels.attention_prefill_mma(*args, 0)
+    assert rel_err(out[-1], v[far]) < 1e-2
+    kernels.attention_prefill_mma(*args, n - far)
+    assert rel_err(out[-1], v[far]) < 1e-2
+    kernels.attention_prefill_mma(*args, n - far - 1)
+    assert (out[-1].float() - v[far].float()).abs().max() > 0.1
