@@ -78,6 +78,98 @@ struct DecodeArgs {
     float scale;
 };
 
+// Writes this chunk's (maximum, normaliser), counts the chunk in and, in the
+// CTA that arrives last for the (sequence, head group), merges all chunks:
+// out = sum_s e^{m_s - M} acc_s / sum_s e^{m_s - M} l_s, in chunk order.
+// stat: shared [gc][2] holding this chunk's (m, l); wts: shared scratch of wcap
+// floats (free by now); s_last: a shared int.
+template <typename T>
+__device__ __forceinline__ void finish_split(const DecodeArgs& a, int b, int h0, int gc, int used,
+                                             int split, float* stat, float* wts, int wcap,
+                                             int* s_last, T* outp) {
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int nthreads = blockDim.x, nwarps = nthreads >> 5;
+    const int hd = a.hd;
+    if (tid < gc) {
+        float* dst = a.part_ml + (((size_t)b * a.nh + h0 + tid) * a.n_splits + split) * 2;
+        dst[0] = stat[tid * 2];
+        dst[1] = stat[tid * 2 + 1];
+    }
+    __threadfence();
+    __syncthreads();
+    int* counter = a.counters + (size_t)b * gridDim.y + blockIdx.y;
+    if (tid == 0) {
+        const int seen = atomicAdd(counter, 1);
+        *s_last = (seen == used - 1);
+    }
+    __syncthreads();
+    if (!*s_last) return;
+    __threadfence();
+    if (tid == 0) *counter = 0;                         // ready for the next launch
+    // pass 1: the overall maximum and normaliser of each head
+    for (int hh = warp; hh < gc; hh += nwarps) {
+        const float* ml = a.part_ml + ((size_t)b * a.nh + h0 + hh) * a.n_splits * 2;
+        float M = -INFINITY;
+        for (int sp = lane; sp < used; sp += 32) M = fmaxf(M, __ldcg(ml + 2 * sp));
+        M = warp_max(M);
+        float L = 0.f;
+        for (int sp = lane; sp < used; sp += 32)
+            L += expf(__ldcg(ml + 2 * sp) - M) * __ldcg(ml + 2 * sp + 1);
+        L = warp_sum(L);
+        if (lane == 0) {
+            stat[hh * 2] = M;
+            stat[hh * 2 + 1] = L;
+        }
+    }
+    __syncthreads();
+    // pass 2: chunks in segments whose weights fit the shared scratch.  The loads
+    // of a step are issued together, with no branch between them, so they overlap.
+    constexpr int EP = 8, U = 4;        // outputs per thread, chunks per step
+    const int seg = max(1, min(used, wcap / gc));
+    for (int base = 0; base < gc * hd; base += nthreads * EP) {
+        const float* accp[EP];
+        int hk[EP];
+        float v[EP];
+#pragma unroll
+        for (int k = 0; k < EP; ++k) {
+            const int i = min(base + tid + k * nthreads, gc * hd - 1);
+            hk[k] = i / hd;
+            accp[k] = a.part_acc + ((size_t)b * a.nh + h0 + hk[k]) * a.n_splits * hd + i % hd;
+            v[k] = 0.f;
+        }
+        for (int s0 = 0; s0 < used; s0 += seg) {
+            const int ns = min(seg, used - s0);
+            __syncthreads();
+            for (int i = tid; i < gc * ns; i += nthreads) {
+                const int hh = i / ns, sp = s0 + i % ns;
+                const float* ml = a.part_ml + ((size_t)b * a.nh + h0 + hh) * a.n_splits * 2;
+                wts[hh * seg + (sp - s0)] = expf(__ldcg(ml + 2 * sp) - stat[hh * 2]);
+            }
+            __syncthreads();
+            for (int sp = 0; sp < ns; sp += U) {
+                float t[U][EP];
+#pragma unroll
+                for (int u = 0; u < U; ++u)
+#pragma unroll
+                    for (int k = 0; k < EP; ++k)
+                        t[u][k] = __ldcg(accp[k] + (size_t)(s0 + min(sp + u, ns - 1)) * hd);
+#pragma unroll
+                for (int u = 0; u < U; ++u)
+#pragma unroll
+                    for (int k = 0; k < EP; ++k) {
+                        const float w = sp + u < ns ? wts[hk[k] * seg + sp + u] : 0.f;
+                        v[k] = fmaf(w, t[u][k], v[k]);
+                    }
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < EP; ++k) {
+            const int i = base + tid + k * nthreads;
+            if (i < gc * hd) outp[i] = from_f32<T>(v[k] / stat[hk[k] * 2 + 1]);
+        }
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(AD_THREADS)
 attention_decode_split_kernel(DecodeArgs a) {
@@ -212,80 +304,210 @@ attention_decode_split_kernel(DecodeArgs a) {
         }
     }
     if (used == 1) return;
-    if (tid < gc) {
-        float* dst = a.part_ml + (((size_t)b * a.nh + h0 + tid) * a.n_splits + split) * 2;
-        dst[0] = stat[tid * 2];
-        dst[1] = stat[tid * 2 + 1];
+    finish_split<T>(a, b, h0, gc, used, split, stat, reinterpret_cast<float*>(smem_raw),
+                    (int)(((size_t)2 * CH * hd * sizeof(T)) / sizeof(float)), &s_last, outp);
+}
+
+// ------------------------------------------------------- tensor-core variant
+// bfloat16, head sizes in steps of 8 up to 256: the same split of the keys, but
+// a chunk's scores and weighted values are mma.sync m16n8k16 products.  The rows
+// of the left operand are the query heads that share the kv head (up to 16 per
+// CTA), so a group's keys and values are read once for all its heads.
+constexpr int DM_HEADS = 16, DM_KEYS = 64, DM_THREADS = 128;
+
+__device__ __forceinline__ unsigned dm_smem(const void* p) {
+    return (unsigned)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void dm_ldsm4(unsigned addr, unsigned (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void dm_ldsm4t(unsigned addr, unsigned (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void dm_mma(float (&d)[4], const unsigned (&a)[4], unsigned b0,
+                                       unsigned b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+        "{%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// [rows][W] bf16 tiles: the 16-byte chunk c of row r sits at (c & ~7) | ((c ^ r) & 7).
+template <int W>
+__device__ __forceinline__ int dm_swz(int row, int chunk) {
+    return row * W + (((chunk & ~7) | ((chunk ^ row) & 7)) << 3);
+}
+
+template <int HDP>
+__global__ void __launch_bounds__(DM_THREADS)
+attention_decode_mma_kernel(DecodeArgs a) {
+    typedef __nv_bfloat16 T;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    __shared__ int s_last;
+    T* Ks = reinterpret_cast<T*>(smem_raw);                 // [64][HDP]
+    T* Vs = Ks + DM_KEYS * HDP;                             // [64][HDP]
+    T* Qs = Vs + DM_KEYS * HDP;                             // [16][HDP]
+    T* Ps = Qs + DM_HEADS * HDP;                            // [16][64]
+    float* Ss = reinterpret_cast<float*>(Ps + DM_HEADS * DM_KEYS);   // [16][64]
+    float* stat = Ss + DM_HEADS * DM_KEYS;                  // [16][2]
+    int* rowoff = reinterpret_cast<int*>(stat + DM_HEADS * 2);       // [64]
+
+    const int b = blockIdx.z, split = blockIdx.x;
+    const int G = a.nh / a.nkv;
+    const int groups_per_kv = (G + DM_HEADS - 1) / DM_HEADS;
+    const int g = blockIdx.y / groups_per_kv;
+    const int h0 = g * G + (blockIdx.y % groups_per_kv) * DM_HEADS;
+    const int gc = min(DM_HEADS, g * G + G - h0);
+    const int hd = a.hd;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int gid = lane >> 2, tig = lane & 3;
+    T* outp = (T*)a.out + ((size_t)b * a.nh + h0) * hd;
+    const int slot = a.slots[b];
+    if (slot < 0) {
+        if (split == 0)
+            for (int i = tid; i < gc * hd; i += DM_THREADS) outp[i] = __float2bfloat16_rn(0.f);
+        return;
     }
-    // ---- count this chunk in; the last CTA of the (sequence, head group) merges
-    __threadfence();
-    __syncthreads();
-    int* counter = a.counters + (size_t)b * gridDim.y + blockIdx.y;
-    if (tid == 0) {
-        const int seen = atomicAdd(counter, 1);
-        s_last = (seen == used - 1);
+    const int p = a.positions[b];
+    const int lo = a.window > 0 ? max(0, p - a.window + 1) : 0;
+    const int j0 = lo + split * DM_KEYS;
+    if (j0 > p) return;
+    const int n = min(DM_KEYS, p - j0 + 1);
+    const int used = (p - lo) / DM_KEYS + 1;
+
+    const int* table = a.page_table + (size_t)slot * a.max_pages;
+    if (tid < DM_KEYS) {
+        const int row = (j0 + tid) % a.cap;
+        rowoff[tid] = tid < n ? table[row / a.page] * a.page + row % a.page : -1;
+    }
+    // queries of the group: rows beyond the group's heads and dims beyond hd are zero
+    constexpr int CPR = HDP / 8;
+    for (int i = tid; i < DM_HEADS * CPR; i += DM_THREADS) {
+        const int r = i / CPR, c = i % CPR;
+        T* dst = Qs + dm_swz<HDP>(r, c);
+        if (r < gc && c * 8 < hd)
+            cp_async16(dst, (const T*)a.q + (size_t)b * a.q_stride + (size_t)(h0 + r) * hd + c * 8);
+        else
+            *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
     }
     __syncthreads();
-    if (!s_last) return;
-    __threadfence();
-    if (tid == 0) *counter = 0;                         // ready for the next launch
-    // out = sum_s e^{m_s - M} acc_s / sum_s e^{m_s - M} l_s, in chunk order.  The
-    // weights go to shared memory first (the key buffer is free now), then every
-    // thread walks the chunks with several independent loads in flight.
-    float* wts = reinterpret_cast<float*>(smem_raw);            // [gc][used]
-    const int wcap = (int)(((size_t)2 * CH * hd * sizeof(T)) / (AD_GC * sizeof(float)));
-    const bool cached = used <= wcap;
-    for (int hh = warp; hh < gc; hh += AD_THREADS / 32) {
-        const float* ml = a.part_ml + ((size_t)b * a.nh + h0 + hh) * a.n_splits * 2;
-        float M = -INFINITY;
-        for (int sp = lane; sp < used; sp += 32) M = fmaxf(M, __ldcg(ml + 2 * sp));
-        M = warp_max(M);
-        float L = 0.f;
-        for (int sp = lane; sp < used; sp += 32) {
-            const float w = expf(__ldcg(ml + 2 * sp) - M);
-            if (cached) wts[hh * used + sp] = w;
-            L += w * __ldcg(ml + 2 * sp + 1);
+    for (int i = tid; i < DM_KEYS * CPR; i += DM_THREADS) {
+        const int r = i / CPR, c = i % CPR;
+        const int off = dm_swz<HDP>(r, c);
+        if (rowoff[r] >= 0 && c * 8 < hd) {
+            const size_t src = ((size_t)rowoff[r] * a.nkv + g) * hd + c * 8;
+            cp_async16(Ks + off, (const T*)a.k_pool + src);
+            cp_async16(Vs + off, (const T*)a.v_pool + src);
+        } else {
+            *reinterpret_cast<uint4*>(Ks + off) = make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4*>(Vs + off) = make_uint4(0, 0, 0, 0);
         }
-        L = warp_sum(L);
+    }
+    cp_async_wait_all();
+    __syncthreads();
+    // ---- scores of 16 heads x this warp's 16 keys
+    {
+        float s[2][4] = {};
+#pragma unroll
+        for (int kk = 0; kk < HDP / 16; ++kk) {
+            unsigned af[4], bf[4];
+            dm_ldsm4(dm_smem(Qs + dm_swz<HDP>(lane & 15, kk * 2 + (lane >> 4))), af);
+            const int mat = lane >> 3, r = lane & 7;
+            dm_ldsm4(dm_smem(Ks + dm_swz<HDP>(warp * 16 + r + (mat >> 1) * 8, kk * 2 + (mat & 1))),
+                     bf);
+            dm_mma(s[0], af, bf[0], bf[1]);
+            dm_mma(s[1], af, bf[2], bf[3]);
+        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int key = warp * 16 + i * 8 + tig * 2 + (e & 1);
+                const int row = gid + (e >> 1) * 8;
+                Ss[row * DM_KEYS + key] = key < n ? s[i][e] * a.scale : -INFINITY;
+            }
+    }
+    __syncthreads();
+    // ---- softmax weights relative to the chunk's maximum: four rows per warp
+#pragma unroll
+    for (int rr = 0; rr < 4; ++rr) {
+        const int row = warp * 4 + rr;
+        const float s0 = Ss[row * DM_KEYS + lane], s1 = Ss[row * DM_KEYS + lane + 32];
+        const float m = warp_max(fmaxf(s0, s1));
+        const float w0 = expf(s0 - m), w1 = expf(s1 - m);
+        const float l = warp_sum(w0 + w1);
+        Ps[dm_swz<DM_KEYS>(row, lane >> 3) + (lane & 7)] = __float2bfloat16_rn(w0);
+        Ps[dm_swz<DM_KEYS>(row, (lane >> 3) + 4) + (lane & 7)] = __float2bfloat16_rn(w1);
         if (lane == 0) {
-            stat[hh * 2] = M;
-            stat[hh * 2 + 1] = L;
+            stat[row * 2] = m;
+            stat[row * 2 + 1] = l;
         }
     }
     __syncthreads();
-    constexpr int EP = 8;               // outputs a thread accumulates at a time
-    for (int base = 0; base < gc * hd; base += AD_THREADS * EP) {
-        const float* accp[EP];
-        const float* wp[EP];
-        float v[EP], Mh[EP];
-        bool on[EP];
+    // ---- weighted values: this warp's quarter of the head dimension
+    {
+        constexpr int NP = HDP / 64;                       // pairs of 8-wide column tiles per warp
+        float o[NP * 2][4] = {};
 #pragma unroll
-        for (int k = 0; k < EP; ++k) {
-            const int i = base + tid + k * AD_THREADS;
-            on[k] = i < gc * hd;
-            const int hh = on[k] ? i / hd : 0, d = on[k] ? i % hd : 0;
-            accp[k] = a.part_acc + ((size_t)b * a.nh + h0 + hh) * a.n_splits * hd + d;
-            wp[k] = cached ? wts + hh * used
-                           : a.part_ml + ((size_t)b * a.nh + h0 + hh) * a.n_splits * 2;
-            Mh[k] = stat[hh * 2];
-            v[k] = 0.f;
-        }
-#pragma unroll 2
-        for (int sp = 0; sp < used; ++sp) {
+        for (int kk = 0; kk < DM_KEYS / 16; ++kk) {
+            unsigned af[4];
+            dm_ldsm4(dm_smem(Ps + dm_swz<DM_KEYS>(lane & 15, kk * 2 + (lane >> 4))), af);
 #pragma unroll
-            for (int k = 0; k < EP; ++k) {
-                if (on[k]) {
-                    const float w = cached ? wp[k][sp] : expf(__ldcg(wp[k] + 2 * sp) - Mh[k]);
-                    v[k] = fmaf(w, __ldcg(accp[k] + (size_t)sp * hd), v[k]);
-                }
+            for (int nn = 0; nn < NP; ++nn) {
+                unsigned bf[4];
+                const int mat = lane >> 3, r = lane & 7;
+                dm_ldsm4t(dm_smem(Vs + dm_swz<HDP>(kk * 16 + r + (mat & 1) * 8,
+                                                   warp * (HDP / 32) + nn * 2 + (mat >> 1))), bf);
+                dm_mma(o[nn * 2], af, bf[0], bf[1]);
+                dm_mma(o[nn * 2 + 1], af, bf[2], bf[3]);
             }
         }
 #pragma unroll
-        for (int k = 0; k < EP; ++k) {
-            const int i = base + tid + k * AD_THREADS;
-            if (on[k]) outp[i] = from_f32<T>(v[k] / stat[(i / hd) * 2 + 1]);
+        for (int i = 0; i < NP * 2; ++i) {
+            const int d = warp * (HDP / 4) + i * 8 + tig * 2;
+            if (d >= hd) continue;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int row = gid + half * 8;
+                if (row >= gc) continue;
+                const float v0 = o[i][half * 2], v1 = o[i][half * 2 + 1];
+                if (used == 1) {
+                    const float inv = 1.0f / stat[row * 2 + 1];
+                    outp[row * hd + d] = __float2bfloat16_rn(v0 * inv);
+                    outp[row * hd + d + 1] = __float2bfloat16_rn(v1 * inv);
+                } else {
+                    float* dst = a.part_acc +
+                                 (((size_t)b * a.nh + h0 + row) * a.n_splits + split) * hd + d;
+                    dst[0] = v0;
+                    dst[1] = v1;
+                }
+            }
         }
     }
+    if (used == 1) return;
+    finish_split<T>(a, b, h0, gc, used, split, stat, reinterpret_cast<float*>(smem_raw),
+                    (int)((size_t)2 * DM_KEYS * HDP * sizeof(T) / sizeof(float)), &s_last, outp);
+}
+
+template <int HDP>
+int launch_decode_mma(const DecodeArgs& a, int B, cudaStream_t stream) {
+    auto kern = attention_decode_mma_kernel<HDP>;
+    constexpr int smem = (2 * DM_KEYS + DM_HEADS) * HDP * 2 + DM_HEADS * DM_KEYS * (2 + 4) +
+                         DM_HEADS * 2 * 4 + DM_KEYS * 4;
+    static bool configured = false;
+    if (!configured) {
+        AGV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        configured = true;
+    }
+    const int G = a.nh / a.nkv;
+    dim3 grid(a.n_splits, a.nkv * ((G + DM_HEADS - 1) / DM_HEADS), B);
+    kern<<<grid, DM_THREADS, smem, stream>>>(a);
+    AGV_LAUNCH_OK("attention_decode_mma_kernel");
+    return 0;
 }
 
 int pick_chunk(int hd, int elem) {
@@ -349,6 +571,12 @@ AGV_API int agv_attention_decode(const void* q, long long q_stride, void* out, i
                 smem);
     DecodeArgs a{q, q_stride, out, k_pool, v_pool, page_table, slots, positions, part_acc, part_ml,
                  counters, max_pages, page, cap, nh, nkv, hd, window, n_splits, ch, scale};
+    if (dtype == AGV_BF16 && hd % 8 == 0 && hd <= 256 && ch == DM_KEYS &&
+        q_stride % 8 == 0 && agv_aligned(q, 16)) {
+        if (hd <= 64) return launch_decode_mma<64>(a, B, stream);
+        if (hd <= 128) return launch_decode_mma<128>(a, B, stream);
+        return launch_decode_mma<256>(a, B, stream);
+    }
     const int G = nh / nkv;
     dim3 grid(n_splits, nkv * ((G + AD_GC - 1) / AD_GC), B);
     if (dtype == AGV_F32) {

@@ -153,20 +153,31 @@ norm_residual_small_kernel(float* __restrict__ h, const TY* __restrict__ y, int 
         wn[k] = (in && w_next) ? w_next[i] : 1.f;
     }
     if (y) {
-        for (int s0 = 0; s0 < n_splits; s0 += 4) {
-            float t[4][EPT];
+        constexpr int U = EPT <= 2 ? 16 : (EPT <= 4 ? 8 : 4);   // ranges of K loaded together
+        if (n_splits == 1) {
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
+            for (int k = 0; k < EPT; ++k) {
+                const int i = threadIdx.x + k * blockDim.x;
+                v[k] = i < H ? to_f32(y[src + i]) : 0.f;
+            }
+        } else
+        for (int s0 = 0; s0 < n_splits; s0 += U) {
+            float t[U][EPT];
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+#pragma unroll
+                for (int k = 0; k < EPT; ++k) {
+                    const int i = min(threadIdx.x + k * blockDim.x, (unsigned)(H - 1));
+                    const int sp = min(s0 + u, n_splits - 1);
+                    t[u][k] = to_f32(y[(size_t)sp * split_stride + src + i]);
+                }
+#pragma unroll
+            for (int u = 0; u < U; ++u)
 #pragma unroll
                 for (int k = 0; k < EPT; ++k) {
                     const int i = threadIdx.x + k * blockDim.x;
-                    t[u][k] = (i < H && s0 + u < n_splits)
-                                  ? to_f32(y[(size_t)(s0 + u) * split_stride + src + i]) : 0.f;
+                    v[k] += (i < H && s0 + u < n_splits) ? t[u][k] : 0.f;
                 }
-#pragma unroll
-            for (int u = 0; u < 4; ++u)
-#pragma unroll
-                for (int k = 0; k < EPT; ++k) v[k] += t[u][k];
         }
         if (w_post) {
             float ss = 0.f;

@@ -128,23 +128,35 @@ __host__ __device__ constexpr uint32_t umma_idesc(int m, int n) {
            ((uint32_t)(m >> 4) << 24);
 }
 
+// The activation of the gated epilogue.  Its result is rounded to bfloat16
+// (relative step 2^-8), so the hardware tanh (relative error about 2^-11) serves.
 __device__ __forceinline__ float gelu_tanh_fast(float t) {
     const float u = 0.7978845608028654f * (t + 0.044715f * t * t * t);
-    return 0.5f * t * (1.0f + tanhf(u));
+    float th;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(u));
+    return 0.5f * t * (1.0f + th);
 }
 __device__ __forceinline__ float silu_fast(float t) { return t / (1.0f + __expf(-t)); }
 
-template <int BN, bool GATED>
+// MODE 0: plain.  MODE 1: gated, gate and up tiles of 128 rows each with an
+// accumulator of their own (prompts).  MODE 2: gated, 64 gate rows and the 64 up
+// rows of the same features share one 128-row tile and one accumulator, and the
+// epilogue warps exchange the halves through shared memory (decoding: twice as
+// many CTAs stream the weights).
+template <int BN, int MODE>
 struct Tile {
+    static constexpr bool DUAL = MODE == 1;
+    static constexpr bool HALF = MODE == 2;
     static constexpr int A_BYTES = TILE_M * TILE_K * 2;                 // 16 KB
     static constexpr int B_BYTES = BN * TILE_K * 2;
-    static constexpr int STAGE_BYTES = A_BYTES * (GATED ? 2 : 1) + B_BYTES;
-    static constexpr int BUDGET = GATED ? 196 * 1024 : (BN >= 256 ? 196 * 1024 : 108 * 1024);
-    static constexpr int STAGES_RAW = BUDGET / STAGE_BYTES;
+    static constexpr int STAGE_BYTES = A_BYTES * (DUAL ? 2 : 1) + B_BYTES;
+    static constexpr int XCHG_BYTES = HALF ? 64 * BN * 4 : 0;
+    static constexpr int BUDGET = DUAL ? 196 * 1024 : (BN >= 256 ? 196 * 1024 : 108 * 1024);
+    static constexpr int STAGES_RAW = (BUDGET - XCHG_BYTES) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : (STAGES_RAW < 2 ? 2 : STAGES_RAW);
-    static constexpr int TMEM_COLS_RAW = GATED ? 2 * BN : BN;
+    static constexpr int TMEM_COLS_RAW = DUAL ? 2 * BN : BN;
     static constexpr int TMEM_COLS = TMEM_COLS_RAW < 32 ? 32 : TMEM_COLS_RAW;
-    static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+    static constexpr int SMEM = STAGES * STAGE_BYTES + XCHG_BYTES + 1024 /*align*/ + 256;
 };
 
 // out element types
@@ -154,23 +166,26 @@ template <> __device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat
     *p = __float2bfloat16_rn(v);
 }
 
-template <int BN, bool GATED, typename TO>
+template <int BN, int MODE, typename TO>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_w2,
                     const __grid_constant__ CUtensorMap map_x, TO* __restrict__ out, int T, int N,
                     int K, long long ldc, long long split_stride, int kb_per_split, int act) {
-    using TL = Tile<BN, GATED>;
+    using TL = Tile<BN, MODE>;
+    constexpr bool GATED = MODE == 1;          // two accumulators
+    constexpr bool HALF = MODE == 2;           // gate and up rows in one tile
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint64_t* full = (uint64_t*)(smem + TL::STAGES * TL::STAGE_BYTES);
+    float* xchg = (float*)(smem + TL::STAGES * TL::STAGE_BYTES);
+    uint64_t* full = (uint64_t*)(smem + TL::STAGES * TL::STAGE_BYTES + TL::XCHG_BYTES);
     uint64_t* empty = full + TL::STAGES;
     uint64_t* acc_full = empty + TL::STAGES;
     uint32_t* tmem_slot = (uint32_t*)(acc_full + 1);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.x * TILE_M;          // first weight row (output feature)
+    const int m0 = blockIdx.x * (HALF ? TILE_M / 2 : TILE_M);   // first output feature
     const int n0 = blockIdx.y * BN;              // first token
     const int kb_total = (K + TILE_K - 1) / TILE_K;
     const int kb_begin = blockIdx.z * kb_per_split;
@@ -215,6 +230,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
             const int kx = (kb_begin + i) * TILE_K;
             tma_load_2d(st, &map_w, kx, m0, &full[s]);
             if (GATED) tma_load_2d(st + TL::A_BYTES, &map_w2, kx, m0, &full[s]);
+            if (HALF) tma_load_2d(st + TL::A_BYTES / 2, &map_w2, kx, m0, &full[s]);
             tma_load_2d(st + TL::A_BYTES * (GATED ? 2 : 1), &map_x, kx, n0, &full[s]);
             ++issued;
         }
@@ -256,16 +272,53 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
     } else if (warp >= 2) {
         // ------------------------------------------------------------ epilogue
         const int quarter = warp & 3;
-        const int f = m0 + quarter * 32 + lane;           // this thread's output feature
+        // this thread's output feature (in the shared-tile form lanes 64-127 hold the
+        // up rows of the features whose gate rows lanes 0-63 hold)
+        const int f = HALF ? m0 + (quarter & 1) * 32 + lane : m0 + quarter * 32 + lane;
         bool ok = mbar_wait(acc_full, 0);
         if (!ok) {
             atomicCAS(&g_gemm_status, 0, (3 << 8));
             *abort_flag = 1;
         }
         tc_fence_after();
-        if (ok && !*abort_flag && n_kb > 0) {
-            const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
-            TO* obase = out + (size_t)blockIdx.z * split_stride;
+        const bool run = ok && !*abort_flag && n_kb > 0;
+        const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        TO* obase = out + (size_t)blockIdx.z * split_stride;
+        if (HALF) {
+            // up half -> shared memory, then the gate half combines and stores
+            if (run && quarter >= 2) {
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 16) {
+                    uint32_t u[16];
+                    tc_ld16(lane_base + c, u);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        xchg[(c + j) * 64 + (quarter & 1) * 32 + lane] = __uint_as_float(u[j]);
+                }
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");       // the four epilogue warps
+            if (run && quarter < 2) {
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 16) {
+                    uint32_t r[16];
+                    tc_ld16(lane_base + c, r);
+                    tc_wait_ld();
+                    if (f < N) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int n = n0 + c + j;
+                            if (n < T) {
+                                const float gv = __uint_as_float(r[j]);
+                                const float uv = xchg[(c + j) * 64 + quarter * 32 + lane];
+                                store_out<TO>(obase + (size_t)n * ldc + f,
+                                              (act == 1 ? silu_fast(gv) : gelu_tanh_fast(gv)) * uv);
+                            }
+                        }
+                    }
+                }
+            }
+        } else if (run) {
 #pragma unroll 1
             for (int c = 0; c < BN; c += 16) {
                 uint32_t r[16], u[16];
@@ -353,19 +406,20 @@ int make_map(CUtensorMap* out, const void* ptr, long long rows, long long K, lon
     return 0;
 }
 
-template <int BN, bool GATED, typename TO>
+template <int BN, int MODE, typename TO>
 int launch(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx, void* out, int T,
            int N, int K, long long ldc, long long split_stride, int splits, int kb_per_split,
            int act, cudaStream_t stream) {
-    using TL = Tile<BN, GATED>;
-    auto kern = gemm_tcgen05_kernel<BN, GATED, TO>;
+    using TL = Tile<BN, MODE>;
+    auto kern = gemm_tcgen05_kernel<BN, MODE, TO>;
     static bool configured = false;
     if (!configured) {
         AGV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          TL::SMEM));
         configured = true;
     }
-    dim3 grid((N + TILE_M - 1) / TILE_M, (T + BN - 1) / BN, splits);
+    constexpr int rows_per_cta = MODE == 2 ? TILE_M / 2 : TILE_M;
+    dim3 grid((N + rows_per_cta - 1) / rows_per_cta, (T + BN - 1) / BN, splits);
     AGV_REQUIRE(grid.y <= 65535, "linear: %d tokens exceed the grid limit", T);
     kern<<<grid, GEMM_THREADS, TL::SMEM, stream>>>(mw, mw2, mx, (TO*)out, T, N, K, ldc,
                                                    split_stride, kb_per_split, act);
@@ -373,23 +427,23 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx,
     return 0;
 }
 
-template <bool GATED, typename TO>
+template <int MODE, typename TO>
 int launch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx,
               void* out, int T, int N, int K, long long ldc, long long split_stride, int splits,
               int kb_per_split, int act, cudaStream_t stream) {
 #define AGV_BN_CASE(B)                                                                          \
     case B:                                                                                      \
-        return launch<B, GATED, TO>(mw, mw2, mx, out, T, N, K, ldc, split_stride, splits,        \
-                                    kb_per_split, act, stream)
+        return launch<B, MODE, TO>(mw, mw2, mx, out, T, N, K, ldc, split_stride, splits,         \
+                                   kb_per_split, act, stream)
     switch (bn) {
         AGV_BN_CASE(16);
         AGV_BN_CASE(32);
         AGV_BN_CASE(64);
         AGV_BN_CASE(128);
         case 256:
-            if constexpr (!GATED)
-                return launch<256, false, TO>(mw, mw2, mx, out, T, N, K, ldc, split_stride, splits,
-                                              kb_per_split, act, stream);
+            if constexpr (MODE == 0)
+                return launch<256, 0, TO>(mw, mw2, mx, out, T, N, K, ldc, split_stride, splits,
+                                          kb_per_split, act, stream);
     }
 #undef AGV_BN_CASE
     return agv_fail(-1, "linear: no kernel for a token tile of %d", bn);
@@ -427,10 +481,12 @@ AGV_API int agv_linear_tc(const void* x, const void* w, const void* w2, void* ou
     if (splits > kb_total) splits = kb_total;
     const int kb_per = (kb_total + splits - 1) / splits;
     splits = (kb_total + kb_per - 1) / kb_per;       // no empty split
+    // decoding through a gated layer: gate and up rows share a tile (see Tile)
+    const bool half = w2 && T <= 64;
     CUtensorMap mw, mw2, mx;
-    if (int rc = make_map(&mw, w, N, K, K, TILE_M)) return rc;
+    if (int rc = make_map(&mw, w, N, K, K, half ? TILE_M / 2 : TILE_M)) return rc;
     if (w2) {
-        if (int rc = make_map(&mw2, w2, N, K, K, TILE_M)) return rc;
+        if (int rc = make_map(&mw2, w2, N, K, K, half ? TILE_M / 2 : TILE_M)) return rc;
     } else {
         mw2 = mw;
     }
@@ -438,14 +494,17 @@ AGV_API int agv_linear_tc(const void* x, const void* w, const void* w2, void* ou
     const long long split_stride = (long long)T * ldc;
     if (w2) {
         AGV_REQUIRE(out_dtype == AGV_BF16, "linear: the gated form writes bfloat16");
-        return launch_bn<true, __nv_bfloat16>(bn, mw, mw2, mx, out, T, N, K, ldc, 0, 1, kb_total,
-                                              act, stream);
+        if (half)
+            return launch_bn<2, __nv_bfloat16>(bn, mw, mw2, mx, out, T, N, K, ldc, 0, 1, kb_total,
+                                               act, stream);
+        return launch_bn<1, __nv_bfloat16>(bn, mw, mw2, mx, out, T, N, K, ldc, 0, 1, kb_total,
+                                           act, stream);
     }
     if (out_dtype == AGV_BF16)
-        return launch_bn<false, __nv_bfloat16>(bn, mw, mw2, mx, out, T, N, K, ldc, 0, 1, kb_total,
-                                               act, stream);
+        return launch_bn<0, __nv_bfloat16>(bn, mw, mw2, mx, out, T, N, K, ldc, 0, 1, kb_total,
+                                           act, stream);
     if (out_dtype == AGV_F32)
-        return launch_bn<false, float>(bn, mw, mw2, mx, out, T, N, K, ldc, split_stride, splits,
+        return launch_bn<0, float>(bn, mw, mw2, mx, out, T, N, K, ldc, split_stride, splits,
                                        kb_per, act, stream);
     return agv_fail(-1, "linear: unknown output dtype %d", out_dtype);
 }

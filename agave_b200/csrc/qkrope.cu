@@ -43,6 +43,18 @@ qk_norm_rope_store_kernel(T* __restrict__ qkv, long long row_stride,
     T* src = qkv + (size_t)t * row_stride + (size_t)head * hd;
     const bool is_q = head < nh, is_k = !is_q && head < nh + nkv;
     const float* w = is_q ? wq : (is_k ? wk : nullptr);
+    // where the row goes in the cache: these loads depend on one another, so they
+    // start now and overlap the arithmetic below
+    const bool stores = !is_q && cw.k_pool;
+    int c_pos = 0, c_slot = -1, c_len = 0, c_page = 0;
+    if (stores) {
+        const int cb = cw.seq_index[t];
+        c_pos = positions[t];
+        c_slot = cw.slots[cb];
+        c_len = cw.lens[cb];
+        if (c_slot >= 0)
+            c_page = cw.page_table[(size_t)c_slot * cw.max_pages + (c_pos % cw.cap) / cw.page];
+    }
 
     float ss = 0.f;
     if (part) {
@@ -102,14 +114,11 @@ qk_norm_rope_store_kernel(T* __restrict__ qkv, long long row_stride,
         __syncwarp();
         for (int e = lane; e < hd; e += 32) src[e] = from_f32<T>(buf[e]);
     }
-    if (is_q || !cw.k_pool) return;
-    const int b = cw.seq_index[t];
-    const int slot = cw.slots[b];
-    if (slot < 0) return;
-    const int p = positions[t];
-    if (p < cw.lens[b] - cw.cap) return;
+    if (!stores || c_slot < 0) return;
+    const int p = c_pos;
+    if (p < c_len - cw.cap) return;
     const int row = p % cw.cap;
-    const int page = cw.page_table[(size_t)slot * cw.max_pages + row / cw.page];
+    const int page = c_page;
     const int g = is_k ? head - nh : head - nh - nkv;
     T* pool = (T*)(is_k ? cw.k_pool : cw.v_pool);
     T* dst = pool + (((size_t)page * cw.page + row % cw.page) * nkv + g) * hd;
@@ -137,6 +146,7 @@ AGV_API int agv_qk_norm_rope_store(void* qkv, int dtype, long long row_stride, c
     AGV_REQUIRE(!k_pool || (v_pool && page_table && slots && lens && seq_index && page > 0 &&
                             cap > 0 && max_pages > 0), "qk_norm_rope: incomplete cache arguments");
     AGV_REQUIRE(!cosv || (sinv && positions), "qk_norm_rope: cos without sin or positions");
+    AGV_REQUIRE(!k_pool || positions, "qk_norm_rope: the cache store needs positions");
     AGV_REQUIRE(!part || n_splits >= 1, "qk_norm_rope: partial sums need n_splits >= 1");
     if (n_tokens == 0) return 0;
     const long long split_stride = (long long)n_tokens * (nh + 2 * nkv) * hd;

@@ -20,47 +20,83 @@ constexpr int SM_THREADS = 1024;
 constexpr double FIX_ONE = 1099511627776.0;    // 2^40
 
 // ----------------------------------------------------------------- arg max
-__global__ void __launch_bounds__(SM_THREADS)
-argmax_kernel(const float* __restrict__ logits, long long row_stride, int V, int* __restrict__ out) {
+// Two stages so that a few rows still fill the GPU: AM_PARTS CTAs per row each
+// find (greatest value, first index) over a slice, the CTA that finishes last for
+// a row reduces the slices.  Ties go to the lowest index in both stages.
+constexpr int AM_PARTS = 64;
+constexpr int AM_THREADS = 256;
+constexpr int AM_MAX_ROWS = 4096;
+__device__ float g_am_val[AM_MAX_ROWS * AM_PARTS];
+__device__ int g_am_idx[AM_MAX_ROWS * AM_PARTS];
+__device__ int g_am_count[AM_MAX_ROWS];       // zero between launches
+
+__device__ __forceinline__ void am_better(float& best, int& idx, float ov, int oi) {
+    if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
+}
+
+__global__ void __launch_bounds__(AM_THREADS)
+argmax_kernel(const float* __restrict__ logits, long long row_stride, int V, int* __restrict__ out,
+              int row0) {
     __shared__ float sv[32];
     __shared__ int si[32];
-    const float* row = logits + (size_t)blockIdx.x * row_stride;
+    __shared__ int s_last;
+    const int row = blockIdx.y, part = blockIdx.x;
+    const float* src = logits + (size_t)(row0 + row) * row_stride;
+    const int per = (V + AM_PARTS - 1) / AM_PARTS;
+    const int lo = part * per, hi = min(V, lo + per);
     float best = -INFINITY;
     int idx = 0x7fffffff;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-        const float v = row[i];
-        if (v > best || (v == best && i < idx)) { best = v; idx = i; }
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
-        if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
-    }
+    for (int i = lo + threadIdx.x; i < hi; i += AM_THREADS) am_better(best, idx, src[i], i);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+        am_better(best, idx, __shfl_xor_sync(0xffffffffu, best, o),
+                  __shfl_xor_sync(0xffffffffu, idx, o));
     if (lane == 0) { sv[warp] = best; si[warp] = idx; }
     __syncthreads();
     if (warp == 0) {
-        const int nw = (blockDim.x + 31) >> 5;
-        best = lane < nw ? sv[lane] : -INFINITY;
-        idx = lane < nw ? si[lane] : 0x7fffffff;
+        best = lane < AM_THREADS / 32 ? sv[lane] : -INFINITY;
+        idx = lane < AM_THREADS / 32 ? si[lane] : 0x7fffffff;
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
-            if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
+        for (int o = 16; o > 0; o >>= 1)
+            am_better(best, idx, __shfl_xor_sync(0xffffffffu, best, o),
+                      __shfl_xor_sync(0xffffffffu, idx, o));
+        if (lane == 0) {
+            g_am_val[row * AM_PARTS + part] = best;
+            g_am_idx[row * AM_PARTS + part] = idx;
+            __threadfence();
+            s_last = atomicAdd(&g_am_count[row], 1) == AM_PARTS - 1;
         }
-        if (lane == 0) out[blockIdx.x] = idx == 0x7fffffff ? 0 : idx;
+    }
+    __syncthreads();
+    if (!s_last || warp != 0) return;
+    __threadfence();
+    best = -INFINITY;
+    idx = 0x7fffffff;
+    for (int i = lane; i < AM_PARTS; i += 32)
+        am_better(best, idx, __ldcg(&g_am_val[row * AM_PARTS + i]),
+                  __ldcg(&g_am_idx[row * AM_PARTS + i]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+        am_better(best, idx, __shfl_xor_sync(0xffffffffu, best, o),
+                  __shfl_xor_sync(0xffffffffu, idx, o));
+    if (lane == 0) {
+        out[row0 + row] = idx == 0x7fffffff ? 0 : idx;
+        g_am_count[row] = 0;
     }
 }
 
-// out[b] = first index of the greatest logits[b, :].
+// out[b] = first index of the greatest logits[b, :].  Calls on different streams
+// must not overlap: the stages share one table of partial results.
 AGV_API int agv_argmax(const float* logits, long long row_stride, int B, int V, int* out,
                        cudaStream_t stream) {
     AGV_REQUIRE(B >= 0 && V > 0 && row_stride >= V, "argmax: bad sizes B=%d V=%d", B, V);
-    if (B == 0) return 0;
-    argmax_kernel<<<B, SM_THREADS, 0, stream>>>(logits, row_stride, V, out);
-    AGV_LAUNCH_OK("argmax_kernel");
+    for (int row0 = 0; row0 < B; row0 += AM_MAX_ROWS) {
+        const int rows = B - row0 < AM_MAX_ROWS ? B - row0 : AM_MAX_ROWS;
+        argmax_kernel<<<dim3(AM_PARTS, rows), AM_THREADS, 0, stream>>>(logits, row_stride, V, out,
+                                                                      row0);
+        AGV_LAUNCH_OK("argmax_kernel");
+    }
     return 0;
 }
 
