@@ -173,6 +173,8 @@ __device__ __forceinline__ void finish_split(const DecodeArgs& a, int b, int h0,
 template <typename T>
 __global__ void __launch_bounds__(AD_THREADS)
 attention_decode_split_kernel(DecodeArgs a) {
+    pdl_wait();
+    pdl_launch_next();
     constexpr int VEC = Vec16<T>::N;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ int s_last;
@@ -345,6 +347,8 @@ __device__ __forceinline__ int dm_swz(int row, int chunk) {
 template <int HDP>
 __global__ void __launch_bounds__(DM_THREADS)
 attention_decode_mma_kernel(DecodeArgs a) {
+    pdl_wait();
+    pdl_launch_next();
     typedef __nv_bfloat16 T;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ int s_last;
@@ -505,7 +509,7 @@ int launch_decode_mma(const DecodeArgs& a, int B, cudaStream_t stream) {
     }
     const int G = a.nh / a.nkv;
     dim3 grid(a.n_splits, a.nkv * ((G + DM_HEADS - 1) / DM_HEADS), B);
-    kern<<<grid, DM_THREADS, smem, stream>>>(a);
+    agv_launch(kern, grid, DM_THREADS, smem, stream, a);
     AGV_LAUNCH_OK("attention_decode_mma_kernel");
     return 0;
 }
@@ -587,7 +591,7 @@ AGV_API int agv_attention_decode(const void* q, long long q_stride, void* out, i
                                              AD_MAX_SMEM));
             configured = true;
         }
-        kern<<<grid, AD_THREADS, smem, stream>>>(a);
+        agv_launch(kern, grid, AD_THREADS, smem, stream, a);
     } else {
         auto kern = attention_decode_split_kernel<__nv_bfloat16>;
         static bool configured = false;
@@ -596,7 +600,7 @@ AGV_API int agv_attention_decode(const void* q, long long q_stride, void* out, i
                                              AD_MAX_SMEM));
             configured = true;
         }
-        kern<<<grid, AD_THREADS, smem, stream>>>(a);
+        agv_launch(kern, grid, AD_THREADS, smem, stream, a);
     }
     AGV_LAUNCH_OK("attention_decode_split_kernel");
     return 0;

@@ -84,6 +84,8 @@ attention_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_st
                              const __nv_bfloat16* __restrict__ v, long long kv_stride,
                              __nv_bfloat16* __restrict__ out, const int* __restrict__ cu_seqlens,
                              int nh, int nkv, int hd, float scale_log2e, int window) {
+    pdl_wait();
+    pdl_launch_next();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);
     __nv_bfloat16* Ks = Qs + 64 * HDP;
@@ -236,8 +238,7 @@ int launch_fa(const void* q, long long q_stride, const void* k, const void* v, l
         configured = true;
     }
     dim3 grid((max_len + FA_M - 1) / FA_M, nh, B);
-    kern<<<grid, FA_THREADS, smem, stream>>>(
-        (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v,
+    agv_launch(kern, grid, FA_THREADS, smem, stream, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v,
         kv_stride, (__nv_bfloat16*)out, cu_seqlens, nh, nkv, hd,
         scale * 1.4426950408889634f, window);
     AGV_LAUNCH_OK("attention_prefill_mma_kernel");

@@ -30,6 +30,8 @@ attention_simt_kernel(const T* __restrict__ q, long long q_stride, const T* __re
                       const int* __restrict__ positions, const int* __restrict__ seq_index,
                       const int* __restrict__ cu_seqlens, PagedKV pk, int n_tokens, int nh, int nkv,
                       int hd, float scale, int window) {
+    pdl_wait();
+    pdl_launch_next();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long item = (long long)blockIdx.x * AT_WARPS + warp;
     if (item >= (long long)n_tokens * nh) return;
@@ -119,12 +121,10 @@ AGV_API int agv_attention_prefill_simt(const void* q, long long q_stride, const 
     const unsigned grid = (unsigned)((items + AT_WARPS - 1) / AT_WARPS);
     PagedKV pk{};
     if (dtype == AGV_F32)
-        attention_simt_kernel<float, false><<<grid, AT_WARPS * 32, 0, stream>>>(
-            (const float*)q, q_stride, (const float*)k, (const float*)v, kv_stride, (float*)out,
+        agv_launch(attention_simt_kernel<float, false>, grid, AT_WARPS * 32, 0, stream, (const float*)q, q_stride, (const float*)k, (const float*)v, kv_stride, (float*)out,
             positions, seq_index, cu_seqlens, pk, n_tokens, nh, nkv, hd, scale, window);
     else if (dtype == AGV_BF16)
-        attention_simt_kernel<__nv_bfloat16, false><<<grid, AT_WARPS * 32, 0, stream>>>(
-            (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v,
+        agv_launch(attention_simt_kernel<__nv_bfloat16, false>, grid, AT_WARPS * 32, 0, stream, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v,
             kv_stride, (__nv_bfloat16*)out, positions, seq_index, cu_seqlens, pk, n_tokens, nh,
             nkv, hd, scale, window);
     else
@@ -151,12 +151,10 @@ AGV_API int agv_attention_paged_simt(const void* q, long long q_stride, void* ou
     const unsigned grid = (unsigned)((items + AT_WARPS - 1) / AT_WARPS);
     PagedKV pk{k_pool, v_pool, page_table, slots, max_pages, page, cap};
     if (dtype == AGV_F32)
-        attention_simt_kernel<float, true><<<grid, AT_WARPS * 32, 0, stream>>>(
-            (const float*)q, q_stride, nullptr, nullptr, 0, (float*)out, positions, seq_index,
+        agv_launch(attention_simt_kernel<float, true>, grid, AT_WARPS * 32, 0, stream, (const float*)q, q_stride, nullptr, nullptr, 0, (float*)out, positions, seq_index,
             nullptr, pk, n_tokens, nh, nkv, hd, scale, window);
     else if (dtype == AGV_BF16)
-        attention_simt_kernel<__nv_bfloat16, true><<<grid, AT_WARPS * 32, 0, stream>>>(
-            (const __nv_bfloat16*)q, q_stride, nullptr, nullptr, 0, (__nv_bfloat16*)out, positions,
+        agv_launch(attention_simt_kernel<__nv_bfloat16, true>, grid, AT_WARPS * 32, 0, stream, (const __nv_bfloat16*)q, q_stride, nullptr, nullptr, 0, (__nv_bfloat16*)out, positions,
             seq_index, nullptr, pk, n_tokens, nh, nkv, hd, scale, window);
     else
         return agv_fail(-1, "attention: unknown dtype %d", dtype);

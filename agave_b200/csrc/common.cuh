@@ -9,6 +9,7 @@
 #include <stdint.h>
 #include <stdio.h>
 #include <stdarg.h>
+#include <utility>
 
 #define AGV_API extern "C" __attribute__((visibility("default")))
 
@@ -37,6 +38,37 @@ int agv_fail(int code, const char* fmt, ...);
     } while (0)
 
 static inline bool agv_aligned(const void* p, size_t a) { return ((uintptr_t)p % a) == 0; }
+
+// ------------------------------------------------- programmatic dependent launch
+// Every kernel is launched so that it may start while the kernel before it on
+// the stream is still draining: its CTAs are scheduled and run whatever does not
+// depend on earlier results, then pdl_wait() blocks until the earlier kernel has
+// finished and its writes are visible.  No kernel touches global memory before
+// its pdl_wait().  pdl_launch_next() lets the kernel after this one be scheduled.
+__device__ __forceinline__ void pdl_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_launch_next() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+extern int g_agv_pdl;      // 1: launches carry the programmatic-serialization attribute
+
+template <typename... KArgs, typename... Args>
+inline void agv_launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                       cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = g_agv_pdl ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    (void)cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);   // error: cudaGetLastError
+}
 
 // ---------------------------------------------------------------- element types
 __device__ __forceinline__ float to_f32(float v) { return v; }

@@ -13,6 +13,8 @@
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
                              float* __restrict__ out, int H, int V, float scale) {
+    pdl_wait();
+    pdl_launch_next();
     const int t = blockIdx.x;
     int tok = tokens[t];
     if (tok < 0 || tok >= V) tok = 0;   // callers validate ids; never read outside the table
@@ -27,9 +29,9 @@ AGV_API int agv_embed(const int* tokens, const void* table, int table_dtype, flo
     if (T == 0) return 0;
     const int threads = H >= 1024 ? 256 : 128;
     if (table_dtype == AGV_F32)
-        embed_kernel<float><<<T, threads, 0, stream>>>(tokens, (const float*)table, out, H, V, scale);
+        agv_launch(embed_kernel<float>, T, threads, 0, stream, tokens, (const float*)table, out, H, V, scale);
     else if (table_dtype == AGV_BF16)
-        embed_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>(tokens, (const __nv_bfloat16*)table,
+        agv_launch(embed_kernel<__nv_bfloat16>, T, threads, 0, stream, tokens, (const __nv_bfloat16*)table,
                                                                out, H, V, scale);
     else
         return agv_fail(-1, "embed: unknown dtype %d", table_dtype);
@@ -41,6 +43,8 @@ AGV_API int agv_embed(const int* tokens, const void* table, int table_dtype, flo
 __global__ void rope_table_kernel(const int* __restrict__ positions, float* __restrict__ cosv,
                                   float* __restrict__ sinv, int T, int half, double log_theta,
                                   double inv_factor, int rotary_dim) {
+    pdl_wait();
+    pdl_launch_next();
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= T * half) return;
     const int t = idx / half, i = idx % half;
@@ -60,7 +64,7 @@ AGV_API int agv_rope_table(const int* positions, float* cosv, float* sinv, int T
     AGV_REQUIRE(theta > 0 && factor > 0, "rope_table: theta and factor must be positive");
     if (T == 0) return 0;
     const int half = rotary_dim / 2, n = T * half;
-    rope_table_kernel<<<(n + 127) / 128, 128, 0, stream>>>(positions, cosv, sinv, T, half,
+    agv_launch(rope_table_kernel, (n + 127) / 128, 128, 0, stream, positions, cosv, sinv, T, half,
                                                            log(theta), 1.0 / factor, rotary_dim);
     AGV_LAUNCH_OK("rope_table_kernel");
     return 0;
@@ -76,6 +80,8 @@ __global__ void norm_residual_kernel(float* __restrict__ h, const TY* __restrict
                                      const float* __restrict__ w_next, TX* __restrict__ x,
                                      const int* __restrict__ rows, int H, float eps_post,
                                      float eps_next, int add_residual) {
+    pdl_wait();
+    pdl_launch_next();
     extern __shared__ float row[];
     __shared__ float red[33];
     const int r = blockIdx.x;
@@ -138,6 +144,8 @@ norm_residual_small_kernel(float* __restrict__ h, const TY* __restrict__ y, int 
                            const float* __restrict__ w_next, TX* __restrict__ x,
                            const int* __restrict__ rows, int H, float eps_post, float eps_next,
                            int add_residual) {
+    pdl_wait();
+    pdl_launch_next();
     __shared__ float red[33];
     const int r = blockIdx.x;
     const size_t src = (size_t)(rows ? rows[r] : r) * H;
@@ -230,7 +238,7 @@ static int launch_norm(float* h, const void* y, int n_splits, size_t split_strid
         const int threads = H <= 256 ? 128 : H <= 1024 ? 512 : 1024;
         const int ept = (H + threads - 1) / threads;
 #define AGV_SMALL(E)                                                                            \
-    norm_residual_small_kernel<TY, TX, E><<<R, threads, 0, stream>>>(                           \
+    agv_launch(norm_residual_small_kernel<TY, TX, E>, R, threads, 0, stream, \
         h, (const TY*)y, n_splits, split_stride, w_post, w_next, (TX*)x, rows, H, eps_post,     \
         eps_next, add_residual)
         if (ept <= 1) AGV_SMALL(1);
@@ -250,7 +258,7 @@ static int launch_norm(float* h, const void* y, int n_splits, size_t split_strid
                                          (int)smem));
     }
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
-    kern<<<R, threads, smem, stream>>>(h, (const TY*)y, n_splits, split_stride, w_post, w_next,
+    agv_launch(kern, R, threads, smem, stream, h, (const TY*)y, n_splits, split_stride, w_post, w_next,
                                        (TX*)x, rows, H, eps_post, eps_next, add_residual);
     AGV_LAUNCH_OK("norm_residual_kernel");
     return 0;

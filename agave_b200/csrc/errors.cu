@@ -4,6 +4,16 @@
 
 static thread_local char g_msg[1024] = "";
 
+int g_agv_pdl = 1;
+
+// Turns programmatic dependent launch of this library's kernels on (1) or off (0);
+// returns the previous setting.
+AGV_API int agv_set_dependent_launch(int on) {
+    const int old = g_agv_pdl;
+    g_agv_pdl = on ? 1 : 0;
+    return old;
+}
+
 int agv_fail(int code, const char* fmt, ...) {
     va_list ap;
     va_start(ap, fmt);

@@ -29,6 +29,8 @@ template <typename TA, typename TW, typename TO, bool GATED>
 __global__ void __launch_bounds__(256)
 gemm_tn_kernel(const TA* __restrict__ A, const TW* __restrict__ W, const TW* __restrict__ W2,
                TO* __restrict__ C, int M, int N, int K, long long lda, long long ldc, int act) {
+    pdl_wait();
+    pdl_launch_next();
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
     __shared__ float Us[GATED ? BK : 1][GATED ? BN + 4 : 1];
@@ -90,11 +92,9 @@ static int launch_gemm(const void* A, const void* W, const void* W2, void* C, in
                        long long lda, long long ldc, int act, cudaStream_t stream) {
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     if (W2)
-        gemm_tn_kernel<TA, TW, TO, true><<<grid, 256, 0, stream>>>(
-            (const TA*)A, (const TW*)W, (const TW*)W2, (TO*)C, M, N, K, lda, ldc, act);
+        agv_launch(gemm_tn_kernel<TA, TW, TO, true>, grid, 256, 0, stream, (const TA*)A, (const TW*)W, (const TW*)W2, (TO*)C, M, N, K, lda, ldc, act);
     else
-        gemm_tn_kernel<TA, TW, TO, false><<<grid, 256, 0, stream>>>(
-            (const TA*)A, (const TW*)W, nullptr, (TO*)C, M, N, K, lda, ldc, act);
+        agv_launch(gemm_tn_kernel<TA, TW, TO, false>, grid, 256, 0, stream, (const TA*)A, (const TW*)W, nullptr, (TO*)C, M, N, K, lda, ldc, act);
     AGV_LAUNCH_OK("gemm_tn_kernel");
     return 0;
 }

@@ -172,6 +172,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_w2,
                     const __grid_constant__ CUtensorMap map_x, TO* __restrict__ out, int T, int N,
                     int K, long long ldc, long long split_stride, int kb_per_split, int act) {
+    pdl_wait();
+    pdl_launch_next();
     using TL = Tile<BN, MODE>;
     constexpr bool GATED = MODE == 1;          // two accumulators
     constexpr bool HALF = MODE == 2;           // gate and up rows in one tile
@@ -212,6 +214,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_wait();          // barriers and tensor memory are set up; now the operands must be ready
 
     if (warp == 0 && lane == 0) {
         // ------------------------------------------------------------ loader
@@ -421,7 +424,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx,
     constexpr int rows_per_cta = MODE == 2 ? TILE_M / 2 : TILE_M;
     dim3 grid((N + rows_per_cta - 1) / rows_per_cta, (T + BN - 1) / BN, splits);
     AGV_REQUIRE(grid.y <= 65535, "linear: %d tokens exceed the grid limit", T);
-    kern<<<grid, GEMM_THREADS, TL::SMEM, stream>>>(mw, mw2, mx, (TO*)out, T, N, K, ldc,
+    agv_launch(kern, grid, GEMM_THREADS, TL::SMEM, stream, mw, mw2, mx, (TO*)out, T, N, K, ldc,
                                                    split_stride, kb_per_split, act);
     AGV_LAUNCH_OK("gemm_tcgen05_kernel");
     return 0;

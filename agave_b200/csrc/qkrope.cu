@@ -33,6 +33,8 @@ qk_norm_rope_store_kernel(T* __restrict__ qkv, long long row_stride,
                           float eps, const float* __restrict__ cosv,
                           const float* __restrict__ sinv, int rotary_half,
                           const int* __restrict__ positions, CacheWrite cw) {
+    pdl_wait();
+    pdl_launch_next();
     extern __shared__ float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads = nh + 2 * nkv;
@@ -125,6 +127,128 @@ qk_norm_rope_store_kernel(T* __restrict__ qkv, long long row_stride,
     for (int e = lane; e < hd; e += 32) dst[e] = from_f32<T>(buf[e]);
 }
 
+// The same for head sizes that are multiples of 64 up to 256 with the whole head
+// rotated: a lane keeps its NE = hd / 32 elements (lane + 32 i) in registers, the
+// partner of element e in the rotation (e + hd / 2) is its own element i + NE / 2,
+// and every load the row needs (partial sums, weights, cos / sin, the chain that
+// finds the cache row) is issued before the first use, so their latencies overlap.
+template <typename T, int NE>
+__global__ void __launch_bounds__(QK_WARPS * 32)
+qk_norm_rope_store_reg_kernel(T* __restrict__ qkv, long long row_stride,
+                              const float* __restrict__ part, int n_splits,
+                              long long split_stride, int n_tokens, int nh, int nkv,
+                              const float* __restrict__ wq, const float* __restrict__ wk, float eps,
+                              const float* __restrict__ cosv, const float* __restrict__ sinv,
+                              const int* __restrict__ positions, CacheWrite cw) {
+    pdl_wait();
+    pdl_launch_next();
+    constexpr int hd = NE * 32, HALF = NE / 2;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int heads = nh + 2 * nkv;
+    const long long item = (long long)blockIdx.x * QK_WARPS + warp;
+    if (item >= (long long)n_tokens * heads) return;
+    const int t = (int)(item / heads), head = (int)(item % heads);
+    T* src = qkv + (size_t)t * row_stride + (size_t)head * hd;
+    const bool is_q = head < nh, is_k = !is_q && head < nh + nkv, is_v = !is_q && !is_k;
+    const float* w = is_q ? wq : (is_k ? wk : nullptr);
+    const bool stores = !is_q && cw.k_pool;
+    // first links of the chain to the cache row
+    int cb = 0, c_pos = 0;
+    if (stores) {
+        cb = cw.seq_index[t];
+        c_pos = positions[t];
+    }
+    // operands of the arithmetic
+    float wv[NE], cs[HALF > 0 ? HALF : 1], sn[HALF > 0 ? HALF : 1], v[NE];
+#pragma unroll
+    for (int i = 0; i < NE; ++i) wv[i] = w ? w[lane + 32 * i] : 1.f;
+    const bool rotate = cosv && !is_v;
+#pragma unroll
+    for (int i = 0; i < HALF; ++i) {
+        cs[i] = rotate ? cosv[(size_t)t * (hd / 2) + lane + 32 * i] : 1.f;
+        sn[i] = rotate ? sinv[(size_t)t * (hd / 2) + lane + 32 * i] : 0.f;
+    }
+    if (part) {
+        const float* ps = part + (size_t)t * (size_t)(heads * hd) + (size_t)head * hd + lane;
+        constexpr int U = NE >= 8 ? 8 : 16;           // ranges of K loaded together
+#pragma unroll
+        for (int i = 0; i < NE; ++i) v[i] = 0.f;
+        for (int s0 = 0; s0 < n_splits; s0 += U) {
+            float tv[U][NE];
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+#pragma unroll
+                for (int i = 0; i < NE; ++i)
+                    tv[u][i] = ps[(size_t)min(s0 + u, n_splits - 1) * split_stride + 32 * i];
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+#pragma unroll
+                for (int i = 0; i < NE; ++i) v[i] += s0 + u < n_splits ? tv[u][i] : 0.f;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < NE; ++i) v[i] = to_f32(src[lane + 32 * i]);
+    }
+    // second and third links
+    int c_slot = -1, c_len = 0, c_page = 0;
+    if (stores) {
+        c_slot = cw.slots[cb];
+        c_len = cw.lens[cb];
+        if (c_slot >= 0)
+            c_page = cw.page_table[(size_t)c_slot * cw.max_pages + (c_pos % cw.cap) / cw.page];
+    }
+    if (!is_v) {
+        if (w) {
+            float ss = 0.f;
+#pragma unroll
+            for (int i = 0; i < NE; ++i) ss += v[i] * v[i];
+            ss = warp_sum(ss);
+            const float r = 1.0f / sqrtf(ss / (float)hd + eps);
+#pragma unroll
+            for (int i = 0; i < NE; ++i) v[i] = v[i] * r * wv[i];
+        }
+        if (rotate) {
+#pragma unroll
+            for (int i = 0; i < HALF; ++i) {
+                const float re = v[i], im = v[i + HALF];
+                v[i] = re * cs[i] - im * sn[i];
+                v[i + HALF] = re * sn[i] + im * cs[i];
+            }
+        }
+    }
+    if (!is_v || part) {
+#pragma unroll
+        for (int i = 0; i < NE; ++i) src[lane + 32 * i] = from_f32<T>(v[i]);
+    }
+    if (!stores || c_slot < 0) return;
+    if (c_pos < c_len - cw.cap) return;
+    const int row = c_pos % cw.cap;
+    const int g = is_k ? head - nh : head - nh - nkv;
+    T* pool = (T*)(is_k ? cw.k_pool : cw.v_pool);
+    T* dst = pool + (((size_t)c_page * cw.page + row % cw.page) * nkv + g) * hd;
+#pragma unroll
+    for (int i = 0; i < NE; ++i) dst[lane + 32 * i] = from_f32<T>(v[i]);
+}
+
+template <typename T>
+static bool launch_qk_reg(T* qkv, long long row_stride, const float* part, int n_splits,
+                          long long split_stride, int n_tokens, int nh, int nkv, int hd,
+                          const float* wq, const float* wk, float eps, const float* cosv,
+                          const float* sinv, int rotary_dim, const int* positions,
+                          const CacheWrite& cw, unsigned grid, cudaStream_t stream) {
+    if (hd % 64 != 0 || hd > 256 || (cosv && rotary_dim != hd)) return false;
+#define AGV_QK_REG(NE)                                                                          \
+    agv_launch(qk_norm_rope_store_reg_kernel<T, NE>, grid, QK_WARPS * 32, 0, stream, qkv,       \
+               row_stride, part, n_splits, split_stride, n_tokens, nh, nkv, wq, wk, eps, cosv,  \
+               sinv, positions, cw)
+    if (hd == 64) AGV_QK_REG(2);
+    else if (hd == 128) AGV_QK_REG(4);
+    else if (hd == 192) AGV_QK_REG(6);
+    else AGV_QK_REG(8);
+#undef AGV_QK_REG
+    return true;
+}
+
 // qkv: [T, nh + 2 nkv, hd] (row stride in elements), rewritten in place: q and k
 // heads normed (if wq / wk given) and rotated (if cos / sin given).  k and v
 // are also written to the layer's cache pools unless k_pool is null.  With
@@ -155,13 +279,25 @@ AGV_API int agv_qk_norm_rope_store(void* qkv, int dtype, long long row_stride, c
     const unsigned grid = (unsigned)((items + QK_WARPS - 1) / QK_WARPS);
     const size_t smem = (size_t)QK_WARPS * hd * sizeof(float);
     const int half = cosv ? rotary_dim / 2 : 0;
+    if (dtype == AGV_F32 &&
+        launch_qk_reg<float>((float*)qkv, row_stride, part, n_splits, split_stride, n_tokens, nh,
+                             nkv, hd, wq, wk, eps, cosv, sinv, rotary_dim, positions, cw, grid,
+                             stream)) {
+        AGV_LAUNCH_OK("qk_norm_rope_store_reg_kernel");
+        return 0;
+    }
+    if (dtype == AGV_BF16 &&
+        launch_qk_reg<__nv_bfloat16>((__nv_bfloat16*)qkv, row_stride, part, n_splits, split_stride,
+                                     n_tokens, nh, nkv, hd, wq, wk, eps, cosv, sinv, rotary_dim,
+                                     positions, cw, grid, stream)) {
+        AGV_LAUNCH_OK("qk_norm_rope_store_reg_kernel");
+        return 0;
+    }
     if (dtype == AGV_F32)
-        qk_norm_rope_store_kernel<float><<<grid, QK_WARPS * 32, smem, stream>>>(
-            (float*)qkv, row_stride, part, n_splits, split_stride, n_tokens, nh, nkv, hd, wq, wk,
+        agv_launch(qk_norm_rope_store_kernel<float>, grid, QK_WARPS * 32, smem, stream, (float*)qkv, row_stride, part, n_splits, split_stride, n_tokens, nh, nkv, hd, wq, wk,
             eps, cosv, sinv, half, positions, cw);
     else if (dtype == AGV_BF16)
-        qk_norm_rope_store_kernel<__nv_bfloat16><<<grid, QK_WARPS * 32, smem, stream>>>(
-            (__nv_bfloat16*)qkv, row_stride, part, n_splits, split_stride, n_tokens, nh, nkv, hd,
+        agv_launch(qk_norm_rope_store_kernel<__nv_bfloat16>, grid, QK_WARPS * 32, smem, stream, (__nv_bfloat16*)qkv, row_stride, part, n_splits, split_stride, n_tokens, nh, nkv, hd,
             wq, wk, eps, cosv, sinv, half, positions, cw);
     else
         return agv_fail(-1, "qk_norm_rope: unknown dtype %d", dtype);

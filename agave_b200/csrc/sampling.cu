@@ -37,6 +37,8 @@ __device__ __forceinline__ void am_better(float& best, int& idx, float ov, int o
 __global__ void __launch_bounds__(AM_THREADS)
 argmax_kernel(const float* __restrict__ logits, long long row_stride, int V, int* __restrict__ out,
               int row0) {
+    pdl_wait();
+    pdl_launch_next();
     __shared__ float sv[32];
     __shared__ int si[32];
     __shared__ int s_last;
@@ -93,7 +95,7 @@ AGV_API int agv_argmax(const float* logits, long long row_stride, int B, int V, 
     AGV_REQUIRE(B >= 0 && V > 0 && row_stride >= V, "argmax: bad sizes B=%d V=%d", B, V);
     for (int row0 = 0; row0 < B; row0 += AM_MAX_ROWS) {
         const int rows = B - row0 < AM_MAX_ROWS ? B - row0 : AM_MAX_ROWS;
-        argmax_kernel<<<dim3(AM_PARTS, rows), AM_THREADS, 0, stream>>>(logits, row_stride, V, out,
+        agv_launch(argmax_kernel, dim3(AM_PARTS, rows), AM_THREADS, 0, stream, logits, row_stride, V, out,
                                                                       row0);
         AGV_LAUNCH_OK("argmax_kernel");
     }
@@ -108,6 +110,8 @@ AGV_API int agv_argmax(const float* logits, long long row_stride, int B, int V, 
 __global__ void history_append_kernel(const int* __restrict__ tokens, const int* __restrict__ slots,
                                       int* __restrict__ hist, int* __restrict__ hist_len, int cap,
                                       int B) {
+    pdl_wait();
+    pdl_launch_next();
     const int b = blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= B) return;
     const int slot = slots[b];
@@ -123,7 +127,7 @@ AGV_API int agv_history_append(const int* tokens, const int* slots, int* hist, i
                                int cap, int B, cudaStream_t stream) {
     AGV_REQUIRE(cap > 0 && B >= 0, "history_append: bad sizes");
     if (B == 0) return 0;
-    history_append_kernel<<<(B + 127) / 128, 128, 0, stream>>>(tokens, slots, hist, hist_len, cap, B);
+    agv_launch(history_append_kernel, (B + 127) / 128, 128, 0, stream, tokens, slots, hist, hist_len, cap, B);
     AGV_LAUNCH_OK("history_append_kernel");
     return 0;
 }
@@ -133,6 +137,8 @@ AGV_API int agv_history_append(const int* tokens, const int* slots, int* hist, i
 __global__ void repeat_penalty_kernel(float* __restrict__ logits, long long row_stride, int V,
                                       const int* __restrict__ slots, const int* __restrict__ hist,
                                       const int* __restrict__ hist_len, int cap, float penalty) {
+    pdl_wait();
+    pdl_launch_next();
     const int b = blockIdx.y;
     const int slot = slots[b];
     if (slot < 0) return;
@@ -163,7 +169,7 @@ AGV_API int agv_repeat_penalty(float* logits, long long row_stride, int B, int V
     AGV_REQUIRE(cap > 0, "repeat_penalty: bad history capacity");
     if (B == 0) return 0;
     dim3 grid((cap + 255) / 256, B);
-    repeat_penalty_kernel<<<grid, 256, 0, stream>>>(logits, row_stride, V, slots, hist, hist_len,
+    agv_launch(repeat_penalty_kernel, grid, 256, 0, stream, logits, row_stride, V, slots, hist, hist_len,
                                                     cap, penalty);
     AGV_LAUNCH_OK("repeat_penalty_kernel");
     return 0;
@@ -236,6 +242,8 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int V,
               int* __restrict__ out, float inv_temperature, int top_k, float top_p,
               unsigned long long seed, const long long* __restrict__ seq_ids,
               const int* __restrict__ steps) {
+    pdl_wait();
+    pdl_launch_next();
     __shared__ SampleShared sh;
     const float* row = logits + (size_t)blockIdx.x * row_stride;
     auto xval = [&](int i) { return row[i] * inv_temperature; };
@@ -321,7 +329,7 @@ AGV_API int agv_sample(const float* logits, long long row_stride, int B, int V, 
     AGV_REQUIRE(temperature > 0.f, "sample: temperature must be positive (0 is arg max)");
     AGV_REQUIRE(top_k >= 0, "sample: top_k must be >= 0");
     if (B == 0) return 0;
-    sample_kernel<<<B, SM_THREADS, 0, stream>>>(logits, row_stride, V, out, 1.0f / temperature,
+    agv_launch(sample_kernel, B, SM_THREADS, 0, stream, logits, row_stride, V, out, 1.0f / temperature,
                                                 top_k, top_p, seed, seq_ids, steps);
     AGV_LAUNCH_OK("sample_kernel");
     return 0;

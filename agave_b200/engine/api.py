@@ -155,6 +155,7 @@ class Engine:
         self.runner = Runner(self.model, max_tokens, max_seq_len, max_batch)
         self.max_seq_len = self.runner.cache.max_seq_len
         self.sampler = Sampler(max_batch, self.device)
+        kernels.prepare_device(self.device)
         self.use_graphs = use_graphs
         self._graphs: Dict[Tuple, _DecodeGraph] = {}
         self.stats: Dict[str, float] = {}

@@ -435,6 +435,11 @@ def _decode_counters(device: torch.device, n: int) -> torch.Tensor:
     return t
 
 
+def prepare_device(device: torch.device) -> None:
+    """Allocate what the kernels share on a device before any graph is recorded."""
+    _decode_counters(device, 65536)
+
+
 def attention_decode_split(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor,
                            v_pool: torch.Tensor, page_table: torch.Tensor, slots: torch.Tensor,
                            positions: torch.Tensor, page: int, cap: int, n_heads: int,

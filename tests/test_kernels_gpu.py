@@ -162,7 +162,9 @@ def test_embed_and_rope_table():
 
 # ------------------------------------------- q/k norm, rotation and cache store
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("nh,nkv,hd,rd", [(3, 1, 16, 16), (6, 2, 48, 32), (4, 4, 80, 80)])
+@pytest.mark.parametrize("nh,nkv,hd,rd", [(3, 1, 16, 16), (6, 2, 48, 32), (4, 4, 80, 80),
+                                          (4, 1, 256, 256), (8, 2, 128, 128), (2, 2, 64, 64),
+                                          (3, 1, 192, 192), (2, 1, 128, 64)])
 def test_qk_norm_rope_store(dtype, nh, nkv, hd, rd):
     from agave_b200 import kernels
     T, PAGE, cap = 11, 4, 8            # a ring of 8 rows in pages of 4
