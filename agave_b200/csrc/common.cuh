@@ -70,6 +70,27 @@ inline void agv_launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t sme
     (void)cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);   // error: cudaGetLastError
 }
 
+// The same with the CTAs grouped into thread-block clusters of cluster_z along z.
+template <typename... KArgs, typename... Args>
+inline void agv_launch_cluster(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                               cudaStream_t stream, unsigned cluster_z, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = g_agv_pdl ? 1 : 0;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = 1;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = cluster_z;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    (void)cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 // ---------------------------------------------------------------- element types
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }

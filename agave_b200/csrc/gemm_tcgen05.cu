@@ -35,6 +35,7 @@ constexpr int TILE_M = 128;        // weight rows per CTA
 constexpr int TILE_K = 64;         // 64 bf16 = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int GEMM_THREADS = 192;
+constexpr int RED_LD = TILE_M + 4;     // row length of a partial tile in shared memory
 constexpr unsigned WAIT_LIMIT = 1u << 22;
 
 __device__ int g_gemm_status = 0;   // 0 ok; else (role << 8) | stage of the first wait that gave up
@@ -110,6 +111,20 @@ __device__ __forceinline__ void tc_wait_ld() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// ---- thread-block clusters: the CTAs that split one tile's K range
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n"
+                 "barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_peer_f32(const float* local, uint32_t rank) {
+    uint32_t remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local)),
+                 "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes
 // (64 bf16), stored with the 128-byte swizzle: 8-row groups lie 1024 bytes
 // apart (stride byte offset), version 1, layout type 2.
@@ -171,8 +186,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_w2,
                     const __grid_constant__ CUtensorMap map_x, TO* __restrict__ out, int T, int N,
-                    int K, long long ldc, long long split_stride, int kb_per_split, int act) {
-    pdl_wait();
+                    int K, long long ldc, long long split_stride, int kb_per_split, int act,
+                    int cluster_reduce) {
     pdl_launch_next();
     using TL = Tile<BN, MODE>;
     constexpr bool GATED = MODE == 1;          // two accumulators
@@ -287,6 +302,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
         const bool run = ok && !*abort_flag && n_kb > 0;
         const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
         TO* obase = out + (size_t)blockIdx.z * split_stride;
+        if (cluster_reduce && ok && !*abort_flag && n_kb <= 0) {
+            // a rank without a range of K contributes zeros
+            float* red = (float*)smem;
+            const int fl = quarter * 32 + lane;
+            for (int c = 0; c < BN; ++c) red[c * RED_LD + fl] = 0.f;
+        }
         if (HALF) {
             // up half -> shared memory, then the gate half combines and stores
             if (run && quarter >= 2) {
@@ -321,6 +342,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
                     }
                 }
             }
+        } else if (run && cluster_reduce) {
+            // this CTA's partial sums -> shared memory [token][feature], for the cluster
+            float* red = (float*)smem;
+            const int fl = quarter * 32 + lane;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 16) {
+                uint32_t r[16];
+                tc_ld16(lane_base + c, r);
+                tc_wait_ld();
+#pragma unroll
+                for (int j = 0; j < 16; ++j) red[(c + j) * RED_LD + fl] = __uint_as_float(r[j]);
+            }
         } else if (run) {
 #pragma unroll 1
             for (int c = 0; c < BN; c += 16) {
@@ -344,6 +377,31 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
                 }
             }
         }
+    }
+    __syncwarp();
+    if (cluster_reduce) {
+        // The gridDim.z CTAs of a cluster hold partial sums of one tile over
+        // consecutive ranges of K.  Each adds, in rank order, a slice of the tile's
+        // features from every peer's shared memory and writes the result; nobody
+        // leaves before all have read.
+        cluster_sync_all();
+        const int S = cluster_reduce, rank = blockIdx.z % S, group = blockIdx.z / S;
+        const int per = (TILE_M + S - 1) / S;
+        const int f_lo = rank * per, f_hi = min(TILE_M, f_lo + per);
+        const float* red = (const float*)smem;
+        TO* gout = out + (size_t)group * split_stride;
+        if (!*abort_flag && f_hi > f_lo) {
+            const int width = f_hi - f_lo;
+            for (int i = threadIdx.x; i < BN * width; i += GEMM_THREADS) {
+                const int n = i / width, fl = f_lo + i % width;
+                if (n0 + n < T && m0 + fl < N) {
+                    float acc = 0.f;
+                    for (int q = 0; q < S; ++q) acc += ld_peer_f32(red + n * RED_LD + fl, q);
+                    store_out<TO>(gout + (size_t)(n0 + n) * ldc + m0 + fl, acc);
+                }
+            }
+        }
+        cluster_sync_all();
     }
     tc_fence_before();
     __syncthreads();
@@ -412,8 +470,10 @@ int make_map(CUtensorMap* out, const void* ptr, long long rows, long long K, lon
 template <int BN, int MODE, typename TO>
 int launch(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx, void* out, int T,
            int N, int K, long long ldc, long long split_stride, int splits, int kb_per_split,
-           int act, cudaStream_t stream) {
+           int act, int cluster_reduce, cudaStream_t stream) {
     using TL = Tile<BN, MODE>;
+    static_assert(MODE != 0 || BN * RED_LD * 4 <= TL::STAGES * TL::STAGE_BYTES,
+                  "a partial tile must fit the ring of stages");
     auto kern = gemm_tcgen05_kernel<BN, MODE, TO>;
     static bool configured = false;
     if (!configured) {
@@ -424,8 +484,13 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx,
     constexpr int rows_per_cta = MODE == 2 ? TILE_M / 2 : TILE_M;
     dim3 grid((N + rows_per_cta - 1) / rows_per_cta, (T + BN - 1) / BN, splits);
     AGV_REQUIRE(grid.y <= 65535, "linear: %d tokens exceed the grid limit", T);
-    agv_launch(kern, grid, GEMM_THREADS, TL::SMEM, stream, mw, mw2, mx, (TO*)out, T, N, K, ldc,
-                                                   split_stride, kb_per_split, act);
+    if (cluster_reduce)
+        agv_launch_cluster(kern, grid, GEMM_THREADS, TL::SMEM, stream, (unsigned)cluster_reduce, mw,
+                           mw2, mx, (TO*)out, T, N, K, ldc, split_stride, kb_per_split, act,
+                           cluster_reduce);
+    else
+        agv_launch(kern, grid, GEMM_THREADS, TL::SMEM, stream, mw, mw2, mx, (TO*)out, T, N, K, ldc,
+                   split_stride, kb_per_split, act, 0);
     AGV_LAUNCH_OK("gemm_tcgen05_kernel");
     return 0;
 }
@@ -433,11 +498,11 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx,
 template <int MODE, typename TO>
 int launch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx,
               void* out, int T, int N, int K, long long ldc, long long split_stride, int splits,
-              int kb_per_split, int act, cudaStream_t stream) {
+              int kb_per_split, int act, int cluster_reduce, cudaStream_t stream) {
 #define AGV_BN_CASE(B)                                                                          \
     case B:                                                                                      \
         return launch<B, MODE, TO>(mw, mw2, mx, out, T, N, K, ldc, split_stride, splits,         \
-                                   kb_per_split, act, stream)
+                                   kb_per_split, act, cluster_reduce, stream)
     switch (bn) {
         AGV_BN_CASE(16);
         AGV_BN_CASE(32);
@@ -446,7 +511,7 @@ int launch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& mw2, const CUten
         case 256:
             if constexpr (MODE == 0)
                 return launch<256, 0, TO>(mw, mw2, mx, out, T, N, K, ldc, split_stride, splits,
-                                          kb_per_split, act, stream);
+                                          kb_per_split, act, cluster_reduce, stream);
     }
 #undef AGV_BN_CASE
     return agv_fail(-1, "linear: no kernel for a token tile of %d", bn);
@@ -462,12 +527,16 @@ AGV_API int agv_linear_tc_supported(int N, int K, long long lda) {
 }
 
 // x: [T, K] bf16, row stride lda; w (and w2 for the gated form): [N, K] bf16
-// dense; out: [T, N] (bf16 or f32, row stride ldc).  splits > 1 (plain form,
-// f32 out only): out is [splits, T, N] partial sums over K ranges, to be added
-// by the consumer.  token_tile 0 lets the launcher choose.
+// dense; out: [T, N] (bf16 or f32, row stride ldc).  splits > 1 (plain form)
+// cuts K into ranges that run in CTAs of their own.  With cluster 0 (f32 out
+// only) out is [splits, T, N] partial sums, to be added by the consumer.  With
+// cluster c in 2..8 (splits a multiple of c) every c CTAs of a tile form a
+// thread-block cluster, add their partial sums through distributed shared
+// memory in rank order, and out is [splits / c, T, N] (a plain [T, N] when
+// splits == c; bf16 allowed then).  token_tile 0 lets the launcher choose.
 AGV_API int agv_linear_tc(const void* x, const void* w, const void* w2, void* out, int T, int N,
                           int K, long long lda, long long ldc, int out_dtype, int act, int splits,
-                          int token_tile, cudaStream_t stream) {
+                          int cluster, int token_tile, cudaStream_t stream) {
     AGV_REQUIRE(T >= 0 && N > 0 && K > 0, "linear: bad sizes T=%d N=%d K=%d", T, N, K);
     AGV_REQUIRE(K % 8 == 0 && lda % 8 == 0, "linear: the tensor-core kernel needs K (%d) and the "
                 "row stride (%lld) to be multiples of 8", K, lda);
@@ -475,15 +544,24 @@ AGV_API int agv_linear_tc(const void* x, const void* w, const void* w2, void* ou
                 "linear: operands must be 16-byte aligned");
     AGV_REQUIRE(lda >= K && ldc >= N, "linear: row strides shorter than rows");
     AGV_REQUIRE(splits >= 1, "linear: splits must be >= 1");
-    AGV_REQUIRE(splits == 1 || (!w2 && out_dtype == AGV_F32),
-                "linear: partial sums need the plain form and a 32-bit output");
+    AGV_REQUIRE(splits == 1 || !w2, "linear: K can only be split in the plain form");
+    AGV_REQUIRE(cluster == 0 || (cluster >= 2 && cluster <= 8 && splits % cluster == 0),
+                "linear: a cluster holds 2 to 8 ranges of K and must divide the splits (%d, %d)",
+                cluster, splits);
+    AGV_REQUIRE(splits == 1 || splits == cluster || out_dtype == AGV_F32,
+                "linear: partial sums in global memory need a 32-bit output");
     if (T == 0) return 0;
     int bn = token_tile;
     if (bn == 0) bn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : (T <= 128 || w2) ? 128 : 256;
     const int kb_total = (K + TILE_K - 1) / TILE_K;
-    if (splits > kb_total) splits = kb_total;
-    const int kb_per = (kb_total + splits - 1) / splits;
-    splits = (kb_total + kb_per - 1) / kb_per;       // no empty split
+    int kb_per;
+    if (cluster) {
+        kb_per = (kb_total + splits - 1) / splits;   // trailing ranks may get no range of K
+    } else {
+        if (splits > kb_total) splits = kb_total;
+        kb_per = (kb_total + splits - 1) / splits;
+        splits = (kb_total + kb_per - 1) / kb_per;   // no empty split
+    }
     // decoding through a gated layer: gate and up rows share a tile (see Tile)
     const bool half = w2 && T <= 64;
     CUtensorMap mw, mw2, mx;
@@ -495,20 +573,22 @@ AGV_API int agv_linear_tc(const void* x, const void* w, const void* w2, void* ou
     }
     if (int rc = make_map(&mx, x, T, K, lda, bn)) return rc;
     const long long split_stride = (long long)T * ldc;
+    const int creduce = splits > 1 ? cluster : 0;
     if (w2) {
         AGV_REQUIRE(out_dtype == AGV_BF16, "linear: the gated form writes bfloat16");
         if (half)
             return launch_bn<2, __nv_bfloat16>(bn, mw, mw2, mx, out, T, N, K, ldc, 0, 1, kb_total,
-                                               act, stream);
+                                               act, 0, stream);
         return launch_bn<1, __nv_bfloat16>(bn, mw, mw2, mx, out, T, N, K, ldc, 0, 1, kb_total,
-                                           act, stream);
+                                           act, 0, stream);
     }
     if (out_dtype == AGV_BF16)
-        return launch_bn<0, __nv_bfloat16>(bn, mw, mw2, mx, out, T, N, K, ldc, 0, 1, kb_total,
-                                           act, stream);
+        return launch_bn<0, __nv_bfloat16>(bn, mw, mw2, mx, out, T, N, K, ldc, 0,
+                                           creduce ? splits : 1, creduce ? kb_per : kb_total, act,
+                                           creduce, stream);
     if (out_dtype == AGV_F32)
         return launch_bn<0, float>(bn, mw, mw2, mx, out, T, N, K, ldc, split_stride, splits,
-                                       kb_per, act, stream);
+                                   kb_per, act, creduce, stream);
     return agv_fail(-1, "linear: unknown output dtype %d", out_dtype);
 }
 

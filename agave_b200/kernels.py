@@ -301,11 +301,14 @@ def sample(logits: torch.Tensor, out: torch.Tensor, temperature: float, top_k: i
 
 def linear_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
               w2: Optional[torch.Tensor] = None, activation: str = "gelu_tanh",
-              splits: int = 1, token_tile: int = 0) -> None:
+              splits: int = 1, token_tile: int = 0, cluster: int = 0) -> None:
     """bfloat16 product on the tensor cores (tcgen05 + TMA).
 
-    out [T, N] in bfloat16 or 32-bit; with splits > 1, out is [splits, T, N] 32-bit
-    partial sums over ranges of K (use ``linear_tc_splits`` for the real count).
+    out [T, N] in bfloat16 or 32-bit.  With splits > 1, K is cut into ranges that
+    run in CTAs of their own.  ``cluster`` = c (2..8, dividing splits): every c CTAs
+    of a tile add their partial sums through distributed shared memory and out is
+    [splits / c, T, N] (plain [T, N] when splits == c).  ``cluster`` = 0: out is
+    [splits, T, N] 32-bit partial sums (use ``linear_tc_splits`` for the real count).
     """
     T, K = x.shape
     N = w.shape[0]
@@ -315,16 +318,18 @@ def linear_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
     if w2 is not None:
         _dense(w2, "w2")
         assert w2.shape == w.shape and w2.dtype == w.dtype
-    if splits > 1:
-        assert out.dim() == 3 and out.shape[1:] == (T, N) and out.is_contiguous()
+    cluster = int(cluster)
+    groups = splits // cluster if cluster else splits
+    if groups > 1:
+        assert out.dim() == 3 and out.shape == (groups, T, N) and out.is_contiguous()
         ldc = N
     else:
         assert out.shape == (T, N) and out.stride(1) == 1
         ldc = out.stride(0)
     _check(library().agv_linear_tc(
         _ptr(x), _ptr(w), _ptr(w2), _ptr(out), T, N, K, ctypes.c_longlong(x.stride(0)),
-        ctypes.c_longlong(ldc), dtype_code(out.dtype), ACT[activation], splits, token_tile,
-        _stream()))
+        ctypes.c_longlong(ldc), dtype_code(out.dtype), ACT[activation], splits, cluster,
+        token_tile, _stream()))
 
 
 def linear_tc_splits(K: int, splits: int) -> int:
@@ -358,29 +363,38 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
 N_SMS = 148
 
 
-def plan_splits(T: int, N: int, K: int) -> int:
-    """How many ranges of K a product is cut into so that about one CTA per SM
-    is busy when the weight has few row tiles (decoding through narrow layers)."""
-    tile = 16 if T <= 16 else 32 if T <= 32 else 64 if T <= 64 else 128 if T <= 128 else 256
+def plan_splits(T: int, N: int, K: int):
+    """(groups, cluster size) of the ranges K is cut into so that about one CTA per
+    SM is busy when the weight has few row tiles (decoding through narrow
+    layers).  The CTAs of a cluster add their sums in the kernel; the groups are
+    left to the consumer.  Prompts are not cut."""
+    if T > 64:
+        return 1, 0
+    tile = 16 if T <= 16 else 32 if T <= 32 else 64
     ctas = ((N + 127) // 128) * ((T + tile - 1) // tile)
     kb = (K + 63) // 64
-    if ctas >= 100 or kb < 2:
-        return 1
-    return linear_tc_splits(K, min(kb, (N_SMS + ctas - 1) // ctas))
+    want = min(kb, (N_SMS + ctas - 1) // ctas)
+    if ctas >= 100 or want < 2:
+        return 1, 0
+    if want <= 8 or kb < 64:
+        # a single cluster per tile adds its ranges in the kernel
+        c = min(want, 8)
+        return 1, c
+    # a long K: more ranges than a cluster holds; the consumer adds the partial sums
+    return linear_tc_splits(K, min(want, 16)), 0
 
 
 def linear_partial(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-    """x w^T for a consumer that adds partial sums itself: returns [S, T, N] in
-    32-bit on the tensor-core path (S >= 1 ranges of K), else [T, N] in x's dtype."""
+    """x w^T in 32-bit for a consumer that adds over a leading axis: [G, T, N] on
+    the tensor-core path (G >= 1 groups of ranges of K; the ranges of a group
+    are added inside the kernel by a cluster), else [T, N] in x's dtype."""
     T, K = x.shape
     N = w.shape[0]
     if linear_tc_supported(x, w):
-        s = plan_splits(T, N, K)
-        out = torch.empty((s, T, N), dtype=torch.float32, device=x.device)
-        if s > 1:
-            linear_tc(x, w, out, splits=s)
-        else:
-            linear_tc(x, w, out[0])
+        groups, csize = plan_splits(T, N, K)
+        out = torch.empty((groups, T, N), dtype=torch.float32, device=x.device)
+        linear_tc(x, w, out if groups > 1 else out[0], splits=groups * max(csize, 1),
+                  cluster=csize)
         return out
     out = torch.empty((T, N), dtype=x.dtype, device=x.device)
     linear_simt(x, w, out)

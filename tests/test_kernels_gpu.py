@@ -87,6 +87,32 @@ def test_linear_tensor_cores_partial_sums(splits):
     assert rel_err(out.sum(0), x.float() @ w.float().T) < 1e-5
 
 
+@pytest.mark.parametrize("splits", [2, 3, 5, 8])
+@pytest.mark.parametrize("T,tile", [(6, 0), (40, 0), (100, 128), (300, 256)])
+def test_linear_tensor_cores_cluster_reduction(splits, T, tile):
+    """Ranges of K added inside the kernel by a thread-block cluster."""
+    from agave_b200 import kernels
+    N, K = 200, 6912 // 4
+    x, w = rnd(T, K, dtype=torch.bfloat16, seed=12), rnd(N, K, dtype=torch.bfloat16, seed=13)
+    ref = x.float() @ w.float().T
+    for out_dtype in (torch.float32, torch.bfloat16):
+        out = torch.full((T, N), float("nan"), dtype=out_dtype, device=DEV)
+        kernels.linear_tc(x, w, out, splits=splits, cluster=splits, token_tile=tile)
+        assert kernels.linear_tc_status() == 0
+        assert rel_err(out, ref) < (1e-5 if out_dtype == torch.float32 else 5e-3)
+    # several clusters per tile: groups of partial sums, and ranks without a range of K
+    for groups, c in ((2, splits), (3, 2)):
+        out = torch.full((groups, T, N), float("nan"), dtype=torch.float32, device=DEV)
+        kernels.linear_tc(x, w, out, splits=groups * c, cluster=c, token_tile=tile)
+        assert kernels.linear_tc_status() == 0
+        assert rel_err(out.sum(0), ref) < 1e-5
+    small = rnd(T, 128, dtype=torch.bfloat16, seed=14)           # two blocks of K, eight ranks
+    wsm = rnd(N, 128, dtype=torch.bfloat16, seed=15)
+    out = torch.full((T, N), float("nan"), dtype=torch.float32, device=DEV)
+    kernels.linear_tc(small, wsm, out, splits=8, cluster=8, token_tile=tile)
+    assert rel_err(out, small.float() @ wsm.float().T) < 1e-5
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_linear_simt_plain_and_gated(dtype):
     from agave_b200 import kernels
