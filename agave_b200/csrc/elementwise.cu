@@ -137,8 +137,8 @@ __global__ void norm_residual_kernel(float* __restrict__ h, const TY* __restrict
 // operand a thread needs (branch partial sums, stream, both weights) loaded up
 // front into registers: the loads of one row overlap instead of queueing behind
 // the reductions.  This is the variant decode steps run.
-template <typename TY, typename TX, int EPT>
-__global__ void __launch_bounds__(1024)
+template <typename TY, typename TX, int EPT, int MAXT>
+__global__ void __launch_bounds__(MAXT)
 norm_residual_small_kernel(float* __restrict__ h, const TY* __restrict__ y, int n_splits,
                            size_t split_stride, const float* __restrict__ w_post,
                            const float* __restrict__ w_next, TX* __restrict__ x,
@@ -161,7 +161,7 @@ norm_residual_small_kernel(float* __restrict__ h, const TY* __restrict__ y, int 
         wn[k] = (in && w_next) ? w_next[i] : 1.f;
     }
     if (y) {
-        constexpr int U = EPT <= 2 ? 16 : (EPT <= 4 ? 8 : 4);   // ranges of K loaded together
+        constexpr int U = EPT <= 2 ? 16 : (EPT <= 4 ? 8 : (EPT <= 8 ? 4 : (EPT <= 16 ? 2 : 1)));
         if (n_splits == 1) {
 #pragma unroll
             for (int k = 0; k < EPT; ++k) {
@@ -233,18 +233,29 @@ static int launch_norm(float* h, const void* y, int n_splits, size_t split_strid
                        const float* w_post, const float* w_next, void* x, const int* rows, int R,
                        int H, float eps_post, float eps_next, int add_residual,
                        cudaStream_t stream) {
-    // few rows (decode, final norm): the register-resident kernel, one row per CTA
-    if (R <= 256 && H <= 8 * 1024) {
-        const int threads = H <= 256 ? 128 : H <= 1024 ? 512 : 1024;
+    // the register-resident kernel, one row per CTA: many threads per row when the
+    // rows are few (decode, final norm), few threads per row when they are many
+    if (H <= 8 * 1024) {
+        const int threads = R <= 256 ? (H <= 256 ? 128 : H <= 1024 ? 512 : 1024)
+                                     : (H <= 512 ? 128 : 256);
         const int ept = (H + threads - 1) / threads;
-#define AGV_SMALL(E)                                                                            \
-    agv_launch(norm_residual_small_kernel<TY, TX, E>, R, threads, 0, stream, \
-        h, (const TY*)y, n_splits, split_stride, w_post, w_next, (TX*)x, rows, H, eps_post,     \
-        eps_next, add_residual)
-        if (ept <= 1) AGV_SMALL(1);
-        else if (ept <= 2) AGV_SMALL(2);
-        else if (ept <= 4) AGV_SMALL(4);
-        else AGV_SMALL(8);
+#define AGV_SMALL(E, MT)                                                                        \
+    agv_launch(norm_residual_small_kernel<TY, TX, E, MT>, R, threads, 0, stream, h,             \
+               (const TY*)y, n_splits, split_stride, w_post, w_next, (TX*)x, rows, H, eps_post, \
+               eps_next, add_residual)
+        if (threads > 256) {
+            if (ept <= 1) AGV_SMALL(1, 1024);
+            else if (ept <= 2) AGV_SMALL(2, 1024);
+            else if (ept <= 4) AGV_SMALL(4, 1024);
+            else AGV_SMALL(8, 1024);
+        } else {
+            if (ept <= 1) AGV_SMALL(1, 256);
+            else if (ept <= 2) AGV_SMALL(2, 256);
+            else if (ept <= 4) AGV_SMALL(4, 256);
+            else if (ept <= 8) AGV_SMALL(8, 256);
+            else if (ept <= 16) AGV_SMALL(16, 256);
+            else AGV_SMALL(32, 256);
+        }
 #undef AGV_SMALL
         AGV_LAUNCH_OK("norm_residual_small_kernel");
         return 0;

@@ -38,6 +38,11 @@ def library() -> ctypes.CDLL:
                 except OSError as e:
                     raise KernelError(f"the CUDA library {path} could not be loaded: {e}") from None
                 lib.agv_last_error.restype = ctypes.c_char_p
+                import os
+                if os.environ.get("AGAVE_B200_DEPENDENT_LAUNCH", "1") == "0":
+                    # kernels then start only after the one before has ended, which
+                    # makes per-kernel durations in a profiler additive
+                    lib.agv_set_dependent_launch(0)
                 _lib = lib
     return _lib
 
