@@ -166,7 +166,9 @@ struct Tile {
     static constexpr int B_BYTES = BN * TILE_K * 2;
     static constexpr int STAGE_BYTES = A_BYTES * (DUAL ? 2 : 1) + B_BYTES;
     static constexpr int XCHG_BYTES = HALF ? 64 * BN * 4 : 0;
-    static constexpr int BUDGET = DUAL ? 196 * 1024 : (BN >= 256 ? 196 * 1024 : 108 * 1024);
+    // token tiles of 128 and more run one CTA per SM with a deep ring; smaller ones
+    // (decoding) leave room for a second CTA that hides this one's start and end
+    static constexpr int BUDGET = DUAL ? 196 * 1024 : (BN >= 128 ? 196 * 1024 : 108 * 1024);
     static constexpr int STAGES_RAW = (BUDGET - XCHG_BYTES) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : (STAGES_RAW < 2 ? 2 : STAGES_RAW);
     static constexpr int TMEM_COLS_RAW = DUAL ? 2 * BN : BN;
@@ -354,25 +356,48 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
 #pragma unroll
                 for (int j = 0; j < 16; ++j) red[(c + j) * RED_LD + fl] = __uint_as_float(r[j]);
             }
-        } else if (run) {
+        } else {
+            // plain and two-accumulator forms: the tile goes through shared memory
+            // (the ring of stages is free by now) so that rows leave in 16-byte pieces
+            static_assert(BN * TILE_M * (int)sizeof(TO) <= TL::STAGES * TL::STAGE_BYTES,
+                          "the output tile must fit the ring of stages");
+            TO* ctile = (TO*)smem;                       // [BN][TILE_M]
+            const int fl = quarter * 32 + lane;
+            if (run) {
 #pragma unroll 1
-            for (int c = 0; c < BN; c += 16) {
-                uint32_t r[16], u[16];
-                tc_ld16(lane_base + c, r);
-                if (GATED) tc_ld16(lane_base + BN + c, u);
-                tc_wait_ld();
-                if (f < N) {
+                for (int c = 0; c < BN; c += 16) {
+                    uint32_t r[16], u[16];
+                    tc_ld16(lane_base + c, r);
+                    if (GATED) tc_ld16(lane_base + BN + c, u);
+                    tc_wait_ld();
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
-                        const int n = n0 + c + j;
-                        if (n < T) {
-                            float v = __uint_as_float(r[j]);
-                            if (GATED) {
-                                v = (act == 1 ? silu_fast(v) : gelu_tanh_fast(v)) *
-                                    __uint_as_float(u[j]);
-                            }
-                            store_out<TO>(obase + (size_t)n * ldc + f, v);
-                        }
+                        float v = __uint_as_float(r[j]);
+                        if (GATED)
+                            v = (act == 1 ? silu_fast(v) : gelu_tanh_fast(v)) * __uint_as_float(u[j]);
+                        store_out<TO>(ctile + (c + j) * TILE_M + fl, v);
+                    }
+                }
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");       // the four epilogue warps
+            if (run) {
+                constexpr int EPV = 16 / (int)sizeof(TO);          // elements per 16 bytes
+                constexpr int VPR = TILE_M / EPV;                  // 16-byte pieces per row
+                const int et = (warp - 2) * 32 + lane;
+                const int rows = min(BN, T - n0);
+                TO* gbase = obase + (size_t)n0 * ldc + m0;
+                const bool fast = m0 + TILE_M <= N && ldc % EPV == 0 &&
+                                  ((uintptr_t)gbase & 15) == 0;
+                if (fast) {
+                    for (int i = et; i < rows * VPR; i += 128) {
+                        const int n = i / VPR, vi = i % VPR;
+                        const uint4 val = reinterpret_cast<const uint4*>(ctile)[i];
+                        *reinterpret_cast<uint4*>(gbase + (size_t)n * ldc + vi * EPV) = val;
+                    }
+                } else {
+                    for (int i = et; i < rows * TILE_M; i += 128) {
+                        const int n = i / TILE_M, f2 = i % TILE_M;
+                        if (m0 + f2 < N) gbase[(size_t)n * ldc + f2] = ctile[i];
                     }
                 }
             }
@@ -509,9 +534,9 @@ int launch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& mw2, const CUten
         AGV_BN_CASE(64);
         AGV_BN_CASE(128);
         case 256:
-            if constexpr (MODE == 0)
-                return launch<256, 0, TO>(mw, mw2, mx, out, T, N, K, ldc, split_stride, splits,
-                                          kb_per_split, act, cluster_reduce, stream);
+            if constexpr (MODE != 2)
+                return launch<256, MODE, TO>(mw, mw2, mx, out, T, N, K, ldc, split_stride, splits,
+                                             kb_per_split, act, cluster_reduce, stream);
     }
 #undef AGV_BN_CASE
     return agv_fail(-1, "linear: no kernel for a token tile of %d", bn);
@@ -552,7 +577,9 @@ AGV_API int agv_linear_tc(const void* x, const void* w, const void* w2, void* ou
                 "linear: partial sums in global memory need a 32-bit output");
     if (T == 0) return 0;
     int bn = token_tile;
-    if (bn == 0) bn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : (T <= 128 || w2) ? 128 : 256;
+    if (bn == 0) {
+        bn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
+    }
     const int kb_total = (K + TILE_K - 1) / TILE_K;
     int kb_per;
     if (cluster) {

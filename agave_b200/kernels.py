@@ -374,6 +374,12 @@ def plan_splits(T: int, N: int, K: int):
     layers).  The CTAs of a cluster add their sums in the kernel; the groups are
     left to the consumer.  Prompts are not cut."""
     if T > 64:
+        # prompts: only a long K over few tiles is cut, in two, with the partial
+        # sums left to the consumer (a cluster's exchange is slow for wide tiles)
+        tile = 128 if T <= 128 else 256
+        ctas = ((N + 127) // 128) * ((T + tile - 1) // tile)
+        if ctas <= N_SMS // 2 + 6 and (K + 63) // 64 >= 32:
+            return 2, 0
         return 1, 0
     tile = 16 if T <= 16 else 32 if T <= 32 else 64
     ctas = ((N + 127) // 128) * ((T + tile - 1) // tile)
