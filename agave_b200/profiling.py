@@ -1,0 +1,207 @@
+"""Small, self-contained workloads of single kernels and of a decode step, for
+profilers and timing.
+
+    python -m agave_b200.profiling <case> [--iters N]
+
+Cases (Gemma 3 1B layer sizes, random bfloat16 data):
+  gemm_gated_prefill   gate/up product with the activation epilogue, 2,048 tokens
+  gemm_down_prefill    down projection, 2,048 tokens
+  gemm_gated_decode    gate/up product, 8 tokens
+  gemm_down_decode     down projection, 8 tokens (K split over a cluster or partial sums)
+  gemm_lm_head_decode  the head over a 262,144-row table, 8 tokens
+  attention_prefill    prompt attention, one sequence of 2,048 tokens, no window
+  attention_decode_window   decode attention, 8 sequences of 128..2,048 positions, window 512
+  attention_decode_full     the same without a window
+  norm_decode          residual sum + two RMS norms over 8 rows of 16 partial sums
+  decode_step          whole decode steps of a 6-layer model (vocabulary 32,768), batch 8
+
+Each case prints the mean time per call: the calls run back to back from a CUDA
+graph, each on the next of several copies of its operands, the copies together
+larger than L2, so operands come from HBM as they do in a model step.  The
+working set stays below 2 GB.
+"""
+from __future__ import annotations
+
+import argparse
+import sys
+
+import torch
+
+DEV = "cuda:0"
+H, FF, NH, NKV, HD, V = 1152, 6912, 4, 1, 256, 262144
+
+
+def _rnd(*shape, scale=1.0):
+    return (torch.randn(*shape, device=DEV) * scale).to(torch.bfloat16)
+
+
+L2_BYTES = 126 * 1024 * 1024
+
+
+def _copies(nbytes: int) -> int:
+    """How many copies of an operand set make the ring larger than L2 (twice over)."""
+    return max(1, min(64, (2 * L2_BYTES + nbytes - 1) // max(nbytes, 1)))
+
+
+def _run(fn, copies: int, iters: int) -> float:
+    """Mean microseconds per call: the calls run back to back from a CUDA graph,
+    each on the next copy of its operands, so that none finds them in L2."""
+    n = max(copies, 8)
+    for i in range(min(n, 3)):
+        fn(i % copies)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for i in range(n):
+            fn(i % copies)
+    g.replay()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        total += e0.elapsed_time(e1)
+    return total / iters / n * 1e3
+
+
+def case_gemm_gated(T):
+    from . import kernels
+    nbytes = (2 * FF * H + T * H + T * FF) * 2
+    c = _copies(2 * FF * H * 2)
+    x = _rnd(T, H)
+    wg = [_rnd(FF, H, scale=0.02) for _ in range(c)]
+    wu = [_rnd(FF, H, scale=0.02) for _ in range(c)]
+    out = torch.empty(T, FF, dtype=torch.bfloat16, device=DEV)
+    return (lambda i: kernels.linear_tc(x, wg[i], out, w2=wu[i])), 4 * T * FF * H, nbytes, c
+
+
+def case_gemm_down(T):
+    from . import kernels
+    c = _copies(FF * H * 2)
+    x = _rnd(T, FF)
+    w = [_rnd(H, FF, scale=0.02) for _ in range(c)]
+    return (lambda i: kernels.linear_partial(x, w[i])), 2 * T * FF * H, \
+        (FF * H + T * FF) * 2 + T * H * 4, c
+
+
+def case_lm_head():
+    from . import kernels
+    x, w = _rnd(8, H), _rnd(V, H, scale=0.02)
+    out = torch.empty(8, V, dtype=torch.float32, device=DEV)
+    return (lambda i: kernels.linear_tc(x, w, out)), 2 * 8 * V * H, V * H * 2 + 8 * V * 4, 1
+
+
+def case_attention_prefill():
+    from . import kernels
+    T = 2048
+    c = 8
+    qkv = [_rnd(T, (NH + 2 * NKV) * HD, scale=0.5) for _ in range(c)]
+    out = torch.empty(T, NH * HD, dtype=torch.bfloat16, device=DEV)
+    cu = torch.tensor([0, T], dtype=torch.int32, device=DEV)
+    flops = 4 * NH * HD * T * (T + 1) // 2
+
+    def fn(i):
+        t = qkv[i]
+        kernels.attention_prefill_mma(t[:, :NH * HD], t[:, NH * HD:(NH + NKV) * HD],
+                                      t[:, (NH + NKV) * HD:], out, cu, T, NH, NKV, HD, 0.0625, 0)
+    return fn, flops, qkv[0].numel() * 2 + out.numel() * 2, c
+
+
+def case_attention_decode(window, max_keys):
+    from . import kernels
+    B, PAGE, max_pages = 8, 64, 40
+    c = 16
+    pools = [(_rnd(B * max_pages, PAGE, NKV, HD), _rnd(B * max_pages, PAGE, NKV, HD))
+             for _ in range(c)]
+    table = torch.arange(B * max_pages, dtype=torch.int32, device=DEV).reshape(B, max_pages)
+    slots = torch.arange(B, dtype=torch.int32, device=DEV)
+    lens = torch.linspace(128, 2048, B).round().int().tolist()
+    positions = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=DEV)
+    q = _rnd(B, NH * HD)
+    out = torch.empty_like(q)
+    kernels.prepare_device(torch.device(DEV))
+
+    def fn(i):
+        kernels.attention_decode_split(q, out, pools[i][0], pools[i][1], table, slots, positions,
+                                       PAGE, max_pages * PAGE, NH, NKV, HD, 0.0625, window,
+                                       max_keys)
+    nbytes = sum(min(n, window) if window else n for n in lens) * NKV * HD * 2 * 2
+    return fn, 0, nbytes, c
+
+
+def case_norm_decode():
+    from . import kernels
+    h = torch.randn(8, H, device=DEV)
+    y = torch.randn(16, 8, H, device=DEV)
+    w = torch.ones(H, device=DEV)
+    x = torch.empty(8, H, dtype=torch.bfloat16, device=DEV)
+    return (lambda i: kernels.norm_residual(h, y, w, w, x, 1e-6, 1e-6)), 0, \
+        y.numel() * 4 + 3 * 8 * H * 4, 1
+
+
+def case_decode_step():
+    from .engine.api import Engine
+    cfg = {
+        "architectures": ["Gemma3ForCausalLM"], "model_type": "gemma3_text",
+        "num_hidden_layers": 6, "hidden_size": H, "num_attention_heads": NH,
+        "num_key_value_heads": NKV, "head_dim": HD, "query_pre_attn_scalar": HD,
+        "intermediate_size": FF, "vocab_size": 32768, "sliding_window": 512,
+        "sliding_window_pattern": 6, "rope_local_base_freq": 10000.0, "rope_theta": 1000000.0,
+        "rms_norm_eps": 1e-6, "max_position_embeddings": 8192, "eos_token_id": 1}
+    eng = Engine.from_config(cfg, seed=2, dtype="bfloat16", max_tokens=16 * 8192, ctx_size=8192,
+                             max_batch=16, use_graphs=False)
+    g = torch.Generator().manual_seed(0)
+    lens = torch.linspace(128, 2048, 8).round().int().tolist()
+    prompts = [torch.randint(3, 32768, (n,), generator=g).tolist() for n in lens]
+    slots = [eng.acquire() for _ in prompts]
+    eng.step([(s, p) for s, p in zip(slots, prompts)], [[] for _ in prompts])
+    return (lambda i: eng.step([(s, [5]) for s in slots], [[0]] * 8)), 0, 0, 0
+
+
+CASES = {
+    "gemm_gated_prefill": lambda: case_gemm_gated(2048),
+    "gemm_down_prefill": lambda: case_gemm_down(2048),
+    "gemm_gated_decode": lambda: case_gemm_gated(8),
+    "gemm_down_decode": lambda: case_gemm_down(8),
+    "gemm_lm_head_decode": case_lm_head,
+    "attention_prefill": case_attention_prefill,
+    "attention_decode_window": lambda: case_attention_decode(512, 512),
+    "attention_decode_full": lambda: case_attention_decode(0, 2048),
+    "norm_decode": case_norm_decode,
+    "decode_step": case_decode_step,
+}
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="agave_b200.profiling", description=__doc__.split("\n\n")[0])
+    ap.add_argument("case", choices=sorted(CASES))
+    ap.add_argument("--iters", type=int, default=5)
+    args = ap.parse_args(argv)
+    fn, flops, nbytes, copies = CASES[args.case]()
+    if copies == 0:                      # a whole step: host work included, no graph
+        for _ in range(3):
+            fn(0)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.iters):
+            fn(0)
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) / args.iters * 1e3
+    else:
+        us = _run(fn, copies, args.iters)
+    msg = f"{args.case}: {us:.1f} us per call"
+    if flops:
+        msg += f", {flops / us / 1e6:.0f} TFLOP/s"
+    if nbytes:
+        msg += f", {nbytes / us / 1e3:.0f} GB/s of {nbytes / 1e6:.1f} MB"
+    print(msg)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
