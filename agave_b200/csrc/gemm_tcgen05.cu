@@ -231,12 +231,27 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    pdl_wait();          // barriers and tensor memory are set up; now the operands must be ready
 
     if (warp == 0 && lane == 0) {
         // ------------------------------------------------------------ loader
-        int issued = 0;
-        for (int i = 0; i < n_kb; ++i) {
+        // The weights never change, so the first ring of weight boxes is requested
+        // before this kernel waits for its predecessor (which produces x): the
+        // stream from HBM starts while the predecessor is still running.
+        const int early = min(n_kb, TL::STAGES);
+        for (int i = 0; i < early; ++i) {
+            uint8_t* st = smem + i * TL::STAGE_BYTES;
+            mbar_expect_tx(&full[i], TL::STAGE_BYTES);
+            const int kx = (kb_begin + i) * TILE_K;
+            tma_load_2d(st, &map_w, kx, m0, &full[i]);
+            if (GATED) tma_load_2d(st + TL::A_BYTES, &map_w2, kx, m0, &full[i]);
+            if (HALF) tma_load_2d(st + TL::A_BYTES / 2, &map_w2, kx, m0, &full[i]);
+        }
+        pdl_wait();
+        for (int i = 0; i < early; ++i)
+            tma_load_2d(smem + i * TL::STAGE_BYTES + TL::A_BYTES * (GATED ? 2 : 1), &map_x,
+                        (kb_begin + i) * TILE_K, n0, &full[i]);
+        int issued = early;
+        for (int i = early; i < n_kb; ++i) {
             const int s = i % TL::STAGES;
             const uint32_t ph = (i / TL::STAGES) & 1;
             if (*abort_flag) break;
@@ -295,6 +310,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
         // this thread's output feature (in the shared-tile form lanes 64-127 hold the
         // up rows of the features whose gate rows lanes 0-63 hold)
         const int f = HALF ? m0 + (quarter & 1) * 32 + lane : m0 + quarter * 32 + lane;
+        pdl_wait();          // this warp writes global memory: not before the predecessor is done
         bool ok = mbar_wait(acc_full, 0);
         if (!ok) {
             atomicCAS(&g_gemm_status, 0, (3 << 8));
@@ -310,7 +326,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
             const int fl = quarter * 32 + lane;
             for (int c = 0; c < BN; ++c) red[c * RED_LD + fl] = 0.f;
         }
-        if (HALF) {
+        if (run && cluster_reduce) {
+            // this CTA's partial sums -> shared memory [token][tile row], for the cluster
+            float* red = (float*)smem;
+            const int fl = quarter * 32 + lane;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 16) {
+                uint32_t r[16];
+                tc_ld16(lane_base + c, r);
+                tc_wait_ld();
+#pragma unroll
+                for (int j = 0; j < 16; ++j) red[(c + j) * RED_LD + fl] = __uint_as_float(r[j]);
+            }
+        } else if (HALF) {
             // up half -> shared memory, then the gate half combines and stores
             if (run && quarter >= 2) {
 #pragma unroll 1
@@ -343,18 +371,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
                         }
                     }
                 }
-            }
-        } else if (run && cluster_reduce) {
-            // this CTA's partial sums -> shared memory [token][feature], for the cluster
-            float* red = (float*)smem;
-            const int fl = quarter * 32 + lane;
-#pragma unroll 1
-            for (int c = 0; c < BN; c += 16) {
-                uint32_t r[16];
-                tc_ld16(lane_base + c, r);
-                tc_wait_ld();
-#pragma unroll
-                for (int j = 0; j < 16; ++j) red[(c + j) * RED_LD + fl] = __uint_as_float(r[j]);
             }
         } else {
             // plain and two-accumulator forms: the tile goes through shared memory
@@ -405,14 +421,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
     }
     __syncwarp();
     if (cluster_reduce) {
+        pdl_wait();
         // The gridDim.z CTAs of a cluster hold partial sums of one tile over
         // consecutive ranges of K.  Each adds, in rank order, a slice of the tile's
         // features from every peer's shared memory and writes the result; nobody
         // leaves before all have read.
         cluster_sync_all();
         const int S = cluster_reduce, rank = blockIdx.z % S, group = blockIdx.z / S;
-        const int per = (TILE_M + S - 1) / S;
-        const int f_lo = rank * per, f_hi = min(TILE_M, f_lo + per);
+        constexpr int FEATS = HALF ? TILE_M / 2 : TILE_M;      // output features of the tile
+        const int per = (FEATS + S - 1) / S;
+        const int f_lo = rank * per, f_hi = min(FEATS, f_lo + per);
         const float* red = (const float*)smem;
         TO* gout = out + (size_t)group * split_stride;
         if (!*abort_flag && f_hi > f_lo) {
@@ -422,6 +440,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
                 if (n0 + n < T && m0 + fl < N) {
                     float acc = 0.f;
                     for (int q = 0; q < S; ++q) acc += ld_peer_f32(red + n * RED_LD + fl, q);
+                    if (HALF) {
+                        // rows 64..127 of the tile are the up rows of the same features
+                        float up = 0.f;
+                        for (int q = 0; q < S; ++q)
+                            up += ld_peer_f32(red + n * RED_LD + TILE_M / 2 + fl, q);
+                        acc = (act == 1 ? silu_fast(acc) : gelu_tanh_fast(acc)) * up;
+                    }
                     store_out<TO>(gout + (size_t)(n0 + n) * ldc + m0 + fl, acc);
                 }
             }
@@ -499,6 +524,8 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx,
     using TL = Tile<BN, MODE>;
     static_assert(MODE != 0 || BN * RED_LD * 4 <= TL::STAGES * TL::STAGE_BYTES,
                   "a partial tile must fit the ring of stages");
+    AGV_REQUIRE(!cluster_reduce || BN * RED_LD * 4 <= TL::STAGES * TL::STAGE_BYTES,
+                "linear: a partial tile of %d tokens does not fit the ring of stages", BN);
     auto kern = gemm_tcgen05_kernel<BN, MODE, TO>;
     static bool configured = false;
     if (!configured) {
@@ -569,7 +596,8 @@ AGV_API int agv_linear_tc(const void* x, const void* w, const void* w2, void* ou
                 "linear: operands must be 16-byte aligned");
     AGV_REQUIRE(lda >= K && ldc >= N, "linear: row strides shorter than rows");
     AGV_REQUIRE(splits >= 1, "linear: splits must be >= 1");
-    AGV_REQUIRE(splits == 1 || !w2, "linear: K can only be split in the plain form");
+    AGV_REQUIRE(splits == 1 || !w2 || (cluster == splits && T <= 64),
+                "linear: the gated form splits K only over one cluster and for at most 64 tokens");
     AGV_REQUIRE(cluster == 0 || (cluster >= 2 && cluster <= 8 && splits % cluster == 0),
                 "linear: a cluster holds 2 to 8 ranges of K and must divide the splits (%d, %d)",
                 cluster, splits);
@@ -604,8 +632,9 @@ AGV_API int agv_linear_tc(const void* x, const void* w, const void* w2, void* ou
     if (w2) {
         AGV_REQUIRE(out_dtype == AGV_BF16, "linear: the gated form writes bfloat16");
         if (half)
-            return launch_bn<2, __nv_bfloat16>(bn, mw, mw2, mx, out, T, N, K, ldc, 0, 1, kb_total,
-                                               act, 0, stream);
+            return launch_bn<2, __nv_bfloat16>(bn, mw, mw2, mx, out, T, N, K, ldc, 0,
+                                               creduce ? splits : 1, creduce ? kb_per : kb_total,
+                                               act, creduce, stream);
         return launch_bn<1, __nv_bfloat16>(bn, mw, mw2, mx, out, T, N, K, ldc, 0, 1, kb_total,
                                            act, 0, stream);
     }

@@ -355,17 +355,23 @@ def linear_tc_status() -> int:
 
 
 # ------------------------------------------------------------------ dispatch
+N_SMS = 148
+
 def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
            w2: Optional[torch.Tensor] = None, activation: str = "gelu_tanh") -> None:
     """out = x w^T (or the gated pair).  The kernel is chosen from the dtype and
     the weight's shape only, never from the number of rows of x."""
     if linear_tc_supported(x, w) and (w2 is None or out.dtype == torch.bfloat16):
-        linear_tc(x, w, out, w2, activation)
+        c = 0
+        if w2 is not None and x.shape[0] <= 64:
+            # decoding through a gated layer with few 64-feature tiles: two or four
+            # CTAs per tile, each on a range of K, joined by a cluster
+            tiles = (w.shape[0] + 63) // 64
+            kb = (w.shape[1] + 63) // 64
+            c = 4 if tiles * 4 <= N_SMS and kb >= 8 else 2 if tiles * 2 <= 2 * N_SMS and kb >= 4 else 0
+        linear_tc(x, w, out, w2, activation, splits=max(c, 1), cluster=c)
     else:
         linear_simt(x, w, out, w2, activation)
-
-
-N_SMS = 148
 
 
 def plan_splits(T: int, N: int, K: int):

@@ -73,6 +73,12 @@ def test_linear_tensor_cores_gated(T, N, K, act):
     kernels.linear_tc(x, wg, out, w2=wu, activation=act)
     assert kernels.linear_tc_status() == 0
     assert rel_err(out, a * u) < 6e-3
+    if T <= 64:
+        for c in (2, 4):                      # K over a cluster, the activation after the sum
+            out2 = torch.full_like(out, float("nan"))
+            kernels.linear_tc(x, wg, out2, w2=wu, activation=act, splits=c, cluster=c)
+            assert kernels.linear_tc_status() == 0
+            assert rel_err(out2, a * u) < 6e-3
 
 
 @pytest.mark.parametrize("splits", [2, 3, 7])
