@@ -86,11 +86,13 @@ struct DecodeArgs {
 template <typename T>
 __device__ __forceinline__ void finish_split(const DecodeArgs& a, int b, int h0, int gc, int used,
                                              int split, float* stat, float* wts, int wcap,
-                                             int* s_last, T* outp) {
+                                             int* s_last, T* outp, int arrivals = 0,
+                                             bool write_ml = true) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nthreads = blockDim.x, nwarps = nthreads >> 5;
     const int hd = a.hd;
-    if (tid < gc) {
+    if (arrivals == 0) arrivals = used;        // one arrival per partial result
+    if (write_ml && tid < gc) {
         float* dst = a.part_ml + (((size_t)b * a.nh + h0 + tid) * a.n_splits + split) * 2;
         dst[0] = stat[tid * 2];
         dst[1] = stat[tid * 2 + 1];
@@ -100,7 +102,7 @@ __device__ __forceinline__ void finish_split(const DecodeArgs& a, int b, int h0,
     int* counter = a.counters + (size_t)b * gridDim.y + blockIdx.y;
     if (tid == 0) {
         const int seen = atomicAdd(counter, 1);
-        *s_last = (seen == used - 1);
+        *s_last = (seen == arrivals - 1);
     }
     __syncthreads();
     if (!*s_last) return;
@@ -176,7 +178,7 @@ attention_decode_split_kernel(DecodeArgs a) {
     pdl_wait();
     pdl_launch_next();
     constexpr int VEC = Vec16<T>::N;
-    extern __shared__ __align__(16) unsigned char smem_raw[];
+    extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ int s_last;
     const int b = blockIdx.z, split = blockIdx.x;
     const int G = a.nh / a.nkv;
@@ -344,9 +346,27 @@ __device__ __forceinline__ int dm_swz(int row, int chunk) {
     return row * W + (((chunk & ~7) | ((chunk ^ row) & 7)) << 3);
 }
 
+__device__ __forceinline__ void dm_cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n"
+                 "barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float dm_ld_peer(const float* local, unsigned rank) {
+    unsigned remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(dm_smem(local)),
+                 "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
+// cs = 1: every chunk's partial result goes through global scratch and the last
+// CTA to arrive merges.  cs = 2, 4, 8: the cs CTAs of consecutive chunks form a
+// thread-block cluster and merge through distributed shared memory; only a
+// sequence longer than one cluster's chunks still goes through global scratch,
+// with one partial result per cluster.
 template <int HDP>
 __global__ void __launch_bounds__(DM_THREADS)
-attention_decode_mma_kernel(DecodeArgs a) {
+attention_decode_mma_kernel(DecodeArgs a, int cs) {
     pdl_wait();
     pdl_launch_next();
     typedef __nv_bfloat16 T;
@@ -379,10 +399,15 @@ attention_decode_mma_kernel(DecodeArgs a) {
     const int p = a.positions[b];
     const int lo = a.window > 0 ? max(0, p - a.window + 1) : 0;
     const int j0 = lo + split * DM_KEYS;
-    if (j0 > p) return;
-    const int n = min(DM_KEYS, p - j0 + 1);
-    const int used = (p - lo) / DM_KEYS + 1;
+    const int used = (p - lo) / DM_KEYS + 1;                  // chunks this sequence has
+    const int cid = split / cs, crank = split % cs;
+    const int used_clusters = (used + cs - 1) / cs;
+    if (cid >= used_clusters) return;                         // the whole cluster is past the end
+    const bool has = j0 <= p;                                 // (always true when cs == 1)
+    const int n = has ? min(DM_KEYS, p - j0 + 1) : 0;
+    float* Osm = reinterpret_cast<float*>(Ks);                // [16][HDP], after the scores are done
 
+    if (has) {
     const int* table = a.page_table + (size_t)slot * a.max_pages;
     if (tid < DM_KEYS) {
         const int row = (j0 + tid) % a.cap;
@@ -483,6 +508,9 @@ attention_decode_mma_kernel(DecodeArgs a) {
                     const float inv = 1.0f / stat[row * 2 + 1];
                     outp[row * hd + d] = __float2bfloat16_rn(v0 * inv);
                     outp[row * hd + d + 1] = __float2bfloat16_rn(v1 * inv);
+                } else if (cs > 1) {
+                    Osm[row * HDP + d] = v0;
+                    Osm[row * HDP + d + 1] = v1;
                 } else {
                     float* dst = a.part_acc +
                                  (((size_t)b * a.nh + h0 + row) * a.n_splits + split) * hd + d;
@@ -492,9 +520,64 @@ attention_decode_mma_kernel(DecodeArgs a) {
             }
         }
     }
-    if (used == 1) return;
-    finish_split<T>(a, b, h0, gc, used, split, stat, reinterpret_cast<float*>(smem_raw),
-                    (int)((size_t)2 * DM_KEYS * HDP * sizeof(T) / sizeof(float)), &s_last, outp);
+    } else if (tid < DM_HEADS) {
+        // a chunk past the sequence's end inside a live cluster contributes nothing
+        stat[tid * 2] = -INFINITY;
+        stat[tid * 2 + 1] = 0.f;
+    }
+    if (used == 1) return;                     // (one chunk: its cluster has no other live CTA)
+    const int wcap = (int)((size_t)2 * DM_KEYS * HDP * sizeof(T) / sizeof(float));
+    if (cs == 1) {
+        finish_split<T>(a, b, h0, gc, used, split, stat, reinterpret_cast<float*>(smem_raw), wcap,
+                        &s_last, outp);
+        return;
+    }
+    // ---- merge inside the cluster: rank r owns a slice of the head dimension
+    dm_cluster_sync();
+    {
+        const int DS = HDP / cs;                               // dims per rank
+        for (int item = tid; item < gc * DS; item += DM_THREADS) {
+            const int row = item / DS, d = crank * DS + item % DS;
+            float mq[8], lq[8], oq[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const unsigned qq = q < cs ? q : 0;
+                mq[q] = dm_ld_peer(stat + row * 2, qq);
+                lq[q] = dm_ld_peer(stat + row * 2 + 1, qq);
+                oq[q] = dm_ld_peer(Osm + row * HDP + d, qq);
+            }
+            float M = -INFINITY;
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+                if (q < cs) M = fmaxf(M, mq[q]);
+            float L = 0.f, O = 0.f;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                if (q < cs && lq[q] > 0.f) {                  // a peer without keys holds no data
+                    const float w = expf(mq[q] - M);
+                    L = fmaf(w, lq[q], L);
+                    O = fmaf(w, oq[q], O);
+                }
+            }
+            if (d < hd) {
+                if (used_clusters == 1) {
+                    outp[row * hd + d] = __float2bfloat16_rn(O / L);
+                } else {
+                    a.part_acc[(((size_t)b * a.nh + h0 + row) * a.n_splits + cid) * hd + d] = O;
+                    if (d == 0) {
+                        float* ml = a.part_ml + (((size_t)b * a.nh + h0 + row) * a.n_splits + cid) * 2;
+                        ml[0] = M;
+                        ml[1] = L;
+                    }
+                }
+            }
+        }
+    }
+    dm_cluster_sync();                         // nobody leaves while a peer may still read it
+    if (used_clusters == 1) return;
+    // a long sequence: one partial result per cluster, merged by the last CTA to arrive
+    finish_split<T>(a, b, h0, gc, used_clusters, cid, stat, reinterpret_cast<float*>(smem_raw), wcap,
+                    &s_last, outp, used_clusters * cs, false);
 }
 
 template <int HDP>
@@ -508,8 +591,14 @@ int launch_decode_mma(const DecodeArgs& a, int B, cudaStream_t stream) {
         configured = true;
     }
     const int G = a.nh / a.nkv;
-    dim3 grid(a.n_splits, a.nkv * ((G + DM_HEADS - 1) / DM_HEADS), B);
-    agv_launch(kern, grid, DM_THREADS, smem, stream, a);
+    int cs = 1;
+    while (cs < 8 && cs * 2 <= a.n_splits) cs *= 2;
+    const int splits_grid = (a.n_splits + cs - 1) / cs * cs;
+    dim3 grid(splits_grid, a.nkv * ((G + DM_HEADS - 1) / DM_HEADS), B);
+    if (cs > 1)
+        agv_launch_cluster(kern, grid, DM_THREADS, smem, stream, dim3(cs, 1, 1), a, cs);
+    else
+        agv_launch(kern, grid, DM_THREADS, smem, stream, a, 1);
     AGV_LAUNCH_OK("attention_decode_mma_kernel");
     return 0;
 }

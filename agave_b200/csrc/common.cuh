@@ -70,10 +70,10 @@ inline void agv_launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t sme
     (void)cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);   // error: cudaGetLastError
 }
 
-// The same with the CTAs grouped into thread-block clusters of cluster_z along z.
+// The same with the CTAs grouped into thread-block clusters.
 template <typename... KArgs, typename... Args>
 inline void agv_launch_cluster(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
-                               cudaStream_t stream, unsigned cluster_z, Args&&... args) {
+                               cudaStream_t stream, dim3 cluster, Args&&... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -83,9 +83,9 @@ inline void agv_launch_cluster(void (*kern)(KArgs...), dim3 grid, dim3 block, si
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = g_agv_pdl ? 1 : 0;
     attr[1].id = cudaLaunchAttributeClusterDimension;
-    attr[1].val.clusterDim.x = 1;
-    attr[1].val.clusterDim.y = 1;
-    attr[1].val.clusterDim.z = cluster_z;
+    attr[1].val.clusterDim.x = cluster.x;
+    attr[1].val.clusterDim.y = cluster.y;
+    attr[1].val.clusterDim.z = cluster.z;
     cfg.attrs = attr;
     cfg.numAttrs = 2;
     (void)cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);

@@ -537,7 +537,8 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx,
     dim3 grid((N + rows_per_cta - 1) / rows_per_cta, (T + BN - 1) / BN, splits);
     AGV_REQUIRE(grid.y <= 65535, "linear: %d tokens exceed the grid limit", T);
     if (cluster_reduce)
-        agv_launch_cluster(kern, grid, GEMM_THREADS, TL::SMEM, stream, (unsigned)cluster_reduce, mw,
+        agv_launch_cluster(kern, grid, GEMM_THREADS, TL::SMEM, stream,
+                           dim3(1, 1, (unsigned)cluster_reduce), mw,
                            mw2, mx, (TO*)out, T, N, K, ldc, split_stride, kb_per_split, act,
                            cluster_reduce);
     else
