@@ -8,7 +8,6 @@
 // rotation angle src/backend/kernels/cuda/rope.zig:9-37 (here without the
 // approximate sin/cos).
 #include "common.cuh"
-#include <stdlib.h>
 
 // ------------------------------------------------------------------ embedding
 template <typename TW>
@@ -237,9 +236,9 @@ static int launch_norm(float* h, const void* y, int n_splits, size_t split_strid
     // the register-resident kernel, one row per CTA: many threads per row when the
     // rows are few (decode, final norm), few threads per row when they are many
     if (H <= 8 * 1024) {
-        int threads = R <= 256 ? (H <= 256 ? 128 : H <= 1024 ? 512 : 1024)
+        const int threads = R <= 256 ? (H <= 256 ? 128 : H <= 1024 ? 512 : 1024)
                                : (H <= 512 ? 128 : 256);
-        if (const char* e = getenv("AGV_NORM_THREADS")) threads = atoi(e);
+
         const int ept = (H + threads - 1) / threads;
 #define AGV_SMALL(E, MT)                                                                        \
     agv_launch(norm_residual_small_kernel<TY, TX, E, MT>, R, threads, 0, stream, h,             \

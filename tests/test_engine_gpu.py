@@ -168,3 +168,46 @@ def test_greedy_generation_through_the_entry_point(name, dtype):
     # one batch after another through the same engine gives the same tokens
     eng2_out = eng.generate(prompts + prompts, max_new_tokens=n_new, stop_token_ids=[])
     assert eng2_out[:len(prompts)] == got and eng2_out[len(prompts):] == got
+
+
+# Layer sizes of the larger family members (two layers, small vocabulary): head size
+# 128 with 32 heads in 16 groups, a width above 4,096, a score scale that is not
+# 1/sqrt(head size), rotary scaling; one sliding and one global layer.
+BIG = {
+    "4b": dict(hidden_size=2560, num_attention_heads=8, num_key_value_heads=4, head_dim=256,
+               query_pre_attn_scalar=256, intermediate_size=10240),
+    "27b": dict(hidden_size=5376, num_attention_heads=32, num_key_value_heads=16, head_dim=128,
+                query_pre_attn_scalar=168, intermediate_size=21504),
+}
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("size", ["4b", "27b"])
+def test_layer_sizes_of_the_larger_models(size, dtype):
+    import tempfile
+    from agave_b200.engine.api import Engine
+    from agave_b200.weights import write_model_folder
+    cfg = {"architectures": ["Gemma3ForCausalLM"], "model_type": "gemma3_text",
+           "num_hidden_layers": 2, "vocab_size": 2051, "sliding_window": 24,
+           "sliding_window_pattern": 2, "rope_local_base_freq": 10000.0, "rope_theta": 1000000.0,
+           "rope_scaling": {"rope_type": "linear", "factor": 8.0}, "rms_norm_eps": 1e-6,
+           "max_position_embeddings": 512, "eos_token_id": 1, **BIG[size]}
+    store = torch.float32 if dtype == "float32" else torch.bfloat16
+    with tempfile.TemporaryDirectory() as d:
+        write_model_folder(d, cfg, seed=4, std=0.02, norm_std=0.1, dtype=store)
+        eng = Engine(d, dtype=dtype, max_tokens=512, max_batch=4)
+        seqs = [random_tokens(n, 2051, 300 + n) for n in (70, 9)]
+        refs = [plain_logits(d, s) for s in seqs]
+    slots = [eng.acquire() for _ in seqs]
+    starts = [60, 5]
+    out = eng.step([(slots[i], seqs[i][:starts[i]]) for i in range(2)],
+                   [list(range(starts[i])) for i in range(2)])
+    got = [[out[:60]], [out[60:]]]
+    for k in range(10):
+        live = [i for i in range(2) if starts[i] + k < len(seqs[i])]
+        o = eng.step([(slots[i], [seqs[i][starts[i] + k]]) for i in live], [[0]] * len(live))
+        for j, i in enumerate(live):
+            got[i].append(o[j:j + 1])
+    for i in range(2):
+        close(torch.cat(got[i]), refs[i], TOL[dtype])
+        eng.release(slots[i])
