@@ -25,6 +25,7 @@
 // prompts (src/backend/cuda.zig:1569-1570).
 #include "common.cuh"
 #include <cuda.h>
+#include <stdlib.h>
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -463,6 +464,238 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
     }
 }
 
+// ------------------------------------------------------------ persistent form
+// Prompts: one CTA per SM walks over output tiles.  The accumulator in tensor
+// memory is double-buffered, so the products of a tile run while the epilogue
+// warps still read and store the tile before it; the ring of operand stages runs
+// on across tile boundaries.  Plain (MODE 0) and two-accumulator gated (MODE 1)
+// forms; K may be cut into `splits` ranges whose partial sums go to
+// out + split * split_stride (MODE 0, 32-bit out).
+template <int BN, int MODE>
+struct PTile {
+    static constexpr bool DUAL = MODE == 1;
+    static constexpr int A_BYTES = TILE_M * TILE_K * 2;
+    static constexpr int B_BYTES = BN * TILE_K * 2;
+    static constexpr int STAGE_BYTES = A_BYTES * (DUAL ? 2 : 1) + B_BYTES;
+    static constexpr int ACC_COLS = DUAL ? 2 * BN : BN;
+    static constexpr int TMEM_COLS = 2 * ACC_COLS;              // two accumulator stages
+    static constexpr int STAGES_RAW = (200 * 1024) / STAGE_BYTES;
+    static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+    static constexpr int EPI_BYTES = 4 * 16 * 32 * 4;           // per-warp staging, worst case f32
+    static constexpr int SMEM = STAGES * STAGE_BYTES + EPI_BYTES + 1024 + 256;
+    static_assert(TMEM_COLS <= 512 && TMEM_COLS >= 32, "accumulators must fit tensor memory");
+};
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+template <int BN, int MODE, typename TO>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w,
+                               const __grid_constant__ CUtensorMap map_w2,
+                               const __grid_constant__ CUtensorMap map_x, TO* __restrict__ out,
+                               int T, int N, int K, long long ldc, long long split_stride,
+                               int splits, int kb_per_split, int act) {
+    pdl_launch_next();
+    using TL = PTile<BN, MODE>;
+    constexpr bool GATED = MODE == 1;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* epi = smem + TL::STAGES * TL::STAGE_BYTES;
+    uint64_t* full = (uint64_t*)(epi + TL::EPI_BYTES);
+    uint64_t* empty = full + TL::STAGES;
+    uint64_t* acc_full = empty + TL::STAGES;        // [2]
+    uint64_t* acc_empty = acc_full + 2;             // [2]
+    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m_tiles = (N + TILE_M - 1) / TILE_M, n_tiles = (T + BN - 1) / BN;
+    const int tiles = m_tiles * n_tiles, items = tiles * splits;
+    const int kb_total = (K + TILE_K - 1) / TILE_K;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TL::STAGES; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&acc_full[s], 1);
+            mbar_init(&acc_empty[s], 4);            // one arrival per epilogue warp
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         smem_u32(tmem_slot)),
+                     "r"((uint32_t)TL::TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    // item -> (split, weight tile, token tile); token tiles vary fastest so that the
+    // CTAs of a wave share weight tiles in L2
+    auto decode_item = [&](int item, int& m0, int& n0, int& kb_begin, int& n_kb, int& split) {
+        split = item / tiles;
+        const int t = item % tiles;
+        m0 = (t / n_tiles) * TILE_M;
+        n0 = (t % n_tiles) * BN;
+        kb_begin = split * kb_per_split;
+        n_kb = min(kb_total, kb_begin + kb_per_split) - kb_begin;
+    };
+
+    if (warp == 0 && lane == 0) {
+        // ------------------------------------------------------------ loader
+        int it = 0;                       // k-blocks issued so far, over all tiles
+        bool waited = false;
+        for (int item = blockIdx.x; item < items && !*abort_flag; item += gridDim.x) {
+            int m0, n0, kb_begin, n_kb, split;
+            decode_item(item, m0, n0, kb_begin, n_kb, split);
+            for (int i = 0; i < n_kb; ++i, ++it) {
+                const int s = it % TL::STAGES;
+                const uint32_t ph = (it / TL::STAGES) & 1;
+                if (!mbar_wait(&empty[s], ph ^ 1)) {
+                    atomicCAS(&g_gemm_status, 0, (1 << 8) | s);
+                    *abort_flag = 1;
+                    break;
+                }
+                uint8_t* st = smem + s * TL::STAGE_BYTES;
+                mbar_expect_tx(&full[s], TL::STAGE_BYTES);
+                const int kx = (kb_begin + i) * TILE_K;
+                tma_load_2d(st, &map_w, kx, m0, &full[s]);
+                if (GATED) tma_load_2d(st + TL::A_BYTES, &map_w2, kx, m0, &full[s]);
+                if (!waited) {
+                    // the weights never change: the first box is requested before the
+                    // predecessor (which produces x) is known to have finished
+                    pdl_wait();
+                    waited = true;
+                }
+                tma_load_2d(st + TL::A_BYTES * (GATED ? 2 : 1), &map_x, kx, n0, &full[s]);
+            }
+        }
+        if (*abort_flag) {
+            const int first = it > TL::STAGES ? it - TL::STAGES : 0;
+            for (int i = first; i < it; ++i) mbar_wait(&full[i % TL::STAGES], (i / TL::STAGES) & 1);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ------------------------------------------------------------ products
+        constexpr uint32_t idesc = umma_idesc(TILE_M, BN);
+        int it = 0, li = 0;
+        for (int item = blockIdx.x; item < items && !*abort_flag; item += gridDim.x, ++li) {
+            int m0, n0, kb_begin, n_kb, split;
+            decode_item(item, m0, n0, kb_begin, n_kb, split);
+            const int as = li & 1;
+            if (!mbar_wait(&acc_empty[as], ((li >> 1) & 1) ^ 1)) {
+                atomicCAS(&g_gemm_status, 0, (4 << 8) | as);
+                *abort_flag = 1;
+                break;
+            }
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + as * TL::ACC_COLS;
+            for (int i = 0; i < n_kb; ++i, ++it) {
+                const int s = it % TL::STAGES;
+                const uint32_t ph = (it / TL::STAGES) & 1;
+                if (!mbar_wait(&full[s], ph)) {
+                    atomicCAS(&g_gemm_status, 0, (2 << 8) | s);
+                    *abort_flag = 1;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t a_addr = smem_u32(smem + s * TL::STAGE_BYTES);
+                const uint32_t b_addr = a_addr + TL::A_BYTES * (GATED ? 2 : 1);
+#pragma unroll
+                for (int k = 0; k < TILE_K / UMMA_K; ++k) {
+                    const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
+                    const uint64_t bd = umma_desc(b_addr + k * UMMA_K * 2);
+                    tc_mma_bf16(d_tmem, umma_desc(a_addr + k * UMMA_K * 2), bd, idesc, acc);
+                    if (GATED)
+                        tc_mma_bf16(d_tmem + BN,
+                                    umma_desc(a_addr + TL::A_BYTES + k * UMMA_K * 2), bd, idesc, acc);
+                }
+                tc_commit(&empty[s]);
+            }
+            tc_commit(&acc_full[as]);
+        }
+    } else if (warp >= 2) {
+        // ------------------------------------------------------------ epilogue
+        pdl_wait();
+        const int quarter = warp & 3;
+        TO* wst = (TO*)(epi + (warp - 2) * (TL::EPI_BYTES / 4));     // [16 tokens][32 features]
+        constexpr int EPV = 16 / (int)sizeof(TO);                    // elements per 16 bytes
+        constexpr int VPR = 32 / EPV;                                // 16-byte pieces per staged row
+        int li = 0;
+        for (int item = blockIdx.x; item < items; item += gridDim.x, ++li) {
+            int m0, n0, kb_begin, n_kb, split;
+            decode_item(item, m0, n0, kb_begin, n_kb, split);
+            const int as = li & 1;
+            bool ok = !*abort_flag && mbar_wait(&acc_full[as], (li >> 1) & 1);
+            if (!ok) {
+                if (!*abort_flag) atomicCAS(&g_gemm_status, 0, (3 << 8) | as);
+                *abort_flag = 1;
+                break;
+            }
+            tc_fence_after();
+            const uint32_t lane_base =
+                tmem_base + as * TL::ACC_COLS + ((uint32_t)(quarter * 32) << 16);
+            const int f0 = m0 + quarter * 32;                        // this warp's first feature
+            TO* gbase = out + (size_t)split * split_stride + (size_t)n0 * ldc + f0;
+            const bool fast = f0 + 32 <= N && ldc % EPV == 0 && ((uintptr_t)gbase & 15) == 0;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 16) {
+                uint32_t r[16], u[16];
+                tc_ld16(lane_base + c, r);
+                if (GATED) tc_ld16(lane_base + BN + c, u);
+                tc_wait_ld();
+                if (c + 16 >= BN) {
+                    // every value of this accumulator is in registers: hand it back
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&acc_empty[as]);
+                }
+                if (n_kb <= 0) continue;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    float v = __uint_as_float(r[j]);
+                    if (GATED)
+                        v = (act == 1 ? silu_fast(v) : gelu_tanh_fast(v)) * __uint_as_float(u[j]);
+                    store_out<TO>(wst + j * 32 + lane, v);
+                }
+                __syncwarp();
+                const int rows = min(16, T - n0 - c);
+                if (fast) {
+#pragma unroll
+                    for (int i = 0; i < 16 * VPR / 32; ++i) {
+                        const int vi = lane + 32 * i, row = vi / VPR, part = vi % VPR;
+                        if (row < rows)
+                            *reinterpret_cast<uint4*>(gbase + (size_t)(c + row) * ldc + part * EPV) =
+                                reinterpret_cast<const uint4*>(wst)[vi];
+                    }
+                } else {
+                    for (int i = lane; i < 16 * 32; i += 32) {
+                        const int row = i / 32, fl = i % 32;
+                        if (row < rows && f0 + fl < N) gbase[(size_t)(c + row) * ldc + fl] = wst[i];
+                    }
+                }
+                __syncwarp();
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                     "r"((uint32_t)TL::TMEM_COLS)
+                     : "memory");
+    }
+}
+
 // ---------------------------------------------------------------- tensor maps
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -548,6 +781,31 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx,
     return 0;
 }
 
+template <int BN, int MODE, typename TO>
+int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx,
+                      void* out, int T, int N, int K, long long ldc, long long split_stride,
+                      int splits, int kb_per_split, int act, cudaStream_t stream) {
+    using TL = PTile<BN, MODE>;
+    auto kern = gemm_tcgen05_persistent_kernel<BN, MODE, TO>;
+    static bool configured = false;
+    static int sms = 0;
+    if (!configured) {
+        AGV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         TL::SMEM));
+        int dev = 0;
+        AGV_CUDA_OK(cudaGetDevice(&dev));
+        AGV_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        configured = true;
+    }
+    const long long items =
+        (long long)((N + TILE_M - 1) / TILE_M) * ((T + BN - 1) / BN) * splits;
+    const int grid = (int)(items < sms ? items : sms);
+    agv_launch(kern, grid, GEMM_THREADS, TL::SMEM, stream, mw, mw2, mx, (TO*)out, T, N, K, ldc,
+               split_stride, splits, kb_per_split, act);
+    AGV_LAUNCH_OK("gemm_tcgen05_persistent_kernel");
+    return 0;
+}
+
 template <int MODE, typename TO>
 int launch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx,
               void* out, int T, int N, int K, long long ldc, long long split_stride, int splits,
@@ -627,9 +885,23 @@ AGV_API int agv_linear_tc(const void* x, const void* w, const void* w2, void* ou
     } else {
         mw2 = mw;
     }
+    const bool persistent = T > 128 && !cluster && token_tile == 0 && getenv("AGV_GEMM_ONESHOT") == nullptr;
+    if (persistent) bn = w2 ? 128 : 256;
     if (int rc = make_map(&mx, x, T, K, lda, bn)) return rc;
     const long long split_stride = (long long)T * ldc;
     const int creduce = splits > 1 ? cluster : 0;
+    if (persistent) {
+        if (w2) {
+            AGV_REQUIRE(out_dtype == AGV_BF16, "linear: the gated form writes bfloat16");
+            return launch_persistent<128, 1, __nv_bfloat16>(mw, mw2, mx, out, T, N, K, ldc, 0, 1,
+                                                            kb_total, act, stream);
+        }
+        if (out_dtype == AGV_BF16)
+            return launch_persistent<256, 0, __nv_bfloat16>(mw, mw2, mx, out, T, N, K, ldc, 0, 1,
+                                                            kb_total, act, stream);
+        return launch_persistent<256, 0, float>(mw, mw2, mx, out, T, N, K, ldc, split_stride,
+                                                splits, kb_per, act, stream);
+    }
     if (w2) {
         AGV_REQUIRE(out_dtype == AGV_BF16, "linear: the gated form writes bfloat16");
         if (half)

@@ -34,6 +34,15 @@ CONFIG_1B = {
     "max_position_embeddings": 32768, "hidden_activation": "gelu_pytorch_tanh",
     "bos_token_id": 2, "eos_token_id": 1,
 }
+# layer sizes of the larger family members (--shapes 4b / 27b); the default run is 1b
+CONFIG_4B = dict(CONFIG_1B, num_hidden_layers=34, hidden_size=2560, num_attention_heads=8,
+                 num_key_value_heads=4, head_dim=256, query_pre_attn_scalar=256,
+                 intermediate_size=10240, vocab_size=262208, sliding_window=1024,
+                 rope_scaling={"rope_type": "linear", "factor": 8.0}, max_position_embeddings=131072)
+CONFIG_27B = dict(CONFIG_4B, num_hidden_layers=62, hidden_size=5376, num_attention_heads=32,
+                  num_key_value_heads=16, head_dim=128, query_pre_attn_scalar=168,
+                  intermediate_size=21504)
+SHAPES = {"1b": (CONFIG_1B, 2), "4b": (CONFIG_4B, 3), "27b": (CONFIG_27B, 4)}
 CONTEXT = 8192
 PREFILL_TOKENS = 2048
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
@@ -195,6 +204,8 @@ def main():
     ap.add_argument("--layers", type=int, default=0,
                     help="run fewer layers than the configuration has (0 = all)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--shapes", default="1b", choices=sorted(SHAPES),
+                    help="layer sizes to run (the default, 1b, is the benchmark configuration)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -207,12 +218,13 @@ def main():
     from agave_b200 import kernels
     from agave_b200.engine.api import Engine
 
-    cfg = dict(CONFIG_1B)
+    base_cfg, seed = SHAPES[args.shapes]
+    cfg = dict(base_cfg)
     full_layers = cfg["num_hidden_layers"]
     if args.layers:
         cfg["num_hidden_layers"] = args.layers
     pk = peaks()
-    engine = Engine.from_config(cfg, seed=2, std=0.02, norm_std=0.1, dtype="bfloat16",
+    engine = Engine.from_config(cfg, seed=seed, std=0.02, norm_std=0.1, dtype="bfloat16",
                                 max_tokens=64 * CONTEXT, ctx_size=CONTEXT, max_batch=64)
     V = engine.spec.vocab_size
     g = torch.Generator().manual_seed(5)
@@ -268,18 +280,18 @@ def main():
            "d2h_bytes_per_step": int(graph.next_host.numel() * 4)}
 
     out = {
-        "metric": "Gemma3-1B bf16 decode tokens/s at batch 8 (context 8192)",
+        "metric": f"Gemma3-{args.shapes.upper()} bf16 decode tokens/s at batch 8 (context 8192)",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(ms8, 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {
-            "model": "gemma3-1b-shapes-random", "layers": cfg["num_hidden_layers"],
+            "model": f"gemma3-{args.shapes}-shapes-random", "layers": cfg["num_hidden_layers"],
             "layers_full": full_layers, "hidden": cfg["hidden_size"],
             "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
             "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"],
             "vocab": cfg["vocab_size"], "sliding_window": cfg["sliding_window"],
             "local_per_global": cfg["sliding_window_pattern"] - 1, "global_batch": 8,
-            "seq_len": CONTEXT, "prompt_lens": "128..2048 unequal", "seed": 2,
+            "seq_len": CONTEXT, "prompt_lens": "128..2048 unequal", "seed": seed,
             "parallelism": "single-gpu", "cache": "paged bf16",
             "l2": "inputs larger than L2 (2 GB weights per step)"},
         "prefill": prefill, "roofline": roofline, "points": points, "e2e": e2e,
