@@ -211,3 +211,44 @@ def test_layer_sizes_of_the_larger_models(size, dtype):
     for i in range(2):
         close(torch.cat(got[i]), refs[i], TOL[dtype])
         eng.release(slots[i])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_sizes_the_fast_kernels_refuse_take_the_other_path(dtype):
+    """A width that is no multiple of 8 (no TMA rows), a head size of 48, three heads
+    in three groups, a vocabulary and a feed-forward width that are no power of two."""
+    import tempfile
+    from agave_b200.engine.api import Engine
+    from agave_b200.weights import write_model_folder
+    cfg = {"architectures": ["Gemma3ForCausalLM"], "model_type": "gemma3_text",
+           "num_hidden_layers": 3, "hidden_size": 100, "num_attention_heads": 3,
+           "num_key_value_heads": 3, "head_dim": 48, "query_pre_attn_scalar": 30,
+           "intermediate_size": 136, "vocab_size": 301, "sliding_window": 10,
+           "sliding_window_pattern": 3, "rope_local_base_freq": 7000.0, "rope_theta": 300000.0,
+           "rope_scaling": {"rope_type": "linear", "factor": 4.0}, "rms_norm_eps": 1e-5,
+           "max_position_embeddings": 512, "eos_token_id": 1}
+    store = torch.float32 if dtype == "float32" else torch.bfloat16
+    with tempfile.TemporaryDirectory() as d:
+        write_model_folder(d, cfg, seed=11, std=0.05, norm_std=0.2, dtype=store)
+        eng = Engine(d, dtype=dtype, max_tokens=512, max_batch=4)
+        seqs = [random_tokens(n, 301, 500 + n) for n in (37, 80)]
+        refs = [plain_logits(d, s) for s in seqs]
+    slots = [eng.acquire() for _ in seqs]
+    starts = [30, 70]
+    out = eng.step([(slots[i], seqs[i][:starts[i]]) for i in range(2)],
+                   [list(range(starts[i])) for i in range(2)])
+    got = [[out[:30]], [out[30:]]]
+    for k in range(10):
+        live = [i for i in range(2) if starts[i] + k < len(seqs[i])]
+        o = eng.step([(slots[i], [seqs[i][starts[i] + k]]) for i in live], [[0]] * len(live))
+        for j, i in enumerate(live):
+            got[i].append(o[j:j + 1])
+    for i in range(2):
+        close(torch.cat(got[i]), refs[i], TOL[dtype])
+        eng.release(slots[i])
+    # and generation with sampling options runs through the same engine
+    outs = eng.generate([seqs[0][:5]], max_new_tokens=6, temperature=0.8, top_k=12, top_p=0.9,
+                        repeat_penalty=1.2, seed=3, stop_token_ids=[])
+    again = eng.generate([seqs[0][:5]], max_new_tokens=6, temperature=0.8, top_k=12, top_p=0.9,
+                         repeat_penalty=1.2, seed=3, stop_token_ids=[])
+    assert outs == again and len(outs[0]) == 6
