@@ -53,9 +53,13 @@ class _DecodeGraph:
         dev = engine.device
         B = size
         n_int = round_up(3 * B + 3 * B + 1 + B, 2)     # step arrays, sampling steps; even
-        self.host = torch.zeros(n_int + 2 * B, dtype=torch.int32, pin_memory=True)
+        # two pinned staging buffers: the next step's arrays are filled while the
+        # copy of this step's may still be in flight
+        self.hosts = [torch.zeros(n_int + 2 * B, dtype=torch.int32, pin_memory=True)
+                      for _ in range(2)]
+        self.hosts_np = [h.numpy() for h in self.hosts]
+        self.host, self.host_np = self.hosts[0], self.hosts_np[0]
         self.dev = torch.zeros(n_int + 2 * B, dtype=torch.int32, device=dev)
-        self.host_np = self.host.numpy()
         d = self.dev
         o = 3 * B
         self.views = dict(tokens=d[:B], positions=d[B:2 * B], seq_index=d[2 * B:3 * B],
@@ -101,14 +105,22 @@ class _DecodeGraph:
         self.kernels_per_step = kernels.launch_count() - n0
         self.graph = g
 
-    def run(self, engine: "Engine", params: SamplingParams, seed: int) -> None:
-        self.dev.copy_(self.host, non_blocking=True)
+    def launch(self, engine: "Engine", params: SamplingParams, seed: int, which: int = 0) -> None:
+        """Copy staging buffer ``which`` in, run the step, start the copy of the
+        chosen tokens out; returns without waiting."""
+        self.dev.copy_(self.hosts[which], non_blocking=True)
         if self.graph is not None:
             self.graph.replay()
         else:
             self._body(engine, params, seed)
         self.next_host.copy_(self.next_dev, non_blocking=True)
+
+    def wait(self) -> None:
         torch.cuda.current_stream().synchronize()
+
+    def run(self, engine: "Engine", params: SamplingParams, seed: int) -> None:
+        self.launch(engine, params, seed)
+        self.wait()
 
 
 class Engine:
@@ -240,17 +252,7 @@ class Engine:
                 r.slot = -1
             # one token each until the batch is empty
             t0 = time.perf_counter()
-            while True:
-                live = plan.live()
-                if not live:
-                    break
-                sampled = self._decode_step(live, params, seed)
-                stats["decode_steps"] += 1
-                stats["decode_tokens"] += len(live)
-                ended = plan.accept({r.index: sampled[i] for i, r in enumerate(live)})
-                for r in ended:
-                    self.release(r.slot)
-                    r.slot = -1
+            self._decode_loop(plan, params, seed, stats)
             stats["decode_seconds"] += time.perf_counter() - t0
         finally:
             for r in batch:
@@ -268,39 +270,71 @@ class Engine:
             g = self._graphs[key] = _DecodeGraph(self, size, params, seed)
         return g
 
-    def _decode_step(self, live, params: SamplingParams, seed: int) -> List[int]:
-        """Feed each live sequence its last token; return the next ones."""
+    def _stage_step(self, live, params: SamplingParams, seed: int, ahead: int, which: int):
+        """Fill staging buffer ``which`` of the live set's graph with everything a
+        decode step needs except the token ids, for the step ``ahead`` steps after
+        the last committed one; reserves the cache rows it will write."""
         n = len(live)
         B = _bucket(n)
         g = self._graph_for(B, params, seed)
         book = self.runner.cache.book
         for r in live:
-            self.runner.cache.reserve(r.slot, book.length[r.slot] + 1)
-        self.runner.cache.flush()
-        a = g.host_np
-        lens = np.fromiter((book.length[r.slot] for r in live), dtype=np.int32, count=n)
-        a[:B] = 0
-        a[:n] = np.fromiter((r.output[-1] for r in live), dtype=np.int32, count=n)
-        a[B:2 * B] = 0
+            self.runner.cache.reserve(r.slot, book.length[r.slot] + ahead + 1)
+        a = g.hosts_np[which]
+        lens = np.fromiter((book.length[r.slot] + ahead for r in live), dtype=np.int32, count=n)
+        a[:2 * B] = 0
         a[B:B + n] = lens
         a[2 * B:3 * B] = np.arange(B, dtype=np.int32)
         o = 3 * B
         a[o:o + B + 1] = np.arange(B + 1, dtype=np.int32)
         a[o + B + 1:o + 2 * B + 1] = -1
         a[o + B + 1:o + B + 1 + n] = np.fromiter((r.slot for r in live), dtype=np.int32, count=n)
-        a[o + 2 * B + 1:o + 3 * B + 1] = 0
+        a[o + 2 * B + 1:o + 4 * B + 1] = 0
         a[o + 2 * B + 1:o + 2 * B + 1 + n] = lens + 1
-        a[o + 3 * B + 1:o + 4 * B + 1] = 0
-        a[o + 3 * B + 1:o + 3 * B + 1 + n] = np.fromiter((len(r.output) for r in live),
+        a[o + 3 * B + 1:o + 3 * B + 1 + n] = np.fromiter((len(r.output) + ahead for r in live),
                                                         dtype=np.int32, count=n)
         ids = a[g.n_int:].view(np.int64)
         ids[:] = 0
         ids[:n] = np.fromiter((r.index for r in live), dtype=np.int64, count=n)
-        g.run(self, params, seed)
-        for r in live:
-            book.set_length(r.slot, book.length[r.slot] + 1)
-        out = g.next_host.numpy()
-        return [int(out[i]) for i in range(n)]
+        return g
+
+    def _decode_loop(self, plan: GenerationPlan, params: SamplingParams, seed: int,
+                     stats: dict) -> None:
+        """One token for every live sequence per step until the batch is empty.
+        While a step runs on the GPU the host stages the next one (all but the
+        token ids, which it does not know yet) on the guess that nobody ends."""
+        book = self.runner.cache.book
+        live = plan.live()
+        staged = None                      # (graph, buffer index) staged for `live`
+        which = 0
+        while live:
+            n = len(live)
+            if staged is None:
+                staged = (self._stage_step(live, params, seed, 0, which), which)
+            g, w = staged
+            g.hosts_np[w][:n] = np.fromiter((r.output[-1] for r in live), dtype=np.int32, count=n)
+            self.runner.cache.flush()
+            g.launch(self, params, seed, w)
+            # meanwhile: the step after this one
+            staged, which = None, 1 - w
+            try:
+                staged = (self._stage_step(live, params, seed, 1, which), which)
+            except Exception:
+                staged = None              # a sequence is at its limit; it ends with this step
+            g.wait()
+            out = g.next_host.numpy()
+            sampled = {r.index: int(out[i]) for i, r in enumerate(live)}
+            for r in live:
+                book.set_length(r.slot, book.length[r.slot] + 1)
+            stats["decode_steps"] += 1
+            stats["decode_tokens"] += n
+            ended = plan.accept(sampled)
+            for r in ended:
+                self.release(r.slot)
+                r.slot = -1
+            if ended:
+                staged = None              # the batch changed: stage afresh
+                live = plan.live()
 
     # ----------------------------------------------------------------- info
     def model_info(self) -> dict:

@@ -162,7 +162,7 @@ def timed_decode(engine, torch, kernels, batch, steps, warmup, seed):
     for s in slots:
         engine.runner.cache.reserve(s, book.length[s] + total)
     engine.runner.cache.flush()
-    staged = torch.zeros((total, graph.host.numel()), dtype=torch.int32)
+    staged = torch.zeros((total, graph.hosts[0].numel()), dtype=torch.int32)
     toks = torch.randint(3, V, (total, batch), generator=g, dtype=torch.int32)
     for k in range(total):
         a = staged[k].numpy()
@@ -276,7 +276,7 @@ def main():
     e2e_val = st["decode_tokens"] / st["decode_seconds"]
     graph = next(iter(engine._graphs.values()))
     e2e = {"value": round(e2e_val, 1), "unit": "tokens/s",
-           "h2d_bytes_per_step": int(graph.host.numel() * 4),
+           "h2d_bytes_per_step": int(graph.hosts[0].numel() * 4),
            "d2h_bytes_per_step": int(graph.next_host.numel() * 4)}
 
     out = {
