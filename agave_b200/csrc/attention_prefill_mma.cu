@@ -94,7 +94,8 @@ attention_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_st
 
     const int b = blockIdx.z, h = blockIdx.y;
     const int seq0 = cu_seqlens[b], len = cu_seqlens[b + 1] - seq0;
-    const int m0 = blockIdx.x * FA_M;
+    // tiles at the end of a sequence walk the most key tiles: they are scheduled first
+    const int m0 = (gridDim.x - 1 - blockIdx.x) * FA_M;
     if (m0 >= len) return;
     const int g = h / (nh / nkv);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;

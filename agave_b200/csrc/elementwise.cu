@@ -8,6 +8,7 @@
 // rotation angle src/backend/kernels/cuda/rope.zig:9-37 (here without the
 // approximate sin/cos).
 #include "common.cuh"
+#include <type_traits>
 
 // ------------------------------------------------------------------ embedding
 template <typename TW>
@@ -228,11 +229,142 @@ norm_residual_small_kernel(float* __restrict__ h, const TY* __restrict__ y, int 
     }
 }
 
+// Many rows (prompts), 32-bit branch input, width a multiple of 4 up to 2,048: one
+// warp per row with 16-byte loads and no block-wide barrier.
+template <typename TX> struct Pack4;
+template <> struct Pack4<float> {
+    __device__ static void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Pack4<__nv_bfloat16> {
+    __device__ static void store(__nv_bfloat16* p, float4 v) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        uint2 u;
+        u.x = *reinterpret_cast<unsigned*>(&a);
+        u.y = *reinterpret_cast<unsigned*>(&b);
+        *reinterpret_cast<uint2*>(p) = u;
+    }
+};
+
+template <typename TX, int NV>
+__global__ void __launch_bounds__(128)
+norm_residual_warp_kernel(float* __restrict__ h, const float* __restrict__ y, int n_splits,
+                          size_t split_stride, const float* __restrict__ w_post,
+                          const float* __restrict__ w_next, TX* __restrict__ x, int R, int H,
+                          float eps_post, float eps_next, int add_residual) {
+    pdl_wait();
+    pdl_launch_next();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x * 4 + warp;
+    if (row >= R) return;
+    const int H4 = H >> 2;
+    const size_t base = (size_t)row * H;
+    float4 v[NV], hv[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int idx = lane + 32 * i;
+        const bool in = idx < H4;
+        v[i] = in ? reinterpret_cast<const float4*>(y + base)[idx] : make_float4(0, 0, 0, 0);
+        hv[i] = (in && add_residual) ? reinterpret_cast<const float4*>(h + base)[idx]
+                                     : make_float4(0, 0, 0, 0);
+    }
+    for (int s = 1; s < n_splits; ++s) {
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int idx = lane + 32 * i;
+            if (idx < H4) {
+                const float4 t = reinterpret_cast<const float4*>(y + s * split_stride + base)[idx];
+                v[i].x += t.x; v[i].y += t.y; v[i].z += t.z; v[i].w += t.w;
+            }
+        }
+    }
+    float rs = 1.f;
+    if (w_post) {
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < NV; ++i)
+            ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+        ss = warp_sum(ss);
+        rs = 1.0f / sqrtf(ss / (float)H + eps_post);
+    }
+    float ss2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int idx = lane + 32 * i;
+        if (idx < H4) {
+            if (w_post) {
+                const float4 w = reinterpret_cast<const float4*>(w_post)[idx];
+                v[i].x = v[i].x * rs * w.x; v[i].y = v[i].y * rs * w.y;
+                v[i].z = v[i].z * rs * w.z; v[i].w = v[i].w * rs * w.w;
+            }
+            if (add_residual) {
+                v[i].x += hv[i].x; v[i].y += hv[i].y; v[i].z += hv[i].z; v[i].w += hv[i].w;
+                reinterpret_cast<float4*>(h + base)[idx] = v[i];
+            }
+            ss2 += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+        }
+    }
+    if (w_next) {
+        ss2 = warp_sum(ss2);
+        const float r2 = 1.0f / sqrtf(ss2 / (float)H + eps_next);
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int idx = lane + 32 * i;
+            if (idx < H4) {
+                const float4 w = reinterpret_cast<const float4*>(w_next)[idx];
+                Pack4<TX>::store(x + base + 4 * idx,
+                                 make_float4(v[i].x * r2 * w.x, v[i].y * r2 * w.y,
+                                             v[i].z * r2 * w.z, v[i].w * r2 * w.w));
+            }
+        }
+    } else if (x) {
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int idx = lane + 32 * i;
+            if (idx < H4) Pack4<TX>::store(x + base + 4 * idx, v[i]);
+        }
+    }
+}
+
+template <typename TX>
+static bool launch_norm_warp(float* h, const float* y, int n_splits, size_t split_stride,
+                             const float* w_post, const float* w_next, TX* x, int R, int H,
+                             float eps_post, float eps_next, int add_residual,
+                             cudaStream_t stream) {
+    const int nv = (H / 4 + 31) / 32;
+    const unsigned grid = (unsigned)((R + 3) / 4);
+#define AGV_WARP(NV)                                                                            \
+    agv_launch(norm_residual_warp_kernel<TX, NV>, grid, 128, 0, stream, h, y, n_splits,         \
+               split_stride, w_post, w_next, x, R, H, eps_post, eps_next, add_residual)
+    if (nv <= 2) AGV_WARP(2);
+    else if (nv <= 4) AGV_WARP(4);
+    else if (nv <= 6) AGV_WARP(6);
+    else if (nv <= 8) AGV_WARP(8);
+    else if (nv <= 10) AGV_WARP(10);
+    else if (nv <= 12) AGV_WARP(12);
+    else if (nv <= 16) AGV_WARP(16);
+    else return false;
+#undef AGV_WARP
+    return true;
+}
+
 template <typename TY, typename TX>
 static int launch_norm(float* h, const void* y, int n_splits, size_t split_stride,
                        const float* w_post, const float* w_next, void* x, const int* rows, int R,
                        int H, float eps_post, float eps_next, int add_residual,
                        cudaStream_t stream) {
+    // many rows with a 32-bit branch input: one warp per row
+    if constexpr (std::is_same<TY, float>::value) {
+        if (R > 256 && y && !rows && H % 4 == 0 && H <= 2048 && agv_aligned(y, 16) &&
+            agv_aligned(h, 16) && agv_aligned(x, 16) && split_stride % 4 == 0 &&
+            (!w_post || agv_aligned(w_post, 16)) && (!w_next || agv_aligned(w_next, 16)) &&
+            (add_residual || !h || true)) {
+            if (launch_norm_warp<TX>(h, (const float*)y, n_splits, split_stride, w_post, w_next,
+                                     (TX*)x, R, H, eps_post, eps_next, add_residual, stream)) {
+                AGV_LAUNCH_OK("norm_residual_warp_kernel");
+                return 0;
+            }
+        }
+    }
     // the register-resident kernel, one row per CTA: many threads per row when the
     // rows are few (decode, final norm), few threads per row when they are many
     if (H <= 8 * 1024) {

@@ -141,10 +141,9 @@ def test_linear_simt_plain_and_gated(dtype):
 
 
 # ---------------------------------------------------------------------- norms
-@pytest.mark.parametrize("H", [48, 1000, 5376])
-def test_norm_family(H):
+@pytest.mark.parametrize("H,R", [(48, 7), (1000, 7), (5376, 7), (1152, 300), (2048, 257), (72, 513)])
+def test_norm_family(H, R):
     from agave_b200 import kernels
-    R = 7
     h = rnd(R, H, seed=1)
     y = rnd(R, H, dtype=torch.bfloat16, seed=2)
     wp, wn = rnd(H, seed=3) * 0.2 + 1, rnd(H, seed=4) * 0.2 + 1
@@ -155,6 +154,7 @@ def test_norm_family(H):
 
     # plain norm with a row gather
     rows = torch.tensor([6, 0, 3], dtype=torch.int32, device=DEV)
+    # (with many rows and a 32-bit branch the one-warp-per-row kernel runs below)
     x = torch.empty((3, H), dtype=torch.float32, device=DEV)
     kernels.norm_residual(h, None, None, wn, x, eps_next=eps_n, rows=rows)
     assert rel_err(x, norm(h[rows.long()], wn, eps_n)) < 1e-6
@@ -170,6 +170,12 @@ def test_norm_family(H):
     h3 = h.clone()
     kernels.norm_residual(h3, parts, None, None, None)
     assert rel_err(h3, h + parts.sum(0)) < 1e-6
+    # 32-bit partial sums with both norms (what follows a tensor-core product)
+    h4 = h.clone()
+    kernels.norm_residual(h4, parts, wp, wn, xb, eps_post=eps_p, eps_next=eps_n)
+    href = h + norm(parts.sum(0), wp, eps_p)
+    assert rel_err(h4, href) < 1e-6
+    assert rel_err(xb, norm(href, wn, eps_n)) < 5e-3
 
 
 # ------------------------------------------------------ embedding and rotation
