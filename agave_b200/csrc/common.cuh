@@ -48,8 +48,12 @@ static inline bool agv_aligned(const void* p, size_t a) { return ((uintptr_t)p %
 __device__ __forceinline__ void pdl_wait() {
     asm volatile("griddepcontrol.wait;" ::: "memory");
 }
+// Only a grid of at most about two waves lets its successor in early: the
+// successor's CTAs sit on SMs while they wait, and a longer grid needs those SMs for
+// its own later waves (a prompt step ran 6 % slower with the early trigger).
 __device__ __forceinline__ void pdl_launch_next() {
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (gridDim.x * gridDim.y * gridDim.z <= 320u)
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
 extern int g_agv_pdl;      // 1: launches carry the programmatic-serialization attribute

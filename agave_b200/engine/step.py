@@ -15,6 +15,7 @@ from __future__ import annotations
 
 from typing import List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 from ..cache import Cache, CacheError
@@ -36,21 +37,6 @@ class Runner:
         self.vocab_size = model.spec.vocab_size
 
     # ------------------------------------------------------------- contexts
-    def _pack(self, tokens: Sequence[int], positions: Sequence[int], seq_index: Sequence[int],
-              cu: Sequence[int], slots: Sequence[int], lens: Sequence[int]):
-        T, B = len(tokens), len(slots)
-        host = torch.empty(3 * T + 3 * B + 1, dtype=torch.int32, pin_memory=True)
-        host[:T] = torch.tensor(tokens, dtype=torch.int32)
-        host[T:2 * T] = torch.tensor(positions, dtype=torch.int32)
-        host[2 * T:3 * T] = torch.tensor(seq_index, dtype=torch.int32)
-        o = 3 * T
-        host[o:o + B + 1] = torch.tensor(cu, dtype=torch.int32)
-        host[o + B + 1:o + 2 * B + 1] = torch.tensor(slots, dtype=torch.int32)
-        host[o + 2 * B + 1:] = torch.tensor(lens, dtype=torch.int32)
-        dev = host.to(self.device, non_blocking=True)
-        return (dev[:T], dev[T:2 * T], dev[2 * T:3 * T], dev[o:o + B + 1],
-                dev[o + B + 1:o + 2 * B + 1], dev[o + 2 * B + 1:])
-
     def context(self, entries: Sequence[Tuple[int, Sequence[int]]]) -> StepContext:
         """Check a batch, reserve its cache room and build its device arrays.
 
@@ -60,58 +46,62 @@ class Runner:
         if not entries:
             raise StepError("a step needs at least one sequence")
         book = self.cache.book
-        real = [(s, t) for s, t in entries if s >= 0]
+        B = len(entries)
+        slots = np.fromiter((s for s, _ in entries), dtype=np.int64, count=B)
+        toks = [np.asarray(t, dtype=np.int64).reshape(-1) for _, t in entries]
+        counts = np.fromiter((t.size for t in toks), dtype=np.int64, count=B)
+        real = slots >= 0
         seen = set()
-        for s, toks in real:
+        for s, c in zip(slots.tolist(), counts.tolist()):
+            if s < 0:
+                continue
             if s not in book.length:
                 raise StepError(f"slot {s} is not held")
             if s in seen:
                 raise StepError(f"slot {s} appears twice in one step")
             seen.add(s)
-            if len(toks) == 0:
+            if c == 0:
                 raise StepError(f"slot {s} brings no tokens")
+        tokens = np.concatenate(toks) if B else np.zeros(0, dtype=np.int64)
         V = self.vocab_size
-        for s, toks in entries:
-            for t in toks:
-                if not 0 <= int(t) < V:
-                    raise StepError(f"token id {t} is outside the vocabulary of {V}")
-        starts = [book.length[s] for s, _ in real]
-        if real and all(st == 0 for st in starts) and len(real) == len(entries):
+        if tokens.size and (tokens.min() < 0 or tokens.max() >= V):
+            bad = tokens[(tokens < 0) | (tokens >= V)][0]
+            raise StepError(f"token id {int(bad)} is outside the vocabulary of {V}")
+        starts = np.fromiter((book.length[s] if s >= 0 else 0 for s in slots.tolist()),
+                             dtype=np.int64, count=B)
+        if real.all() and (starts == 0).all():
             mode = PREFILL
-        elif all(len(t) == 1 for _, t in entries) and all(st > 0 for st in starts):
+        elif (counts == 1).all() and (starts[real] > 0).all():
             mode = DECODE
         else:
             raise StepError("the sequences of a step must either all start at position 0 or "
                             "all go on by exactly one token")
-        # all-or-nothing reservation
-        reserved = []
-        try:
-            for s, toks in real:
-                book_len = book.length[s]
-                self.cache.reserve(s, book_len + len(toks))
-                reserved.append(s)
-        except CacheError:
-            raise
-        tokens: List[int] = []
-        positions: List[int] = []
-        seq_index: List[int] = []
-        cu = [0]
-        slots, lens = [], []
-        for b, (s, toks) in enumerate(entries):
-            start = book.length[s] if s >= 0 else 0
-            tokens.extend(int(t) for t in toks)
-            positions.extend(range(start, start + len(toks)))
-            seq_index.extend([b] * len(toks))
-            cu.append(len(tokens))
-            slots.append(s)
-            lens.append(start + len(toks) if s >= 0 else 0)
+        for s, st, c in zip(slots.tolist(), starts.tolist(), counts.tolist()):
+            if s >= 0:
+                self.cache.reserve(s, st + c)
         self.cache.flush()
-        d = self._pack(tokens, positions, seq_index, cu, slots, lens)
-        ctx = StepContext(mode=mode, n_tokens=len(tokens), batch=len(entries), tokens=d[0],
-                          positions=d[1], seq_index=d[2], cu_seqlens=d[3], slots=d[4], lens=d[5],
-                          max_len=max(lens), max_new=max(len(t) for _, t in entries),
-                          cache=self.cache, dtype=self.dtype, device=self.device)
-        return ctx
+        T = int(counts.sum())
+        cu = np.zeros(B + 1, dtype=np.int64)
+        np.cumsum(counts, out=cu[1:])
+        seq_index = np.repeat(np.arange(B, dtype=np.int64), counts)
+        positions = np.arange(T, dtype=np.int64) - cu[:-1][seq_index] + starts[seq_index]
+        lens = np.where(real, starts + counts, 0)
+        host = torch.empty(3 * T + 3 * B + 1, dtype=torch.int32, pin_memory=True)
+        a = host.numpy()
+        a[:T] = tokens
+        a[T:2 * T] = positions
+        a[2 * T:3 * T] = seq_index
+        o = 3 * T
+        a[o:o + B + 1] = cu
+        a[o + B + 1:o + 2 * B + 1] = slots
+        a[o + 2 * B + 1:] = lens
+        dev = host.to(self.device, non_blocking=True)
+        return StepContext(mode=mode, n_tokens=T, batch=B, tokens=dev[:T],
+                           positions=dev[T:2 * T], seq_index=dev[2 * T:3 * T],
+                           cu_seqlens=dev[o:o + B + 1], slots=dev[o + B + 1:o + 2 * B + 1],
+                           lens=dev[o + 2 * B + 1:], max_len=int(lens.max()),
+                           max_new=int(counts.max()), cache=self.cache, dtype=self.dtype,
+                           device=self.device)
 
     def commit(self, entries: Sequence[Tuple[int, Sequence[int]]]) -> None:
         """Record that the step ran: lengths grow by the tokens brought."""
@@ -143,7 +133,8 @@ class Runner:
         self.commit(entries)
         if not rows:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
-        rows_dev = torch.tensor(rows, dtype=torch.int32).to(self.device)
+        rows_host = torch.tensor(rows, dtype=torch.int32).pin_memory()
+        rows_dev = rows_host.to(self.device, non_blocking=True)
         return self.model.logits(h, rows_dev, ctx)
 
     # ------------------------------------------------------------ lifecycle
