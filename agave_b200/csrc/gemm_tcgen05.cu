@@ -152,7 +152,7 @@ __device__ __forceinline__ float gelu_tanh_fast(float t) {
     asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(u));
     return 0.5f * t * (1.0f + th);
 }
-__device__ __forceinline__ float silu_fast(float t) { return t / (1.0f + __expf(-t)); }
+__device__ __forceinline__ float silu_fast(float t) { return __fdividef(t, 1.0f + __expf(-t)); }
 
 // MODE 0: plain.  MODE 1: gated, gate and up tiles of 128 rows each with an
 // accumulator of their own (prompts).  MODE 2: gated, 64 gate rows and the 64 up
@@ -471,6 +471,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
 // on across tile boundaries.  Plain (MODE 0) and two-accumulator gated (MODE 1)
 // forms; K may be cut into `splits` ranges whose partial sums go to
 // out + split * split_stride (MODE 0, 32-bit out).
+constexpr int PERSISTENT_EPI_WARPS = 8;
+constexpr int PERSISTENT_THREADS = 64 + 32 * PERSISTENT_EPI_WARPS;
+
 template <int BN, int MODE>
 struct PTile {
     static constexpr bool DUAL = MODE == 1;
@@ -481,7 +484,7 @@ struct PTile {
     static constexpr int TMEM_COLS = 2 * ACC_COLS;              // two accumulator stages
     static constexpr int STAGES_RAW = (200 * 1024) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
-    static constexpr int EPI_BYTES = 4 * 16 * 32 * 4;           // per-warp staging, worst case f32
+    static constexpr int EPI_BYTES = PERSISTENT_EPI_WARPS * 16 * 32 * 4;   // per-warp staging, f32
     static constexpr int SMEM = STAGES * STAGE_BYTES + EPI_BYTES + 1024 + 256;
     static_assert(TMEM_COLS <= 512 && TMEM_COLS >= 32, "accumulators must fit tensor memory");
 };
@@ -491,7 +494,7 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 }
 
 template <int BN, int MODE, typename TO>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__(PERSISTENT_THREADS, 1)
 gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w,
                                const __grid_constant__ CUtensorMap map_w2,
                                const __grid_constant__ CUtensorMap map_x, TO* __restrict__ out,
@@ -522,7 +525,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w,
         }
         for (int s = 0; s < 2; ++s) {
             mbar_init(&acc_full[s], 1);
-            mbar_init(&acc_empty[s], 4);            // one arrival per epilogue warp
+            mbar_init(&acc_empty[s], PERSISTENT_EPI_WARPS);     // one arrival per epilogue warp
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -624,11 +627,16 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w,
         }
     } else if (warp >= 2) {
         // ------------------------------------------------------------ epilogue
+        // Eight warps: a warp may read only the TMEM lanes of its quarter (warp % 4), so
+        // two warps share each quarter and take half of the token columns each.  The
+        // load of the next 16 columns is in flight while the current ones are worked.
         pdl_wait();
-        const int quarter = warp & 3;
-        TO* wst = (TO*)(epi + (warp - 2) * (TL::EPI_BYTES / 4));     // [16 tokens][32 features]
+        const int quarter = warp & 3, half = (warp - 2) >> 2;
+        TO* wst = (TO*)(epi + (warp - 2) * (TL::EPI_BYTES / PERSISTENT_EPI_WARPS));
         constexpr int EPV = 16 / (int)sizeof(TO);                    // elements per 16 bytes
         constexpr int VPR = 32 / EPV;                                // 16-byte pieces per staged row
+        constexpr int HALF_COLS = BN / 2;
+        static_assert(HALF_COLS % 32 == 0, "the column loop works in pairs of 16");
         int li = 0;
         for (int item = blockIdx.x; item < items; item += gridDim.x, ++li) {
             int m0, n0, kb_begin, n_kb, split;
@@ -646,25 +654,32 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w,
             const int f0 = m0 + quarter * 32;                        // this warp's first feature
             TO* gbase = out + (size_t)split * split_stride + (size_t)n0 * ldc + f0;
             const bool fast = f0 + 32 <= N && ldc % EPV == 0 && ((uintptr_t)gbase & 15) == 0;
-#pragma unroll 1
-            for (int c = 0; c < BN; c += 16) {
-                uint32_t r[16], u[16];
-                tc_ld16(lane_base + c, r);
-                if (GATED) tc_ld16(lane_base + BN + c, u);
-                tc_wait_ld();
-                if (c + 16 >= BN) {
-                    // every value of this accumulator is in registers: hand it back
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&acc_empty[as]);
-                }
-                if (n_kb <= 0) continue;
+            const int c_begin = half * HALF_COLS, c_end = c_begin + HALF_COLS;
+
+            auto release = [&]() {
+                // every value of this accumulator that the warp needs is in registers
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty[as]);
+            };
+            auto work = [&](const uint32_t (&r)[16], const uint32_t (&u)[16], int c) {
+                if (GATED) {
+                    if (act == 1) {
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    float v = __uint_as_float(r[j]);
-                    if (GATED)
-                        v = (act == 1 ? silu_fast(v) : gelu_tanh_fast(v)) * __uint_as_float(u[j]);
-                    store_out<TO>(wst + j * 32 + lane, v);
+                        for (int j = 0; j < 16; ++j)
+                            store_out<TO>(wst + j * 32 + lane, silu_fast(__uint_as_float(r[j])) *
+                                                                   __uint_as_float(u[j]));
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            store_out<TO>(wst + j * 32 + lane,
+                                          gelu_tanh_fast(__uint_as_float(r[j])) *
+                                              __uint_as_float(u[j]));
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        store_out<TO>(wst + j * 32 + lane, __uint_as_float(r[j]));
                 }
                 __syncwarp();
                 const int rows = min(16, T - n0 - c);
@@ -683,6 +698,29 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w,
                     }
                 }
                 __syncwarp();
+            };
+
+            if (n_kb <= 0) {
+                release();
+                continue;
+            }
+            uint32_t ra[16], ua[16], rb[16], ub[16];
+            tc_ld16(lane_base + c_begin, ra);
+            if (GATED) tc_ld16(lane_base + BN + c_begin, ua);
+#pragma unroll 1
+            for (int c = c_begin; c < c_end; c += 32) {
+                tc_wait_ld();
+                tc_ld16(lane_base + c + 16, rb);
+                if (GATED) tc_ld16(lane_base + BN + c + 16, ub);
+                work(ra, ua, c);
+                tc_wait_ld();
+                if (c + 32 < c_end) {
+                    tc_ld16(lane_base + c + 32, ra);
+                    if (GATED) tc_ld16(lane_base + BN + c + 32, ua);
+                } else {
+                    release();
+                }
+                work(rb, ub, c + 16);
             }
         }
     }
@@ -800,8 +838,8 @@ int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mw2, const CUten
     const long long items =
         (long long)((N + TILE_M - 1) / TILE_M) * ((T + BN - 1) / BN) * splits;
     const int grid = (int)(items < sms ? items : sms);
-    agv_launch(kern, grid, GEMM_THREADS, TL::SMEM, stream, mw, mw2, mx, (TO*)out, T, N, K, ldc,
-               split_stride, splits, kb_per_split, act);
+    agv_launch(kern, grid, PERSISTENT_THREADS, TL::SMEM, stream, mw, mw2, mx, (TO*)out, T, N, K,
+               ldc, split_stride, splits, kb_per_split, act);
     AGV_LAUNCH_OK("gemm_tcgen05_persistent_kernel");
     return 0;
 }

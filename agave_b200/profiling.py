@@ -14,6 +14,7 @@ Cases (Gemma 3 1B layer sizes, random bfloat16 data):
   attention_decode_full     the same without a window
   norm_decode          residual sum + two RMS norms over 8 rows of 16 partial sums
   decode_step          whole decode steps of a 6-layer model (vocabulary 32,768), batch 8
+  prefill_step         whole prompt steps of the same model, one prompt of 2,048 tokens
 
 Each case prints the mean time per call: the calls run back to back from a CUDA
 graph, each on the next of several copies of its operands, the copies together
@@ -142,7 +143,7 @@ def case_norm_decode():
         y.numel() * 4 + 3 * 8 * H * 4, 1
 
 
-def case_decode_step():
+def _six_layer_engine():
     from .engine.api import Engine
     cfg = {
         "architectures": ["Gemma3ForCausalLM"], "model_type": "gemma3_text",
@@ -151,8 +152,24 @@ def case_decode_step():
         "intermediate_size": FF, "vocab_size": 32768, "sliding_window": 512,
         "sliding_window_pattern": 6, "rope_local_base_freq": 10000.0, "rope_theta": 1000000.0,
         "rms_norm_eps": 1e-6, "max_position_embeddings": 8192, "eos_token_id": 1}
-    eng = Engine.from_config(cfg, seed=2, dtype="bfloat16", max_tokens=16 * 8192, ctx_size=8192,
-                             max_batch=16, use_graphs=False)
+    return Engine.from_config(cfg, seed=2, dtype="bfloat16", max_tokens=16 * 8192, ctx_size=8192,
+                              max_batch=16, use_graphs=False)
+
+
+def case_prefill_step():
+    eng = _six_layer_engine()
+    g = torch.Generator().manual_seed(0)
+    prompt = torch.randint(3, 32768, (2048,), generator=g).tolist()
+
+    def fn(i):
+        s = eng.acquire()
+        eng.step([(s, prompt)], [[2047]])
+        eng.release(s)
+    return fn, 0, 0, 0
+
+
+def case_decode_step():
+    eng = _six_layer_engine()
     g = torch.Generator().manual_seed(0)
     lens = torch.linspace(128, 2048, 8).round().int().tolist()
     prompts = [torch.randint(3, 32768, (n,), generator=g).tolist() for n in lens]
@@ -172,6 +189,7 @@ CASES = {
     "attention_decode_full": lambda: case_attention_decode(0, 2048),
     "norm_decode": case_norm_decode,
     "decode_step": case_decode_step,
+    "prefill_step": case_prefill_step,
 }
 
 
