@@ -128,10 +128,66 @@ qk_norm_rope_store_kernel(T* __restrict__ qkv, long long row_stride,
 }
 
 // The same for head sizes that are multiples of 64 up to 256 with the whole head
-// rotated: a lane keeps its NE = hd / 32 elements (lane + 32 i) in registers, the
-// partner of element e in the rotation (e + hd / 2) is its own element i + NE / 2,
-// and every load the row needs (partial sums, weights, cos / sin, the chain that
-// finds the cache row) is issued before the first use, so their latencies overlap.
+// in registers.  A lane keeps two runs of HALF = hd / 64 consecutive elements: one
+// in the first half of the head (from lane * HALF) and its partners in the rotation
+// (the same offsets in the second half).  Runs of 2 or 4 elements move as one
+// 8- or 16-byte access.  Every load the row needs (partial sums, weights, cos / sin,
+// the chain that finds the cache row) is issued before the first use, so their
+// latencies overlap.
+template <int N>
+__device__ __forceinline__ void ld_run(const float* __restrict__ p, float* o) {
+    if constexpr (N == 4) {
+        const float4 t = *reinterpret_cast<const float4*>(p);
+        o[0] = t.x, o[1] = t.y, o[2] = t.z, o[3] = t.w;
+    } else if constexpr (N == 2) {
+        const float2 t = *reinterpret_cast<const float2*>(p);
+        o[0] = t.x, o[1] = t.y;
+    } else {
+#pragma unroll
+        for (int i = 0; i < N; ++i) o[i] = p[i];
+    }
+}
+template <int N>
+__device__ __forceinline__ void ld_run(const __nv_bfloat16* __restrict__ p, float* o) {
+    if constexpr (N == 4) {
+        const uint2 t = *reinterpret_cast<const uint2*>(p);
+        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&t.x);
+        const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&t.y);
+        o[0] = __low2float(a), o[1] = __high2float(a), o[2] = __low2float(b), o[3] = __high2float(b);
+    } else if constexpr (N == 2) {
+        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(p);
+        o[0] = __low2float(a), o[1] = __high2float(a);
+    } else {
+#pragma unroll
+        for (int i = 0; i < N; ++i) o[i] = __bfloat162float(p[i]);
+    }
+}
+template <int N>
+__device__ __forceinline__ void st_run(float* p, const float* v) {
+    if constexpr (N == 4) *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    else if constexpr (N == 2) *reinterpret_cast<float2*>(p) = make_float2(v[0], v[1]);
+    else {
+#pragma unroll
+        for (int i = 0; i < N; ++i) p[i] = v[i];
+    }
+}
+template <int N>
+__device__ __forceinline__ void st_run(__nv_bfloat16* p, const float* v) {
+    if constexpr (N == 4) {
+        const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]);
+        const __nv_bfloat162 b = __floats2bfloat162_rn(v[2], v[3]);
+        uint2 t;
+        t.x = *reinterpret_cast<const uint32_t*>(&a);
+        t.y = *reinterpret_cast<const uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(p) = t;
+    } else if constexpr (N == 2) {
+        *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(v[0], v[1]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < N; ++i) p[i] = __float2bfloat16(v[i]);
+    }
+}
+
 template <typename T, int NE>
 __global__ void __launch_bounds__(QK_WARPS * 32)
 qk_norm_rope_store_reg_kernel(T* __restrict__ qkv, long long row_stride,
@@ -142,13 +198,14 @@ qk_norm_rope_store_reg_kernel(T* __restrict__ qkv, long long row_stride,
                               const int* __restrict__ positions, CacheWrite cw) {
     pdl_wait();
     pdl_launch_next();
-    constexpr int hd = NE * 32, HALF = NE / 2;
+    constexpr int hd = NE * 32, HALF = NE / 2, H2 = hd / 2;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads = nh + 2 * nkv;
     const long long item = (long long)blockIdx.x * QK_WARPS + warp;
     if (item >= (long long)n_tokens * heads) return;
     const int t = (int)(item / heads), head = (int)(item % heads);
-    T* src = qkv + (size_t)t * row_stride + (size_t)head * hd;
+    const int e0 = lane * HALF;                       // first run; the second is at e0 + H2
+    T* src = qkv + (size_t)t * row_stride + (size_t)head * hd + e0;
     const bool is_q = head < nh, is_k = !is_q && head < nh + nkv, is_v = !is_q && !is_k;
     const float* w = is_q ? wq : (is_k ? wk : nullptr);
     const bool stores = !is_q && cw.k_pool;
@@ -158,36 +215,49 @@ qk_norm_rope_store_reg_kernel(T* __restrict__ qkv, long long row_stride,
         cb = cw.seq_index[t];
         c_pos = positions[t];
     }
-    // operands of the arithmetic
-    float wv[NE], cs[HALF > 0 ? HALF : 1], sn[HALF > 0 ? HALF : 1], v[NE];
-#pragma unroll
-    for (int i = 0; i < NE; ++i) wv[i] = w ? w[lane + 32 * i] : 1.f;
-    const bool rotate = cosv && !is_v;
-#pragma unroll
-    for (int i = 0; i < HALF; ++i) {
-        cs[i] = rotate ? cosv[(size_t)t * (hd / 2) + lane + 32 * i] : 1.f;
-        sn[i] = rotate ? sinv[(size_t)t * (hd / 2) + lane + 32 * i] : 0.f;
-    }
-    if (part) {
-        const float* ps = part + (size_t)t * (size_t)(heads * hd) + (size_t)head * hd + lane;
-        constexpr int U = NE >= 8 ? 8 : 16;           // ranges of K loaded together
-#pragma unroll
-        for (int i = 0; i < NE; ++i) v[i] = 0.f;
-        for (int s0 = 0; s0 < n_splits; s0 += U) {
-            float tv[U][NE];
-#pragma unroll
-            for (int u = 0; u < U; ++u)
-#pragma unroll
-                for (int i = 0; i < NE; ++i)
-                    tv[u][i] = ps[(size_t)min(s0 + u, n_splits - 1) * split_stride + 32 * i];
-#pragma unroll
-            for (int u = 0; u < U; ++u)
-#pragma unroll
-                for (int i = 0; i < NE; ++i) v[i] += s0 + u < n_splits ? tv[u][i] : 0.f;
-        }
+    // operands of the arithmetic: v[0..HALF) first run, v[HALF..NE) second run
+    float wv[NE], cs[HALF], sn[HALF], v[NE];
+    if (w) {
+        ld_run<HALF>(w + e0, wv);
+        ld_run<HALF>(w + H2 + e0, wv + HALF);
     } else {
 #pragma unroll
-        for (int i = 0; i < NE; ++i) v[i] = to_f32(src[lane + 32 * i]);
+        for (int i = 0; i < NE; ++i) wv[i] = 1.f;
+    }
+    const bool rotate = cosv && !is_v;
+    if (rotate) {
+        ld_run<HALF>(cosv + (size_t)t * H2 + e0, cs);
+        ld_run<HALF>(sinv + (size_t)t * H2 + e0, sn);
+    } else {
+#pragma unroll
+        for (int i = 0; i < HALF; ++i) cs[i] = 1.f, sn[i] = 0.f;
+    }
+    if (part) {
+        const float* ps = part + (size_t)t * (size_t)(heads * hd) + (size_t)head * hd + e0;
+        if (n_splits == 1) {
+            ld_run<HALF>(ps, v);
+            ld_run<HALF>(ps + H2, v + HALF);
+        } else {
+            constexpr int U = 8;                      // ranges of K loaded together
+#pragma unroll
+            for (int i = 0; i < NE; ++i) v[i] = 0.f;
+            for (int s0 = 0; s0 < n_splits; s0 += U) {
+                float tv[U][NE];
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const float* row = ps + (size_t)min(s0 + u, n_splits - 1) * split_stride;
+                    ld_run<HALF>(row, tv[u]);
+                    ld_run<HALF>(row + H2, tv[u] + HALF);
+                }
+#pragma unroll
+                for (int u = 0; u < U; ++u)
+#pragma unroll
+                    for (int i = 0; i < NE; ++i) v[i] += s0 + u < n_splits ? tv[u][i] : 0.f;
+            }
+        }
+    } else {
+        ld_run<HALF>(src, v);
+        ld_run<HALF>(src + H2, v + HALF);
     }
     // second and third links
     int c_slot = -1, c_len = 0, c_page = 0;
@@ -217,17 +287,17 @@ qk_norm_rope_store_reg_kernel(T* __restrict__ qkv, long long row_stride,
         }
     }
     if (!is_v || part) {
-#pragma unroll
-        for (int i = 0; i < NE; ++i) src[lane + 32 * i] = from_f32<T>(v[i]);
+        st_run<HALF>(src, v);
+        st_run<HALF>(src + H2, v + HALF);
     }
     if (!stores || c_slot < 0) return;
     if (c_pos < c_len - cw.cap) return;
     const int row = c_pos % cw.cap;
     const int g = is_k ? head - nh : head - nh - nkv;
     T* pool = (T*)(is_k ? cw.k_pool : cw.v_pool);
-    T* dst = pool + (((size_t)c_page * cw.page + row % cw.page) * nkv + g) * hd;
-#pragma unroll
-    for (int i = 0; i < NE; ++i) dst[lane + 32 * i] = from_f32<T>(v[i]);
+    T* dst = pool + (((size_t)c_page * cw.page + row % cw.page) * nkv + g) * hd + e0;
+    st_run<HALF>(dst, v);
+    st_run<HALF>(dst + H2, v + HALF);
 }
 
 template <typename T>
@@ -237,6 +307,11 @@ static bool launch_qk_reg(T* qkv, long long row_stride, const float* part, int n
                           const float* sinv, int rotary_dim, const int* positions,
                           const CacheWrite& cw, unsigned grid, cudaStream_t stream) {
     if (hd % 64 != 0 || hd > 256 || (cosv && rotary_dim != hd)) return false;
+    // runs of hd / 64 elements move as single accesses: everything must sit on 16 bytes
+    if (row_stride % 8 || !agv_aligned(qkv, 16) || !agv_aligned(part, 16) ||
+        !agv_aligned(wq, 16) || !agv_aligned(wk, 16) || !agv_aligned(cosv, 16) ||
+        !agv_aligned(sinv, 16) || !agv_aligned(cw.k_pool, 16) || !agv_aligned(cw.v_pool, 16))
+        return false;
 #define AGV_QK_REG(NE)                                                                          \
     agv_launch(qk_norm_rope_store_reg_kernel<T, NE>, grid, QK_WARPS * 32, 0, stream, qkv,       \
                row_stride, part, n_splits, split_stride, n_tokens, nh, nkv, wq, wk, eps, cosv,  \
