@@ -10,6 +10,7 @@
 // slot; the row's page comes from the slot's page table.  A token whose row a
 // later token of the same step overwrites (p < len_after - cap) is not stored.
 #include "common.cuh"
+#include <type_traits>
 
 constexpr int QK_WARPS = 4;
 constexpr int QK_MAX_HD = 1024;
@@ -23,6 +24,22 @@ struct CacheWrite {
     const int* seq_index;      // [T] token -> batch entry
     int max_pages, page, cap;
 };
+
+// The step's values once more, transposed, for the prompt attention whose
+// O += P V product wants its V operand with the keys contiguous:
+// vt[g * hd + d, start(b) + p] = v[token of (b, p), g, d], where start(b) is the sum
+// of the earlier sequences' lengths, each rounded up to 64; the columns between a
+// sequence's end and the next multiple of 64 are zero.
+struct VtWrite {
+    __nv_bfloat16* vt;         // [nkv * hd, ld]; null: not wanted
+    long long ld;
+    const int* cu;             // [n_seq + 1] first token of each sequence
+    const int* seq_index;      // [T]
+};
+
+extern "C" int agv_transpose_values(const void* v, long long kv_stride, void* vt, long long vt_ld,
+                                    const int* cu_seqlens, int B, int max_len, int nkv, int hd,
+                                    cudaStream_t stream);
 
 template <typename T>
 __global__ void __launch_bounds__(QK_WARPS * 32)
@@ -195,13 +212,85 @@ qk_norm_rope_store_reg_kernel(T* __restrict__ qkv, long long row_stride,
                               long long split_stride, int n_tokens, int nh, int nkv,
                               const float* __restrict__ wq, const float* __restrict__ wk, float eps,
                               const float* __restrict__ cosv, const float* __restrict__ sinv,
-                              const int* __restrict__ positions, CacheWrite cw) {
+                              const int* __restrict__ positions, CacheWrite cw, VtWrite vw,
+                              int vt_blocks) {
     pdl_wait();
     pdl_launch_next();
     constexpr int hd = NE * 32, HALF = NE / 2, H2 = hd / 2;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads = nh + 2 * nkv;
-    const long long item = (long long)blockIdx.x * QK_WARPS + warp;
+    if ((int)blockIdx.x < vt_blocks) {
+        // ---- the first blocks write the values transposed (they take longest, so they
+        // start first): one tile of 64 tokens x 64 of the nkv * hd value columns each
+        if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+            __shared__ __nv_bfloat16 tile[64][66];
+            __shared__ int cols[64], pads[64];
+            const int vb = blockIdx.x, ncb = nkv * hd / 64;
+            const int t0 = (vb / ncb) * 64, c0 = (vb % ncb) * 64;
+            if (threadIdx.x < 64) {
+                const int t = t0 + threadIdx.x;
+                int col = -1, pad = 0;
+                if (t < n_tokens) {
+                    const int b = vw.seq_index[t], p = positions[t];
+                    int start = 0;
+                    for (int i = 0; i < b; ++i) start += (vw.cu[i + 1] - vw.cu[i] + 63) & ~63;
+                    col = start + p;
+                    const int len = vw.cu[b + 1] - vw.cu[b];
+                    if (p == len - 1) pad = ((len + 63) & ~63) - len;
+                }
+                cols[threadIdx.x] = col;
+                pads[threadIdx.x] = pad;
+            }
+            // 16 threads per token row (4 columns each), 8 rows per pass
+            const int tr = threadIdx.x >> 4, tc = (threadIdx.x & 15) * 4;
+            const size_t vcol = (size_t)(nh + nkv) * hd + c0 + tc;
+            float val[8][4];
+#pragma unroll
+            for (int ps = 0; ps < 8; ++ps) {
+                const int t = t0 + ps * 8 + tr;
+                val[ps][0] = val[ps][1] = val[ps][2] = val[ps][3] = 0.f;
+                if (t < n_tokens) {
+                    if (part) {
+                        for (int sp = 0; sp < n_splits; ++sp) {
+                            float x[4];
+                            ld_run<4>(part + (size_t)sp * split_stride +
+                                          (size_t)t * (size_t)(heads * hd) + vcol, x);
+                            val[ps][0] += x[0], val[ps][1] += x[1], val[ps][2] += x[2],
+                                val[ps][3] += x[3];
+                        }
+                    } else {
+                        ld_run<4>(qkv + (size_t)t * row_stride + vcol, val[ps]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int ps = 0; ps < 8; ++ps)
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    tile[tc + e][ps * 8 + tr] = __float2bfloat16(val[ps][e]);
+            __syncthreads();
+            const int g = c0 / hd, d0 = c0 % hd;
+            for (int d = warp; d < 64; d += QK_WARPS) {
+                __nv_bfloat16* dst = vw.vt + (size_t)(g * hd + d0 + d) * vw.ld;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int tl = h * 32 + lane, col = cols[tl];
+                    if (col >= 0) dst[col] = tile[d][tl];
+                }
+            }
+            for (int tl = 0; tl < 64; ++tl) {
+                const int pad = pads[tl];
+                if (pad == 0) continue;
+                for (int i = threadIdx.x; i < 64 * pad; i += QK_WARPS * 32) {
+                    const int d = i / pad, pc = i % pad;
+                    vw.vt[(size_t)(g * hd + d0 + d) * vw.ld + cols[tl] + 1 + pc] =
+                        __float2bfloat16(0.f);
+                }
+            }
+        }
+        return;
+    }
+    const long long item = (long long)(blockIdx.x - vt_blocks) * QK_WARPS + warp;
     if (item >= (long long)n_tokens * heads) return;
     const int t = (int)(item / heads), head = (int)(item % heads);
     const int e0 = lane * HALF;                       // first run; the second is at e0 + H2
@@ -305,8 +394,13 @@ static bool launch_qk_reg(T* qkv, long long row_stride, const float* part, int n
                           long long split_stride, int n_tokens, int nh, int nkv, int hd,
                           const float* wq, const float* wk, float eps, const float* cosv,
                           const float* sinv, int rotary_dim, const int* positions,
-                          const CacheWrite& cw, unsigned grid, cudaStream_t stream) {
+                          const CacheWrite& cw, const VtWrite& vw, unsigned main_blocks,
+                          cudaStream_t stream) {
     if (hd % 64 != 0 || hd > 256 || (cosv && rotary_dim != hd)) return false;
+    if (vw.vt && !std::is_same<T, __nv_bfloat16>::value) return false;
+    const unsigned vt_blocks =
+        vw.vt ? (unsigned)((n_tokens + 63) / 64) * (unsigned)(nkv * hd / 64) : 0u;
+    const unsigned grid = main_blocks + vt_blocks;
     // runs of hd / 64 elements move as single accesses: everything must sit on 16 bytes
     if (row_stride % 8 || !agv_aligned(qkv, 16) || !agv_aligned(part, 16) ||
         !agv_aligned(wq, 16) || !agv_aligned(wk, 16) || !agv_aligned(cosv, 16) ||
@@ -315,7 +409,7 @@ static bool launch_qk_reg(T* qkv, long long row_stride, const float* part, int n
 #define AGV_QK_REG(NE)                                                                          \
     agv_launch(qk_norm_rope_store_reg_kernel<T, NE>, grid, QK_WARPS * 32, 0, stream, qkv,       \
                row_stride, part, n_splits, split_stride, n_tokens, nh, nkv, wq, wk, eps, cosv,  \
-               sinv, positions, cw)
+               sinv, positions, cw, vw, (int)vt_blocks)
     if (hd == 64) AGV_QK_REG(2);
     else if (hd == 128) AGV_QK_REG(4);
     else if (hd == 192) AGV_QK_REG(6);
@@ -329,6 +423,9 @@ static bool launch_qk_reg(T* qkv, long long row_stride, const float* part, int n
 // are also written to the layer's cache pools unless k_pool is null.  With
 // part != null the input is read from part [n_splits, T, (nh + 2 nkv) * hd]
 // (32-bit partial sums, dense) instead, and qkv only receives the result.
+// With vt != null (bfloat16 only) the values are also written transposed into
+// vt [nkv * hd, vt_ld] (see VtWrite); that needs seq_index, positions, cu_seqlens
+// [n_seq + 1] and the greatest sequence length.
 AGV_API int agv_qk_norm_rope_store(void* qkv, int dtype, long long row_stride, const float* part,
                                    int n_splits, int n_tokens, int nh,
                                    int nkv, int hd, const float* wq, const float* wk, float eps,
@@ -336,7 +433,8 @@ AGV_API int agv_qk_norm_rope_store(void* qkv, int dtype, long long row_stride, c
                                    const int* positions, void* k_pool, void* v_pool,
                                    const int* page_table, const int* slots, const int* lens,
                                    const int* seq_index, int max_pages, int page, int cap,
-                                   cudaStream_t stream) {
+                                   void* vt, long long vt_ld, const int* cu_seqlens, int n_seq,
+                                   int max_len, cudaStream_t stream) {
     AGV_REQUIRE(n_tokens >= 0 && nh > 0 && nkv > 0 && hd > 0, "qk_norm_rope: bad sizes");
     AGV_REQUIRE(hd <= QK_MAX_HD, "qk_norm_rope: head_dim %d exceeds %d", hd, QK_MAX_HD);
     AGV_REQUIRE(rotary_dim % 2 == 0 && rotary_dim <= hd, "qk_norm_rope: rotary_dim %d must be even "
@@ -347,7 +445,12 @@ AGV_API int agv_qk_norm_rope_store(void* qkv, int dtype, long long row_stride, c
     AGV_REQUIRE(!cosv || (sinv && positions), "qk_norm_rope: cos without sin or positions");
     AGV_REQUIRE(!k_pool || positions, "qk_norm_rope: the cache store needs positions");
     AGV_REQUIRE(!part || n_splits >= 1, "qk_norm_rope: partial sums need n_splits >= 1");
+    AGV_REQUIRE(!vt || (dtype == AGV_BF16 && seq_index && positions && cu_seqlens && n_seq > 0 &&
+                        vt_ld % 64 == 0 && agv_aligned(vt, 16)),
+                "qk_norm_rope: the transposed values need bfloat16, seq_index, positions and "
+                "cu_seqlens");
     if (n_tokens == 0) return 0;
+    VtWrite vw{(__nv_bfloat16*)vt, vt_ld, cu_seqlens, seq_index};
     const long long split_stride = (long long)n_tokens * (nh + 2 * nkv) * hd;
     CacheWrite cw{k_pool, v_pool, page_table, slots, lens, seq_index, max_pages, page, cap};
     const long long items = (long long)n_tokens * (nh + 2 * nkv);
@@ -356,7 +459,7 @@ AGV_API int agv_qk_norm_rope_store(void* qkv, int dtype, long long row_stride, c
     const int half = cosv ? rotary_dim / 2 : 0;
     if (dtype == AGV_F32 &&
         launch_qk_reg<float>((float*)qkv, row_stride, part, n_splits, split_stride, n_tokens, nh,
-                             nkv, hd, wq, wk, eps, cosv, sinv, rotary_dim, positions, cw, grid,
+                             nkv, hd, wq, wk, eps, cosv, sinv, rotary_dim, positions, cw, vw, grid,
                              stream)) {
         AGV_LAUNCH_OK("qk_norm_rope_store_reg_kernel");
         return 0;
@@ -364,7 +467,7 @@ AGV_API int agv_qk_norm_rope_store(void* qkv, int dtype, long long row_stride, c
     if (dtype == AGV_BF16 &&
         launch_qk_reg<__nv_bfloat16>((__nv_bfloat16*)qkv, row_stride, part, n_splits, split_stride,
                                      n_tokens, nh, nkv, hd, wq, wk, eps, cosv, sinv, rotary_dim,
-                                     positions, cw, grid, stream)) {
+                                     positions, cw, vw, grid, stream)) {
         AGV_LAUNCH_OK("qk_norm_rope_store_reg_kernel");
         return 0;
     }
@@ -377,5 +480,12 @@ AGV_API int agv_qk_norm_rope_store(void* qkv, int dtype, long long row_stride, c
     else
         return agv_fail(-1, "qk_norm_rope: unknown dtype %d", dtype);
     AGV_LAUNCH_OK("qk_norm_rope_store_kernel");
+    if (vt) {
+        // the general kernel does not transpose: a kernel of its own reads the values
+        // that the launch above wrote
+        const __nv_bfloat16* v = (const __nv_bfloat16*)qkv + (size_t)(nh + nkv) * hd;
+        return agv_transpose_values(v, row_stride, vt, vt_ld, cu_seqlens, n_seq, max_len, nkv, hd,
+                                    stream);
+    }
     return 0;
 }

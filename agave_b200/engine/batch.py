@@ -35,7 +35,7 @@ class StepContext:
     device: torch.device
     # per-step scratch shared between layers
     rope_tables: Dict[Tuple, Tuple[torch.Tensor, torch.Tensor]] = field(default_factory=dict)
-    step_kv: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = field(default_factory=dict)
+    step_kv: Dict[int, Tuple] = field(default_factory=dict)
 
     def new(self, *shape, dtype=None) -> torch.Tensor:
         return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)

@@ -8,6 +8,7 @@ compiled library, or on a tensor that is not on a CUDA device, the call raises.
 from __future__ import annotations
 
 import ctypes
+import os
 import threading
 from typing import Optional
 
@@ -38,7 +39,7 @@ def library() -> ctypes.CDLL:
                 except OSError as e:
                     raise KernelError(f"the CUDA library {path} could not be loaded: {e}") from None
                 lib.agv_last_error.restype = ctypes.c_char_p
-                import os
+                lib.agv_attention_prefill_tc_vt_cols.restype = ctypes.c_longlong
                 if os.environ.get("AGAVE_B200_DEPENDENT_LAUNCH", "1") == "0":
                     # kernels then start only after the one before has ended, which
                     # makes per-kernel durations in a profiler additive
@@ -194,11 +195,15 @@ def qk_norm_rope_store(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_di
                        page_table: Optional[torch.Tensor] = None,
                        slots: Optional[torch.Tensor] = None, lens: Optional[torch.Tensor] = None,
                        seq_index: Optional[torch.Tensor] = None, page: int = 0,
-                       cap: int = 0, partial: Optional[torch.Tensor] = None) -> None:
+                       cap: int = 0, partial: Optional[torch.Tensor] = None,
+                       vt: Optional[torch.Tensor] = None, cu_seqlens: Optional[torch.Tensor] = None,
+                       max_len: int = 0) -> None:
     """In place on qkv [T, (nh + 2 nkv) * hd]: per-head norm of q and k, rotation,
     and (if pools are given) the store of k and v rows into the paged cache.
     ``partial`` [S, T, (nh + 2 nkv) * hd] (32-bit partial sums of the projection)
-    replaces qkv as the input; qkv then only receives the result."""
+    replaces qkv as the input; qkv then only receives the result.  ``vt`` (from
+    ``prefill_values_scratch``) also receives the values transposed, for the prompt
+    attention; that needs seq_index, positions, cu_seqlens and the greatest length."""
     T = qkv.shape[0]
     n_splits = 0
     if partial is not None:
@@ -215,11 +220,18 @@ def qk_norm_rope_store(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_di
         _dense(k_pool, "k_pool"); _dense(v_pool, "v_pool")
         assert k_pool.dtype == qkv.dtype and v_pool.dtype == qkv.dtype
     max_pages = page_table.shape[1] if page_table is not None else 0
+    n_seq = 0
+    if vt is not None:
+        _dense(vt, "vt"); _i32(cu_seqlens, "cu_seqlens")
+        assert vt.dtype == torch.bfloat16 and vt.shape[0] == n_kv_heads * head_dim
+        n_seq = cu_seqlens.numel() - 1
     _check(library().agv_qk_norm_rope_store(
         _ptr(qkv), dtype_code(qkv.dtype), ctypes.c_longlong(qkv.stride(0)), _ptr(partial),
         n_splits, T, n_heads, n_kv_heads, head_dim, _ptr(wq), _ptr(wk), ctypes.c_float(eps), _ptr(cos), _ptr(sin),
         rotary_dim, _ptr(positions), _ptr(k_pool), _ptr(v_pool), _ptr(page_table), _ptr(slots),
-        _ptr(lens), _ptr(seq_index), max_pages, page, cap, _stream()))
+        _ptr(lens), _ptr(seq_index), max_pages, page, cap, _ptr(vt),
+        ctypes.c_longlong(vt.shape[1] if vt is not None else 0), _ptr(cu_seqlens), n_seq, max_len,
+        _stream()))
 
 
 def attention_prefill_simt(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor,
@@ -356,6 +368,7 @@ def linear_tc_status() -> int:
 
 # ------------------------------------------------------------------ dispatch
 N_SMS = 148
+_PREFILL_TC = os.environ.get("AGAVE_B200_PREFILL_ATTENTION", "tcgen05") != "mma"
 
 def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
            w2: Optional[torch.Tensor] = None, activation: str = "gelu_tanh") -> None:
@@ -433,12 +446,64 @@ def attention_prefill_mma(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out
         max_len, n_heads, n_kv_heads, head_dim, ctypes.c_float(scale), window, _stream()))
 
 
-def attention_prefill(q, k, v, out, ctx, n_heads, n_kv_heads, head_dim, scale, window) -> None:
-    """Prompt attention of one layer: the tensor-core kernel for bfloat16 and head
-    sizes in steps of 8 up to 256, else the one-warp-per-(token, head) kernel."""
-    if (q.dtype == torch.bfloat16 and head_dim % 8 == 0 and head_dim <= 256 and
-            q.stride(0) % 8 == 0 and k.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and
-            k.data_ptr() % 16 == 0 and v.data_ptr() % 16 == 0):
+def prefill_values_scratch(T: int, B: int, n_kv_heads: int, head_dim: int,
+                           device: torch.device) -> torch.Tensor:
+    """The buffer the tcgen05 prompt attention reads the values from, transposed:
+    [nkv * hd, columns], every sequence padded to a multiple of 64 columns."""
+    cols = library().agv_attention_prefill_tc_vt_cols(T, B)
+    return torch.empty((n_kv_heads * head_dim, cols), dtype=torch.bfloat16, device=device)
+
+
+def attention_prefill_tc(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor,
+                         cu_seqlens: torch.Tensor, max_len: int, n_heads: int, n_kv_heads: int,
+                         head_dim: int, scale: float, window: int,
+                         vt: Optional[torch.Tensor] = None) -> None:
+    """Prompts that start at 0 on the tcgen05 tensor cores (bfloat16, head sizes in
+    steps of 16 up to 256); q, k, v are row-strided views, out is dense.  ``vt``:
+    the values already transposed (by ``qk_norm_rope_store``); else this call
+    transposes them."""
+    assert q.dtype == torch.bfloat16 and k.dtype == q.dtype and v.dtype == q.dtype
+    assert q.stride(1) == 1 and k.stride(1) == 1 and v.stride(1) == 1
+    assert k.stride(0) == v.stride(0)
+    _dense(out, "out"); _i32(cu_seqlens, "cu_seqlens")
+    T, B = q.shape[0], cu_seqlens.numel() - 1
+    ready = vt is not None
+    if vt is None:
+        vt = prefill_values_scratch(T, B, n_kv_heads, head_dim, q.device)
+    _dense(vt, "vt")
+    _check(library().agv_attention_prefill_tc(
+        _ptr(q), ctypes.c_longlong(q.stride(0)), _ptr(k), _ptr(v),
+        ctypes.c_longlong(k.stride(0)), _ptr(out), _ptr(vt), ctypes.c_longlong(vt.shape[1]),
+        1 if ready else 0, _ptr(cu_seqlens), B, T, max_len, n_heads, n_kv_heads, head_dim,
+        ctypes.c_float(scale), window, _stream()))
+
+
+def attention_tc_status() -> int:
+    """0, or the code of the first bounded wait of the tcgen05 attention kernel that
+    gave up since the last call (this call synchronises the device)."""
+    torch.cuda.synchronize()
+    return library().agv_attention_tc_status()
+
+
+def attention_prefill_wants_transposed_values(qkv: torch.Tensor, head_dim: int) -> bool:
+    """Whether ``attention_prefill`` on views of this projection output will take the
+    tcgen05 kernel, which reads the values transposed."""
+    return (_PREFILL_TC and qkv.dtype == torch.bfloat16 and head_dim % 16 == 0 and
+            head_dim <= 256 and qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0)
+
+
+def attention_prefill(q, k, v, out, ctx, n_heads, n_kv_heads, head_dim, scale, window,
+                      vt=None) -> None:
+    """Prompt attention of one layer in bfloat16: the tcgen05 kernel for head sizes
+    in steps of 16 up to 256, the mma.sync kernel for the other multiples of 8; else
+    the one-warp-per-(token, head) kernel."""
+    aligned = (q.dtype == torch.bfloat16 and head_dim <= 256 and
+               q.stride(0) % 8 == 0 and k.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and
+               k.data_ptr() % 16 == 0 and v.data_ptr() % 16 == 0)
+    if aligned and head_dim % 16 == 0 and _PREFILL_TC:
+        attention_prefill_tc(q, k, v, out, ctx.cu_seqlens, ctx.max_new, n_heads, n_kv_heads,
+                             head_dim, scale, window, vt=vt)
+    elif aligned and head_dim % 8 == 0:
         attention_prefill_mma(q, k, v, out, ctx.cu_seqlens, ctx.max_new, n_heads, n_kv_heads,
                               head_dim, scale, window)
     else:

@@ -93,10 +93,16 @@ class AttentionMixer:
         view = ctx.cache.kv_view(cache_entry)
         eps = s.qk_norm.eps if s.qk_norm is not None else 0.0
         if writes_cache:
+            # a prompt step on the tcgen05 attention kernel reads the values transposed:
+            # the same launch writes that copy
+            vt = None
+            if ctx.mode == PREFILL and kernels.attention_prefill_wants_transposed_values(qkv, hd):
+                vt = kernels.prefill_values_scratch(T, ctx.batch, nkv, hd, qkv.device)
             kernels.qk_norm_rope_store(
                 qkv, nh, nkv, hd, self.q_norm_weight, self.k_norm_weight, eps, cos, sin,
                 rotary_dim, ctx.positions, view.k_pool, view.v_pool, view.page_table, ctx.slots,
-                ctx.lens, ctx.seq_index, view.page, view.cap, partial=part)
+                ctx.lens, ctx.seq_index, view.page, view.cap, partial=part, vt=vt,
+                cu_seqlens=ctx.cu_seqlens, max_len=ctx.max_new)
         else:
             kernels.qk_norm_rope_store(qkv, nh, nkv, hd, self.q_norm_weight, self.k_norm_weight,
                                        eps, cos, sin, rotary_dim, ctx.positions, partial=part)
@@ -107,10 +113,10 @@ class AttentionMixer:
             if writes_cache:
                 k = qkv[:, nh * hd:(nh + nkv) * hd]
                 v = qkv[:, (nh + nkv) * hd:]
-                ctx.step_kv[cache_entry] = (k, v)
+                ctx.step_kv[cache_entry] = (k, v, vt)
             else:
-                k, v = ctx.step_kv[cache_entry]
-            kernels.attention_prefill(q, k, v, out, ctx, nh, nkv, hd, s.scale, window)
+                k, v, vt = ctx.step_kv[cache_entry]
+            kernels.attention_prefill(q, k, v, out, ctx, nh, nkv, hd, s.scale, window, vt=vt)
         else:
             kernels.attention_decode(q, out, view, ctx, nh, nkv, hd, s.scale, window)
         return self.out.partial(out)

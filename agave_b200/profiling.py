@@ -9,7 +9,9 @@ Cases (Gemma 3 1B layer sizes, random bfloat16 data):
   gemm_gated_decode    gate/up product, 8 tokens
   gemm_down_decode     down projection, 8 tokens (K split over a cluster or partial sums)
   gemm_lm_head_decode  the head over a 262,144-row table, 8 tokens
-  attention_prefill    prompt attention, one sequence of 2,048 tokens, no window
+  attention_prefill    prompt attention (tcgen05), one sequence of 2,048 tokens, no window
+  attention_prefill_window   the same with a window of 512
+  attention_prefill_mma      the mma.sync kernel on the first workload
   attention_decode_window   decode attention, 8 sequences of 128..2,048 positions, window 512
   attention_decode_full     the same without a window
   norm_decode          residual sum + two RMS norms over 8 rows of 16 partial sums
@@ -95,19 +97,21 @@ def case_lm_head():
     return (lambda i: kernels.linear_tc(x, w, out)), 2 * 8 * V * H, V * H * 2 + 8 * V * 4, 1
 
 
-def case_attention_prefill():
+def case_attention_prefill(window=0, legacy=False):
     from . import kernels
     T = 2048
     c = 8
     qkv = [_rnd(T, (NH + 2 * NKV) * HD, scale=0.5) for _ in range(c)]
     out = torch.empty(T, NH * HD, dtype=torch.bfloat16, device=DEV)
     cu = torch.tensor([0, T], dtype=torch.int32, device=DEV)
-    flops = 4 * NH * HD * T * (T + 1) // 2
+    pairs = T * (T + 1) // 2 if not window else sum(min(p + 1, window) for p in range(T))
+    flops = 4 * NH * HD * pairs
+    kern = kernels.attention_prefill_mma if legacy else kernels.attention_prefill_tc
 
     def fn(i):
         t = qkv[i]
-        kernels.attention_prefill_mma(t[:, :NH * HD], t[:, NH * HD:(NH + NKV) * HD],
-                                      t[:, (NH + NKV) * HD:], out, cu, T, NH, NKV, HD, 0.0625, 0)
+        kern(t[:, :NH * HD], t[:, NH * HD:(NH + NKV) * HD], t[:, (NH + NKV) * HD:], out, cu, T,
+             NH, NKV, HD, 0.0625, window)
     return fn, flops, qkv[0].numel() * 2 + out.numel() * 2, c
 
 
@@ -185,6 +189,8 @@ CASES = {
     "gemm_down_decode": lambda: case_gemm_down(8),
     "gemm_lm_head_decode": case_lm_head,
     "attention_prefill": case_attention_prefill,
+    "attention_prefill_window": lambda: case_attention_prefill(512),
+    "attention_prefill_mma": lambda: case_attention_prefill(0, True),
     "attention_decode_window": lambda: case_attention_decode(512, 512),
     "attention_decode_full": lambda: case_attention_decode(0, 2048),
     "norm_decode": case_norm_decode,

@@ -496,6 +496,108 @@ def test_attention_prefill_tensor_cores(nh, nkv, hd, window):
     assert rel_err(out[o:o + n], exact) < 1.2e-2
 
 
+@pytest.mark.parametrize("nh,nkv,hd,window", [(4, 1, 256, 0), (4, 1, 256, 100), (8, 4, 256, 0),
+                                              (6, 2, 128, 70), (3, 3, 64, 0), (4, 2, 16, 5),
+                                              (2, 1, 48, 33), (2, 1, 208, 64), (32, 2, 32, 0)])
+def test_attention_prefill_tcgen05(nh, nkv, hd, window):
+    """The tcgen05 kernel against the one-warp kernel and a 64-bit statement: ragged
+    batch whose lengths straddle the tiles, heads packed per CTA (4, 2, 16), not
+    packed (3 heads per kv head; 1), head sizes that end inside a 64-wide block."""
+    from agave_b200 import kernels
+    lens = [1, 63, 64, 65, 200, 130, 31, 450]
+    T = sum(lens)
+    qkv = rnd(T, (nh + 2 * nkv) * hd, dtype=torch.bfloat16, seed=1, scale=0.5)
+    q, k, v = qkv[:, :nh * hd], qkv[:, nh * hd:(nh + nkv) * hd], qkv[:, (nh + nkv) * hd:]
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=DEV)
+    positions = torch.tensor(sum([list(range(n)) for n in lens], []), dtype=torch.int32, device=DEV)
+    seq_index = torch.tensor(sum([[i] * n for i, n in enumerate(lens)], []), dtype=torch.int32, device=DEV)
+    ref = torch.empty((T, nh * hd), dtype=torch.bfloat16, device=DEV)
+    kernels.attention_prefill_simt(q, k, v, ref, positions, seq_index, cu, nh, nkv, hd, 0.3, window)
+    out = torch.full_like(ref, float("nan"))
+    kernels.attention_prefill_tc(q, k, v, out, cu, max(lens), nh, nkv, hd, 0.3, window)
+    assert kernels.attention_tc_status() == 0
+    assert torch.isfinite(out.float()).all()
+    assert rel_err(out, ref) < 1.2e-2
+    o = sum(lens[:4])
+    n = lens[4]
+    exact = ref_attention(q[o:o + n].float().cpu().reshape(n, nh, hd),
+                          k[o:o + n].float().cpu().reshape(n, nkv, hd),
+                          v[o:o + n].float().cpu().reshape(n, nkv, hd), 0.3, window)
+    assert rel_err(out[o:o + n], exact) < 1.2e-2
+
+
+def test_attention_prefill_tcgen05_far_key_window_edge_and_growing_scores():
+    """One score that stands out among hundreds; the window's edge; and scores that
+    grow along the sequence, so that the running maximum moves by more than the
+    kernel lets it lag and the accumulator is rescaled."""
+    from agave_b200 import kernels
+    hd, n, far = 256, 300, 3
+    k = rnd(n, hd, dtype=torch.bfloat16, seed=1, scale=0.1)
+    v = rnd(n, hd, dtype=torch.bfloat16, seed=2)
+    q = rnd(n, hd, dtype=torch.bfloat16, seed=3, scale=0.1)
+    k[far] = 0; k[far, 0] = 40.0
+    q[-1] = 0; q[-1, 0] = 40.0
+    qkv = torch.cat([q, k, v], dim=1).contiguous()
+    cu = torch.tensor([0, n], dtype=torch.int32, device=DEV)
+    out = torch.empty((n, hd), dtype=torch.bfloat16, device=DEV)
+    args = (qkv[:, :hd], qkv[:, hd:2 * hd], qkv[:, 2 * hd:], out, cu, n, 1, 1, hd, 1.0)
+    kernels.attention_prefill_tc(*args, 0)
+    assert rel_err(out[-1], v[far]) < 1e-2
+    kernels.attention_prefill_tc(*args, n - far)
+    assert rel_err(out[-1], v[far]) < 1e-2
+    kernels.attention_prefill_tc(*args, n - far - 1)
+    assert (out[-1].float() - v[far].float()).abs().max() > 0.1
+    # scores grow by about 0.2 per key: the maximum rises by 60 over the sequence
+    k2 = torch.zeros(n, hd, dtype=torch.bfloat16, device=DEV)
+    k2[:, 0] = torch.arange(n, device=DEV).to(torch.bfloat16) * 0.2
+    q2 = torch.zeros(n, hd, dtype=torch.bfloat16, device=DEV)
+    q2[:, 0] = 1.0
+    qkv2 = torch.cat([q2, k2, v], dim=1).contiguous()
+    kernels.attention_prefill_tc(qkv2[:, :hd], qkv2[:, hd:2 * hd], qkv2[:, 2 * hd:], out, cu, n, 1,
+                                 1, hd, 1.0, 0)
+    assert kernels.attention_tc_status() == 0
+    exact = ref_attention(q2.float().cpu().reshape(n, 1, hd), k2.float().cpu().reshape(n, 1, hd),
+                          v.float().cpu().reshape(n, 1, hd), 1.0, 0)
+    assert rel_err(out, exact) < 1.2e-2
+
+
+@pytest.mark.parametrize("nh,nkv,hd,splits", [(4, 1, 256, 1), (4, 2, 128, 2), (2, 2, 64, 0),
+                                              (2, 1, 48, 1), (2, 1, 208, 0)])
+def test_qk_norm_rope_store_writes_values_transposed(nh, nkv, hd, splits):
+    """The transposed copy of the values: every sequence starts at a multiple of 64
+    columns and is followed by zeros up to the next one; from partial sums (splits
+    > 0) and from the projected rows; head sizes that take the general kernel."""
+    from agave_b200 import kernels
+    lens = [1, 63, 64, 65, 200, 130]
+    T, B = sum(lens), len(lens)
+    width = (nh + 2 * nkv) * hd
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=DEV)
+    positions = torch.tensor(sum([list(range(n)) for n in lens], []), dtype=torch.int32, device=DEV)
+    seq_index = torch.tensor(sum([[i] * n for i, n in enumerate(lens)], []), dtype=torch.int32, device=DEV)
+    if splits:
+        part = rnd(splits, T, width, seed=4, scale=0.5)
+        qkv = torch.empty(T, width, dtype=torch.bfloat16, device=DEV)
+        want_v = part.sum(0)[:, (nh + nkv) * hd:].to(torch.bfloat16)
+    else:
+        part = None
+        qkv = rnd(T, width, dtype=torch.bfloat16, seed=4, scale=0.5)
+        want_v = qkv[:, (nh + nkv) * hd:].clone()
+    vt = kernels.prefill_values_scratch(T, B, nkv, hd, DEV)
+    vt.fill_(float("nan"))
+    kernels.qk_norm_rope_store(qkv, nh, nkv, hd, None, None, 0.0, None, None, 0, positions,
+                               seq_index=seq_index, partial=part, vt=vt, cu_seqlens=cu,
+                               max_len=max(lens))
+    start = 0
+    for b, n in enumerate(lens):
+        o = int(cu[b])
+        padded = (n + 63) // 64 * 64
+        got = vt[:, start:start + padded].float()
+        assert torch.equal(got[:, :n], want_v[o:o + n].float().t()), b
+        assert (got[:, n:] == 0).all(), b
+        start += padded
+    assert torch.equal(qkv[:, (nh + nkv) * hd:].float(), want_v.float())
+
+
 def test_attention_prefill_tensor_cores_far_key_and_window_edge():
     from agave_b200 import kernels
     hd, n, far = 256, 300, 3
