@@ -366,9 +366,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
 // Prompts: one CTA per SM walks over output tiles.  The accumulator in tensor
 // memory is double-buffered, so the products of a tile run while the epilogue
 // warps still read and store the tile before it; the ring of operand stages runs
-// on across tile boundaries.  Plain (MODE 0) and two-accumulator gated (MODE 1)
-// forms; K may be cut into `splits` ranges whose partial sums go to
-// out + split * split_stride (MODE 0, 32-bit out).
+// on across tile boundaries.  Plain (MODE 0): weight rows on M, BN tokens on N.
+// Gated (MODE 1): the 128-token tile is the M operand and the gate and up weight
+// tiles together are one N operand of 256 rows, because a product of N 256 keeps
+// the tensor pipe busy where two of N 128 do not; the accumulator's lanes are
+// tokens, columns 0..127 gate and 128..255 up values of the same features, and
+// each epilogue thread writes 16 consecutive features of its token.  K may be cut
+// into `splits` ranges whose partial sums go to out + split * split_stride
+// (MODE 0, 32-bit out).
 constexpr int PERSISTENT_EPI_WARPS = 8;
 constexpr int PERSISTENT_THREADS = 64 + 32 * PERSISTENT_EPI_WARPS;
 
@@ -483,7 +488,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w,
         }
     } else if (warp == 1 && lane == 0) {
         // ------------------------------------------------------------ products
-        constexpr uint32_t idesc = umma_idesc(TILE_M, BN);
+        constexpr uint32_t idesc = GATED ? umma_idesc(BN, 2 * TILE_M) : umma_idesc(TILE_M, BN);
         int it = 0, li = 0;
         for (int item = blockIdx.x; item < items && !*abort_flag; item += gridDim.x, ++li) {
             int m0, n0, kb_begin, n_kb, split;
@@ -510,11 +515,14 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w,
 #pragma unroll
                 for (int k = 0; k < TILE_K / UMMA_K; ++k) {
                     const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
-                    const uint64_t bd = umma_desc(b_addr + k * UMMA_K * 2);
-                    tc_mma_bf16(d_tmem, umma_desc(a_addr + k * UMMA_K * 2), bd, idesc, acc);
                     if (GATED)
-                        tc_mma_bf16(d_tmem + BN,
-                                    umma_desc(a_addr + TL::A_BYTES + k * UMMA_K * 2), bd, idesc, acc);
+                        // the token tile is the M operand; the gate tile and the up tile,
+                        // one after the other in the stage, are one N operand of 256 rows
+                        tc_mma_bf16(d_tmem, umma_desc(b_addr + k * UMMA_K * 2),
+                                    umma_desc(a_addr + k * UMMA_K * 2), idesc, acc);
+                    else
+                        tc_mma_bf16(d_tmem, umma_desc(a_addr + k * UMMA_K * 2),
+                                    umma_desc(b_addr + k * UMMA_K * 2), idesc, acc);
                 }
                 tc_commit(&empty[s]);
             }
@@ -530,8 +538,11 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w,
         TO* wst = (TO*)(epi + (warp - 2) * (TL::EPI_BYTES / PERSISTENT_EPI_WARPS));
         constexpr int EPV = 16 / (int)sizeof(TO);                    // elements per 16 bytes
         constexpr int VPR = 32 / EPV;                                // 16-byte pieces per staged row
-        constexpr int HALF_COLS = BN / 2;
+        // plain: BN token columns; gated: 128 feature columns (gate), the up values 128 further
+        constexpr int HALF_COLS = (GATED ? TILE_M : BN) / 2;
+        constexpr int UP_COL = GATED ? TILE_M : BN;
         static_assert(HALF_COLS % 32 == 0, "the column loop works in pairs of 16");
+        static_assert(!GATED || BN == 128, "the gated form puts a tile of 128 tokens on M");
         int li = 0;
         for (int item = blockIdx.x; item < items; item += gridDim.x, ++li) {
             int m0, n0, kb_begin, n_kb, split;
@@ -550,6 +561,10 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w,
             TO* gbase = out + (size_t)split * split_stride + (size_t)n0 * ldc + f0;
             const bool fast = f0 + 32 <= N && ldc % EPV == 0 && ((uintptr_t)gbase & 15) == 0;
             const int c_begin = half * HALF_COLS, c_end = c_begin + HALF_COLS;
+            // gated: lanes are tokens, columns 0..127 gate features, 128..255 up features
+            const int tok = n0 + quarter * 32 + lane;
+            TO* grow = out + (size_t)tok * ldc + m0;
+            const bool gfast = m0 + TILE_M <= N && ldc % EPV == 0 && ((uintptr_t)out & 15) == 0;
 
             auto release = [&]() {
                 // every value of this accumulator that the warp needs is in registers
@@ -558,6 +573,35 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w,
                 if (lane == 0) mbar_arrive(&acc_empty[as]);
             };
             auto work = [&](const uint32_t (&r)[16], const uint32_t (&u)[16], int c) {
+                if constexpr (GATED) {
+                    float v[16];
+                    if (act == 1) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            v[j] = silu_fast(__uint_as_float(r[j])) * __uint_as_float(u[j]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            v[j] = gelu_tanh_fast(__uint_as_float(r[j])) * __uint_as_float(u[j]);
+                    }
+                    if (tok < T) {
+                        if (gfast) {
+                            TO tmp[16];
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) store_out<TO>(tmp + j, v[j]);
+                            constexpr int NV = 16 * (int)sizeof(TO) / 16;
+#pragma unroll
+                            for (int q = 0; q < NV; ++q)
+                                reinterpret_cast<uint4*>(grow + c)[q] =
+                                    reinterpret_cast<const uint4*>(tmp)[q];
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j)
+                                if (m0 + c + j < N) store_out<TO>(grow + c + j, v[j]);
+                        }
+                    }
+                    return;
+                }
                 if (GATED) {
                     if (act == 1) {
 #pragma unroll
@@ -601,17 +645,17 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w,
             }
             uint32_t ra[16], ua[16], rb[16], ub[16];
             tc_ld16(lane_base + c_begin, ra);
-            if (GATED) tc_ld16(lane_base + BN + c_begin, ua);
+            if (GATED) tc_ld16(lane_base + UP_COL + c_begin, ua);
 #pragma unroll 1
             for (int c = c_begin; c < c_end; c += 32) {
                 tc_wait_ld();
                 tc_ld16(lane_base + c + 16, rb);
-                if (GATED) tc_ld16(lane_base + BN + c + 16, ub);
+                if (GATED) tc_ld16(lane_base + UP_COL + c + 16, ub);
                 work(ra, ua, c);
                 tc_wait_ld();
                 if (c + 32 < c_end) {
                     tc_ld16(lane_base + c + 32, ra);
-                    if (GATED) tc_ld16(lane_base + BN + c + 32, ua);
+                    if (GATED) tc_ld16(lane_base + UP_COL + c + 32, ua);
                 } else {
                     release();
                 }

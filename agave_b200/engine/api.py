@@ -164,7 +164,8 @@ class Engine:
         if max_batch is None:
             max_batch = max(1, min(1024, round_up(max_tokens, PAGE) // PAGE))
         self.max_batch, self.max_tokens = max_batch, max_tokens
-        self.runner = Runner(self.model, max_tokens, max_seq_len, max_batch)
+        self.runner = Runner(self.model, max_tokens, max_seq_len, max_batch,
+                             use_graphs=use_graphs)
         self.max_seq_len = self.runner.cache.max_seq_len
         self.sampler = Sampler(max_batch, self.device)
         kernels.prepare_device(self.device)

@@ -252,3 +252,35 @@ def test_sizes_the_fast_kernels_refuse_take_the_other_path(dtype):
     again = eng.generate([seqs[0][:5]], max_new_tokens=6, temperature=0.8, top_k=12, top_p=0.9,
                          repeat_penalty=1.2, seed=3, stop_token_ids=[])
     assert outs == again and len(outs[0]) == 6
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_recorded_prompt_steps_match_the_plain_implementation(name, dtype):
+    """A prompt step whose sizes repeat runs from a recording: the same total, batch
+    and greatest length with other tokens, other lengths and other slots must give
+    what the plain implementation gives, and decoding goes on from its cache."""
+    eng, folder = engine_for(name, dtype)
+    V = vocab(name)
+    shapes = [(40, 23, 7), (40, 7, 23), (23, 40, 7), (40, 23, 7)]     # total 70, greatest 40
+    held = []
+    for round_, lens in enumerate(shapes):
+        prompts = [random_tokens(n, V, 100 + 10 * round_ + i) for i, n in enumerate(lens)]
+        slots = [eng.acquire() for _ in prompts]
+        got = eng.step(list(zip(slots, prompts)), [[n - 1] for n in lens])
+        for i, p in enumerate(prompts):
+            close(got[i:i + 1], plain_logits(folder, p)[-1:], TOL[dtype])
+        # one more token each, from the cache the recorded step wrote
+        nxt = [int(got[i].argmax()) for i in range(len(prompts))]
+        dec = eng.step([(s, [t]) for s, t in zip(slots, nxt)], [[0]] * len(prompts))
+        for i, p in enumerate(prompts):
+            close(dec[i:i + 1], plain_logits(folder, p + [nxt[i]])[-1:], TOL[dtype])
+        if round_ % 2:
+            for s in slots:
+                eng.release(s)
+        else:
+            held.append(slots)               # the next round gets other slots
+    for slots in held:
+        for s in slots:
+            eng.release(s)
+    assert len(eng.runner._prompt_graphs) >= 1
