@@ -120,6 +120,9 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                             const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_vt, AtArgs a) {
+#ifdef AT_TIMING
+    const long long t_entry = clock64();
+#endif
     pdl_wait();
     pdl_launch_next();
     extern __shared__ uint8_t smem_raw[];
@@ -330,6 +333,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         const bool prof = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 64;
         long long tacc[16] = {0};
         long long tprev = clock64();
+        tacc[12] = tprev - t_entry;
 #endif
         for (int j = 0; j < n_tiles; ++j) {
             const int s = j & 1;
@@ -438,6 +442,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
             AT_T(7)
         }
         AT_DUMP(0, 8)
+#ifdef AT_TIMING
+        if (prof) g_attn_prof[12] = tacc[12];
+        const long long t_loop_end = clock64();
+#endif
         if (ok && !*abort_flag) {
             if (!mbar_wait(o_done, (n_tiles - 1) & 1)) {
                 give_up(3, 3);
@@ -447,25 +455,41 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                 __nv_bfloat16* dst = a.out + (size_t)(seq0 + qp) * ((size_t)a.nh * a.hd) +
                                      (size_t)(head0 + hl) * a.hd;
                 const bool valid = qp < len;
-                for (int c = 0; c < a.hd; c += 16) {
-                    uint32_t o[16];
-                    tc_ld16(lane_addr + AT_O_COL + c, o);
+                // 64 columns per wait: four loads in flight, then their stores
+                for (int c0 = 0; c0 < a.hd; c0 += 64) {
+                    uint32_t o[4][16];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        if (c0 + q * 16 < a.hd) tc_ld16(lane_addr + AT_O_COL + c0 + q * 16, o[q]);
                     tc_wait_ld();
                     if (valid) {
-                        uint32_t w[8];
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            const __nv_bfloat162 t = __floats2bfloat162_rn(
-                                __uint_as_float(o[2 * i]) * inv, __uint_as_float(o[2 * i + 1]) * inv);
-                            w[i] = *reinterpret_cast<const uint32_t*>(&t);
+                        for (int q = 0; q < 4; ++q) {
+                            const int c = c0 + q * 16;
+                            if (c < a.hd) {
+                                uint32_t w[8];
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) {
+                                    const __nv_bfloat162 t = __floats2bfloat162_rn(
+                                        __uint_as_float(o[q][2 * i]) * inv,
+                                        __uint_as_float(o[q][2 * i + 1]) * inv);
+                                    w[i] = *reinterpret_cast<const uint32_t*>(&t);
+                                }
+                                *reinterpret_cast<uint4*>(dst + c) = make_uint4(w[0], w[1], w[2], w[3]);
+                                *reinterpret_cast<uint4*>(dst + c + 8) =
+                                    make_uint4(w[4], w[5], w[6], w[7]);
+                            }
                         }
-                        *reinterpret_cast<uint4*>(dst + c) = make_uint4(w[0], w[1], w[2], w[3]);
-                        *reinterpret_cast<uint4*>(dst + c + 8) = make_uint4(w[4], w[5], w[6], w[7]);
                     }
                 }
             }
         }
     }
+#ifdef AT_TIMING
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 64) {
+        g_attn_prof[13] = clock64() - t_entry;
+    }
+#endif
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {

@@ -460,6 +460,17 @@ def prefill_values_scratch(T: int, B: int, n_kv_heads: int, head_dim: int,
     return torch.empty((n_kv_heads * head_dim, cols), dtype=torch.bfloat16, device=device)
 
 
+def transpose_values(v: torch.Tensor, vt: torch.Tensor, cu_seqlens: torch.Tensor, max_len: int,
+                     n_kv_heads: int, head_dim: int) -> None:
+    """vt (from ``prefill_values_scratch``) = the values v [T, nkv * hd] (row-strided
+    view) transposed, every sequence padded with zeros to a multiple of 64 columns."""
+    assert v.dtype == torch.bfloat16 and vt.dtype == torch.bfloat16 and v.stride(1) == 1
+    _dense(vt, "vt"); _i32(cu_seqlens, "cu_seqlens")
+    _check(library().agv_transpose_values(
+        _ptr(v), ctypes.c_longlong(v.stride(0)), _ptr(vt), ctypes.c_longlong(vt.shape[1]),
+        _ptr(cu_seqlens), cu_seqlens.numel() - 1, max_len, n_kv_heads, head_dim, _stream()))
+
+
 def attention_prefill_tc(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor,
                          cu_seqlens: torch.Tensor, max_len: int, n_heads: int, n_kv_heads: int,
                          head_dim: int, scale: float, window: int,

@@ -16,6 +16,7 @@ Cases (Gemma 3 1B layer sizes, random bfloat16 data):
   attention_decode_full     the same without a window
   norm_decode          residual sum + two RMS norms over 8 rows of 16 partial sums
   decode_step          whole decode steps of a 6-layer model (vocabulary 32,768), batch 8
+  decode_step_b64      the same at batch 64
   prefill_step         whole prompt steps of the same model, one prompt of 2,048 tokens
 
 Each case prints the mean time per call: the calls run back to back from a CUDA
@@ -106,12 +107,21 @@ def case_attention_prefill(window=0, legacy=False):
     cu = torch.tensor([0, T], dtype=torch.int32, device=DEV)
     pairs = T * (T + 1) // 2 if not window else sum(min(p + 1, window) for p in range(T))
     flops = 4 * NH * HD * pairs
-    kern = kernels.attention_prefill_mma if legacy else kernels.attention_prefill_tc
+    # the values transposed, as the q/k norm launch leaves them in a model step
+    vts = []
+    for t in qkv:
+        vt = kernels.prefill_values_scratch(T, 1, NKV, HD, t.device)
+        kernels.transpose_values(t[:, (NH + NKV) * HD:], vt, cu, T, NKV, HD)
+        vts.append(vt)
 
     def fn(i):
         t = qkv[i]
-        kern(t[:, :NH * HD], t[:, NH * HD:(NH + NKV) * HD], t[:, (NH + NKV) * HD:], out, cu, T,
-             NH, NKV, HD, 0.0625, window)
+        q, k, v = t[:, :NH * HD], t[:, NH * HD:(NH + NKV) * HD], t[:, (NH + NKV) * HD:]
+        if legacy:
+            kernels.attention_prefill_mma(q, k, v, out, cu, T, NH, NKV, HD, 0.0625, window)
+        else:
+            kernels.attention_prefill_tc(q, k, v, out, cu, T, NH, NKV, HD, 0.0625, window,
+                                         vt=vts[i])
     return fn, flops, qkv[0].numel() * 2 + out.numel() * 2, c
 
 
@@ -147,7 +157,7 @@ def case_norm_decode():
         y.numel() * 4 + 3 * 8 * H * 4, 1
 
 
-def _six_layer_engine():
+def _six_layer_engine(max_batch=16):
     from .engine.api import Engine
     cfg = {
         "architectures": ["Gemma3ForCausalLM"], "model_type": "gemma3_text",
@@ -156,8 +166,8 @@ def _six_layer_engine():
         "intermediate_size": FF, "vocab_size": 32768, "sliding_window": 512,
         "sliding_window_pattern": 6, "rope_local_base_freq": 10000.0, "rope_theta": 1000000.0,
         "rms_norm_eps": 1e-6, "max_position_embeddings": 8192, "eos_token_id": 1}
-    return Engine.from_config(cfg, seed=2, dtype="bfloat16", max_tokens=16 * 8192, ctx_size=8192,
-                              max_batch=16, use_graphs=False)
+    return Engine.from_config(cfg, seed=2, dtype="bfloat16", max_tokens=max_batch * 8192,
+                              ctx_size=8192, max_batch=max_batch, use_graphs=False)
 
 
 def case_prefill_step():
@@ -172,14 +182,14 @@ def case_prefill_step():
     return fn, 0, 0, 0
 
 
-def case_decode_step():
-    eng = _six_layer_engine()
+def case_decode_step(batch=8):
+    eng = _six_layer_engine(max_batch=max(16, batch))
     g = torch.Generator().manual_seed(0)
-    lens = torch.linspace(128, 2048, 8).round().int().tolist()
+    lens = torch.linspace(128, 2048, batch).round().int().tolist()
     prompts = [torch.randint(3, 32768, (n,), generator=g).tolist() for n in lens]
     slots = [eng.acquire() for _ in prompts]
     eng.step([(s, p) for s, p in zip(slots, prompts)], [[] for _ in prompts])
-    return (lambda i: eng.step([(s, [5]) for s in slots], [[0]] * 8)), 0, 0, 0
+    return (lambda i: eng.step([(s, [5]) for s in slots], [[0]] * batch)), 0, 0, 0
 
 
 CASES = {
@@ -195,6 +205,7 @@ CASES = {
     "attention_decode_full": lambda: case_attention_decode(0, 2048),
     "norm_decode": case_norm_decode,
     "decode_step": case_decode_step,
+    "decode_step_b64": lambda: case_decode_step(64),
     "prefill_step": case_prefill_step,
 }
 

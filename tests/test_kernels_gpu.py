@@ -526,6 +526,28 @@ def test_attention_prefill_tcgen05(nh, nkv, hd, window):
     assert rel_err(out[o:o + n], exact) < 1.2e-2
 
 
+@pytest.mark.parametrize("window", [0, 512])
+def test_attention_prefill_tcgen05_long_sequences(window):
+    """Thousands of positions, two sequences: the tcgen05 kernel and the mma.sync
+    kernel are two independent implementations of the same sum."""
+    from agave_b200 import kernels
+    nh, nkv, hd = 4, 1, 256
+    lens = [2048, 1500]
+    T = sum(lens)
+    qkv = rnd(T, (nh + 2 * nkv) * hd, dtype=torch.bfloat16, seed=5, scale=0.7)
+    q, k, v = qkv[:, :nh * hd], qkv[:, nh * hd:(nh + nkv) * hd], qkv[:, (nh + nkv) * hd:]
+    cu = torch.tensor([0, lens[0], T], dtype=torch.int32, device=DEV)
+    ref = torch.empty((T, nh * hd), dtype=torch.bfloat16, device=DEV)
+    kernels.attention_prefill_mma(q, k, v, ref, cu, max(lens), nh, nkv, hd, 0.0625, window)
+    out = torch.full_like(ref, float("nan"))
+    kernels.attention_prefill_tc(q, k, v, out, cu, max(lens), nh, nkv, hd, 0.0625, window)
+    assert kernels.attention_tc_status() == 0
+    assert torch.isfinite(out.float()).all()
+    assert rel_err(out, ref) < 1.2e-2
+    for row in (0, 63, 64, 2047, 2048, T - 1):
+        assert rel_err(out[row], ref[row]) < 2e-2, row
+
+
 def test_attention_prefill_tcgen05_far_key_window_edge_and_growing_scores():
     """One score that stands out among hundreds; the window's edge; and scores that
     grow along the sequence, so that the running maximum moves by more than the
