@@ -337,13 +337,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
             for (int i = threadIdx.x; i < BN * width; i += GEMM_THREADS) {
                 const int n = i / width, fl = f_lo + i % width;
                 if (n0 + n < T && m0 + fl < N) {
-                    float acc = 0.f;
-                    for (int q = 0; q < S; ++q) acc += ld_peer_f32(red + n * RED_LD + fl, q);
-                    if (HALF) {
+                    // every peer's value is requested before the first is used: a load
+                    // from a peer's shared memory takes hundreds of cycles
+                    float pv[8], pu[8];
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) {
+                        pv[q] = q < S ? ld_peer_f32(red + n * RED_LD + fl, q) : 0.f;
                         // rows 64..127 of the tile are the up rows of the same features
+                        if (HALF) pu[q] = q < S ? ld_peer_f32(red + n * RED_LD + TILE_M / 2 + fl, q) : 0.f;
+                    }
+                    float acc = 0.f;
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) acc += pv[q];          // in rank order
+                    if (HALF) {
                         float up = 0.f;
-                        for (int q = 0; q < S; ++q)
-                            up += ld_peer_f32(red + n * RED_LD + TILE_M / 2 + fl, q);
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) up += pu[q];
                         acc = (act == 1 ? silu_fast(acc) : gelu_tanh_fast(acc)) * up;
                     }
                     store_out<TO>(gout + (size_t)(n0 + n) * ldc + m0 + fl, acc);
