@@ -367,7 +367,10 @@ __device__ __forceinline__ float dm_ld_peer(const float* local, unsigned rank) {
 template <int HDP>
 __global__ void __launch_bounds__(DM_THREADS)
 attention_decode_mma_kernel(DecodeArgs a, int cs) {
-    pdl_wait();
+    // Slots, positions and page tables are written by copies at the start of the step,
+    // before any kernel of it runs, so they are read before this kernel waits for its
+    // predecessor (which writes q and the new key and value): two dependent trips to
+    // memory leave the chain.
     pdl_launch_next();
     typedef __nv_bfloat16 T;
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -392,6 +395,7 @@ attention_decode_mma_kernel(DecodeArgs a, int cs) {
     T* outp = (T*)a.out + ((size_t)b * a.nh + h0) * hd;
     const int slot = a.slots[b];
     if (slot < 0) {
+        pdl_wait();
         if (split == 0)
             for (int i = tid; i < gc * hd; i += DM_THREADS) outp[i] = __float2bfloat16_rn(0.f);
         return;
@@ -402,19 +406,42 @@ attention_decode_mma_kernel(DecodeArgs a, int cs) {
     const int used = (p - lo) / DM_KEYS + 1;                  // chunks this sequence has
     const int cid = split / cs, crank = split % cs;
     const int used_clusters = (used + cs - 1) / cs;
-    if (cid >= used_clusters) return;                         // the whole cluster is past the end
+    if (cid >= used_clusters) {                               // the whole cluster is past the end
+        pdl_wait();
+        return;
+    }
     const bool has = j0 <= p;                                 // (always true when cs == 1)
     const int n = has ? min(DM_KEYS, p - j0 + 1) : 0;
     float* Osm = reinterpret_cast<float*>(Ks);                // [16][HDP], after the scores are done
 
-    if (has) {
-    const int* table = a.page_table + (size_t)slot * a.max_pages;
-    if (tid < DM_KEYS) {
+    if (has && tid < DM_KEYS) {
+        const int* table = a.page_table + (size_t)slot * a.max_pages;
         const int row = (j0 + tid) % a.cap;
         rowoff[tid] = tid < n ? table[row / a.page] * a.page + row % a.page : -1;
     }
-    // queries of the group: rows beyond the group's heads and dims beyond hd are zero
+    __syncthreads();
     constexpr int CPR = HDP / 8;
+    // Keys and values of earlier positions were stored by earlier steps: their copies
+    // start before the wait too.  Only the row of position p is the predecessor's.
+    const int r_new = p - j0;                                 // in [0, n) in the last chunk only
+    if (has) {
+        for (int i = tid; i < DM_KEYS * CPR; i += DM_THREADS) {
+            const int r = i / CPR, c = i % CPR;
+            const int off = dm_swz<HDP>(r, c);
+            if (r == r_new) continue;
+            if (rowoff[r] >= 0 && c * 8 < hd) {
+                const size_t src = ((size_t)rowoff[r] * a.nkv + g) * hd + c * 8;
+                cp_async16(Ks + off, (const T*)a.k_pool + src);
+                cp_async16(Vs + off, (const T*)a.v_pool + src);
+            } else {
+                *reinterpret_cast<uint4*>(Ks + off) = make_uint4(0, 0, 0, 0);
+                *reinterpret_cast<uint4*>(Vs + off) = make_uint4(0, 0, 0, 0);
+            }
+        }
+    }
+    pdl_wait();
+    if (has) {
+    // queries of the group: rows beyond the group's heads and dims beyond hd are zero
     for (int i = tid; i < DM_HEADS * CPR; i += DM_THREADS) {
         const int r = i / CPR, c = i % CPR;
         T* dst = Qs + dm_swz<HDP>(r, c);
@@ -423,17 +450,18 @@ attention_decode_mma_kernel(DecodeArgs a, int cs) {
         else
             *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
     }
-    __syncthreads();
-    for (int i = tid; i < DM_KEYS * CPR; i += DM_THREADS) {
-        const int r = i / CPR, c = i % CPR;
-        const int off = dm_swz<HDP>(r, c);
-        if (rowoff[r] >= 0 && c * 8 < hd) {
-            const size_t src = ((size_t)rowoff[r] * a.nkv + g) * hd + c * 8;
-            cp_async16(Ks + off, (const T*)a.k_pool + src);
-            cp_async16(Vs + off, (const T*)a.v_pool + src);
-        } else {
-            *reinterpret_cast<uint4*>(Ks + off) = make_uint4(0, 0, 0, 0);
-            *reinterpret_cast<uint4*>(Vs + off) = make_uint4(0, 0, 0, 0);
+    if (r_new >= 0 && r_new < DM_KEYS) {
+        // the new position's key and value
+        for (int c = tid; c < CPR; c += DM_THREADS) {
+            const int off = dm_swz<HDP>(r_new, c);
+            if (rowoff[r_new] >= 0 && c * 8 < hd) {
+                const size_t src = ((size_t)rowoff[r_new] * a.nkv + g) * hd + c * 8;
+                cp_async16(Ks + off, (const T*)a.k_pool + src);
+                cp_async16(Vs + off, (const T*)a.v_pool + src);
+            } else {
+                *reinterpret_cast<uint4*>(Ks + off) = make_uint4(0, 0, 0, 0);
+                *reinterpret_cast<uint4*>(Vs + off) = make_uint4(0, 0, 0, 0);
+            }
         }
     }
     cp_async_wait_all();

@@ -214,7 +214,9 @@ qk_norm_rope_store_reg_kernel(T* __restrict__ qkv, long long row_stride,
                               const float* __restrict__ cosv, const float* __restrict__ sinv,
                               const int* __restrict__ positions, CacheWrite cw, VtWrite vw,
                               int vt_blocks) {
-    pdl_wait();
+    // What the host copied in at the start of the step (positions, sequence index, slots,
+    // lengths, page table) and the norm weights are read before the wait for the
+    // predecessor, which only produces the projection (and, early in a step, cos / sin).
     pdl_launch_next();
     constexpr int hd = NE * 32, HALF = NE / 2, H2 = hd / 2;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -241,6 +243,7 @@ qk_norm_rope_store_reg_kernel(T* __restrict__ qkv, long long row_stride,
                 cols[threadIdx.x] = col;
                 pads[threadIdx.x] = pad;
             }
+            pdl_wait();
             // 16 threads per token row (4 columns each), 8 rows per pass
             const int tr = threadIdx.x >> 4, tc = (threadIdx.x & 15) * 4;
             const size_t vcol = (size_t)(nh + nkv) * hd + c0 + tc;
@@ -287,22 +290,31 @@ qk_norm_rope_store_reg_kernel(T* __restrict__ qkv, long long row_stride,
                         __float2bfloat16(0.f);
                 }
             }
+        } else {
+            pdl_wait();
         }
         return;
     }
     const long long item = (long long)(blockIdx.x - vt_blocks) * QK_WARPS + warp;
-    if (item >= (long long)n_tokens * heads) return;
+    if (item >= (long long)n_tokens * heads) {
+        pdl_wait();
+        return;
+    }
     const int t = (int)(item / heads), head = (int)(item % heads);
     const int e0 = lane * HALF;                       // first run; the second is at e0 + H2
     T* src = qkv + (size_t)t * row_stride + (size_t)head * hd + e0;
     const bool is_q = head < nh, is_k = !is_q && head < nh + nkv, is_v = !is_q && !is_k;
     const float* w = is_q ? wq : (is_k ? wk : nullptr);
     const bool stores = !is_q && cw.k_pool;
-    // first links of the chain to the cache row
-    int cb = 0, c_pos = 0;
+    // the chain to the cache row
+    int c_pos = 0, c_slot = -1, c_len = 0, c_page = 0;
     if (stores) {
-        cb = cw.seq_index[t];
+        const int cb = cw.seq_index[t];
         c_pos = positions[t];
+        c_slot = cw.slots[cb];
+        c_len = cw.lens[cb];
+        if (c_slot >= 0)
+            c_page = cw.page_table[(size_t)c_slot * cw.max_pages + (c_pos % cw.cap) / cw.page];
     }
     // operands of the arithmetic: v[0..HALF) first run, v[HALF..NE) second run
     float wv[NE], cs[HALF], sn[HALF], v[NE];
@@ -313,6 +325,7 @@ qk_norm_rope_store_reg_kernel(T* __restrict__ qkv, long long row_stride,
 #pragma unroll
         for (int i = 0; i < NE; ++i) wv[i] = 1.f;
     }
+    pdl_wait();
     const bool rotate = cosv && !is_v;
     if (rotate) {
         ld_run<HALF>(cosv + (size_t)t * H2 + e0, cs);
@@ -347,14 +360,6 @@ qk_norm_rope_store_reg_kernel(T* __restrict__ qkv, long long row_stride,
     } else {
         ld_run<HALF>(src, v);
         ld_run<HALF>(src + H2, v + HALF);
-    }
-    // second and third links
-    int c_slot = -1, c_len = 0, c_page = 0;
-    if (stores) {
-        c_slot = cw.slots[cb];
-        c_len = cw.lens[cb];
-        if (c_slot >= 0)
-            c_page = cw.page_table[(size_t)c_slot * cw.max_pages + (c_pos % cw.cap) / cw.page];
     }
     if (!is_v) {
         if (w) {
