@@ -393,11 +393,13 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
         linear_simt(x, w, out, w2, activation)
 
 
-def plan_splits(T: int, N: int, K: int):
+def plan_splits(T: int, N: int, K: int, cheap_sum: bool = False):
     """(groups, cluster size) of the ranges K is cut into so that about one CTA per
     SM is busy when the weight has few row tiles (decoding through narrow
     layers).  The CTAs of a cluster add their sums in the kernel; the groups are
-    left to the consumer.  Prompts are not cut."""
+    left to the consumer.  ``cheap_sum``: the consumer adds partial sums in the
+    loads it makes anyway (the q/k norm kernel), so up to eight groups are better
+    than a cluster, whose exchange costs about 2 us.  Prompts are not cut."""
     if T > 64:
         # prompts: only a long K over few tiles is cut, in two, with the partial
         # sums left to the consumer (a cluster's exchange is slow for wide tiles)
@@ -412,6 +414,12 @@ def plan_splits(T: int, N: int, K: int):
     want = min(kb, (N_SMS + ctas - 1) // ctas)
     if ctas >= 100 or want < 2:
         return 1, 0
+    if T > 16:
+        # tiles of 32 and 64 tokens: a cluster's exchange grows with the tile, the
+        # consumer's extra reads do not matter yet
+        return linear_tc_splits(K, min(want, 16)), 0
+    if cheap_sum:
+        return linear_tc_splits(K, min(want, 8)), 0
     if want <= 8 or kb < 64:
         # a single cluster per tile adds its ranges in the kernel
         c = min(want, 8)
@@ -420,14 +428,15 @@ def plan_splits(T: int, N: int, K: int):
     return linear_tc_splits(K, min(want, 16)), 0
 
 
-def linear_partial(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+def linear_partial(x: torch.Tensor, w: torch.Tensor, cheap_sum: bool = False) -> torch.Tensor:
     """x w^T in 32-bit for a consumer that adds over a leading axis: [G, T, N] on
     the tensor-core path (G >= 1 groups of ranges of K; the ranges of a group
-    are added inside the kernel by a cluster), else [T, N] in x's dtype."""
+    are added inside the kernel by a cluster), else [T, N] in x's dtype.
+    ``cheap_sum``: see ``plan_splits``."""
     T, K = x.shape
     N = w.shape[0]
     if linear_tc_supported(x, w):
-        groups, csize = plan_splits(T, N, K)
+        groups, csize = plan_splits(T, N, K, cheap_sum)
         out = torch.empty((groups, T, N), dtype=torch.float32, device=x.device)
         linear_tc(x, w, out if groups > 1 else out[0], splits=groups * max(csize, 1),
                   cluster=csize)

@@ -80,7 +80,7 @@ class AttentionMixer:
         s = self.spec
         nh, nkv, hd = s.n_heads, s.n_kv_heads, s.head_dim
         T = x.shape[0]
-        proj = self.qkv.partial(x)
+        proj = self.qkv.partial(x, cheap_sum=True)
         if proj.dim() == 3:
             part, qkv = proj, ctx.new(T, (nh + 2 * nkv) * hd)
         else:

@@ -28,11 +28,12 @@ class Linear:
         kernels.linear(x, self.weight, out)
         return out
 
-    def partial(self, x: torch.Tensor) -> torch.Tensor:
+    def partial(self, x: torch.Tensor, cheap_sum: bool = False) -> torch.Tensor:
         """x w^T for a consumer that sums over a leading axis itself: [S, T, N]
         32-bit partial sums over ranges of K on the tensor-core path (S may be
-        1), else the plain [T, N] result."""
-        return kernels.linear_partial(x, self.weight)
+        1), else the plain [T, N] result.  ``cheap_sum``: the consumer adds the
+        partial sums in loads it makes anyway, so more of them are welcome."""
+        return kernels.linear_partial(x, self.weight, cheap_sum)
 
 
 class GatedLinear:
