@@ -123,7 +123,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
 #ifdef AT_TIMING
     const long long t_entry = clock64();
 #endif
-    pdl_wait();
+    // barriers, tensor memory and the sequence bounds (copied in at the start of the
+    // step) are set up while the predecessor still runs; the loader and the softmax
+    // warps wait for it before they touch q, k, v or out
     pdl_launch_next();
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -154,7 +156,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
     const int seq0 = a.cu[b], len = a.cu[b + 1] - seq0;
     // tiles at the end of a sequence walk the most key tiles: they are scheduled first
     const int q0 = (gridDim.x - 1 - blockIdx.x) * a.QT;
-    if (q0 >= len) return;
+    if (q0 >= len) {
+        pdl_wait();
+        return;
+    }
     const int heads_per_kv = a.nh / a.nkv;
     const int head0 = a.G > 1 ? blockIdx.y * a.G : blockIdx.y;   // first query head of this CTA
     const int kvh = head0 / heads_per_kv;
@@ -199,6 +204,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
     if (warp == 0 && lane == 0) {
         // ------------------------------------------------------------ loader
         const int vt0 = padded_start(a.cu, b);
+        pdl_wait();
         mbar_expect_tx(q_full, (uint32_t)q_bytes);
         for (int hl = 0; hl < a.G; ++hl)
             for (int kb = 0; kb < a.kb; ++kb)
@@ -329,6 +335,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         const int q_min = q0, q_max = q0 + a.QT - 1;
         float m_used = -INFINITY, l = 0.f;
         bool ok = true;
+        pdl_wait();
 #ifdef AT_TIMING
         const bool prof = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 64;
         long long tacc[16] = {0};

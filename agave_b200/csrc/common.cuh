@@ -43,17 +43,17 @@ static inline bool agv_aligned(const void* p, size_t a) { return ((uintptr_t)p %
 // Every kernel is launched so that it may start while the kernel before it on
 // the stream is still draining: its CTAs are scheduled and run whatever does not
 // depend on earlier results, then pdl_wait() blocks until the earlier kernel has
-// finished and its writes are visible.  No kernel touches global memory before
-// its pdl_wait().  pdl_launch_next() lets the kernel after this one be scheduled.
+// finished and its writes are visible.  Before its pdl_wait() a kernel reads only what
+// no kernel of the step writes (weights, what the host copied in at the start of the
+// step, cache rows of earlier steps) and writes nothing to global memory.
+// pdl_launch_next() lets the kernel after this one be scheduled.
 __device__ __forceinline__ void pdl_wait() {
     asm volatile("griddepcontrol.wait;" ::: "memory");
 }
-// Only a grid of at most about two waves lets its successor in early: the
-// successor's CTAs sit on SMs while they wait, and a longer grid needs those SMs for
-// its own later waves (a prompt step ran 6 % slower with the early trigger).
+// Every kernel lets its successor in as soon as it runs: the successor's CTAs set up,
+// read what does not depend on this kernel (weights, step metadata) and then wait.
 __device__ __forceinline__ void pdl_launch_next() {
-    if (gridDim.x * gridDim.y * gridDim.z <= 320u)
-        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
 extern int g_agv_pdl;      // 1: launches carry the programmatic-serialization attribute
