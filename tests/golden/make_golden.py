@@ -18,7 +18,9 @@ import torch
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        sys.exit("usage: python tests/golden/make_golden.py /path/to/agave")
+    root = sys.argv[1]
     path = os.path.join(root, "research", "kernels", "reference.py")
     spec = importlib.util.spec_from_file_location("agave_reference_kernels", path)
     ref = importlib.util.module_from_spec(spec)
