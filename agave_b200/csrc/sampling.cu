@@ -132,6 +132,28 @@ AGV_API int agv_history_append(const int* tokens, const int* slots, int* hist, i
     return 0;
 }
 
+// A decode step launched before the host has read the step before it takes its
+// input tokens from that step's choices on the device: tokens[b] = prev[b] when
+// *take is set (ids outside the vocabulary, possible only in padding rows, become 0).
+__global__ void take_tokens_kernel(int* __restrict__ tokens, const int* __restrict__ prev,
+                                   const int* __restrict__ take, int B, int V) {
+    pdl_wait();
+    pdl_launch_next();
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= B || !*take) return;
+    const int t = prev[b];
+    tokens[b] = (t >= 0 && t < V) ? t : 0;
+}
+
+AGV_API int agv_take_tokens(int* tokens, const int* prev, const int* take, int B, int V,
+                            cudaStream_t stream) {
+    AGV_REQUIRE(B >= 0 && V > 0, "take_tokens: bad sizes");
+    if (B == 0) return 0;
+    agv_launch(take_tokens_kernel, (B + 127) / 128, 128, 0, stream, tokens, prev, take, B, V);
+    AGV_LAUNCH_OK("take_tokens_kernel");
+    return 0;
+}
+
 // The thread of an id's first occurrence applies the penalty once per
 // occurrence, so no two threads touch one logit.
 __global__ void repeat_penalty_kernel(float* __restrict__ logits, long long row_stride, int V,

@@ -22,14 +22,14 @@ import numpy as np
 import torch
 
 from .. import kernels
-from ..cache import PAGE, round_up
+from ..cache import PAGE, CacheError, round_up
 from ..config import load_config, resolve_architecture
 from ..models.decoder import DecoderModel, decoder_param_specs
 from ..sampling import Sampler, SamplingParams
 from ..weights import load_weights, random_tensors
 from .batch import DECODE, PREFILL, StepContext
-from .generate import GenerationPlan
-from .step import Runner
+from .generate import GenerationPlan, RequestState
+from .step import Runner, StepError
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
            "float32": torch.float32, "fp32": torch.float32, "f32": torch.float32}
@@ -52,7 +52,7 @@ class _DecodeGraph:
         self.size = size
         dev = engine.device
         B = size
-        n_int = round_up(3 * B + 3 * B + 1 + B, 2)     # step arrays, sampling steps; even
+        n_int = round_up(3 * B + 3 * B + 1 + B + 1, 2)  # step arrays, sampling steps, flag; even
         # two pinned staging buffers: the next step's arrays are filled while the
         # copy of this step's may still be in flight
         self.hosts = [torch.zeros(n_int + 2 * B, dtype=torch.int32, pin_memory=True)
@@ -65,12 +65,17 @@ class _DecodeGraph:
         self.views = dict(tokens=d[:B], positions=d[B:2 * B], seq_index=d[2 * B:3 * B],
                           cu=d[o:o + B + 1], slots=d[o + B + 1:o + 2 * B + 1],
                           lens=d[o + 2 * B + 1:o + 3 * B + 1],
-                          steps=d[o + 3 * B + 1:o + 4 * B + 1])
+                          steps=d[o + 3 * B + 1:o + 4 * B + 1],
+                          take=d[o + 4 * B + 1:o + 4 * B + 2])
+        self.flag_at = o + 4 * B + 1
         self.seq_ids = d[n_int:].view(torch.int64)
         self.n_int = n_int
         self.rows = torch.arange(B, dtype=torch.int32, device=dev)
         self.next_dev = torch.zeros(B, dtype=torch.int32, device=dev)
-        self.next_host = torch.zeros(B, dtype=torch.int32, pin_memory=True)
+        # one result buffer and one event per staging buffer: a step may be launched
+        # before the result of the step before it has been read
+        self.next_hosts = [torch.zeros(B, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self.done = [torch.cuda.Event() for _ in range(2)]
         self.logits: Optional[torch.Tensor] = None
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.kernels_per_step = 0
@@ -79,6 +84,8 @@ class _DecodeGraph:
     def _body(self, engine: "Engine", params: SamplingParams, seed: int) -> None:
         v = self.views
         runner = engine.runner
+        # a step launched ahead takes its token ids from the choices of the step before
+        kernels.take_tokens(v["tokens"], self.next_dev, v["take"], runner.vocab_size)
         ctx = StepContext(mode=DECODE, n_tokens=self.size, batch=self.size, tokens=v["tokens"],
                           positions=v["positions"], seq_index=v["seq_index"],
                           cu_seqlens=v["cu"], slots=v["slots"], lens=v["lens"],
@@ -113,10 +120,13 @@ class _DecodeGraph:
             self.graph.replay()
         else:
             self._body(engine, params, seed)
-        self.next_host.copy_(self.next_dev, non_blocking=True)
+        self.next_hosts[which].copy_(self.next_dev, non_blocking=True)
+        self.done[which].record()
 
-    def wait(self) -> None:
-        torch.cuda.current_stream().synchronize()
+    def wait(self, which: int = 0) -> "np.ndarray":
+        """The tokens chosen by the step launched from staging buffer ``which``."""
+        self.done[which].synchronize()
+        return self.next_hosts[which].numpy()
 
     def run(self, engine: "Engine", params: SamplingParams, seed: int) -> None:
         self.launch(engine, params, seed)
@@ -302,40 +312,61 @@ class Engine:
     def _decode_loop(self, plan: GenerationPlan, params: SamplingParams, seed: int,
                      stats: dict) -> None:
         """One token for every live sequence per step until the batch is empty.
-        While a step runs on the GPU the host stages the next one (all but the
-        token ids, which it does not know yet) on the guess that nobody ends."""
+
+        A step is launched before the host has read the step before it (its token
+        ids come from that step's choices on the device), unless a sequence reaches
+        its token limit with the step in flight; so the GPU does not idle while the
+        host reads tokens and checks stop ids.  When a stop id turns up, the step
+        already in flight still ran the ended sequence: its token is dropped and its
+        slot is released once that step has been read.
+        """
         book = self.runner.cache.book
+        cache = self.runner.cache
         live = plan.live()
-        staged = None                      # (graph, buffer index) staged for `live`
         which = 0
-        while live:
-            n = len(live)
-            if staged is None:
-                staged = (self._stage_step(live, params, seed, 0, which), which)
-            g, w = staged
-            g.hosts_np[w][:n] = np.fromiter((r.output[-1] for r in live), dtype=np.int32, count=n)
-            self.runner.cache.flush()
-            g.launch(self, params, seed, w)
-            # meanwhile: the step after this one
-            staged, which = None, 1 - w
-            try:
-                staged = (self._stage_step(live, params, seed, 1, which), which)
-            except Exception:
-                staged = None              # a sequence is at its limit; it ends with this step
-            g.wait()
-            out = g.next_host.numpy()
-            sampled = {r.index: int(out[i]) for i, r in enumerate(live)}
-            for r in live:
+        inflight = None                    # (graph, staging buffer, requests) launched, not read
+        held: List[RequestState] = []      # ended, but a step in flight still uses their slots
+        while live or inflight is not None:
+            if inflight is None:
+                n = len(live)
+                g = self._stage_step(live, params, seed, 0, which)
+                g.hosts_np[which][:n] = np.fromiter((r.output[-1] for r in live), dtype=np.int32,
+                                                    count=n)
+                g.hosts_np[which][g.flag_at] = 0
+                cache.flush()
+                g.launch(self, params, seed, which)
+                inflight = (g, which, list(live))
+            g, w, reqs = inflight
+            # the step after it, for the same sequences
+            ahead = None
+            if all(not r.done and len(r.output) + 1 < r.max_new for r in reqs):
+                try:
+                    g2 = self._stage_step(reqs, params, seed, 1, 1 - w)
+                    g2.hosts_np[1 - w][g2.flag_at] = 1
+                    cache.flush()
+                    g2.launch(self, params, seed, 1 - w)
+                    ahead = (g2, 1 - w, reqs)
+                except (CacheError, StepError):
+                    ahead = None           # a sequence is at the end of its room
+            out = g.wait(w)
+            current = [(i, r) for i, r in enumerate(reqs) if not r.done]
+            sampled = {r.index: int(out[i]) for i, r in current}
+            for _, r in current:
                 book.set_length(r.slot, book.length[r.slot] + 1)
             stats["decode_steps"] += 1
-            stats["decode_tokens"] += n
+            stats["decode_tokens"] += len(current)
             ended = plan.accept(sampled)
-            for r in ended:
-                self.release(r.slot)
-                r.slot = -1
-            if ended:
-                staged = None              # the batch changed: stage afresh
+            if ahead is not None:
+                held.extend(ended)
+                inflight = ahead
+            else:
+                for r in held + ended:
+                    self.release(r.slot)
+                    r.slot = -1
+                held = []
+                inflight = None
                 live = plan.live()
+                which = 1 - w
 
     # ----------------------------------------------------------------- info
     def model_info(self) -> dict:

@@ -296,6 +296,16 @@ def history_append(tokens: torch.Tensor, slots: torch.Tensor, hist: torch.Tensor
                                         hist.shape[1], slots.numel(), _stream()))
 
 
+def take_tokens(tokens: torch.Tensor, prev: torch.Tensor, take: torch.Tensor,
+                vocab_size: int) -> None:
+    """tokens[b] = prev[b] for every b if take[0] is set (on the device)."""
+    for t, n in ((tokens, "tokens"), (prev, "prev"), (take, "take")):
+        _i32(t, n)
+    assert prev.numel() >= tokens.numel() and take.numel() >= 1
+    _check(library().agv_take_tokens(_ptr(tokens), _ptr(prev), _ptr(take), tokens.numel(),
+                                     vocab_size, _stream()))
+
+
 def repeat_penalty(logits: torch.Tensor, slots: torch.Tensor, hist: torch.Tensor,
                    hist_len: torch.Tensor, penalty: float) -> None:
     """Penalise, in place, every id in each row's slot history, once per occurrence."""

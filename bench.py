@@ -277,7 +277,7 @@ def main():
     graph = next(iter(engine._graphs.values()))
     e2e = {"value": round(e2e_val, 1), "unit": "tokens/s",
            "h2d_bytes_per_step": int(graph.hosts[0].numel() * 4),
-           "d2h_bytes_per_step": int(graph.next_host.numel() * 4)}
+           "d2h_bytes_per_step": int(graph.next_hosts[0].numel() * 4)}
 
     out = {
         "metric": f"Gemma3-{args.shapes.upper()} bf16 decode tokens/s at batch 8 (context 8192)",
