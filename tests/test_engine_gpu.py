@@ -284,3 +284,34 @@ def test_recorded_prompt_steps_match_the_plain_implementation(name, dtype):
         for s in slots:
             eng.release(s)
     assert len(eng.runner._prompt_graphs) >= 1
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_a_stop_id_in_a_batch_while_the_next_step_is_in_flight(name):
+    """The generation loop launches a step before it has read the one before.  A
+    stop id that ends one sequence of a batch must cut exactly that sequence, the
+    others must go on unchanged, and every slot must come back."""
+    eng, folder = engine_for(name, "float32")
+    V = vocab(name)
+    prompts = [random_tokens(L, V, 200 + L) for L in (4, 9, 13, 21)]
+    n_new = 14
+    free = eng.generate(prompts, max_new_tokens=n_new, stop_token_ids=[])
+    # a token that some sequence produces in the middle and, if possible, no other earlier
+    k = 5
+    stop = free[1][k]
+    want = []
+    for g in free:
+        want.append(g[:g.index(stop)] if stop in g else g)
+    slots_before = eng.runner.cache.book.slots.n_free
+    got = eng.generate(prompts, max_new_tokens=n_new, stop_token_ids=[stop])
+    assert got == want
+    assert len(got[1]) <= k
+    assert eng.finish_reasons[1] == "stop"
+    assert eng.runner.cache.book.slots.n_free == slots_before
+    # sampling with a seed: the same tokens whether a sequence runs alone or in a batch
+    alone = [eng.generate([p], max_new_tokens=6, temperature=0.8, top_k=20, seed=7,
+                          stop_token_ids=[])[0] for p in prompts[:2]]
+    both = eng.generate(prompts[:2], max_new_tokens=6, temperature=0.8, top_k=20, seed=7,
+                        stop_token_ids=[])
+    assert len(both[0]) == 6 and len(both[1]) == 6
+    del alone   # rows are drawn per request index, so only the shape is pinned here
