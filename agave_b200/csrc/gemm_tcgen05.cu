@@ -67,13 +67,27 @@ struct Tile {
     static constexpr int XCHG_BYTES = HALF ? 64 * BN * 4 : 0;
     // token tiles of 128 and more run one CTA per SM with a deep ring; smaller ones
     // (decoding) leave room for a second CTA that hides this one's start and end
-    static constexpr int BUDGET = DUAL ? 196 * 1024 : (BN >= 128 ? 196 * 1024 : 108 * 1024);
+    // A cluster of token tiles of 16 adds its partial sums by pushing them into the shared
+    // memory of the CTA that owns the features (PUSH); the inbox must not overlap the
+    // stages, which a slower CTA still reads while faster peers already push.
+    static constexpr bool PUSH = BN == 16 && !DUAL;
+    static constexpr int INBOX_BYTES = PUSH ? BN * 144 * 4 : 0;
+    static constexpr int BUDGET =
+        DUAL ? 196 * 1024 : (BN >= 128 ? 196 * 1024 : (PUSH ? 96 * 1024 : 108 * 1024));
     static constexpr int STAGES_RAW = (BUDGET - XCHG_BYTES) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : (STAGES_RAW < 2 ? 2 : STAGES_RAW);
     static constexpr int TMEM_COLS_RAW = DUAL ? 2 * BN : BN;
     static constexpr int TMEM_COLS = TMEM_COLS_RAW < 32 ? 32 : TMEM_COLS_RAW;
-    static constexpr int SMEM = STAGES * STAGE_BYTES + XCHG_BYTES + 1024 /*align*/ + 256;
+    static constexpr int SMEM =
+        STAGES * STAGE_BYTES + XCHG_BYTES + 1024 /*align*/ + 256 + (PUSH ? 1024 + INBOX_BYTES : 0);
 };
+
+__device__ __forceinline__ void st_peer_f32(float* local, uint32_t rank, float v) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local)),
+                 "r"(rank));
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+}
 
 // out element types
 template <typename TO> __device__ __forceinline__ void store_out(TO* p, float v);
@@ -101,6 +115,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
     uint64_t* acc_full = empty + TL::STAGES;
     uint32_t* tmem_slot = (uint32_t*)(acc_full + 1);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+    // [rank][token][row of this CTA's slice]: what the cluster's CTAs push here
+    float* inbox = (float*)(smem + TL::STAGES * TL::STAGE_BYTES + TL::XCHG_BYTES + 1024);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.x * (HALF ? TILE_M / 2 : TILE_M);   // first output feature
@@ -219,13 +235,37 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
         const bool run = ok && !*abort_flag && n_kb > 0;
         const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
         TO* obase = out + (size_t)blockIdx.z * split_stride;
-        if (cluster_reduce && ok && !*abort_flag && n_kb <= 0) {
+        if (TL::PUSH && cluster_reduce) {
+            // token tiles of 16: every value goes straight into the inbox of the CTA that
+            // adds this feature (a rank without a range of K, or one that gave up, sends
+            // zeros), so that after one cluster barrier everybody adds from its own
+            // shared memory and may leave
+            constexpr int FEATS_T = HALF ? TILE_M / 2 : TILE_M;
+            const int S = cluster_reduce, rank = blockIdx.z % S;
+            const int per = (FEATS_T + S - 1) / S, rows = HALF ? 2 * per : per;
+            const int fl = quarter * 32 + lane;                       // row of the tile
+            const int feat = HALF ? fl % FEATS_T : fl, part = HALF ? fl / FEATS_T : 0;
+            const int dest = feat / per, j = part * per + feat % per;
+            uint32_t r[16];
+            if (run) {
+                tc_ld16(lane_base, r);
+                tc_wait_ld();
+            } else {
+#pragma unroll
+                for (int n = 0; n < 16; ++n) r[n] = 0u;
+            }
+#pragma unroll
+            for (int n = 0; n < 16; ++n)
+                st_peer_f32(inbox + ((size_t)rank * BN + n) * rows + j, (uint32_t)dest,
+                            __uint_as_float(r[n]));
+        } else if (cluster_reduce && ok && !*abort_flag && n_kb <= 0) {
             // a rank without a range of K contributes zeros
             float* red = (float*)smem;
             const int fl = quarter * 32 + lane;
             for (int c = 0; c < BN; ++c) red[c * RED_LD + fl] = 0.f;
         }
-        if (run && cluster_reduce) {
+        if (TL::PUSH && cluster_reduce) {
+        } else if (run && cluster_reduce) {
             // this CTA's partial sums -> shared memory [token][tile row], for the cluster
             float* red = (float*)smem;
             const int fl = quarter * 32 + lane;
@@ -323,8 +363,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
         pdl_wait();
         // The gridDim.z CTAs of a cluster hold partial sums of one tile over
         // consecutive ranges of K.  Each adds, in rank order, a slice of the tile's
-        // features from every peer's shared memory and writes the result; nobody
-        // leaves before all have read.
+        // features and writes the result.  Token tiles of 16: the values were pushed
+        // into the adder's inbox, one barrier and everybody adds locally.  Wider tiles:
+        // the adder reads every peer's shared memory, and nobody leaves before all
+        // have read.
         cluster_sync_all();
         const int S = cluster_reduce, rank = blockIdx.z % S, group = blockIdx.z / S;
         constexpr int FEATS = HALF ? TILE_M / 2 : TILE_M;      // output features of the tile
@@ -332,6 +374,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
         const int f_lo = rank * per, f_hi = min(FEATS, f_lo + per);
         const float* red = (const float*)smem;
         TO* gout = out + (size_t)group * split_stride;
+        if (TL::PUSH) {
+            // the peers' values for this CTA's features lie in its own inbox
+            const int rows = HALF ? 2 * per : per;
+            const int width = f_hi - f_lo;
+            if (!*abort_flag && width > 0)
+            for (int i = threadIdx.x; i < BN * width; i += GEMM_THREADS) {
+                const int n = i / width, jl = i % width, fl = f_lo + jl;
+                if (n0 + n < T && m0 + fl < N) {
+                    float acc = 0.f, up = 0.f;
+                    for (int q = 0; q < S; ++q) {                      // in rank order
+                        acc += inbox[((size_t)q * BN + n) * rows + jl];
+                        if (HALF) up += inbox[((size_t)q * BN + n) * rows + per + jl];
+                    }
+                    if (HALF) acc = (act == 1 ? silu_fast(acc) : gelu_tanh_fast(acc)) * up;
+                    store_out<TO>(gout + (size_t)(n0 + n) * ldc + m0 + fl, acc);
+                }
+            }
+        } else {
         if (!*abort_flag && f_hi > f_lo) {
             const int width = f_hi - f_lo;
             for (int i = threadIdx.x; i < BN * width; i += GEMM_THREADS) {
@@ -360,6 +420,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
             }
         }
         cluster_sync_all();
+        }
     }
     tc_fence_before();
     __syncthreads();
