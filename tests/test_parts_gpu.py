@@ -1,7 +1,7 @@
 """Each part alone against the plain functions, and the generality of the
 assembly: a toy mixer with state of its own, another arrangement, activation
 and norm flavour, a block called twice and a layer that reads another layer's
-cache.  The toy parts live here and are registered from here; no file of the
+cache, a feed-forward with routing and a position encoding of another formula.  The toy parts live here and are registered from here; no file of the
 library changes for them."""
 import dataclasses
 import json
@@ -314,3 +314,154 @@ def test_a_block_called_twice_and_a_layer_reading_anothers_cache(dtype):
         got.append(eng.step([(s, [toks[i]])], [[0]]))
     eng.release(s)
     close(torch.cat(got), ref, TOL[dtype])
+
+
+# ------------- a feed-forward with routing and another position encoding, both toys
+class Top1Spec:
+    kind = "toy_top1_experts"
+
+    def __init__(self, n_experts, inter):
+        self.n_experts, self.inter = n_experts, inter
+
+
+class Top1Experts:
+    """Each token goes to the expert with the greatest router logit (computed in
+    32-bit) and is scaled by the softmax weight of that logit: a feed-forward whose
+    work depends on the data.  Built on the library's own gated-linear kernels."""
+
+    def __init__(self, spec, hidden_size, dtype, device):
+        self.spec, self.hidden_size, self.dtype, self.device = spec, hidden_size, dtype, device
+
+    @classmethod
+    def param_specs(cls, spec, hidden_size):
+        from agave_b200.parts import ParamSpec
+        p = {"router.weight": ParamSpec((spec.n_experts, hidden_size), "float32")}
+        for e in range(spec.n_experts):
+            p[f"experts.{e}.gate_proj.weight"] = ParamSpec((spec.inter, hidden_size))
+            p[f"experts.{e}.up_proj.weight"] = ParamSpec((spec.inter, hidden_size))
+            p[f"experts.{e}.down_proj.weight"] = ParamSpec((hidden_size, spec.inter))
+        return p
+
+    def load(self, tensors, dtype, device):
+        from agave_b200.parts.linear import GatedLinear, Linear
+        self.router = tensors["router.weight"].to(device=device, dtype=torch.float32)
+        self.experts = []
+        for e in range(self.spec.n_experts):
+            m = lambda n: tensors[f"experts.{e}.{n}"].to(device=device, dtype=dtype).contiguous()
+            self.experts.append((GatedLinear(m("gate_proj.weight"), m("up_proj.weight"), "silu"),
+                                 Linear(m("down_proj.weight"))))
+
+    def forward(self, x, ctx):
+        logits = x.float() @ self.router.T                         # 32-bit router
+        weight, choice = torch.softmax(logits, dim=-1).max(dim=-1)
+        out = torch.zeros(x.shape, dtype=torch.float32, device=x.device)
+        for e, (gate_up, down) in enumerate(self.experts):
+            rows = (choice == e).nonzero().flatten()
+            if rows.numel() == 0:
+                continue
+            y = down(gate_up(x[rows].contiguous()), out_dtype=torch.float32)
+            out[rows] = y.float() * weight[rows, None]
+        return out
+
+
+class LinearPhaseSpec:
+    """angle(p, i) = p * slope * (i + 1) over the first ``rotary_dim`` dims of a head."""
+    kind = "toy_linear_phase"
+
+    def __init__(self, slope, rotary_dim):
+        self.slope, self.rotary_dim = slope, rotary_dim
+
+
+class LinearPhase:
+    def __init__(self, spec, head_dim):
+        self.spec, self.rotary_dim = spec, spec.rotary_dim
+
+    def tables(self, ctx):
+        key = ("toy_linear_phase", self.spec.slope, self.rotary_dim)
+        hit = ctx.rope_tables.get(key)
+        if hit is None:
+            i = torch.arange(1, self.rotary_dim // 2 + 1, device=ctx.device, dtype=torch.float64)
+            ang = ctx.positions.double()[:, None] * (self.spec.slope * i)[None, :]
+            hit = ctx.rope_tables[key] = (torch.cos(ang).float().contiguous(),
+                                          torch.sin(ang).float().contiguous())
+        return hit
+
+
+class RoutedConfig:
+    def __init__(self, raw):
+        self.raw = raw
+
+    @classmethod
+    def from_dict(cls, raw):
+        return cls(raw)
+
+    def to_model_spec(self):
+        from agave_b200.config import (AttentionSpec, BlockSpec, ModelSpec, NormSpec,
+                                       default_schedule)
+        r = self.raw
+        norm = NormSpec(eps=r["eps"], zero_centered=False)
+        att = AttentionSpec(n_heads=r["heads"], n_kv_heads=r["kv_heads"], head_dim=r["head_dim"],
+                            scale=r["head_dim"] ** -0.5, window=None, qk_norm=None,
+                            position=LinearPhaseSpec(r["slope"], r["rotary_dim"]))
+        blocks = tuple(BlockSpec(mixer=att, feed_forward=Top1Spec(r["experts"], r["inter"]),
+                                 norm=norm, arrangement="pre") for _ in range(r["layers"]))
+        return ModelSpec(hidden_size=r["hidden"], vocab_size=r["vocab"], embed_scale=1.0,
+                         blocks=blocks, schedule=default_schedule(len(blocks)), final_norm=norm,
+                         tie_embeddings=True, max_positions=256)
+
+
+def routed_plain(raw, w, tokens):
+    T = len(tokens)
+    nh, nkv, hd, rd = raw["heads"], raw["kv_heads"], raw["head_dim"], raw["rotary_dim"]
+    i = torch.arange(1, rd // 2 + 1, dtype=torch.float64)
+    ang = torch.arange(T, dtype=torch.float64)[:, None] * (raw["slope"] * i)[None, :]
+    h = w["toy.embed.weight"][torch.tensor(tokens)]
+    for l in range(raw["layers"]):
+        p = f"toy.blocks.{l}."
+        x = P.rms_norm(h, w[p + "pre_mixer_norm.weight"], raw["eps"], add_one=False)
+        q = P.apply_rope((x @ w[p + "mixer.q_proj.weight"].T).reshape(T, nh, hd), ang)
+        k = P.apply_rope((x @ w[p + "mixer.k_proj.weight"].T).reshape(T, nkv, hd), ang)
+        v = (x @ w[p + "mixer.v_proj.weight"].T).reshape(T, nkv, hd)
+        h = h + P.attention(q, k, v, hd ** -0.5, None) @ w[p + "mixer.o_proj.weight"].T
+        x = P.rms_norm(h, w[p + "pre_ffn_norm.weight"], raw["eps"], add_one=False)
+        prob = torch.softmax(x @ w[p + "ffn.router.weight"].T, dim=-1)
+        weight, choice = prob.max(dim=-1)
+        d = torch.zeros_like(h)
+        for t in range(T):
+            e = int(choice[t])
+            g = x[t] @ w[p + f"ffn.experts.{e}.gate_proj.weight"].T
+            u = x[t] @ w[p + f"ffn.experts.{e}.up_proj.weight"].T
+            d[t] = (g * torch.sigmoid(g) * u) @ w[p + f"ffn.experts.{e}.down_proj.weight"].T \
+                * weight[t]
+        h = h + d
+    return P.rms_norm(h, w["toy.final_norm.weight"], raw["eps"], add_one=False) \
+        @ w["toy.embed.weight"].T
+
+
+def test_toy_routed_feed_forward_and_toy_position_encoding():
+    """A feed-forward with routing and a position encoding of another formula (over
+    part of the head only), registered here, in a model whose mixers are the
+    library's attention: built, loaded by name, stepped whole and token by token."""
+    from safetensors.torch import load_file
+    from agave_b200.config import register_architecture
+    from agave_b200.engine.api import Engine
+    from agave_b200.parts import register_feed_forward, register_position
+    from agave_b200.weights import write_model_folder
+    register_feed_forward("toy_top1_experts", Top1Experts)
+    register_position("toy_linear_phase", LinearPhase)
+    register_architecture("ToyRoutedLM", RoutedConfig, lambda c: ToyNames())
+    raw = {"architectures": ["ToyRoutedLM"], "hidden": 80, "vocab": 200, "layers": 2,
+           "heads": 6, "kv_heads": 3, "head_dim": 24, "rotary_dim": 16, "slope": 0.07,
+           "experts": 3, "inter": 56, "eps": 1e-5}
+    with tempfile.TemporaryDirectory() as d:
+        write_model_folder(d, raw, seed=11, std=0.08, norm_std=0.1, dtype=torch.float32)
+        w = {k: v.double() for k, v in load_file(os.path.join(d, "model.safetensors")).items()}
+        eng = Engine(d, dtype="float32", max_tokens=512, max_batch=2)
+    toks = random_tokens(23, 200, 3)
+    ref = routed_plain(raw, w, toks)
+    s = eng.acquire()
+    got = [eng.step([(s, toks[:15])], [list(range(15))])]
+    for t in toks[15:]:
+        got.append(eng.step([(s, [t])], [[0]]))
+    eng.release(s)
+    close(torch.cat(got), ref, 2e-4)
