@@ -14,6 +14,8 @@ Cases (Gemma 3 1B layer sizes, random bfloat16 data):
   attention_prefill_mma      the mma.sync kernel on the first workload
   attention_decode_window   decode attention, 8 sequences of 128..2,048 positions, window 512
   attention_decode_full     the same without a window
+  attention_decode_window_b64, attention_decode_full_b64   the same for 64 sequences (the
+                       second with a grid sized for a context of 8,192)
   norm_decode          residual sum + two RMS norms over 8 rows of 16 partial sums
   decode_step          whole decode steps of a 6-layer model (vocabulary 32,768), batch 8
   decode_step_b64      the same at batch 64
@@ -125,10 +127,10 @@ def case_attention_prefill(window=0, legacy=False):
     return fn, flops, qkv[0].numel() * 2 + out.numel() * 2, c
 
 
-def case_attention_decode(window, max_keys):
+def case_attention_decode(window, max_keys, B=8, grid_keys=0):
     from . import kernels
-    B, PAGE, max_pages = 8, 64, 40
-    c = 16
+    PAGE, max_pages = 64, 40
+    c = 16 if B <= 8 else 4
     pools = [(_rnd(B * max_pages, PAGE, NKV, HD), _rnd(B * max_pages, PAGE, NKV, HD))
              for _ in range(c)]
     table = torch.arange(B * max_pages, dtype=torch.int32, device=DEV).reshape(B, max_pages)
@@ -142,7 +144,7 @@ def case_attention_decode(window, max_keys):
     def fn(i):
         kernels.attention_decode_split(q, out, pools[i][0], pools[i][1], table, slots, positions,
                                        PAGE, max_pages * PAGE, NH, NKV, HD, 0.0625, window,
-                                       max_keys)
+                                       grid_keys or max_keys)
     nbytes = sum(min(n, window) if window else n for n in lens) * NKV * HD * 2 * 2
     return fn, 0, nbytes, c
 
@@ -203,6 +205,9 @@ CASES = {
     "attention_prefill_mma": lambda: case_attention_prefill(0, True),
     "attention_decode_window": lambda: case_attention_decode(512, 512),
     "attention_decode_full": lambda: case_attention_decode(0, 2048),
+    "attention_decode_window_b64": lambda: case_attention_decode(512, 512, 64),
+    "attention_decode_full_b64": lambda: case_attention_decode(0, 2048, 64, 8192),
+    "attention_decode_full_b64_tight": lambda: case_attention_decode(0, 2048, 64, 2048),
     "norm_decode": case_norm_decode,
     "decode_step": case_decode_step,
     "decode_step_b64": lambda: case_decode_step(64),
