@@ -380,9 +380,16 @@ attention_decode_mma_kernel(DecodeArgs a, int cs) {
     T* Qs = Vs + DM_KEYS * HDP;                             // [16][HDP]
     T* Ps = Qs + DM_HEADS * HDP;                            // [16][64]
     float* Ss = reinterpret_cast<float*>(Ps + DM_HEADS * DM_KEYS);   // [16][64]
-    float* stat = Ss + DM_HEADS * DM_KEYS;                  // [16][2]
-    int* rowoff = reinterpret_cast<int*>(stat + DM_HEADS * 2);       // [64]
+    float* stat = Ss + DM_HEADS * DM_KEYS;                  // [16][2] running maximum and sum
+    float* fac = stat + DM_HEADS * 2;                       // [16] what a new maximum scales O by
+    int* rowoff = reinterpret_cast<int*>(fac + DM_HEADS);   // [2][64]: this tile's and the next
 
+    // The W = gridDim.x CTAs of a sequence share its tiles of 64 keys: CTA w walks the
+    // tiles w, w + W, w + 2 W, ... with a running softmax.  W is chosen from the batch
+    // (all CTAs of a launch resident at once), not from the context length, so a short
+    // sequence leaves no CTA without work but the last ones, and a long one costs more
+    // tiles per CTA, not more CTAs.
+    const int W = gridDim.x;
     const int b = blockIdx.z, split = blockIdx.x;
     const int G = a.nh / a.nkv;
     const int groups_per_kv = (G + DM_HEADS - 1) / DM_HEADS;
@@ -402,29 +409,33 @@ attention_decode_mma_kernel(DecodeArgs a, int cs) {
     }
     const int p = a.positions[b];
     const int lo = a.window > 0 ? max(0, p - a.window + 1) : 0;
-    const int j0 = lo + split * DM_KEYS;
-    const int used = (p - lo) / DM_KEYS + 1;                  // chunks this sequence has
+    const int all_tiles = (p - lo) / DM_KEYS + 1;             // tiles this sequence has
+    const int used = min(W, all_tiles);                       // CTAs of it with work
     const int cid = split / cs, crank = split % cs;
     const int used_clusters = (used + cs - 1) / cs;
-    if (cid >= used_clusters) {                               // the whole cluster is past the end
+    if (cid >= used_clusters) {                               // the whole cluster is without work
         pdl_wait();
         return;
     }
-    const bool has = j0 <= p;                                 // (always true when cs == 1)
-    const int n = has ? min(DM_KEYS, p - j0 + 1) : 0;
+    const bool has = split < all_tiles;                       // (always true when cs == 1)
+    const int n_tiles = has ? (all_tiles - 1 - split) / W + 1 : 0;    // tiles this CTA walks
+    const int j0 = lo + split * DM_KEYS;                      // first key of its first tile
     float* Osm = reinterpret_cast<float*>(Ks);                // [16][HDP], after the scores are done
-
-    if (has && tid < DM_KEYS) {
-        const int* table = a.page_table + (size_t)slot * a.max_pages;
-        const int row = (j0 + tid) % a.cap;
-        rowoff[tid] = tid < n ? table[row / a.page] * a.page + row % a.page : -1;
-    }
+    const int* table = a.page_table + (size_t)slot * a.max_pages;
+    // cache row of key (first + tid), or -1 beyond position p
+    auto row_of = [&](int first) {
+        const int key = first + tid;
+        const int row = key % a.cap;
+        return key <= p ? table[row / a.page] * a.page + row % a.page : -1;
+    };
+    if (has && tid < DM_KEYS) rowoff[tid] = row_of(j0);
     __syncthreads();
     constexpr int CPR = HDP / 8;
     // Keys and values of earlier positions were stored by earlier steps: their copies
     // start before the wait too.  Only the row of position p is the predecessor's.
-    const int r_new = p - j0;                                 // in [0, n) in the last chunk only
+    const int r_new = p - j0;                                 // in [0, 64): the first tile holds p
     if (has) {
+        // (the first tile; the others are loaded inside the walk below, after the wait)
         for (int i = tid; i < DM_KEYS * CPR; i += DM_THREADS) {
             const int r = i / CPR, c = i % CPR;
             const int off = dm_swz<HDP>(r, c);
@@ -464,6 +475,31 @@ attention_decode_mma_kernel(DecodeArgs a, int cs) {
             }
         }
     }
+    constexpr int NP = HDP / 64;                           // pairs of 8-wide column tiles per warp
+    float o[NP * 2][4] = {};
+    for (int tt = 0; tt < n_tiles; ++tt) {
+    const int jt = j0 + tt * W * DM_KEYS;                   // first key of this tile
+    const int n = min(DM_KEYS, p - jt + 1);                 // its keys
+    // the rows of the next tile: the lookup runs beside this tile's work
+    int next_row = -1;
+    if (tt + 1 < n_tiles && tid < DM_KEYS) next_row = row_of(jt + W * DM_KEYS);
+    if (tt > 0) {
+        // the tile before has been used up: this one replaces it
+        __syncthreads();
+        const int* ro = rowoff + (tt & 1) * DM_KEYS;
+        for (int i = tid; i < DM_KEYS * CPR; i += DM_THREADS) {
+            const int r = i / CPR, c = i % CPR;
+            const int off = dm_swz<HDP>(r, c);
+            if (ro[r] >= 0 && c * 8 < hd) {
+                const size_t src = ((size_t)ro[r] * a.nkv + g) * hd + c * 8;
+                cp_async16(Ks + off, (const T*)a.k_pool + src);
+                cp_async16(Vs + off, (const T*)a.v_pool + src);
+            } else {
+                *reinterpret_cast<uint4*>(Ks + off) = make_uint4(0, 0, 0, 0);
+                *reinterpret_cast<uint4*>(Vs + off) = make_uint4(0, 0, 0, 0);
+            }
+        }
+    }
     cp_async_wait_all();
     __syncthreads();
     // ---- scores of 16 heads x this warp's 16 keys
@@ -489,26 +525,37 @@ attention_decode_mma_kernel(DecodeArgs a, int cs) {
             }
     }
     __syncthreads();
-    // ---- softmax weights relative to the chunk's maximum: four rows per warp
+    // ---- softmax weights relative to the running maximum: four rows per warp
 #pragma unroll
     for (int rr = 0; rr < 4; ++rr) {
         const int row = warp * 4 + rr;
         const float s0 = Ss[row * DM_KEYS + lane], s1 = Ss[row * DM_KEYS + lane + 32];
-        const float m = warp_max(fmaxf(s0, s1));
+        const float m_old = tt > 0 ? stat[row * 2] : -INFINITY;
+        const float l_old = tt > 0 ? stat[row * 2 + 1] : 0.f;
+        const float m = fmaxf(m_old, warp_max(fmaxf(s0, s1)));
+        const float alpha = tt > 0 ? expf(m_old - m) : 0.f;
         const float w0 = expf(s0 - m), w1 = expf(s1 - m);
-        const float l = warp_sum(w0 + w1);
+        const float l = fmaf(l_old, alpha, warp_sum(w0 + w1));
         Ps[dm_swz<DM_KEYS>(row, lane >> 3) + (lane & 7)] = __float2bfloat16_rn(w0);
         Ps[dm_swz<DM_KEYS>(row, (lane >> 3) + 4) + (lane & 7)] = __float2bfloat16_rn(w1);
+        __syncwarp();                              // every lane has read the old values
         if (lane == 0) {
             stat[row * 2] = m;
             stat[row * 2 + 1] = l;
+            fac[row] = alpha;
         }
     }
     __syncthreads();
     // ---- weighted values: this warp's quarter of the head dimension
     {
-        constexpr int NP = HDP / 64;                       // pairs of 8-wide column tiles per warp
-        float o[NP * 2][4] = {};
+        if (tt > 0) {
+            const float f0 = fac[gid], f1 = fac[gid + 8];
+#pragma unroll
+            for (int i = 0; i < NP * 2; ++i) {
+                o[i][0] *= f0, o[i][1] *= f0;
+                o[i][2] *= f1, o[i][3] *= f1;
+            }
+        }
 #pragma unroll
         for (int kk = 0; kk < DM_KEYS / 16; ++kk) {
             unsigned af[4];
@@ -523,6 +570,11 @@ attention_decode_mma_kernel(DecodeArgs a, int cs) {
                 dm_mma(o[nn * 2 + 1], af, bf[2], bf[3]);
             }
         }
+    }
+    if (tt + 1 < n_tiles && tid < DM_KEYS) rowoff[((tt + 1) & 1) * DM_KEYS + tid] = next_row;
+    }   // tiles
+    {
+        if (cs > 1 && used > 1) __syncthreads();   // Osm lies over the last key tile
 #pragma unroll
         for (int i = 0; i < NP * 2; ++i) {
             const int d = warp * (HDP / 4) + i * 8 + tig * 2;
@@ -609,20 +661,37 @@ attention_decode_mma_kernel(DecodeArgs a, int cs) {
 }
 
 template <int HDP>
-int launch_decode_mma(const DecodeArgs& a, int B, cudaStream_t stream) {
+int launch_decode_mma(const DecodeArgs& a0, int B, cudaStream_t stream) {
     auto kern = attention_decode_mma_kernel<HDP>;
     constexpr int smem = (2 * DM_KEYS + DM_HEADS) * HDP * 2 + DM_HEADS * DM_KEYS * (2 + 4) +
-                         DM_HEADS * 2 * 4 + DM_KEYS * 4;
+                         DM_HEADS * 3 * 4 + 2 * DM_KEYS * 4;
     static bool configured = false;
+    static int resident = 0;
     if (!configured) {
         AGV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        int dev = 0, sms = 0, per_sm = 0;
+        AGV_CUDA_OK(cudaGetDevice(&dev));
+        AGV_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        AGV_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, DM_THREADS, smem));
+        resident = sms * (per_sm > 0 ? per_sm : 1);
         configured = true;
     }
+    DecodeArgs a = a0;
     const int G = a.nh / a.nkv;
+    const int groups = a.nkv * ((G + DM_HEADS - 1) / DM_HEADS);
+    // CTAs per sequence: as many as stay resident together over the whole batch, at
+    // most one per tile of the longest sequence this launch may see (a.n_splits on
+    // entry); up to eight form a cluster, more clusters leave one partial result each
+    int per_seq = resident / (groups * B);
+    if (per_seq > a.n_splits) per_seq = a.n_splits;
+    if (per_seq < 1) per_seq = 1;
     int cs = 1;
-    while (cs < 8 && cs * 2 <= a.n_splits) cs *= 2;
-    const int splits_grid = (a.n_splits + cs - 1) / cs * cs;
-    dim3 grid(splits_grid, a.nkv * ((G + DM_HEADS - 1) / DM_HEADS), B);
+    while (cs < 8 && cs * 2 <= per_seq) cs *= 2;
+    int clusters = per_seq / cs;
+    if (clusters < 1) clusters = 1;
+    if (clusters > 16) clusters = 16;
+    a.n_splits = clusters;                         // partial results per (sequence, head)
+    dim3 grid(clusters * cs, groups, B);
     if (cs > 1)
         agv_launch_cluster(kern, grid, DM_THREADS, smem, stream, dim3(cs, 1, 1), a, cs);
     else
