@@ -12,7 +12,9 @@
 // sequence's end exit at once, so the grid can be sized for the longest
 // sequence the cache allows and the launch replayed from a CUDA graph.  Scores,
 // softmax and sums are 32-bit.  The arrival counters must be zero before a
-// launch; every launch leaves them zero.
+// launch; every launch leaves them zero.  (The bfloat16 tensor-core form below
+// shares a sequence's tiles among a number of CTAs that follows the batch size
+// instead; see attention_decode_mma_kernel.)
 //
 // Reference: one block per head, scores of all positions in shared memory,
 // softmax by the first 32 threads (src/backend/kernels/cuda/sdpa.zig:16-104);
@@ -359,11 +361,13 @@ __device__ __forceinline__ float dm_ld_peer(const float* local, unsigned rank) {
     return v;
 }
 
-// cs = 1: every chunk's partial result goes through global scratch and the last
-// CTA to arrive merges.  cs = 2, 4, 8: the cs CTAs of consecutive chunks form a
-// thread-block cluster and merge through distributed shared memory; only a
-// sequence longer than one cluster's chunks still goes through global scratch,
-// with one partial result per cluster.
+// The tensor-core form (bfloat16).  The gridDim.x CTAs of a (sequence, head group)
+// share the sequence's tiles of 64 keys by stride, each with a running softmax over
+// the tiles it walks.  cs = 2, 4, 8: every cs of them form a thread-block cluster
+// and merge through distributed shared memory; with more than one cluster per
+// sequence each cluster leaves one partial result in global scratch and the last
+// CTA to arrive merges them.  cs = 1 with several CTAs: every CTA's partial result
+// goes through scratch.
 template <int HDP>
 __global__ void __launch_bounds__(DM_THREADS)
 attention_decode_mma_kernel(DecodeArgs a, int cs) {
