@@ -454,12 +454,15 @@ struct PTile {
     static constexpr int B_BYTES = BN * TILE_K * 2;
     static constexpr int STAGE_BYTES = A_BYTES * (DUAL ? 2 : 1) + B_BYTES;
     static constexpr int ACC_COLS = DUAL ? 2 * BN : BN;
-    static constexpr int TMEM_COLS = 2 * ACC_COLS;              // two accumulator stages
+    static constexpr int TMEM_USED = 2 * ACC_COLS;              // two accumulator stages
+    // (an allocation is a power of two)
+    static constexpr int TMEM_COLS = TMEM_USED <= 32 ? 32 : TMEM_USED <= 64 ? 64 :
+                                     TMEM_USED <= 128 ? 128 : TMEM_USED <= 256 ? 256 : 512;
     static constexpr int STAGES_RAW = (200 * 1024) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
     static constexpr int EPI_BYTES = PERSISTENT_EPI_WARPS * 16 * 32 * 4;   // per-warp staging, f32
     static constexpr int SMEM = STAGES * STAGE_BYTES + EPI_BYTES + 1024 + 256;
-    static_assert(TMEM_COLS <= 512 && TMEM_COLS >= 32, "accumulators must fit tensor memory");
+    static_assert(TMEM_USED <= 512, "accumulators must fit tensor memory");
 };
 
 
@@ -914,7 +917,25 @@ AGV_API int agv_linear_tc(const void* x, const void* w, const void* w2, void* ou
         mw2 = mw;
     }
     const bool persistent = T > 128 && !cluster && token_tile == 0 && getenv("AGV_GEMM_ONESHOT") == nullptr;
-    if (persistent) bn = w2 ? 128 : 256;
+    if (persistent) {
+        bn = w2 ? 128 : 256;
+        if (!w2 && out_dtype == AGV_F32) {
+            // the token tile that needs the fewest rounds of the SMs times its products'
+            // time (a product of N <= 128 still takes the time of one of N 128)
+            int sms = 148;
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
+            const long long m_tiles = (N + TILE_M - 1) / TILE_M;
+            long long best = -1;
+            for (int cand : {256, 192, 128}) {
+                const long long items = m_tiles * ((T + cand - 1) / cand) * splits;
+                const long long cost = ((items + sms - 1) / sms) * cand;
+                if (best < 0 || cost < best) {
+                    best = cost;
+                    bn = cand;
+                }
+            }
+        }
+    }
     if (int rc = make_map(&mx, x, T, K, lda, bn)) return rc;
     const long long split_stride = (long long)T * ldc;
     const int creduce = splits > 1 ? cluster : 0;
@@ -927,6 +948,12 @@ AGV_API int agv_linear_tc(const void* x, const void* w, const void* w2, void* ou
         if (out_dtype == AGV_BF16)
             return launch_persistent<256, 0, __nv_bfloat16>(mw, mw2, mx, out, T, N, K, ldc, 0, 1,
                                                             kb_total, act, stream);
+        if (bn == 128)
+            return launch_persistent<128, 0, float>(mw, mw2, mx, out, T, N, K, ldc, split_stride,
+                                                    splits, kb_per, act, stream);
+        if (bn == 192)
+            return launch_persistent<192, 0, float>(mw, mw2, mx, out, T, N, K, ldc, split_stride,
+                                                    splits, kb_per, act, stream);
         return launch_persistent<256, 0, float>(mw, mw2, mx, out, T, N, K, ldc, split_stride,
                                                 splits, kb_per, act, stream);
     }
