@@ -47,14 +47,6 @@ constexpr int AT_S_COLS = 64;      // one S buffer
 constexpr int AT_O_COL = 2 * AT_S_COLS;
 constexpr float AT_LAZY = 8.0f;    // log2 units the maximum may lag before O is rescaled
 
-#ifdef AT_TIMING
-__device__ long long g_attn_prof[16];
-#define AT_T(i) { const long long now_ = clock64(); tacc[i] += now_ - tprev; tprev = now_; }
-#define AT_DUMP(lo, hi) if (prof) { for (int i_ = lo; i_ < hi; ++i_) g_attn_prof[i_] = tacc[i_]; }
-#else
-#define AT_T(i)
-#define AT_DUMP(lo, hi)
-#endif
 __device__ int g_attn_status = 0;  // 0 ok; else (role << 8) | detail of the first wait that gave up
 
 struct AtArgs {
@@ -120,9 +112,6 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                             const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_vt, AtArgs a) {
-#ifdef AT_TIMING
-    const long long t_entry = clock64();
-#endif
     // barriers, tensor memory and the sequence bounds (copied in at the start of the
     // step) are set up while the predecessor still runs; the loader and the softmax
     // warps wait for it before they touch q, k, v or out
@@ -255,35 +244,23 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         // ------------------------------------------------------------ S = Q K^T
         // two issuers, one for the even tiles and one for the odd ones (each S buffer
         // and each K stage has its own), so that one's waits hide behind the other's work
-#ifdef AT_EXP_N
-        const uint32_t idesc_s = umma_idesc(AT_M, AT_EXP_N);
-#else
         const uint32_t idesc_s = umma_idesc(AT_M, AT_N);
-#endif
         // a descriptor is linear in the address: the steps add constants to it
         const uint64_t q_desc0 = umma_desc(smem_u32(Qs)), k_desc0 = umma_desc(smem_u32(Ks));
         const int full_kb = a.hd / 64, tail_steps = (a.hd % 64) / 16;
         bool ok = mbar_wait(q_full, 0);
         if (!ok) give_up(2, 0);
-#ifdef AT_TIMING
-        const bool prof = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && warp == 1;
-        long long tacc[16] = {0};
-        long long tprev = clock64();
-#endif
         for (int j = warp == 1 ? 0 : 1; ok && j < n_tiles && !*abort_flag; j += 2) {
             const int s = j & 1;
             const uint32_t ph = (j >> 1) & 1;
-            AT_T(8)
             if (!mbar_wait(&k_full[s], ph)) {
                 give_up(2, 2 + s);
                 break;
             }
-            AT_T(9)
             if (j >= 2 && !mbar_wait(&s_free[s], ph ^ 1)) {
                 give_up(2, 8 + s);
                 break;
             }
-            AT_T(10)
             tc_fence_after();
             const uint32_t d = tmem_base + s * AT_S_COLS;
             uint64_t qd = q_desc0, kd = k_desc0 + (uint64_t)((s * k_bytes) >> 4);
@@ -298,9 +275,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                 tc_mma_bf16(d, qd + 2 * k, kd + 2 * k, idesc_s, (full_kb > 0 || k > 0) ? 1u : 0u);
             tc_commit(&k_empty[s]);
             tc_commit(&s_full[s]);
-            AT_T(11)
         }
-        AT_DUMP(8, 12)
     } else if (warp == 6 && lane == 0) {
         // ------------------------------------------------------------ O += P V
         const uint32_t idesc_o = umma_idesc(AT_M, a.hd);
@@ -336,12 +311,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         float m_used = -INFINITY, l = 0.f;
         bool ok = true;
         pdl_wait();
-#ifdef AT_TIMING
-        const bool prof = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 64;
-        long long tacc[16] = {0};
-        long long tprev = clock64();
-        tacc[12] = tprev - t_entry;
-#endif
         for (int j = 0; j < n_tiles; ++j) {
             const int s = j & 1;
             const uint32_t ph = (j >> 1) & 1;
@@ -351,7 +320,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                 break;
             }
             tc_fence_after();
-            AT_T(0)
             uint32_t sr[4][16];
 #pragma unroll
             for (int c = 0; c < 4; ++c) tc_ld16(lane_addr + s * AT_S_COLS + c * 16, sr[c]);
@@ -359,7 +327,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&s_free[s]);
-            AT_T(1)
             const int j0 = (t_lo + j) * AT_N;
             // a tile every row of the CTA sees whole needs no bounds
             const bool whole = j0 + AT_N - 1 <= q_min && (a.window <= 0 || j0 > q_max - a.window);
@@ -412,7 +379,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                 pk[(c >> 1) + 1] = *reinterpret_cast<const uint32_t*>(&t1);
             }
             l += (ps[0] + ps[1]) + (ps[2] + ps[3]);
-            AT_T(2)
             // O and the P buffer of two tiles ago are free once the product of the last tile ended
             if (j > 0) {
                 if (!mbar_wait(o_done, (j - 1) & 1)) {
@@ -421,7 +387,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                     break;
                 }
                 tc_fence_after();
-                AT_T(3)
                 if (__any_sync(0xffffffffu, rescale)) {
                     for (int c = 0; c < a.hd; c += 16) {
                         uint32_t o[16];
@@ -434,25 +399,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                     tc_wait_st();
                 }
             }
-            AT_T(4)
             uint8_t* prow = Ps + s * p_bytes + row * 128;
 #pragma unroll
             for (int c = 0; c < 8; ++c)
                 *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) =
                     make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-            AT_T(5)
             fence_async_shared();
-            AT_T(6)
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&p_full[s]);
-            AT_T(7)
         }
-        AT_DUMP(0, 8)
-#ifdef AT_TIMING
-        if (prof) g_attn_prof[12] = tacc[12];
-        const long long t_loop_end = clock64();
-#endif
         if (ok && !*abort_flag) {
             if (!mbar_wait(o_done, (n_tiles - 1) & 1)) {
                 give_up(3, 3);
@@ -492,11 +448,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
             }
         }
     }
-#ifdef AT_TIMING
-    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 64) {
-        g_attn_prof[13] = clock64() - t_entry;
-    }
-#endif
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -556,14 +507,6 @@ AGV_API long long agv_attention_prefill_tc_vt_cols(int T, int B) {
     return ((long long)T + 63LL * B + 63) / 64 * 64;
 }
 
-#ifdef AT_TIMING
-AGV_API int agv_attention_tc_prof(long long* out) {
-    cudaMemcpyFromSymbol(out, g_attn_prof, sizeof(long long) * 16);
-    long long z[16] = {0};
-    cudaMemcpyToSymbol(g_attn_prof, z, sizeof(z));
-    return 0;
-}
-#endif
 
 AGV_API int agv_attention_tc_status() {
     int v = 0;
