@@ -205,8 +205,8 @@ __device__ __forceinline__ void st_run(__nv_bfloat16* p, const float* v) {
     }
 }
 
-template <typename T, int NE>
-__global__ void __launch_bounds__(QK_WARPS * 32)
+template <typename T, int NE, bool MULTI>
+__global__ void __launch_bounds__(QK_WARPS * 32, MULTI ? 1 : 8)
 qk_norm_rope_store_reg_kernel(T* __restrict__ qkv, long long row_stride,
                               const float* __restrict__ part, int n_splits,
                               long long split_stride, int n_tokens, int nh, int nkv,
@@ -254,7 +254,7 @@ qk_norm_rope_store_reg_kernel(T* __restrict__ qkv, long long row_stride,
                 val[ps][0] = val[ps][1] = val[ps][2] = val[ps][3] = 0.f;
                 if (t < n_tokens) {
                     if (part) {
-                        for (int sp = 0; sp < n_splits; ++sp) {
+                        for (int sp = 0; sp < (MULTI ? n_splits : 1); ++sp) {
                             float x[4];
                             ld_run<4>(part + (size_t)sp * split_stride +
                                           (size_t)t * (size_t)(heads * hd) + vcol, x);
@@ -336,7 +336,8 @@ qk_norm_rope_store_reg_kernel(T* __restrict__ qkv, long long row_stride,
     }
     if (part) {
         const float* ps = part + (size_t)t * (size_t)(heads * hd) + (size_t)head * hd + e0;
-        if (n_splits == 1) {
+        if (!MULTI) {
+            // (one range of K: prompts, whose many warps need their registers few)
             ld_run<HALF>(ps, v);
             ld_run<HALF>(ps + H2, v + HALF);
         } else {
@@ -412,13 +413,18 @@ static bool launch_qk_reg(T* qkv, long long row_stride, const float* part, int n
         !agv_aligned(sinv, 16) || !agv_aligned(cw.k_pool, 16) || !agv_aligned(cw.v_pool, 16))
         return false;
 #define AGV_QK_REG(NE)                                                                          \
-    agv_launch(qk_norm_rope_store_reg_kernel<T, NE>, grid, QK_WARPS * 32, 0, stream, qkv,       \
-               row_stride, part, n_splits, split_stride, n_tokens, nh, nkv, wq, wk, eps, cosv,  \
-               sinv, positions, cw, vw, (int)vt_blocks)
-    if (hd == 64) AGV_QK_REG(2);
-    else if (hd == 128) AGV_QK_REG(4);
-    else if (hd == 192) AGV_QK_REG(6);
-    else AGV_QK_REG(8);
+    if (part && n_splits > 1)                                                                   \
+        agv_launch(qk_norm_rope_store_reg_kernel<T, NE, true>, grid, QK_WARPS * 32, 0, stream,  \
+                   qkv, row_stride, part, n_splits, split_stride, n_tokens, nh, nkv, wq, wk,    \
+                   eps, cosv, sinv, positions, cw, vw, (int)vt_blocks);                         \
+    else                                                                                        \
+        agv_launch(qk_norm_rope_store_reg_kernel<T, NE, false>, grid, QK_WARPS * 32, 0, stream, \
+                   qkv, row_stride, part, n_splits, split_stride, n_tokens, nh, nkv, wq, wk,    \
+                   eps, cosv, sinv, positions, cw, vw, (int)vt_blocks)
+    if (hd == 64) { AGV_QK_REG(2); }
+    else if (hd == 128) { AGV_QK_REG(4); }
+    else if (hd == 192) { AGV_QK_REG(6); }
+    else { AGV_QK_REG(8); }
 #undef AGV_QK_REG
     return true;
 }
