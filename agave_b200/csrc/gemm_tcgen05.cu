@@ -920,15 +920,19 @@ AGV_API int agv_linear_tc(const void* x, const void* w, const void* w2, void* ou
     if (persistent) {
         bn = w2 ? 128 : 256;
         if (!w2 && out_dtype == AGV_F32) {
-            // the token tile that needs the fewest rounds of the SMs times its products'
-            // time (a product of N <= 128 still takes the time of one of N 128)
+            // the token tile that needs the least time: rounds of the SMs times the time
+            // of a k-block, which is the slower of its four products (2 cycles per token
+            // column, at least 256) and its bytes from L2 at the 69 B/clk an SM gets
+            // while all SMs ask (measured)
             int sms = 148;
             cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
             const long long m_tiles = (N + TILE_M - 1) / TILE_M;
             long long best = -1;
             for (int cand : {256, 192, 128}) {
                 const long long items = m_tiles * ((T + cand - 1) / cand) * splits;
-                const long long cost = ((items + sms - 1) / sms) * cand;
+                const long long products = cand * 2 < 256 ? 256 : cand * 2;
+                const long long feed = (long long)(TILE_M + cand) * TILE_K * 2 / 69;
+                const long long cost = ((items + sms - 1) / sms) * (products > feed ? products : feed);
                 if (best < 0 || cost < best) {
                     best = cost;
                     bn = cand;
