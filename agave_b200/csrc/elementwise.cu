@@ -325,6 +325,88 @@ norm_residual_warp_kernel(float* __restrict__ h, const float* __restrict__ y, in
     }
 }
 
+// The same for rows too wide for a warp's registers (above 2,048 values): one CTA of
+// 256 threads per row, 16-byte loads issued up front, two block-wide sums.
+template <typename TX, int NV>
+__global__ void __launch_bounds__(256)
+norm_residual_row_kernel(float* __restrict__ h, const float* __restrict__ y, int n_splits,
+                          size_t split_stride, const float* __restrict__ w_post,
+                          const float* __restrict__ w_next, TX* __restrict__ x, int R, int H,
+                          float eps_post, float eps_next, int add_residual) {
+    pdl_wait();
+    pdl_launch_next();
+    __shared__ float red[33];
+    const int lane = threadIdx.x;                   // 256 threads share the row
+    const int row = blockIdx.x;
+    const int H4 = H >> 2;
+    const size_t base = (size_t)row * H;
+    float4 v[NV], hv[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int idx = lane + 256 * i;
+        const bool in = idx < H4;
+        v[i] = in ? reinterpret_cast<const float4*>(y + base)[idx] : make_float4(0, 0, 0, 0);
+        hv[i] = (in && add_residual) ? reinterpret_cast<const float4*>(h + base)[idx]
+                                     : make_float4(0, 0, 0, 0);
+    }
+    for (int s = 1; s < n_splits; ++s) {
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int idx = lane + 256 * i;
+            if (idx < H4) {
+                const float4 t = reinterpret_cast<const float4*>(y + s * split_stride + base)[idx];
+                v[i].x += t.x; v[i].y += t.y; v[i].z += t.z; v[i].w += t.w;
+            }
+        }
+    }
+    float rs = 1.f;
+    if (w_post) {
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < NV; ++i)
+            ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+        ss = block_sum(ss, red);
+        rs = 1.0f / sqrtf(ss / (float)H + eps_post);
+    }
+    float ss2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int idx = lane + 256 * i;
+        if (idx < H4) {
+            if (w_post) {
+                const float4 w = reinterpret_cast<const float4*>(w_post)[idx];
+                v[i].x = v[i].x * rs * w.x; v[i].y = v[i].y * rs * w.y;
+                v[i].z = v[i].z * rs * w.z; v[i].w = v[i].w * rs * w.w;
+            }
+            if (add_residual) {
+                v[i].x += hv[i].x; v[i].y += hv[i].y; v[i].z += hv[i].z; v[i].w += hv[i].w;
+                reinterpret_cast<float4*>(h + base)[idx] = v[i];
+            }
+            ss2 += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+        }
+    }
+    if (w_next) {
+        ss2 = block_sum(ss2, red);
+        const float r2 = 1.0f / sqrtf(ss2 / (float)H + eps_next);
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int idx = lane + 256 * i;
+            if (idx < H4) {
+                const float4 w = reinterpret_cast<const float4*>(w_next)[idx];
+                Pack4<TX>::store(x + base + 4 * idx,
+                                 make_float4(v[i].x * r2 * w.x, v[i].y * r2 * w.y,
+                                             v[i].z * r2 * w.z, v[i].w * r2 * w.w));
+            }
+        }
+    } else if (x) {
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int idx = lane + 256 * i;
+            if (idx < H4) Pack4<TX>::store(x + base + 4 * idx, v[i]);
+        }
+    }
+}
+
 template <typename TX>
 static bool launch_norm_warp(float* h, const float* y, int n_splits, size_t split_stride,
                              const float* w_post, const float* w_next, TX* x, int R, int H,
@@ -347,6 +429,24 @@ static bool launch_norm_warp(float* h, const float* y, int n_splits, size_t spli
     return true;
 }
 
+template <typename TX>
+static bool launch_norm_row(float* h, const float* y, int n_splits, size_t split_stride,
+                            const float* w_post, const float* w_next, TX* x, int R, int H,
+                            float eps_post, float eps_next, int add_residual,
+                            cudaStream_t stream) {
+    const int nv = (H / 4 + 255) / 256;
+#define AGV_ROW(NV)                                                                             \
+    agv_launch(norm_residual_row_kernel<TX, NV>, (unsigned)R, 256, 0, stream, h, y, n_splits,   \
+               split_stride, w_post, w_next, x, R, H, eps_post, eps_next, add_residual)
+    if (nv <= 2) AGV_ROW(2);
+    else if (nv <= 4) AGV_ROW(4);
+    else if (nv <= 6) AGV_ROW(6);
+    else if (nv <= 8) AGV_ROW(8);
+    else return false;
+#undef AGV_ROW
+    return true;
+}
+
 template <typename TY, typename TX>
 static int launch_norm(float* h, const void* y, int n_splits, size_t split_stride,
                        const float* w_post, const float* w_next, void* x, const int* rows, int R,
@@ -361,6 +461,15 @@ static int launch_norm(float* h, const void* y, int n_splits, size_t split_strid
             if (launch_norm_warp<TX>(h, (const float*)y, n_splits, split_stride, w_post, w_next,
                                      (TX*)x, R, H, eps_post, eps_next, add_residual, stream)) {
                 AGV_LAUNCH_OK("norm_residual_warp_kernel");
+                return 0;
+            }
+        }
+        if (R > 256 && y && !rows && H % 4 == 0 && H > 2048 && H <= 8192 && agv_aligned(y, 16) &&
+            agv_aligned(h, 16) && agv_aligned(x, 16) && split_stride % 4 == 0 &&
+            (!w_post || agv_aligned(w_post, 16)) && (!w_next || agv_aligned(w_next, 16))) {
+            if (launch_norm_row<TX>(h, (const float*)y, n_splits, split_stride, w_post, w_next,
+                                    (TX*)x, R, H, eps_post, eps_next, add_residual, stream)) {
+                AGV_LAUNCH_OK("norm_residual_row_kernel");
                 return 0;
             }
         }

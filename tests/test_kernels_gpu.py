@@ -141,7 +141,8 @@ def test_linear_simt_plain_and_gated(dtype):
 
 
 # ---------------------------------------------------------------------- norms
-@pytest.mark.parametrize("H,R", [(48, 7), (1000, 7), (5376, 7), (1152, 300), (2048, 257), (72, 513)])
+@pytest.mark.parametrize("H,R", [(48, 7), (1000, 7), (5376, 7), (1152, 300), (2048, 257), (72, 513),
+                                 (2560, 300), (5376, 260), (8192, 257), (2052, 258)])
 def test_norm_family(H, R):
     from agave_b200 import kernels
     h = rnd(R, H, seed=1)
