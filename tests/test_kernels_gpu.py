@@ -469,6 +469,42 @@ def test_attention_decode_split_long_sequences(dtype, nh, nkv, hd):
             assert (out[0, :hd].float() - v_pool[page5, 5, 0].float()).abs().max() > 0.1
 
 
+@pytest.mark.parametrize("B,nh,nkv,hd", [(64, 8, 4, 256), (96, 4, 1, 128), (200, 4, 2, 64)])
+def test_attention_decode_many_sequences_walk_several_tiles(B, nh, nkv, hd):
+    """With many sequences a sequence gets few CTAs, each of which walks several key
+    tiles with a running softmax (and, with fewer still, a single CTA the whole
+    sequence): unequal lengths up to a dozen tiles, padding entries in between, a
+    window, against the one-warp kernel."""
+    from agave_b200 import kernels
+    PAGE, max_pages = 64, 12
+    g = torch.Generator().manual_seed(7)
+    lens = torch.randint(1, max_pages * PAGE, (B,), generator=g).tolist()
+    lens[0], lens[1], lens[2] = max_pages * PAGE, 1, 64
+    k_pool = rnd(B * max_pages, PAGE, nkv, hd, dtype=torch.bfloat16, seed=1, scale=0.3)
+    v_pool = rnd(B * max_pages, PAGE, nkv, hd, dtype=torch.bfloat16, seed=2)
+    table = torch.randperm(B * max_pages, generator=g).int().reshape(B, max_pages).contiguous().to(DEV)
+    slots = torch.arange(B, dtype=torch.int32)
+    slots[5::17] = -1                                   # padding entries
+    slots = slots.to(DEV)
+    q = rnd(B, nh * hd, dtype=torch.bfloat16, seed=4, scale=0.3)
+    positions = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=DEV)
+    seq_index = torch.arange(B, dtype=torch.int32, device=DEV)
+    cap = max_pages * PAGE
+    for window in (0, 200):
+        ref = torch.empty((B, nh * hd), dtype=torch.bfloat16, device=DEV)
+        live = (slots >= 0).nonzero().flatten()
+        kernels.attention_paged_simt(q[live].contiguous(), ref[: live.numel()], k_pool, v_pool, table,
+                                     slots[live].contiguous(), positions[live].contiguous(),
+                                     torch.arange(live.numel(), dtype=torch.int32, device=DEV),
+                                     PAGE, cap, nh, nkv, hd, 0.5, window)
+        out = torch.full((B, nh * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+        kernels.attention_decode_split(q, out, k_pool, v_pool, table, slots, positions, PAGE, cap,
+                                       nh, nkv, hd, 0.5, window, window or cap)
+        assert torch.isfinite(out.float()).all()
+        assert rel_err(out[live], ref[: live.numel()]) < 8e-3, window
+        assert (out[slots < 0] == 0).all()
+
+
 @pytest.mark.parametrize("nh,nkv,hd,window", [(4, 1, 256, 0), (4, 1, 256, 100), (6, 2, 128, 70),
                                               (3, 3, 64, 0), (4, 2, 16, 5), (2, 1, 40, 33),
                                               (2, 1, 200, 64)])
