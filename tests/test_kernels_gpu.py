@@ -36,6 +36,31 @@ def test_linear_tensor_cores_plain(T, N, K):
         assert rel_err(out, ref) < tol, (T, N, K, out_dtype)
 
 
+@pytest.mark.parametrize("T,N,K,splits", [(2048, 1536, 1152, 1), (2048, 1152, 1024, 1),
+                                          (2000, 1152, 2304, 2), (1999, 8192, 256, 1),
+                                          (700, 200, 320, 1), (3000, 2560, 192, 1)])
+def test_linear_tensor_cores_prompts_every_token_tile_choice(T, N, K, splits):
+    """The persistent kernel picks token tiles of 256, 192 or 128 from the shape: sizes
+    that take each, token counts that end inside a tile, and K in two halves."""
+    from agave_b200 import kernels
+    x, w = rnd(T, K, dtype=torch.bfloat16, seed=21), rnd(N, K, dtype=torch.bfloat16, seed=22)
+    ref = x.float() @ w.float().T
+    s_real = kernels.linear_tc_splits(K, splits)
+    out = torch.full((s_real, T, N) if s_real > 1 else (T, N), float("nan"), dtype=torch.float32,
+                     device=DEV)
+    kernels.linear_tc(x, w, out, splits=splits)
+    assert kernels.linear_tc_status() == 0
+    got = out.sum(0) if s_real > 1 else out
+    assert torch.isfinite(got).all()
+    assert rel_err(got, ref) < 1e-5
+    wu = rnd(N, K, dtype=torch.bfloat16, seed=23, scale=0.3)
+    if splits == 1 and N <= 2560:
+        ob = torch.full((T, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+        kernels.linear_tc(x, w, ob, w2=wu, activation="gelu_tanh")
+        g, u = ref, x.float() @ wu.float().T
+        assert rel_err(ob, torch.nn.functional.gelu(g, approximate="tanh") * u) < 6e-3
+
+
 @pytest.mark.parametrize("tile", [16, 32, 64, 128, 256])
 def test_linear_tensor_cores_every_token_tile(tile):
     from agave_b200 import kernels
