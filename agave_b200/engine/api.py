@@ -107,8 +107,15 @@ class _DecodeGraph:
         torch.cuda.synchronize()
         g = torch.cuda.CUDAGraph()
         n0 = kernels.launch_count()
-        with torch.cuda.graph(g):
-            self._body(engine, params, seed)
+        try:
+            with torch.cuda.graph(g):
+                self._body(engine, params, seed)
+        except RuntimeError:
+            # a part that cannot be recorded (one that reads device data on the host,
+            # say): this batch size runs launch by launch
+            torch.cuda.synchronize()
+            self.kernels_per_step = kernels.launch_count() - n0
+            return
         self.kernels_per_step = kernels.launch_count() - n0
         self.graph = g
 

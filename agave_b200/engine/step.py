@@ -184,7 +184,13 @@ class Runner:
                 and T <= PROMPT_GRAPH_TOKENS):
             graph = self._prompt_graphs.get(key)
             if graph is None and self._prompt_seen.get(key, 0) >= 1:
-                graph = self._record_prompt(plan, rows, key)
+                try:
+                    graph = self._record_prompt(plan, rows, key)
+                except RuntimeError:
+                    # a part that cannot be recorded (one that reads device data on the
+                    # host, say): these sizes keep running launch by launch
+                    torch.cuda.synchronize()
+                    self._prompt_seen[key] = -(1 << 60)
             self._prompt_seen[key] = self._prompt_seen.get(key, 0) + 1
             if len(self._prompt_seen) > 4096:
                 self._prompt_seen.clear()

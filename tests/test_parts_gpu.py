@@ -235,6 +235,19 @@ def test_toy_mixer_with_state_registers_builds_and_steps(dtype):
         for i in order:
             close(torch.cat(got[i]), refs[i], 1e-4 if dtype == "float32" else 3e-2)
             eng.release(slots[i])
+    # through the generation loop, twice with the same sizes: this mixer reads device
+    # data on the host, so neither a prompt step nor a decode step of it can be recorded
+    # into a CUDA graph; the engine must notice and run it launch by launch
+    if dtype == "float32":
+        prompts = [seqs[0][:5], seqs[1][:5]]
+        first = eng.generate(prompts, max_new_tokens=3, stop_token_ids=[])
+        again = eng.generate(prompts, max_new_tokens=3, stop_token_ids=[])
+        assert first == again and all(len(o) == 3 for o in first)
+        for pr, o in zip(prompts, first):
+            ref = toy_plain(raw, w, pr + o)
+            for k, t in enumerate(o):
+                row = ref[len(pr) - 1 + k]
+                assert row[t] >= row.max() - 1e-3 * row.abs().max()
 
 
 # ------------------------- the run order is data: a block twice, a shared cache
