@@ -319,7 +319,21 @@ attention_decode_split_kernel(DecodeArgs a) {
 // a chunk's scores and weighted values are mma.sync m16n8k16 products.  The rows
 // of the left operand are the query heads that share the kv head (up to 16 per
 // CTA), so a group's keys and values are read once for all its heads.
-constexpr int DM_HEADS = 16, DM_KEYS = 64, DM_THREADS = 128;
+constexpr int DM_HEADS = 16, DM_KEYS = 64;
+// How a CTA's warps share a tile.  The arithmetic of a tile is a chain of short
+// dependent instructions, so its time goes with the work per warp, not with the tensor
+// pipe: head sizes above 64 take eight warps (8 keys of the scores, 2 rows of the
+// softmax and an eighth of the head dimension each), head size 64 four.
+template <int HDP>
+struct DmShape {
+    static constexpr int NT = HDP >= 128 ? 256 : 128;   // threads
+    static constexpr int NW = NT / 32;                  // warps
+    static constexpr int KW = DM_KEYS / NW;             // keys per warp in the scores: 16 or 8
+    static constexpr int RW = DM_HEADS / NW;            // rows per warp in the softmax
+    static constexpr int DW = HDP / NW;                 // dims per warp in the weighted sum
+    static constexpr int NP = DW / 16;                  // pairs of 8-wide column tiles per warp
+    static_assert(DW % 16 == 0 && (KW == 16 || KW == 8), "unsupported split of a tile over warps");
+};
 
 __device__ __forceinline__ unsigned dm_smem(const void* p) {
     return (unsigned)__cvta_generic_to_shared(p);
@@ -369,8 +383,10 @@ __device__ __forceinline__ float dm_ld_peer(const float* local, unsigned rank) {
 // CTA to arrive merges them.  cs = 1 with several CTAs: every CTA's partial result
 // goes through scratch.
 template <int HDP>
-__global__ void __launch_bounds__(DM_THREADS)
+__global__ void __launch_bounds__(DmShape<HDP>::NT, DmShape<HDP>::NT == 256 ? 2 : 3)
 attention_decode_mma_kernel(DecodeArgs a, int cs) {
+    typedef DmShape<HDP> Sh;
+    constexpr int DM_THREADS = Sh::NT;
     // Slots, positions and page tables are written by copies at the start of the step,
     // before any kernel of it runs, so they are read before this kernel waits for its
     // predecessor (which writes q and the new key and value): two dependent trips to
@@ -479,7 +495,7 @@ attention_decode_mma_kernel(DecodeArgs a, int cs) {
             }
         }
     }
-    constexpr int NP = HDP / 64;                           // pairs of 8-wide column tiles per warp
+    constexpr int NP = Sh::NP;
     float o[NP * 2][4] = {};
     for (int tt = 0; tt < n_tiles; ++tt) {
     const int jt = j0 + tt * W * DM_KEYS;                   // first key of this tile
@@ -506,8 +522,8 @@ attention_decode_mma_kernel(DecodeArgs a, int cs) {
     }
     cp_async_wait_all();
     __syncthreads();
-    // ---- scores of 16 heads x this warp's 16 keys
-    {
+    // ---- scores of 16 heads x this warp's keys
+    if constexpr (Sh::KW == 16) {
         float s[2][4] = {};
 #pragma unroll
         for (int kk = 0; kk < HDP / 16; ++kk) {
@@ -527,12 +543,31 @@ attention_decode_mma_kernel(DecodeArgs a, int cs) {
                 const int row = gid + (e >> 1) * 8;
                 Ss[row * DM_KEYS + key] = key < n ? s[i][e] * a.scale : -INFINITY;
             }
+    } else {
+        // 8 keys: one load brings their chunks of 32 dims, two products into sums of
+        // their own (no chain between them), added at the end
+        float s[2][4] = {};
+#pragma unroll
+        for (int k2 = 0; k2 < HDP / 32; ++k2) {
+            unsigned a0[4], a1[4], bf[4];
+            dm_ldsm4(dm_smem(Qs + dm_swz<HDP>(lane & 15, k2 * 4 + (lane >> 4))), a0);
+            dm_ldsm4(dm_smem(Qs + dm_swz<HDP>(lane & 15, k2 * 4 + 2 + (lane >> 4))), a1);
+            dm_ldsm4(dm_smem(Ks + dm_swz<HDP>(warp * 8 + (lane & 7), k2 * 4 + (lane >> 3))), bf);
+            dm_mma(s[0], a0, bf[0], bf[1]);
+            dm_mma(s[1], a1, bf[2], bf[3]);
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int key = warp * 8 + tig * 2 + (e & 1);
+            const int row = gid + (e >> 1) * 8;
+            Ss[row * DM_KEYS + key] = key < n ? (s[0][e] + s[1][e]) * a.scale : -INFINITY;
+        }
     }
     __syncthreads();
-    // ---- softmax weights relative to the running maximum: four rows per warp
+    // ---- softmax weights relative to the running maximum: a warp's rows
 #pragma unroll
-    for (int rr = 0; rr < 4; ++rr) {
-        const int row = warp * 4 + rr;
+    for (int rr = 0; rr < Sh::RW; ++rr) {
+        const int row = warp * Sh::RW + rr;
         const float s0 = Ss[row * DM_KEYS + lane], s1 = Ss[row * DM_KEYS + lane + 32];
         const float m_old = tt > 0 ? stat[row * 2] : -INFINITY;
         const float l_old = tt > 0 ? stat[row * 2 + 1] : 0.f;
@@ -550,7 +585,7 @@ attention_decode_mma_kernel(DecodeArgs a, int cs) {
         }
     }
     __syncthreads();
-    // ---- weighted values: this warp's quarter of the head dimension
+    // ---- weighted values: this warp's share of the head dimension
     {
         if (tt > 0) {
             const float f0 = fac[gid], f1 = fac[gid + 8];
@@ -569,7 +604,7 @@ attention_decode_mma_kernel(DecodeArgs a, int cs) {
                 unsigned bf[4];
                 const int mat = lane >> 3, r = lane & 7;
                 dm_ldsm4t(dm_smem(Vs + dm_swz<HDP>(kk * 16 + r + (mat & 1) * 8,
-                                                   warp * (HDP / 32) + nn * 2 + (mat >> 1))), bf);
+                                                   warp * (Sh::DW / 8) + nn * 2 + (mat >> 1))), bf);
                 dm_mma(o[nn * 2], af, bf[0], bf[1]);
                 dm_mma(o[nn * 2 + 1], af, bf[2], bf[3]);
             }
@@ -581,7 +616,7 @@ attention_decode_mma_kernel(DecodeArgs a, int cs) {
         if (cs > 1 && used > 1) __syncthreads();   // Osm lies over the last key tile
 #pragma unroll
         for (int i = 0; i < NP * 2; ++i) {
-            const int d = warp * (HDP / 4) + i * 8 + tig * 2;
+            const int d = warp * Sh::DW + i * 8 + tig * 2;
             if (d >= hd) continue;
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
@@ -667,6 +702,7 @@ attention_decode_mma_kernel(DecodeArgs a, int cs) {
 template <int HDP>
 int launch_decode_mma(const DecodeArgs& a0, int B, cudaStream_t stream) {
     auto kern = attention_decode_mma_kernel<HDP>;
+    constexpr int DM_THREADS = DmShape<HDP>::NT;
     constexpr int smem = (2 * DM_KEYS + DM_HEADS) * HDP * 2 + DM_HEADS * DM_KEYS * (2 + 4) +
                          DM_HEADS * 3 * 4 + 2 * DM_KEYS * 4;
     static bool configured = false;
