@@ -80,6 +80,26 @@ struct DecodeArgs {
     float scale;
 };
 
+// The decode step's q/k norm, rotation and cache store done by the attention kernel
+// itself (bfloat16 tensor-core form, head sizes 64, 128, 256): with part != null the
+// queries are not read from q but formed from the projection's 32-bit partial sums,
+//     x = sum_g part[g][b][head];  x = x * rsqrt(mean(x^2) + eps) * w  (if w);
+//     pairs (i, i + hd/2) rotated by cos / sin [B, hd/2]  (if cos),
+// and with store_kv the CTA whose tiles hold position p forms the new key (the same
+// way, with wk) and value (the sum alone), uses them and writes them to the cache.
+// That removes a launch, and a trip of q, k and v through global memory, from a chain
+// of dependent kernels.
+struct FuseQK {
+    const float* part;         // [G, B, (nh + 2 nkv) * hd]; null: not fused
+    int G;
+    const float* wq;           // [hd] or null
+    const float* wk;
+    float eps;
+    const float* cosv;         // [B, hd / 2] or null
+    const float* sinv;
+    int store_kv;
+};
+
 // Writes this chunk's (maximum, normaliser), counts the chunk in and, in the
 // CTA that arrives last for the (sequence, head group), merges all chunks:
 // out = sum_s e^{m_s - M} acc_s / sum_s e^{m_s - M} l_s, in chunk order.
@@ -375,6 +395,90 @@ __device__ __forceinline__ float dm_ld_peer(const float* local, unsigned rank) {
     return v;
 }
 
+
+// N consecutive floats (N = 1, 2, 4; p aligned to N floats) in one load.
+template <int N>
+__device__ __forceinline__ void dm_ld_run(const float* p, float* dst) {
+    if constexpr (N == 4) {
+        const float4 t = *reinterpret_cast<const float4*>(p);
+        dst[0] = t.x; dst[1] = t.y; dst[2] = t.z; dst[3] = t.w;
+    } else if constexpr (N == 2) {
+        const float2 t = *reinterpret_cast<const float2*>(p);
+        dst[0] = t.x; dst[1] = t.y;
+    } else {
+        dst[0] = *p;
+    }
+}
+
+// One warp forms one head (hd = 64 * HALF values) from the projection's partial sums:
+// a lane holds the runs [lane * HALF, +HALF) of both halves of the head, so that the
+// partners of the rotation are its own.  Optional norm (w) and rotation (cs / sn rows of
+// hd / 2).  The result goes, as bfloat16, to a row of a swizzled [rows][HDP] tile in
+// shared memory and, if gdst is given, to global memory.  Weights and angles are
+// requested before the sums, so that all loads are in flight together.
+template <int HDP>
+__device__ __forceinline__ void dm_head_from_partials(const float* __restrict__ src, int G,
+                                                      size_t split_stride,
+                                                      const float* __restrict__ w, float eps,
+                                                      const float* __restrict__ cs,
+                                                      const float* __restrict__ sn,
+                                                      __nv_bfloat16* tile, int row,
+                                                      __nv_bfloat16* gdst, int lane) {
+    constexpr int HALF = HDP / 64, H2 = HDP / 2;
+    const int e0 = lane * HALF;
+    float wv[2 * HALF], cv[HALF], sv[HALF];
+    if (w) {
+        dm_ld_run<HALF>(w + e0, wv);
+        dm_ld_run<HALF>(w + H2 + e0, wv + HALF);
+    }
+    if (cs) {
+        dm_ld_run<HALF>(cs + e0, cv);
+        dm_ld_run<HALF>(sn + e0, sv);
+    }
+    float v[2 * HALF];
+#pragma unroll
+    for (int i = 0; i < 2 * HALF; ++i) v[i] = 0.f;
+    constexpr int U = 4;                                  // partial sums loaded together
+    for (int g0 = 0; g0 < G; g0 += U) {
+        float t[U][2 * HALF];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const float* r = src + (size_t)min(g0 + u, G - 1) * split_stride + e0;
+            dm_ld_run<HALF>(r, t[u]);
+            dm_ld_run<HALF>(r + H2, t[u] + HALF);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+#pragma unroll
+            for (int i = 0; i < 2 * HALF; ++i) v[i] += g0 + u < G ? t[u][i] : 0.f;
+    }
+    if (w) {
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < 2 * HALF; ++i) ss += v[i] * v[i];
+        ss = warp_sum(ss);
+        const float rs = 1.0f / sqrtf(ss / (float)HDP + eps);
+#pragma unroll
+        for (int i = 0; i < 2 * HALF; ++i) v[i] = v[i] * rs * wv[i];
+    }
+    if (cs) {
+#pragma unroll
+        for (int i = 0; i < HALF; ++i) {
+            const float re = v[i], im = v[HALF + i];
+            v[i] = re * cv[i] - im * sv[i];
+            v[HALF + i] = re * sv[i] + im * cv[i];
+        }
+    }
+    // (HALF consecutive values of each half: 2 * HALF bytes, inside one 16-byte chunk)
+#pragma unroll
+    for (int i = 0; i < 2 * HALF; ++i) {
+        const int e = (i < HALF ? e0 + i : H2 + e0 + i - HALF);
+        const __nv_bfloat16 x = __float2bfloat16_rn(v[i]);
+        tile[dm_swz<HDP>(row, e >> 3) + (e & 7)] = x;
+        if (gdst) gdst[e] = x;
+    }
+}
+
 // The tensor-core form (bfloat16).  The gridDim.x CTAs of a (sequence, head group)
 // share the sequence's tiles of 64 keys by stride, each with a running softmax over
 // the tiles it walks.  cs = 2, 4, 8: every cs of them form a thread-block cluster
@@ -384,7 +488,7 @@ __device__ __forceinline__ float dm_ld_peer(const float* local, unsigned rank) {
 // goes through scratch.
 template <int HDP>
 __global__ void __launch_bounds__(DmShape<HDP>::NT, DmShape<HDP>::NT == 256 ? 2 : 3)
-attention_decode_mma_kernel(DecodeArgs a, int cs) {
+attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq) {
     typedef DmShape<HDP> Sh;
     constexpr int DM_THREADS = Sh::NT;
     // Slots, positions and page tables are written by copies at the start of the step,
@@ -472,21 +576,47 @@ attention_decode_mma_kernel(DecodeArgs a, int cs) {
     }
     pdl_wait();
     if (has) {
+    const bool fused = fq.part != nullptr;                  // (then hd == HDP)
+    const size_t f_width = (size_t)(a.nh + 2 * a.nkv) * hd;  // a row of the projection
+    const size_t f_stride = (size_t)gridDim.z * f_width;     // one partial sum of the batch
+    const float* f_cos = fused && fq.cosv ? fq.cosv + (size_t)b * (hd / 2) : nullptr;
+    const float* f_sin = fused && fq.cosv ? fq.sinv + (size_t)b * (hd / 2) : nullptr;
     // queries of the group: rows beyond the group's heads and dims beyond hd are zero
     for (int i = tid; i < DM_HEADS * CPR; i += DM_THREADS) {
         const int r = i / CPR, c = i % CPR;
         T* dst = Qs + dm_swz<HDP>(r, c);
-        if (r < gc && c * 8 < hd)
-            cp_async16(dst, (const T*)a.q + (size_t)b * a.q_stride + (size_t)(h0 + r) * hd + c * 8);
-        else
+        if (r < gc && c * 8 < hd) {
+            if (!fused)
+                cp_async16(dst, (const T*)a.q + (size_t)b * a.q_stride + (size_t)(h0 + r) * hd +
+                                    c * 8);
+        } else {
             *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+        }
     }
-    if (r_new >= 0 && r_new < DM_KEYS) {
-        // the new position's key and value
+    if (fused)
+        for (int r = warp; r < gc; r += DM_THREADS / 32)
+            dm_head_from_partials<HDP>(fq.part + (size_t)b * f_width + (size_t)(h0 + r) * hd, fq.G,
+                                       f_stride, fq.wq, fq.eps, f_cos, f_sin, Qs, r, nullptr, lane);
+    // the new position's key and value: from the cache, or formed here and stored
+    auto new_row = [&](int r, int cache_row) {
+        if (fused && fq.store_kv) {
+            const bool writer = blockIdx.y % groups_per_kv == 0 && cache_row >= 0;
+            T* kd = writer ? (T*)a.k_pool + ((size_t)cache_row * a.nkv + g) * hd : nullptr;
+            T* vd = writer ? (T*)a.v_pool + ((size_t)cache_row * a.nkv + g) * hd : nullptr;
+            const float* src = fq.part + (size_t)b * f_width;
+            // (by the warps after those that form the queries, if there are any)
+            if (warp == gc % Sh::NW)
+                dm_head_from_partials<HDP>(src + (size_t)(a.nh + g) * hd, fq.G, f_stride, fq.wk,
+                                           fq.eps, f_cos, f_sin, Ks, r, kd, lane);
+            else if (warp == (gc + 1) % Sh::NW)
+                dm_head_from_partials<HDP>(src + (size_t)(a.nh + a.nkv + g) * hd, fq.G, f_stride,
+                                           nullptr, 0.f, nullptr, nullptr, Vs, r, vd, lane);
+            return;
+        }
         for (int c = tid; c < CPR; c += DM_THREADS) {
-            const int off = dm_swz<HDP>(r_new, c);
-            if (rowoff[r_new] >= 0 && c * 8 < hd) {
-                const size_t src = ((size_t)rowoff[r_new] * a.nkv + g) * hd + c * 8;
+            const int off = dm_swz<HDP>(r, c);
+            if (cache_row >= 0 && c * 8 < hd) {
+                const size_t src = ((size_t)cache_row * a.nkv + g) * hd + c * 8;
                 cp_async16(Ks + off, (const T*)a.k_pool + src);
                 cp_async16(Vs + off, (const T*)a.v_pool + src);
             } else {
@@ -494,7 +624,8 @@ attention_decode_mma_kernel(DecodeArgs a, int cs) {
                 *reinterpret_cast<uint4*>(Vs + off) = make_uint4(0, 0, 0, 0);
             }
         }
-    }
+    };
+    if (r_new >= 0 && r_new < DM_KEYS) new_row(r_new, rowoff[r_new]);
     constexpr int NP = Sh::NP;
     float o[NP * 2][4] = {};
     for (int tt = 0; tt < n_tiles; ++tt) {
@@ -507,9 +638,11 @@ attention_decode_mma_kernel(DecodeArgs a, int cs) {
         // the tile before has been used up: this one replaces it
         __syncthreads();
         const int* ro = rowoff + (tt & 1) * DM_KEYS;
+        const int rn = p - jt;                               // the new position's row, if in this tile
         for (int i = tid; i < DM_KEYS * CPR; i += DM_THREADS) {
             const int r = i / CPR, c = i % CPR;
             const int off = dm_swz<HDP>(r, c);
+            if (r == rn) continue;
             if (ro[r] >= 0 && c * 8 < hd) {
                 const size_t src = ((size_t)ro[r] * a.nkv + g) * hd + c * 8;
                 cp_async16(Ks + off, (const T*)a.k_pool + src);
@@ -519,6 +652,7 @@ attention_decode_mma_kernel(DecodeArgs a, int cs) {
                 *reinterpret_cast<uint4*>(Vs + off) = make_uint4(0, 0, 0, 0);
             }
         }
+        if (rn >= 0 && rn < DM_KEYS) new_row(rn, ro[rn]);
     }
     cp_async_wait_all();
     __syncthreads();
@@ -700,7 +834,7 @@ attention_decode_mma_kernel(DecodeArgs a, int cs) {
 }
 
 template <int HDP>
-int launch_decode_mma(const DecodeArgs& a0, int B, cudaStream_t stream) {
+int launch_decode_mma(const DecodeArgs& a0, int B, cudaStream_t stream, const FuseQK& fq) {
     auto kern = attention_decode_mma_kernel<HDP>;
     constexpr int DM_THREADS = DmShape<HDP>::NT;
     constexpr int smem = (2 * DM_KEYS + DM_HEADS) * HDP * 2 + DM_HEADS * DM_KEYS * (2 + 4) +
@@ -733,9 +867,9 @@ int launch_decode_mma(const DecodeArgs& a0, int B, cudaStream_t stream) {
     a.n_splits = clusters;                         // partial results per (sequence, head)
     dim3 grid(clusters * cs, groups, B);
     if (cs > 1)
-        agv_launch_cluster(kern, grid, DM_THREADS, smem, stream, dim3(cs, 1, 1), a, cs);
+        agv_launch_cluster(kern, grid, DM_THREADS, smem, stream, dim3(cs, 1, 1), a, cs, fq);
     else
-        agv_launch(kern, grid, DM_THREADS, smem, stream, a, 1);
+        agv_launch(kern, grid, DM_THREADS, smem, stream, a, 1, fq);
     AGV_LAUNCH_OK("attention_decode_mma_kernel");
     return 0;
 }
@@ -772,12 +906,12 @@ AGV_API int agv_attention_decode_plan(int hd, int dtype, int max_keys, int* chun
 // agv_attention_decode_plan implies; counters are B * nkv * ceil(nh / nkv / 4)
 // ints that are zero before the call (the call leaves them zero).  A negative
 // slot yields zeros.
-AGV_API int agv_attention_decode(const void* q, long long q_stride, void* out, int dtype,
+static int attention_decode_impl(const void* q, long long q_stride, void* out, int dtype,
                                  const void* k_pool, const void* v_pool, const int* page_table,
                                  const int* slots, const int* positions, int max_pages, int page,
                                  int cap, int B, int nh, int nkv, int hd, float scale, int window,
                                  int max_keys, float* part_acc, float* part_ml, int* counters,
-                                 cudaStream_t stream) {
+                                 cudaStream_t stream, const FuseQK& fq) {
     AGV_REQUIRE(B >= 0 && nh > 0 && nkv > 0 && hd > 0, "attention_decode: bad sizes");
     AGV_REQUIRE(nh % nkv == 0, "attention_decode: %d heads are not a multiple of %d kv heads", nh,
                 nkv);
@@ -802,11 +936,12 @@ AGV_API int agv_attention_decode(const void* q, long long q_stride, void* out, i
     DecodeArgs a{q, q_stride, out, k_pool, v_pool, page_table, slots, positions, part_acc, part_ml,
                  counters, max_pages, page, cap, nh, nkv, hd, window, n_splits, ch, scale};
     if (dtype == AGV_BF16 && hd % 8 == 0 && hd <= 256 && ch == DM_KEYS &&
-        q_stride % 8 == 0 && agv_aligned(q, 16)) {
-        if (hd <= 64) return launch_decode_mma<64>(a, B, stream);
-        if (hd <= 128) return launch_decode_mma<128>(a, B, stream);
-        return launch_decode_mma<256>(a, B, stream);
+        (fq.part || (q_stride % 8 == 0 && agv_aligned(q, 16)))) {
+        if (hd <= 64) return launch_decode_mma<64>(a, B, stream, fq);
+        if (hd <= 128) return launch_decode_mma<128>(a, B, stream, fq);
+        return launch_decode_mma<256>(a, B, stream, fq);
     }
+    AGV_REQUIRE(!fq.part, "attention_decode: the fused form needs the tensor-core kernel");
     const int G = nh / nkv;
     dim3 grid(n_splits, nkv * ((G + AD_GC - 1) / AD_GC), B);
     if (dtype == AGV_F32) {
@@ -830,6 +965,49 @@ AGV_API int agv_attention_decode(const void* q, long long q_stride, void* out, i
     }
     AGV_LAUNCH_OK("attention_decode_split_kernel");
     return 0;
+}
+
+AGV_API int agv_attention_decode(const void* q, long long q_stride, void* out, int dtype,
+                                 const void* k_pool, const void* v_pool, const int* page_table,
+                                 const int* slots, const int* positions, int max_pages, int page,
+                                 int cap, int B, int nh, int nkv, int hd, float scale, int window,
+                                 int max_keys, float* part_acc, float* part_ml, int* counters,
+                                 cudaStream_t stream) {
+    return attention_decode_impl(q, q_stride, out, dtype, k_pool, v_pool, page_table, slots,
+                                 positions, max_pages, page, cap, B, nh, nkv, hd, scale, window,
+                                 max_keys, part_acc, part_ml, counters, stream, FuseQK{});
+}
+
+// Whether agv_attention_decode_fused takes these sizes: bfloat16, head sizes 64, 128,
+// 256, the whole head rotated (or none of it).
+AGV_API int agv_attention_decode_fused_supported(int dtype, int hd, int rotary_dim) {
+    return (dtype == AGV_BF16 && (hd == 64 || hd == 128 || hd == 256) &&
+            (rotary_dim == 0 || rotary_dim == hd)) ? 1 : 0;
+}
+
+// agv_attention_decode with the q/k norm, the rotation and the cache store of the new
+// position inside (see FuseQK): part [G, B, (nh + 2 nkv) * hd] are the projection's
+// 32-bit partial sums; wq, wk [hd] or null; cos, sin [B, hd / 2] or null; store_kv 0
+// for a layer that reads another layer's cache entry (then only q is formed here and
+// the new position's key and value must be in the cache already).  The pools are
+// written, so they are not const.
+AGV_API int agv_attention_decode_fused(const float* part, int G, const float* wq, const float* wk,
+                                       float eps, const float* cosv, const float* sinv,
+                                       int store_kv, void* out, void* k_pool, void* v_pool,
+                                       const int* page_table, const int* slots,
+                                       const int* positions, int max_pages, int page, int cap,
+                                       int B, int nh, int nkv, int hd, float scale, int window,
+                                       int max_keys, float* part_acc, float* part_ml,
+                                       int* counters, cudaStream_t stream) {
+    AGV_REQUIRE(part && G >= 1, "attention_decode_fused: no partial sums");
+    AGV_REQUIRE(agv_attention_decode_fused_supported(AGV_BF16, hd, cosv ? hd : 0),
+                "attention_decode_fused: head_dim %d is not 64, 128 or 256", hd);
+    AGV_REQUIRE(!cosv || sinv, "attention_decode_fused: cos without sin");
+    AGV_REQUIRE(agv_aligned(part, 16), "attention_decode_fused: partial sums must be aligned");
+    FuseQK fq{part, G, wq, wk, eps, cosv, sinv, store_kv};
+    return attention_decode_impl(nullptr, 0, out, AGV_BF16, k_pool, v_pool, page_table, slots,
+                                 positions, max_pages, page, cap, B, nh, nkv, hd, scale, window,
+                                 max_keys, part_acc, part_ml, counters, stream, fq);
 }
 
 // ------------------------------------------------------- no-allocation variant

@@ -602,6 +602,45 @@ def attention_decode_split(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Ten
         _ptr(part_acc), _ptr(part_ml), _ptr(counters), _stream()))
 
 
+_FUSED_DECODE = os.environ.get("AGAVE_B200_FUSED_DECODE_ATTENTION", "1") != "0"
+
+
+def attention_decode_fused_supported(dtype: torch.dtype, head_dim: int, rotary_dim: int) -> bool:
+    """Whether ``attention_decode_fused`` takes a layer of these sizes."""
+    return (_FUSED_DECODE and dtype == torch.bfloat16 and bool(
+        library().agv_attention_decode_fused_supported(BF16, head_dim, rotary_dim)))
+
+
+def attention_decode_fused(partial: torch.Tensor, wq: Optional[torch.Tensor],
+                           wk: Optional[torch.Tensor], eps: float, cos: Optional[torch.Tensor],
+                           sin: Optional[torch.Tensor], store_kv: bool, out: torch.Tensor, view,
+                           ctx, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
+                           window: int) -> None:
+    """Decode attention of one layer with the q/k norm, the rotation and the cache store
+    of the new position inside the attention kernel: ``partial`` [G, B, (nh + 2 nkv) *
+    hd] are the projection's 32-bit partial sums."""
+    _f32(partial, "partial"); _dense(partial, "partial"); _dense(out, "out")
+    _f32(wq, "wq"); _f32(wk, "wk"); _f32(cos, "cos"); _f32(sin, "sin")
+    G, B, width = partial.shape
+    assert width == (n_heads + 2 * n_kv_heads) * head_dim and out.dtype == torch.bfloat16
+    assert view.k_pool.dtype == torch.bfloat16
+    if cos is not None:
+        _dense(cos, "cos"); _dense(sin, "sin")
+        assert cos.shape == (B, head_dim // 2) and sin.shape == cos.shape
+    max_keys = max(1, min(window, ctx.max_len) if window else ctx.max_len)
+    _, n_splits = attention_decode_plan(head_dim, torch.bfloat16, max_keys)
+    part_acc = torch.empty((B, n_heads, n_splits, head_dim), dtype=torch.float32,
+                           device=out.device)
+    part_ml = torch.empty((B, n_heads, n_splits, 2), dtype=torch.float32, device=out.device)
+    counters = _decode_counters(out.device, B * n_heads)
+    _check(library().agv_attention_decode_fused(
+        _ptr(partial), G, _ptr(wq), _ptr(wk), ctypes.c_float(eps), _ptr(cos), _ptr(sin),
+        1 if store_kv else 0, _ptr(out), _ptr(view.k_pool), _ptr(view.v_pool),
+        _ptr(view.page_table), _ptr(ctx.slots), _ptr(ctx.positions), view.page_table.shape[1],
+        view.page, view.cap, B, n_heads, n_kv_heads, head_dim, ctypes.c_float(scale), window,
+        max_keys, _ptr(part_acc), _ptr(part_ml), _ptr(counters), _stream()))
+
+
 def attention_decode(q, out, view, ctx, n_heads, n_kv_heads, head_dim, scale, window) -> None:
     """Decode attention of one layer: the split kernel for head sizes in steps of
     16 up to 512, else the one-warp-per-head kernel."""

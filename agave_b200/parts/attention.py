@@ -81,10 +81,7 @@ class AttentionMixer:
         nh, nkv, hd = s.n_heads, s.n_kv_heads, s.head_dim
         T = x.shape[0]
         proj = self.qkv.partial(x, cheap_sum=True)
-        if proj.dim() == 3:
-            part, qkv = proj, ctx.new(T, (nh + 2 * nkv) * hd)
-        else:
-            part, qkv = None, proj
+        part = proj if proj.dim() == 3 else None
         cos = sin = None
         rotary_dim = 0
         if self.position is not None:
@@ -92,6 +89,17 @@ class AttentionMixer:
             rotary_dim = self.position.rotary_dim
         view = ctx.cache.kv_view(cache_entry)
         eps = s.qk_norm.eps if s.qk_norm is not None else 0.0
+        window = s.window or 0
+        if (ctx.mode == DECODE and part is not None and
+                kernels.attention_decode_fused_supported(self.dtype, hd, rotary_dim)):
+            # decoding: norm, rotation and the store of the new key and value happen inside
+            # the attention kernel, on the projection's partial sums
+            out = ctx.new(T, nh * hd)
+            kernels.attention_decode_fused(part, self.q_norm_weight, self.k_norm_weight, eps, cos,
+                                           sin, writes_cache, out, view, ctx, nh, nkv, hd, s.scale,
+                                           window)
+            return self.out.partial(out)
+        qkv = proj if part is None else ctx.new(T, (nh + 2 * nkv) * hd)
         if writes_cache:
             # a prompt step on the tcgen05 attention kernel reads the values transposed:
             # the same launch writes that copy
@@ -108,7 +116,6 @@ class AttentionMixer:
                                        eps, cos, sin, rotary_dim, ctx.positions, partial=part)
         q = qkv[:, :nh * hd]
         out = ctx.new(T, nh * hd)
-        window = s.window or 0
         if ctx.mode == PREFILL:
             if writes_cache:
                 k = qkv[:, nh * hd:(nh + nkv) * hd]

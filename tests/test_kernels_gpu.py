@@ -530,6 +530,81 @@ def test_attention_decode_many_sequences_walk_several_tiles(B, nh, nkv, hd):
         assert (out[slots < 0] == 0).all()
 
 
+@pytest.mark.parametrize("nh,nkv,hd,window,G", [(4, 1, 256, 0, 8), (4, 1, 256, 100, 3),
+                                                (16, 2, 128, 0, 1), (40, 2, 64, 0, 5),
+                                                (8, 8, 64, 70, 9), (6, 3, 128, 64, 16),
+                                                (32, 2, 256, 0, 2), (20, 1, 128, 0, 4)])
+@pytest.mark.parametrize("norm,rotate", [(True, True), (False, False)])
+def test_attention_decode_with_norm_rotation_and_store_inside(nh, nkv, hd, window, G, norm, rotate):
+    """The decode attention that forms q, k and v of the new position from the
+    projection's partial sums, against the separate norm / rotation / store launch
+    followed by the plain decode attention: the outputs, the cache rows it writes, and
+    that it writes no other row.  Lengths put the new position at a tile's first and
+    last row and in a page's first row; more heads per group than the kernel's head tile
+    (two CTAs form the same key, one writes it) and as many as it has warps; a padding
+    entry; a layer that only reads the cache (store_kv off)."""
+    from types import SimpleNamespace
+    from agave_b200 import kernels
+    assert kernels.attention_decode_fused_supported(torch.bfloat16, hd, hd if rotate else 0)
+    PAGE, max_pages = 64, 12
+    lens = [700, 65, 1, 64, 129, 5, 300]
+    B = len(lens)
+    cap = max_pages * PAGE
+    width = (nh + 2 * nkv) * hd
+    k0 = rnd(B * max_pages, PAGE, nkv, hd, dtype=torch.bfloat16, seed=1, scale=0.3)
+    v0 = rnd(B * max_pages, PAGE, nkv, hd, dtype=torch.bfloat16, seed=2)
+    g = torch.Generator().manual_seed(3)
+    table = torch.randperm(B * max_pages, generator=g).int().reshape(B, max_pages).contiguous().to(DEV)
+    slots = torch.tensor([3, 0, 6, -1, 2, 5, 1], dtype=torch.int32, device=DEV)
+    positions = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=DEV)
+    lens_t = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    seq_index = torch.arange(B, dtype=torch.int32, device=DEV)
+    part = rnd(G, B, width, seed=4, scale=0.5 / G ** 0.5)
+    wq = (1.0 + 0.3 * rnd(hd, seed=5)) if norm else None
+    wk = (1.0 + 0.3 * rnd(hd, seed=6)) if norm else None
+    cos = sin = None
+    if rotate:
+        cos = torch.empty((B, hd // 2), dtype=torch.float32, device=DEV)
+        sin = torch.empty_like(cos)
+        kernels.rope_table(positions, hd, 10000.0, 1.0, cos, sin)
+    view = SimpleNamespace(page_table=table, page=PAGE, cap=cap)
+    ctx = SimpleNamespace(slots=slots, positions=positions, max_len=max(lens))
+
+    k_ref, v_ref = k0.clone(), v0.clone()
+    qkv = torch.empty((B, width), dtype=torch.bfloat16, device=DEV)
+    kernels.qk_norm_rope_store(qkv, nh, nkv, hd, wq, wk, 1e-5, cos, sin, hd if rotate else 0,
+                               positions, k_ref, v_ref, table, slots, lens_t, seq_index, PAGE, cap,
+                               partial=part)
+    ref = torch.full((B, nh * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    kernels.attention_decode_split(qkv[:, :nh * hd], ref, k_ref, v_ref, table, slots, positions,
+                                   PAGE, cap, nh, nkv, hd, 0.4, window, window or cap)
+    k, v = k0.clone(), v0.clone()
+    view.k_pool, view.v_pool = k, v
+    out = torch.full_like(ref, float("nan"))
+    kernels.attention_decode_fused(part, wq, wk, 1e-5, cos, sin, True, out, view, ctx, nh, nkv, hd,
+                                   0.4, window)
+    live = (slots >= 0).nonzero().flatten().tolist()
+    assert torch.isfinite(out.float()).all()
+    assert (out[3] == 0).all()
+    assert rel_err(out[live], ref[live]) < 8e-3
+    touched = torch.zeros(B * max_pages, PAGE, dtype=torch.bool, device=DEV)
+    for b in live:
+        row = (lens[b] - 1) % cap
+        pg = int(table[int(slots[b]), row // PAGE])
+        touched[pg, row % PAGE] = True
+        assert rel_err(k[pg, row % PAGE], k_ref[pg, row % PAGE]) < 6e-3, b
+        assert rel_err(v[pg, row % PAGE], v_ref[pg, row % PAGE]) < 6e-3, b
+        assert not torch.equal(k[pg, row % PAGE], k0[pg, row % PAGE])
+    assert torch.equal(k[~touched], k0[~touched]) and torch.equal(v[~touched], v0[~touched])
+    # a layer that reads another layer's entry: the new row is in the cache already
+    view.k_pool, view.v_pool = k_ref.clone(), v_ref.clone()
+    out2 = torch.full_like(ref, float("nan"))
+    kernels.attention_decode_fused(part, wq, wk, 1e-5, cos, sin, False, out2, view, ctx, nh, nkv,
+                                   hd, 0.4, window)
+    assert rel_err(out2[live], ref[live]) < 8e-3
+    assert torch.equal(view.k_pool, k_ref) and torch.equal(view.v_pool, v_ref)
+
+
 @pytest.mark.parametrize("nh,nkv,hd,window", [(4, 1, 256, 0), (4, 1, 256, 100), (6, 2, 128, 70),
                                               (3, 3, 64, 0), (4, 2, 16, 5), (2, 1, 40, 33),
                                               (2, 1, 200, 64)])
