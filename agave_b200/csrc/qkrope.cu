@@ -225,10 +225,12 @@ qk_norm_rope_store_reg_kernel(T* __restrict__ qkv, long long row_stride,
         // ---- the first blocks write the values transposed (they take longest, so they
         // start first): one tile of 64 tokens x 64 of the nkv * hd value columns each
         if constexpr (std::is_same<T, __nv_bfloat16>::value) {
-            __shared__ __nv_bfloat16 tile[64][66];
-            __shared__ int cols[64], pads[64];
+            __shared__ __align__(16) __nv_bfloat16 tile[64][72];    // rows of 9 x 16 bytes
+            __shared__ int cols[64], pads[64], pad_at[64], n_pads;
             const int vb = blockIdx.x, ncb = nkv * hd / 64;
             const int t0 = (vb / ncb) * 64, c0 = (vb % ncb) * 64;
+            if (threadIdx.x == 0) n_pads = 0;
+            __syncthreads();
             if (threadIdx.x < 64) {
                 const int t = t0 + threadIdx.x;
                 int col = -1, pad = 0;
@@ -242,6 +244,7 @@ qk_norm_rope_store_reg_kernel(T* __restrict__ qkv, long long row_stride,
                 }
                 cols[threadIdx.x] = col;
                 pads[threadIdx.x] = pad;
+                if (pad) pad_at[atomicAdd(&n_pads, 1)] = threadIdx.x;   // (ends of sequences)
             }
             pdl_wait();
             // 16 threads per token row (4 columns each), 8 rows per pass
@@ -273,17 +276,26 @@ qk_norm_rope_store_reg_kernel(T* __restrict__ qkv, long long row_stride,
                     tile[tc + e][ps * 8 + tr] = __float2bfloat16(val[ps][e]);
             __syncthreads();
             const int g = c0 / hd, d0 = c0 % hd;
-            for (int d = warp; d < 64; d += QK_WARPS) {
-                __nv_bfloat16* dst = vw.vt + (size_t)(g * hd + d0 + d) * vw.ld;
+            if (cols[0] >= 0 && (cols[0] & 7) == 0 && cols[63] == cols[0] + 63) {
+                // 64 tokens of one sequence at an aligned column: 16 bytes (8 tokens) a store
+                for (int i = threadIdx.x; i < 64 * 8; i += QK_WARPS * 32) {
+                    const int d = i >> 3, ch = i & 7;
+                    *reinterpret_cast<uint4*>(vw.vt + (size_t)(g * hd + d0 + d) * vw.ld + cols[0] +
+                                              ch * 8) =
+                        *reinterpret_cast<const uint4*>(&tile[d][ch * 8]);
+                }
+            } else {
+                for (int d = warp; d < 64; d += QK_WARPS) {
+                    __nv_bfloat16* dst = vw.vt + (size_t)(g * hd + d0 + d) * vw.ld;
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const int tl = h * 32 + lane, col = cols[tl];
-                    if (col >= 0) dst[col] = tile[d][tl];
+                    for (int h = 0; h < 2; ++h) {
+                        const int tl = h * 32 + lane, col = cols[tl];
+                        if (col >= 0) dst[col] = tile[d][tl];
+                    }
                 }
             }
-            for (int tl = 0; tl < 64; ++tl) {
-                const int pad = pads[tl];
-                if (pad == 0) continue;
+            for (int k = 0; k < n_pads; ++k) {
+                const int tl = pad_at[k], pad = pads[tl];
                 for (int i = threadIdx.x; i < 64 * pad; i += QK_WARPS * 32) {
                     const int d = i / pad, pc = i % pad;
                     vw.vt[(size_t)(g * hd + d0 + d) * vw.ld + cols[tl] + 1 + pc] =
