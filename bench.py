@@ -2,6 +2,7 @@
 """Measures decoding and prefill of Gemma 3 1B layer sizes on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl ours|reference]
+                    [--shapes 1b|4b|27b] [--prompt-lens LO HI] [--prefill-tokens N]
 
 Prints ONE JSON line.  ``value`` is decoded tokens per second of K decode
 steps at batch 8 (context 8,192, prompts of unequal lengths 128..2,048,
@@ -10,7 +11,9 @@ same through ``Engine.generate`` with host token ids in and out every step.
 ``prefill`` is one 2,048-token prompt; ``roofline`` relates the decode step to
 the bytes it has to read; ``points`` holds decoding at batch 1 and 64.
 A step's inputs (2 GB of weights) are larger than the 126 MB L2, so every
-timed iteration reads them from HBM; this is said in ``config``.
+timed iteration reads them from HBM; this is said in ``config``.  The last three
+options measure other layer sizes, longer contexts and longer prompts; what they were
+is in the record's ``config`` and ``prefill``.
 """
 import argparse
 import json
@@ -140,12 +143,12 @@ def run_reference(args):
     return 0
 
 
-def timed_decode(engine, torch, kernels, batch, steps, warmup, seed):
+def timed_decode(engine, torch, kernels, batch, steps, warmup, seed, lo=128, hi=2048):
     """K decode steps at one batch size, device-timed; returns (ms/step, lens, launches/step)."""
     import numpy as np
     g = torch.Generator().manual_seed(seed)
     V = engine.spec.vocab_size
-    lens = torch.linspace(128, 2048, batch).round().int().tolist() if batch > 1 else [1088]
+    lens = torch.linspace(lo, hi, batch).round().int().tolist() if batch > 1 else [(lo + hi) // 2]
     prompts = [torch.randint(3, V, (n,), generator=g).tolist() for n in lens]
     slots = [engine.acquire() for _ in prompts]
     # prompts in chunks of sequences, to bound the prompt step's activations
@@ -206,7 +209,18 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--shapes", default="1b", choices=sorted(SHAPES),
                     help="layer sizes to run (the default, 1b, is the benchmark configuration)")
+    ap.add_argument("--prompt-lens", type=int, nargs=2, default=[128, 2048], metavar=("LO", "HI"),
+                    help="the decode batches' prompt lengths run from LO to HI (default: the "
+                         "benchmark configuration's 128 to 2,048)")
+    ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
+                    help="length of the timed prompt (default: the benchmark configuration's)")
     args = ap.parse_args()
+    lo, hi = args.prompt_lens
+    n_pre = args.prefill_tokens
+    if not (0 < lo <= hi and hi + args.steps + max(3, args.warmup) + 1 <= CONTEXT
+            and 0 < n_pre <= CONTEXT):
+        print(f"bench.py: prompts and the decoded tokens must fit the context of {CONTEXT}")
+        return 2
     if args.impl == "reference":
         return run_reference(args)
     if args.gpus != 1:
@@ -229,30 +243,31 @@ def main():
     V = engine.spec.vocab_size
     g = torch.Generator().manual_seed(5)
 
-    # ---- prefill: one prompt of 2,048 tokens, logits of its last token ----
-    prompt = torch.randint(3, V, (PREFILL_TOKENS,), generator=g).tolist()
+    # ---- prefill: one prompt (2,048 tokens by default), logits of its last token ----
+    prompt = torch.randint(3, V, (n_pre,), generator=g).tolist()
     pre_ms = []
     for it in range(3 + 5):
         s = engine.acquire()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
         e0.record()
-        engine.step([(s, prompt)], [[PREFILL_TOKENS - 1]])
+        engine.step([(s, prompt)], [[n_pre - 1]])
         e1.record()
         torch.cuda.synchronize()
         engine.release(s)
         if it >= 3:
             pre_ms.append(e0.elapsed_time(e1))
     pre_ms = sorted(pre_ms)[len(pre_ms) // 2]
-    pflops = prefill_flops(cfg, PREFILL_TOKENS, 1)
-    prefill = {"value": round(PREFILL_TOKENS / pre_ms * 1e3, 1), "tokens": PREFILL_TOKENS,
+    pflops = prefill_flops(cfg, n_pre, 1)
+    prefill = {"value": round(n_pre / pre_ms * 1e3, 1), "tokens": n_pre,
                "ms": round(pre_ms, 3),
                "frac": round(pflops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
 
     # ---- decode at batch 8 (headline), with clocks sampled meanwhile ----
     clocks = ClockSampler()
     clocks.start()
-    ms8, lens8, launches = timed_decode(engine, torch, kernels, 8, args.steps, args.warmup, 8)
+    ms8, lens8, launches = timed_decode(engine, torch, kernels, 8, args.steps, args.warmup, 8,
+                                        lo, hi)
     clock_rec = clocks.stop()
     value = 8 / ms8 * 1e3
     nbytes = decode_bytes(cfg, lens8)
@@ -262,12 +277,13 @@ def main():
                 "of": pk["source"], "bytes_per_step": nbytes}
 
     # ---- the other batch sizes ----
-    ms1, _, _ = timed_decode(engine, torch, kernels, 1, args.steps, args.warmup, 1)
-    ms64, _, _ = timed_decode(engine, torch, kernels, 64, max(8, args.steps // 2), args.warmup, 64)
+    ms1, _, _ = timed_decode(engine, torch, kernels, 1, args.steps, args.warmup, 1, lo, hi)
+    ms64, _, _ = timed_decode(engine, torch, kernels, 64, max(8, args.steps // 2), args.warmup, 64,
+                              lo, hi)
     points = {"decode_b1": round(1 / ms1 * 1e3, 1), "decode_b64": round(64 / ms64 * 1e3, 1)}
 
     # ---- end to end through the Python entry point ----
-    lens = torch.linspace(128, 2048, 8).round().int().tolist()
+    lens = torch.linspace(lo, hi, 8).round().int().tolist()
     prompts = [torch.randint(3, V, (n,), generator=g).tolist() for n in lens]
     n_new = args.steps + 1
     engine.generate(prompts, max_new_tokens=4, stop_token_ids=[])           # warm-up
@@ -291,7 +307,7 @@ def main():
             "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"],
             "vocab": cfg["vocab_size"], "sliding_window": cfg["sliding_window"],
             "local_per_global": cfg["sliding_window_pattern"] - 1, "global_batch": 8,
-            "seq_len": CONTEXT, "prompt_lens": "128..2048 unequal", "seed": seed,
+            "seq_len": CONTEXT, "prompt_lens": f"{lo}..{hi} unequal", "seed": seed,
             "parallelism": "single-gpu", "cache": "paged bf16",
             "l2": "inputs larger than L2 (2 GB weights per step)"},
         "prefill": prefill, "roofline": roofline, "points": points, "e2e": e2e,
