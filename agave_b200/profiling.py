@@ -9,6 +9,9 @@ Cases (Gemma 3 1B layer sizes, random bfloat16 data):
   gemm_gated_decode    gate/up product, 8 tokens
   gemm_down_decode     down projection, 8 tokens (K split over a cluster or partial sums)
   gemm_lm_head_decode  the head over a 262,144-row table, 8 tokens
+  gemm_qkv_prefill     q/k/v projection (32-bit output), 2,048 tokens
+  qk_norm_rope_prefill q/k norm + rotation + cache store + transposed values, 2,048 tokens
+  norm_prefill         residual sum + two RMS norms over 2,048 rows
   attention_prefill    prompt attention (tcgen05), one sequence of 2,048 tokens, no window
   attention_prefill_window   the same with a window of 512
   attention_prefill_mma      the mma.sync kernel on the first workload
@@ -91,6 +94,55 @@ def case_gemm_down(T):
     w = [_rnd(H, FF, scale=0.02) for _ in range(c)]
     return (lambda i: kernels.linear_partial(x, w[i])), 2 * T * FF * H, \
         (FF * H + T * FF) * 2 + T * H * 4, c
+
+
+def case_gemm_qkv(T):
+    from . import kernels
+    N = (NH + 2 * NKV) * HD
+    c = 8                                  # (the weights are small: they stay in L2, as in a step)
+    x = [_rnd(T, H) for _ in range(c)]
+    w = _rnd(N, H, scale=0.02)
+    return (lambda i: kernels.linear_partial(x[i], w, cheap_sum=True)), 2 * T * N * H, \
+        (N * H + T * H) * 2 + T * N * 4, c
+
+
+def case_qk_norm_rope_prefill(T=2048):
+    from . import kernels
+    width, PAGE = (NH + 2 * NKV) * HD, 64
+    n_pages = T // PAGE
+    c = 12
+    parts = [torch.randn(1, T, width, device=DEV) for _ in range(c)]
+    qkvs = [torch.empty(T, width, dtype=torch.bfloat16, device=DEV) for _ in range(c)]
+    kp = [torch.empty(n_pages, PAGE, NKV, HD, dtype=torch.bfloat16, device=DEV) for _ in range(c)]
+    vp = [torch.empty(n_pages, PAGE, NKV, HD, dtype=torch.bfloat16, device=DEV) for _ in range(c)]
+    table = torch.arange(n_pages, dtype=torch.int32, device=DEV).reshape(1, n_pages)
+    slots = torch.zeros(1, dtype=torch.int32, device=DEV)
+    lens = torch.tensor([T], dtype=torch.int32, device=DEV)
+    seq_index = torch.zeros(T, dtype=torch.int32, device=DEV)
+    positions = torch.arange(T, dtype=torch.int32, device=DEV)
+    cu = torch.tensor([0, T], dtype=torch.int32, device=DEV)
+    cos = torch.empty(T, HD // 2, device=DEV)
+    sin = torch.empty_like(cos)
+    kernels.rope_table(positions, HD, 10000.0, 1.0, cos, sin)
+    w = torch.ones(HD, device=DEV)
+    vt = kernels.prefill_values_scratch(T, 1, NKV, HD, torch.device(DEV))
+
+    def fn(i):
+        kernels.qk_norm_rope_store(qkvs[i], NH, NKV, HD, w, w, 1e-6, cos, sin, HD, positions,
+                                   kp[i], vp[i], table, slots, lens, seq_index, PAGE, T,
+                                   partial=parts[i], vt=vt, cu_seqlens=cu, max_len=T)
+    return fn, 0, T * width * (4 + 2) + 3 * T * NKV * HD * 2, c
+
+
+def case_norm_prefill(T=2048):
+    from . import kernels
+    c = 12
+    hs = [torch.randn(T, H, device=DEV) for _ in range(c)]
+    ys = [torch.randn(1, T, H, device=DEV) for _ in range(c)]
+    xs = [torch.empty(T, H, dtype=torch.bfloat16, device=DEV) for _ in range(c)]
+    w = torch.ones(H, device=DEV)
+    return (lambda i: kernels.norm_residual(hs[i], ys[i], w, w, xs[i], 1e-6, 1e-6)), 0, \
+        T * H * (4 + 4 + 4 + 2), c
 
 
 def case_lm_head():
@@ -200,6 +252,9 @@ CASES = {
     "gemm_gated_decode": lambda: case_gemm_gated(8),
     "gemm_down_decode": lambda: case_gemm_down(8),
     "gemm_lm_head_decode": case_lm_head,
+    "gemm_qkv_prefill": lambda: case_gemm_qkv(2048),
+    "qk_norm_rope_prefill": case_qk_norm_rope_prefill,
+    "norm_prefill": case_norm_prefill,
     "attention_prefill": case_attention_prefill,
     "attention_prefill_window": lambda: case_attention_prefill(512),
     "attention_prefill_mma": lambda: case_attention_prefill(0, True),
