@@ -30,7 +30,20 @@ TINY_B = {
     "tie_word_embeddings": True, "max_position_embeddings": 2048,
     "hidden_activation": "gelu_pytorch_tanh", "bos_token_id": 2, "eos_token_id": [1, 106],
 }
-TINY = {"A": (TINY_A, 0, 0.02, 0.1), "B": (TINY_B, 1, 0.03, 0.2)}
+# A third one with a head size of 64, the smallest that takes the kernels the full-size
+# models run on (tcgen05 prompt attention, decode attention with the q/k norm, the
+# rotation and the cache store inside): two query heads per kv head, three kv heads.
+TINY_C = {
+    "architectures": ["Gemma3ForCausalLM"], "model_type": "gemma3_text",
+    "num_hidden_layers": 5, "hidden_size": 192, "num_attention_heads": 6,
+    "num_key_value_heads": 3, "head_dim": 64, "query_pre_attn_scalar": 48,
+    "intermediate_size": 320, "vocab_size": 500, "sliding_window": 24,
+    "sliding_window_pattern": 4, "rope_local_base_freq": 8000.0, "rope_theta": 200000.0,
+    "rope_scaling": {"rope_type": "linear", "factor": 4.0}, "rms_norm_eps": 2e-6,
+    "tie_word_embeddings": True, "max_position_embeddings": 1024,
+    "hidden_activation": "gelu_pytorch_tanh", "bos_token_id": 2, "eos_token_id": 1,
+}
+TINY = {"A": (TINY_A, 0, 0.02, 0.1), "B": (TINY_B, 1, 0.03, 0.2), "C": (TINY_C, 2, 0.03, 0.15)}
 
 _FOLDERS = {}
 
