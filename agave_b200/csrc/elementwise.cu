@@ -325,8 +325,9 @@ norm_residual_warp_kernel(float* __restrict__ h, const float* __restrict__ y, in
     }
 }
 
-// The same for rows too wide for a warp's registers (above 2,048 values): one CTA of
-// 256 threads per row, 16-byte loads issued up front, two block-wide sums.
+// The same with one CTA of 256 threads per row, 16-byte loads issued up front, two
+// block-wide sums: for rows too wide for a warp's registers (above 2,048 values), and for
+// 32 to 256 rows of any width (decoding many sequences: too few rows for a warp each).
 template <typename TX, int NV>
 __global__ void __launch_bounds__(256)
 norm_residual_row_kernel(float* __restrict__ h, const float* __restrict__ y, int n_splits,
@@ -349,13 +350,28 @@ norm_residual_row_kernel(float* __restrict__ h, const float* __restrict__ y, int
         hv[i] = (in && add_residual) ? reinterpret_cast<const float4*>(h + base)[idx]
                                      : make_float4(0, 0, 0, 0);
     }
-    for (int s = 1; s < n_splits; ++s) {
+    // the other partial sums, four at a time: their loads are issued together (a rolled
+    // loop would make one trip to memory per partial sum)
+    for (int s = 1; s < n_splits; s += 4) {
+        float4 t[4][NV];
 #pragma unroll
-        for (int i = 0; i < NV; ++i) {
-            const int idx = lane + 256 * i;
-            if (idx < H4) {
-                const float4 t = reinterpret_cast<const float4*>(y + s * split_stride + base)[idx];
-                v[i].x += t.x; v[i].y += t.y; v[i].z += t.z; v[i].w += t.w;
+        for (int u = 0; u < 4; ++u) {
+            const float* src = y + (size_t)min(s + u, n_splits - 1) * split_stride + base;
+#pragma unroll
+            for (int i = 0; i < NV; ++i) {
+                const int idx = lane + 256 * i;
+                t[u][i] = idx < H4 ? reinterpret_cast<const float4*>(src)[idx]
+                                   : make_float4(0, 0, 0, 0);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (s + u < n_splits) {
+#pragma unroll
+                for (int i = 0; i < NV; ++i) {
+                    v[i].x += t[u][i].x; v[i].y += t[u][i].y;
+                    v[i].z += t[u][i].z; v[i].w += t[u][i].w;
+                }
             }
         }
     }
@@ -464,7 +480,7 @@ static int launch_norm(float* h, const void* y, int n_splits, size_t split_strid
                 return 0;
             }
         }
-        if (R > 256 && y && !rows && H % 4 == 0 && H > 2048 && H <= 8192 && agv_aligned(y, 16) &&
+        if (((R > 256 && H > 2048) || (R >= 32 && R <= 256)) && y && !rows && H % 4 == 0 && H <= 8192 && agv_aligned(y, 16) &&
             agv_aligned(h, 16) && agv_aligned(x, 16) && split_stride % 4 == 0 &&
             (!w_post || agv_aligned(w_post, 16)) && (!w_next || agv_aligned(w_next, 16))) {
             if (launch_norm_row<TX>(h, (const float*)y, n_splits, split_stride, w_post, w_next,

@@ -167,7 +167,8 @@ def test_linear_simt_plain_and_gated(dtype):
 
 # ---------------------------------------------------------------------- norms
 @pytest.mark.parametrize("H,R", [(48, 7), (1000, 7), (5376, 7), (1152, 300), (2048, 257), (72, 513),
-                                 (2560, 300), (5376, 260), (8192, 257), (2052, 258)])
+                                 (2560, 300), (5376, 260), (8192, 257), (2052, 258),
+                                 (1152, 64), (2560, 40), (5376, 100), (100, 33), (8192, 32)])
 def test_norm_family(H, R):
     from agave_b200 import kernels
     h = rnd(R, H, seed=1)
@@ -392,6 +393,28 @@ def test_attention_over_the_paged_cache(dtype, nh, nkv, hd, window):
         qs = q[b].float().cpu().reshape(1, nh, hd)
         ref = ref_attention(qs, ks, vs, 0.2, 0)
         assert rel_err(out[b:b + 1], ref) < tol, b
+
+
+@pytest.mark.parametrize("H,R,S", [(1152, 64, 16), (2560, 48, 9), (5376, 33, 6), (1152, 8, 16),
+                                   (640, 256, 2), (1152, 300, 5)])
+def test_norm_of_many_partial_sums(H, R, S):
+    """The branch as S 32-bit partial sums (what a product with K cut into ranges leaves),
+    at row counts that take each of the norm kernels; S that is no multiple of the number
+    of partial sums a kernel loads together."""
+    from agave_b200 import kernels
+    h = rnd(R, H, seed=1)
+    parts = rnd(S, R, H, seed=2, scale=0.5)
+    wp, wn = rnd(H, seed=3) * 0.2 + 1, rnd(H, seed=4) * 0.2 + 1
+
+    def norm(v, w, eps):
+        return v * torch.rsqrt((v * v).mean(-1, keepdim=True) + eps) * w
+
+    h2 = h.clone()
+    xb = torch.empty((R, H), dtype=torch.bfloat16, device=DEV)
+    kernels.norm_residual(h2, parts, wp, wn, xb, eps_post=1e-5, eps_next=1e-6)
+    href = (h.double() + norm(parts.double().sum(0), wp.double(), 1e-5)).float()
+    assert rel_err(h2, href) < 2e-6
+    assert rel_err(xb, norm(href, wn, 1e-6)) < 5e-3
 
 
 # ------------------------------------------------------------------- sampling
