@@ -14,7 +14,9 @@ attention with the spec's scale and window, output projection.
 
 Prompts are attended from the step's own keys and values (every sequence of a
 prompt step starts at position 0), so a window ring never has to hold a whole
-prompt; decoding attends from the cache after the new key is stored.  A call
+prompt; decoding attends from the cache after the new key is stored (where the
+sizes allow, the decode attention kernel takes the projection's partial sums and does
+the norm, the rotation and that store itself).  A call
 that does not write the cache reads what the owning call stored: during a
 prompt step through ``ctx.step_kv``, during decoding through the cache.
 """
