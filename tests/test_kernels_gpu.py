@@ -480,7 +480,8 @@ def test_repeat_penalty_per_occurrence_and_history():
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("nh,nkv,hd", [(4, 1, 256), (16, 2, 128), (5, 5, 80), (12, 2, 512)])
+@pytest.mark.parametrize("nh,nkv,hd", [(4, 1, 256), (16, 2, 128), (5, 5, 80), (12, 2, 512),
+                                       (3, 1, 208), (2, 2, 48), (34, 2, 112)])
 def test_attention_decode_split_long_sequences(dtype, nh, nkv, hd):
     """Several chunks per sequence, groups wider than the kernel's head tile,
     a far key that must win, and a window edge in the middle of a chunk."""
