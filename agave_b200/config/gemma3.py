@@ -12,7 +12,13 @@ reference cannot reach from config.json are read here: the window size
 
 Only the defaults the reference itself documents are kept (eps 1e-6, rotary
 bases 1e6 / 1e4, pattern 6, query_pre_attn_scalar = head_dim, factor 1);
-every size must be present.
+every size must be present.  The ``text_config`` of the multimodal family
+members leaves out the sizes that equal their library defaults (head count,
+kv head count, head_dim, vocab_size); the reference falls back to the 1B
+sizes there (src/models/gemma3.zig:40-52), which is wrong for every other
+member.  Here a size that config.json omits is read from the shapes of the
+checkpoint's own tensors when the caller can show them (``shapes``), and is an
+error otherwise.
 """
 from __future__ import annotations
 
@@ -85,12 +91,17 @@ class Gemma3Config:
 
     # ------------------------------------------------------------------ read
     @classmethod
-    def from_dict(cls, raw: Dict[str, Any]) -> "Gemma3Config":
+    def from_dict(cls, raw: Dict[str, Any], shapes=None) -> "Gemma3Config":
+        """``shapes(suffix)``: the shape of the checkpoint tensor whose name ends
+        with ``suffix`` (under whatever prefix), or None; used only for sizes
+        that config.json leaves out."""
         d = dict(raw)
         # keys under text_config override top-level ones
         # (src/format/safetensors.zig:1827-1831)
         if isinstance(d.get("text_config"), dict):
             d.update(d["text_config"])
+        if shapes is not None:
+            cls._sizes_from_shapes(d, shapes)
         n_layers = _need(d, "num_hidden_layers")
         hidden = _need(d, "hidden_size")
         n_heads = _need(d, "num_attention_heads")
@@ -189,6 +200,29 @@ class Gemma3Config:
         )
         cfg.validate()
         return cfg
+
+    @staticmethod
+    def _sizes_from_shapes(d: Dict[str, Any], shapes) -> None:
+        """Fill sizes that config.json omits from the tensors that have them."""
+        def rows(suffix):
+            sh = shapes(suffix)
+            return int(sh[0]) if sh else None
+        if d.get("head_dim") is None:
+            hd = rows("layers.0.self_attn.q_norm.weight")
+            if hd:
+                d["head_dim"] = hd
+        hd = d.get("head_dim")
+        if isinstance(hd, int) and hd > 0:
+            for key, suffix in (("num_attention_heads", "layers.0.self_attn.q_proj.weight"),
+                                ("num_key_value_heads", "layers.0.self_attn.k_proj.weight")):
+                if d.get(key) is None:
+                    r = rows(suffix)
+                    if r and r % hd == 0:
+                        d[key] = r // hd
+        if d.get("vocab_size") is None:
+            v = rows("embed_tokens.weight")
+            if v:
+                d["vocab_size"] = v
 
     @staticmethod
     def _check_scaling(s: Dict[str, Any], where: str, allow_factor: bool) -> float:

@@ -69,8 +69,31 @@ def read_config_json(folder: str) -> Dict[str, Any]:
             raise ConfigError(f"{path}: not valid JSON ({e})") from None
 
 
+def _shape_lookup(folder: str):
+    """suffix -> shape of the folder's tensor whose name ends with it (the
+    shortest such name), reading only the files' headers; None without files."""
+    from ..weights.safetensors_io import SafetensorsError, SafetensorsFolder
+    try:
+        files = SafetensorsFolder(folder)
+    except (SafetensorsError, OSError):
+        return None
+
+    def shapes(suffix: str):
+        hits = [n for n in files.names() if n == suffix or n.endswith("." + suffix)]
+        if not hits:
+            return None
+        return tuple(files.tensors[min(hits, key=len)].shape)
+    return shapes
+
+
 def load_config(folder: str):
-    """(entry, typed config) of a model folder."""
+    """(entry, typed config) of a model folder.  A configuration class whose
+    ``from_dict`` takes ``shapes`` may read sizes that config.json omits from
+    the checkpoint's tensor shapes."""
+    import inspect
     raw = read_config_json(folder)
     entry = resolve_architecture(raw)
-    return entry, entry.config_class.from_dict(raw)
+    from_dict = entry.config_class.from_dict
+    if "shapes" in inspect.signature(from_dict).parameters:
+        return entry, from_dict(raw, shapes=_shape_lookup(folder))
+    return entry, from_dict(raw)

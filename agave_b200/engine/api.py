@@ -12,6 +12,7 @@ fixed input buffers and reads the chosen tokens back.
 """
 from __future__ import annotations
 
+import dataclasses
 import json
 import os
 import time
@@ -26,7 +27,7 @@ from ..cache import PAGE, CacheError, round_up
 from ..config import load_config, resolve_architecture
 from ..models.decoder import DecoderModel, decoder_param_specs
 from ..sampling import Sampler, SamplingParams
-from ..weights import load_weights, random_tensors
+from ..weights import head_is_stored, load_weights, random_tensors
 from .batch import DECODE, PREFILL, StepContext
 from .generate import GenerationPlan, RequestState
 from .step import Runner, StepError
@@ -145,7 +146,7 @@ class Engine:
 
     def __init__(self, model_dir: Optional[str] = None, *, dtype: str = "bfloat16",
                  max_tokens: int = 65536, ctx_size: int = 0, max_batch: Optional[int] = None,
-                 device: str = "cuda:0", use_graphs: bool = True,
+                 device: str = "cuda:0", use_graphs: bool = True, strict: bool = False,
                  _raw_config: Optional[dict] = None, _tensors: Optional[dict] = None):
         if dtype not in _DTYPES:
             raise ValueError(f"dtype {dtype!r} is not supported (bfloat16, float32)")
@@ -164,11 +165,19 @@ class Engine:
             self.entry = resolve_architecture(_raw_config)
             self.config = self.entry.config_class.from_dict(_raw_config)
         self.spec = self.config.to_model_spec()
-        self.model = DecoderModel(self.spec, self.dtype, self.device)
         names = self.entry.weight_names(self.config)
+        self.ignored_tensors: List[str] = []
+        if model_dir is not None and self.spec.tie_embeddings and head_is_stored(
+                model_dir, names.checkpoint_name, names.prefixes):
+            # a head of its own in the files wins over the configuration's word: the
+            # reference ties by absence (src/format/safetensors.zig:531-540)
+            self.spec = dataclasses.replace(self.spec, tie_embeddings=False)
+        self.model = DecoderModel(self.spec, self.dtype, self.device)
         if model_dir is not None:
             tensors = load_weights(model_dir, self.model.param_specs(), names.checkpoint_name,
-                                   names.prefixes)
+                                   names.prefixes, strict=strict,
+                                   ignore_prefixes=getattr(names, "ignore_prefixes", ()))
+            self.ignored_tensors = list(tensors.ignored)
         else:
             tensors = _tensors
         self.model.load(tensors)

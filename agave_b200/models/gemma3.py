@@ -37,6 +37,9 @@ _HEAD_PREFIX = {"model.": "", "language_model.model.": "language_model.",
 @dataclass(frozen=True)
 class Gemma3WeightNames:
     prefixes: Tuple[str, ...] = ("model.", "language_model.model.", "model.language_model.", "")
+    # what a multimodal folder holds beside the text decoder; never read here
+    ignore_prefixes: Tuple[str, ...] = ("vision_tower.", "multi_modal_projector.",
+                                        "model.vision_tower.", "model.multi_modal_projector.")
 
     def checkpoint_name(self, internal: str, prefix: str) -> str:
         if internal == "embed.weight":

@@ -10,6 +10,15 @@ dtype is the model's business, not the loader's.
 The reference reports a missing tensor only when a layer first asks for it
 (``MissingTensor``, src/models/gemma3.zig:352, src/format/safetensors.zig:333-349);
 here the whole list is checked before anything is copied to the device.
+
+A folder may hold more than the decoder: checkpoints of the multimodal family
+members carry a vision tower and a projector beside ``language_model.*``.  The
+reference looks tensors up by name and never sees the rest
+(src/format/safetensors.zig:333-349, prefixes 517-521).  Here a tensor that
+the decoder does not ask for is *unexpected* (an error) when it lies under the
+decoder's own prefix, where a stray name is most likely a mistake, and
+*ignored* when it lies elsewhere in the folder; ``strict=True`` makes every
+unrequested tensor an error.
 """
 from __future__ import annotations
 
@@ -68,12 +77,33 @@ def choose_prefix(file_names, expected_suffixes: Sequence[str], prefixes: Sequen
     return best
 
 
+def head_is_stored(folder: str, checkpoint_name: Callable[[str, str], str],
+                   prefixes: Sequence[str]) -> bool:
+    """Whether the folder holds an output head of its own (``lm_head.weight``
+    beside the decoder it belongs to)."""
+    files = SafetensorsFolder(folder)
+    prefix = choose_prefix(files.names(), [checkpoint_name("embed.weight", ""),
+                                           checkpoint_name("final_norm.weight", "")], prefixes)
+    return checkpoint_name("lm_head.weight", prefix) in files.tensors
+
+
+class LoadedWeights(dict):
+    """{internal name: CPU tensor as stored}, with what the folder held besides:
+    ``prefix`` (where the decoder's tensors sit) and ``ignored`` (names outside it)."""
+    prefix: str = ""
+    ignored: List[str] = []
+
+
 def load_weights(folder: str, param_specs: Dict[str, ParamSpec],
                  checkpoint_name: Callable[[str, str], str],
-                 prefixes: Sequence[str] = ("",)) -> Dict[str, torch.Tensor]:
+                 prefixes: Sequence[str] = ("",), strict: bool = False,
+                 ignore_prefixes: Sequence[str] = ()) -> "LoadedWeights":
     """{internal name: CPU tensor as stored}; raises ``WeightsError``.
 
-    ``checkpoint_name(internal, prefix)`` gives the name in the files.
+    ``checkpoint_name(internal, prefix)`` gives the name in the files.  Tensors
+    the model does not ask for are an error under the decoder's prefix and
+    ignored elsewhere (and under ``ignore_prefixes``); with ``strict`` all of
+    them are errors.  The names ignored are in the result's ``ignored``.
     """
     files = SafetensorsFolder(folder)
     probe = [checkpoint_name(n, "") for n in param_specs]
@@ -92,8 +122,15 @@ def load_weights(folder: str, param_specs: Dict[str, ParamSpec],
         ok = _INTS if spec.role == "table_int" else _FLOATS
         if info.dtype not in ok:
             wrong_dtype.append((ck, info.dtype))
-    unexpected = sorted(n for n in files.names() if n not in wanted)
+    unexpected, ignored = [], []
+    for n in sorted(files.names()):
+        if n in wanted:
+            continue
+        outside = (not n.startswith(prefix)) or any(n.startswith(p) for p in ignore_prefixes)
+        (ignored if outside and not strict else unexpected).append(n)
     if missing or unexpected or wrong_shape or wrong_dtype:
         raise WeightsError(folder, sorted(missing), unexpected, wrong_shape, wrong_dtype)
-    return {internal: _as_stored(files.tensor(ck), param_specs[internal].role)
-            for ck, internal in wanted.items()}
+    out = LoadedWeights((internal, _as_stored(files.tensor(ck), param_specs[internal].role))
+                        for ck, internal in wanted.items())
+    out.prefix, out.ignored = prefix, ignored
+    return out

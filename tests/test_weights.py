@@ -95,6 +95,75 @@ def test_prefixed_names_and_untied_head():
     assert e.value.missing == ["language_model.lm_head.weight"]
 
 
+def multimodal_folder(prefix: str, head_name: str, d=None):
+    """A folder laid out like the multimodal family members: ``model_type`` gemma3, the
+    sizes under ``text_config`` (with the keys those leave out left out), the decoder
+    under ``prefix``, a head of its own, and tensors of a vision tower and a projector."""
+    src = model_folder("B", torch.float32)
+    d = d or tempfile.mkdtemp()
+    text = {k: v for k, v in TINY_B.items()
+            if k not in ("architectures", "num_attention_heads", "num_key_value_heads",
+                         "head_dim", "vocab_size", "tie_word_embeddings")}
+    cfg = {"architectures": ["Gemma3ForConditionalGeneration"], "model_type": "gemma3",
+           "text_config": text, "vision_config": {"hidden_size": 8, "model_type": "siglip"},
+           "mm_tokens_per_image": 4}
+    with open(os.path.join(d, "config.json"), "w") as fh:
+        json.dump(cfg, fh)
+    f = SafetensorsFolder(src)
+    t = {prefix + n[len("model."):]: f.tensor(n).clone() for n in f.names()}
+    t[head_name] = torch.randn(384, 96)
+    vis = "" if prefix.startswith("language_model") else "model."
+    t[vis + "vision_tower.vision_model.encoder.layers.0.self_attn.q_proj.weight"] = torch.zeros(8, 8)
+    t[vis + "vision_tower.vision_model.embeddings.position_embedding.weight"] = torch.zeros(4, 8)
+    t[vis + "multi_modal_projector.mm_input_projection_weight"] = torch.zeros(8, 96)
+    save_safetensors(os.path.join(d, "model.safetensors"), t)
+    return d, t
+
+
+@pytest.mark.parametrize("prefix,head", [("language_model.model.", "language_model.lm_head.weight"),
+                                         ("model.language_model.", "lm_head.weight")])
+def test_multimodal_folder_gives_the_text_decoder(prefix, head):
+    d, t = multimodal_folder(prefix, head)
+    entry, cfg = load_config(d)
+    assert entry.name == "Gemma3ForCausalLM"
+    # the sizes text_config leaves out come from the tensors
+    assert (cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim,
+            cfg.vocab_size) == (6, 2, 32, 384)
+    names = entry.weight_names(cfg)
+    import dataclasses
+    from agave_b200.weights import head_is_stored
+    assert head_is_stored(d, names.checkpoint_name, names.prefixes)
+    spec = dataclasses.replace(cfg.to_model_spec(), tie_embeddings=False)
+    specs = decoder_param_specs(spec)
+    tensors = load_weights(d, specs, names.checkpoint_name, names.prefixes,
+                           ignore_prefixes=names.ignore_prefixes)
+    assert set(tensors) == set(specs) and tensors.prefix == prefix
+    assert torch.equal(tensors["lm_head.weight"], t[head])
+    assert len(tensors.ignored) == 3 and all("vision" in n or "projector" in n
+                                             for n in tensors.ignored)
+    # the strict switch keeps the old rule: every unrequested tensor is an error
+    with pytest.raises(WeightsError) as e:
+        load_weights(d, specs, names.checkpoint_name, names.prefixes, strict=True)
+    assert len(e.value.unexpected) == 3 and not e.value.missing
+    # a stray name inside the decoder is still an error without it
+    t[prefix + "layers.0.self_attn.extra.weight"] = torch.zeros(2)
+    save_safetensors(os.path.join(d, "model.safetensors"), t)
+    with pytest.raises(WeightsError) as e:
+        load_weights(d, specs, names.checkpoint_name, names.prefixes,
+                     ignore_prefixes=names.ignore_prefixes)
+    assert e.value.unexpected == [prefix + "layers.0.self_attn.extra.weight"]
+
+
+def test_sizes_left_out_of_config_need_the_tensors():
+    from agave_b200.config import ConfigError, Gemma3Config
+    raw = {k: v for k, v in TINY_B.items() if k not in ("head_dim", "vocab_size")}
+    with pytest.raises(ConfigError):
+        Gemma3Config.from_dict(raw)
+    shapes = {"layers.0.self_attn.q_norm.weight": (32,), "embed_tokens.weight": (384, 96)}
+    cfg = Gemma3Config.from_dict(raw, shapes=shapes.get)
+    assert cfg.head_dim == 32 and cfg.vocab_size == 384
+
+
 def test_sharded_folder_with_index():
     src = model_folder("A", torch.bfloat16)
     d = tempfile.mkdtemp()
