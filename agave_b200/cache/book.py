@@ -161,6 +161,20 @@ class CacheBook:
                 self.pages[slot][i].extend(self.pools[i].alloc(n))
                 self.dirty.add(slot)
 
+    def trim(self, slot: int, length: Optional[int] = None) -> None:
+        """Give back the pages beyond what ``length`` positions need (default: the
+        slot's recorded length): undoes a reservation whose step did not run."""
+        if slot not in self.length:
+            raise CacheError(f"slot {slot} is not held")
+        n = self.length[slot] if length is None else length
+        for i, g in enumerate(self.groups):
+            keep = g.pages_for(n)
+            extra = self.pages[slot][i][keep:]
+            if extra:
+                self.pools[i].free(extra)
+                del self.pages[slot][i][keep:]
+                self.dirty.add(slot)
+
     def set_length(self, slot: int, length: int) -> None:
         self.length[slot] = length
 

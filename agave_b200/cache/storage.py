@@ -50,15 +50,12 @@ class Cache:
         self.k_pools: List[torch.Tensor] = []
         self.v_pools: List[torch.Tensor] = []
         self.tables: List[torch.Tensor] = []
-        self.tables_host: List[torch.Tensor] = []
         for g in groups:
             shape = (len(g.entries), g.n_pages, PAGE, g.n_kv_heads, g.head_dim)
             self.k_pools.append(torch.zeros(shape, dtype=dtype, device=device))
             self.v_pools.append(torch.zeros(shape, dtype=dtype, device=device))
             self.tables.append(torch.zeros((n_slots, g.max_pages), dtype=torch.int32,
                                            device=device))
-            host = torch.zeros((n_slots, g.max_pages), dtype=torch.int32)
-            self.tables_host.append(host.pin_memory() if device.type == "cuda" else host)
         # fixed-size state: one tensor per distinct size
         self.state_where: Dict[int, Tuple[int, int]] = {}
         sizes: Dict[int, List[int]] = {}
@@ -82,13 +79,22 @@ class Cache:
     def reserve(self, slot: int, new_len: int) -> None:
         self.book.reserve(slot, new_len)
 
+    def trim(self, slot: int) -> None:
+        self.book.trim(slot)
+
     def release(self, slot: int) -> None:
         self.book.release(slot)
 
     def flush(self) -> None:
-        """Copy changed page-table rows to the device (on the current stream)."""
+        """Copy changed page-table rows to the device (on the current stream).
+
+        Every flush stages its rows in pinned memory of its own: a copy that has
+        not run yet must not see what a later flush writes for the same slot (a
+        slot released and taken again with no read in between).  The pinned
+        allocator hands a block out again only after the copies from it have run."""
         if not self.book.dirty:
             return
+        pinned = self.device.type == "cuda"
         for s in sorted(self.book.dirty):
             pages = self.book.pages.get(s)
             if pages is None:
@@ -96,9 +102,10 @@ class Cache:
             for gi, plist in enumerate(pages):
                 if not plist:
                     continue
-                row = self.tables_host[gi][s]
-                row[:len(plist)] = torch.tensor(plist, dtype=torch.int32)
-                self.tables[gi][s, :len(plist)].copy_(row[:len(plist)], non_blocking=True)
+                row = torch.tensor(plist, dtype=torch.int32)
+                if pinned:
+                    row = row.pin_memory()
+                self.tables[gi][s, :len(plist)].copy_(row, non_blocking=True)
         self.book.dirty.clear()
 
     # ----------------------------------------------------------------- views

@@ -10,7 +10,11 @@ own limit; default min(model, 4096)), ``-q/--quiet``, ``--json``,
 ``--model-info``, ``-V/--verbose``, ``-d/--debug``, ``-v/--version``.
 Options of what this library does not have (other backends, quantised caches,
 server, vision, speculative decoding, grammars) are not offered.  Added here:
-``--tokens`` (a prompt as token ids), ``--dtype`` and ``--max-batch``.
+``--tokens`` (a prompt as token ids), ``--dtype``, ``--max-batch``,
+``--random-weights SEED`` (the folder then needs only ``config.json``: seeded random
+weights are drawn on the device) and ``--strict`` (refuse folders that hold tensors the
+decoder does not ask for).  ``--profile`` prints the reference's per-operation table
+(src/perf.zig:84-130), with device times, for a run whose steps go launch by launch.
 
 A text prompt needs ``tokenizer.json`` in the model folder; it is wrapped in
 the Gemma chat template (src/chat_template.zig:153-161) after the BOS token
@@ -117,6 +121,11 @@ def build_parser() -> argparse.ArgumentParser:
                    help="Compute dtype [default: bfloat16].")
     g.add_argument("--max-batch", type=int, default=None,
                    help="Most sequences in one batch [default: as many as prompts].")
+    g.add_argument("--random-weights", type=int, default=None, metavar="SEED",
+                   help="Draw seeded random weights for the folder's config.json instead of "
+                        "reading tensors.")
+    g.add_argument("--strict", action="store_true",
+                   help="Refuse a folder that holds tensors the decoder does not ask for.")
     g = p.add_argument_group("DIAGNOSTICS")
     g.add_argument("-V", "--verbose", action="store_true",
                    help="Show technical details (params, load times, EOG).")
@@ -126,8 +135,24 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--model-info", action="store_true",
                    help="Print model metadata and exit (supports --json).")
     g.add_argument("--profile", action="store_true",
-                   help="Print per-phase timing of the run.")
+                   help="Print a per-operation table of device times (steps then run launch by "
+                        "launch).")
     return p
+
+
+def _peaks() -> dict:
+    """Measured memory and tensor peaks of this GPU, if a record of them is around:
+    the JSON file $AGAVE_B200_PEAKS names, else MEASURED_PEAKS.json beside the package."""
+    here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    for path in (os.environ.get("AGAVE_B200_PEAKS"), os.path.join(here, "MEASURED_PEAKS.json")):
+        if path and os.path.isfile(path):
+            try:
+                with open(path) as f:
+                    p = json.load(f)
+                return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"])}
+            except (OSError, ValueError, KeyError):
+                pass
+    return {}
 
 
 def _fail(msg: str) -> int:
@@ -145,6 +170,8 @@ def main(argv: Optional[List[str]] = None) -> int:
         return _fail("no model folder given")
     if not os.path.isdir(args.model):
         return _fail(f"'{args.model}' is not a model folder")
+    if args.random_weights is not None and args.strict:
+        return _fail("--strict is about tensors in files; --random-weights reads none")
     # the reference's own validation (src/main.zig:555-573)
     if args.temperature < 0:
         return _fail("--temperature must be >= 0")
@@ -157,10 +184,15 @@ def main(argv: Optional[List[str]] = None) -> int:
     args.verbose = args.verbose or args.debug
     quiet = args.quiet or args.json
 
-    from .config import ConfigError, load_config
+    from .config import ConfigError, load_config, read_config_json, resolve_architecture
     from .weights import SafetensorsError, WeightsError
     try:
-        entry, config = load_config(args.model)
+        if args.random_weights is not None:
+            raw_config = read_config_json(args.model)
+            entry = resolve_architecture(raw_config)
+            config = entry.config_class.from_dict(raw_config)
+        else:
+            entry, config = load_config(args.model)
     except ConfigError as e:
         return _fail(str(e))
     spec = config.to_model_spec()
@@ -208,9 +240,13 @@ def main(argv: Optional[List[str]] = None) -> int:
     n = max(1, len(prompts))
     max_batch = args.max_batch or n
     t0 = time.time()
+    sizes = dict(dtype=args.dtype, max_tokens=max_batch * ((ctx + 63) // 64 * 64), ctx_size=ctx,
+                 max_batch=max_batch)
     try:
-        engine = Engine(args.model, dtype=args.dtype, max_tokens=max_batch * ((ctx + 63) // 64 * 64),
-                        ctx_size=ctx, max_batch=max_batch)
+        if args.random_weights is not None:
+            engine = Engine.from_config(raw_config, seed=args.random_weights, **sizes)
+        else:
+            engine = Engine(args.model, strict=args.strict, **sizes)
     except (WeightsError, SafetensorsError, ConfigError, RuntimeError) as e:
         return _fail(str(e))
     info = engine.model_info()
@@ -236,18 +272,30 @@ def main(argv: Optional[List[str]] = None) -> int:
     if args.verbose:
         print(f"weights {info['weight_bytes'] / 1e6:.1f} MB · cache {info['cache_bytes'] / 1e6:.1f} MB"
               f" · EOG {list(spec.eos_token_ids)}", file=sys.stderr)
+        if engine.ignored_tensors:
+            print(f"ignored {len(engine.ignored_tensors)} tensors outside the text decoder: "
+                  + ", ".join(engine.ignored_tensors[:8])
+                  + (" ..." if len(engine.ignored_tensors) > 8 else ""), file=sys.stderr)
     stops = list(spec.eos_token_ids)
     if tok is not None:
         for name in ("<end_of_turn>", "<eos>"):          # src/main.zig:1213-1222
             if name in tok.vocab and tok.vocab[name] not in stops:
                 stops.append(tok.vocab[name])
+    counters = None
     try:
+        if args.profile:
+            from .perf import PerfCounters
+            counters = PerfCounters()
+            counters.__enter__()
         outs = engine.generate(prompts, max_new_tokens=args.max_tokens,
                                temperature=args.temperature, top_k=args.top_k, top_p=args.top_p,
                                repeat_penalty=args.repeat_penalty, seed=args.seed,
                                stop_token_ids=stops)
     except (ValueError, RuntimeError) as e:
         return _fail(str(e))
+    finally:
+        if counters is not None:
+            counters.__exit__(None, None, None)
     st = engine.stats
     n_tok = sum(len(o) for o in outs)
     gen_ms = st["decode_seconds"] * 1e3
@@ -279,4 +327,7 @@ def main(argv: Optional[List[str]] = None) -> int:
         print(f"[profile] load {engine.load_seconds * 1e3:.0f} ms · prefill {pre_ms:.1f} ms "
               f"({st['prefill_tokens']} tok) · decode {gen_ms:.1f} ms ({st['decode_steps']} steps, "
               f"{st['batches']} batches)", file=sys.stderr)
+        pk = _peaks()
+        print(counters.report(pk.get("hbm_gbs", 0.0), pk.get("bf16_tflops", 0.0)),
+              file=sys.stderr)
     return 0

@@ -29,13 +29,17 @@
  *   - The first call on a device looks up the array's device address
  *     (cudaGetSymbolAddress, with that device current).  Make that first call
  *     before any stream capture begins on that device.
+ *   - max_keys must be at least the number of keys any entry attends to
+ *     (position + 1, or the window if that is smaller): it sizes the grid.  An
+ *     entry with more keys gets no output from that call.  The call clears the
+ *     arrival counters it uses before its kernel runs (a memset on the stream),
+ *     so such a mistake does not reach later calls.
  *   - B times the number of head groups (nkv * ceil(nh / nkv / 4)) must not exceed
  *     AGV_NO_ALLOC_COUNTERS; the call is refused otherwise.
  *   - All calls share the one array and it keeps what the last call left.  The
  *     kernels write every value they later read, so nothing has to be cleared.
  *     The only thing that must start at zero is a small table of arrival
- *     counters beside the array: it is zero when the library is loaded and every
- *     call puts it back to zero before it ends.  Two calls that overlap on the
+ *     counters beside the array: every call clears the ones it uses first.  Two calls that overlap on the
  *     GPU (different streams, no ordering between them) race on both.  Order
  *     them, e.g. by using one stream.
  */

@@ -902,7 +902,9 @@ AGV_API int agv_attention_decode_plan(int hd, int dtype, int max_keys, int* chun
 // One query token per batch entry against the paged cache (its own key is
 // stored already).  q: [B, nh * hd] with row stride q_stride; out: [B, nh * hd]
 // dense.  max_keys bounds the number of keys any entry sees in this launch
-// (min(window, greatest length)); part_acc / part_ml are scratch of the sizes
+// (min(window, greatest length)): it sizes the grid, so it must be at least
+// position - window start + 1 of every entry, else that entry's output is not written
+// and its arrival counter stays non-zero; part_acc / part_ml are scratch of the sizes
 // agv_attention_decode_plan implies; counters are B * nkv * ceil(nh / nkv / 4)
 // ints that are zero before the call (the call leaves them zero).  A negative
 // slot yields zeros.
@@ -1067,6 +1069,10 @@ AGV_API int agv_attention_decode_static(const void* q, long long q_stride, void*
         base = g_static_scratch_addr[dev];
         counters = g_static_counters_addr[dev];
     }
+    // The counters this call uses start from zero whatever an earlier call left: a call
+    // whose max_keys was smaller than a sequence's key count never completes its count,
+    // and these counters are not the caller's to clear.  (A memset allocates nothing.)
+    AGV_CUDA_OK(cudaMemsetAsync(counters, 0, sizeof(int) * (size_t)B * (size_t)groups, stream));
     // partial sums first, then the (maximum, normaliser) pairs; both start 16-byte aligned
     return agv_attention_decode(q, q_stride, out, dtype, k_pool, v_pool, page_table, slots,
                                 positions, max_pages, page, cap, B, nh, nkv, hd, scale, window,

@@ -17,6 +17,10 @@
 #include "common.cuh"
 
 constexpr int SM_THREADS = 1024;
+// Sampling options as words on the device, so that one recorded decode step serves
+// every setting: [1 / temperature (float bits), top_k, top_p (float bits), seed low,
+// seed high, repeat penalty (float bits)]; two spare words.
+enum { SP_INV_TEMPERATURE = 0, SP_TOP_K, SP_TOP_P, SP_SEED_LO, SP_SEED_HI, SP_PENALTY, SP_WORDS = 8 };
 constexpr double FIX_ONE = 1099511627776.0;    // 2^40
 
 // ----------------------------------------------------------------- arg max
@@ -158,9 +162,12 @@ AGV_API int agv_take_tokens(int* tokens, const int* prev, const int* take, int B
 // occurrence, so no two threads touch one logit.
 __global__ void repeat_penalty_kernel(float* __restrict__ logits, long long row_stride, int V,
                                       const int* __restrict__ slots, const int* __restrict__ hist,
-                                      const int* __restrict__ hist_len, int cap, float penalty) {
+                                      const int* __restrict__ hist_len, int cap, float penalty,
+                                      const int* __restrict__ dev_params) {
     pdl_wait();
     pdl_launch_next();
+    if (dev_params) penalty = __int_as_float(dev_params[SP_PENALTY]);
+    if (penalty == 1.0f) return;
     const int b = blockIdx.y;
     const int slot = slots[b];
     if (slot < 0) return;
@@ -184,15 +191,17 @@ __global__ void repeat_penalty_kernel(float* __restrict__ logits, long long row_
 }
 
 // logits [B, V] in place; slots [B]; hist [n_slots, cap]; hist_len [n_slots].
+// dev_params (or null): the sampling words on the device (see agv_sample); the penalty
+// is then read from them when the kernel runs, not from the argument.
 AGV_API int agv_repeat_penalty(float* logits, long long row_stride, int B, int V, const int* slots,
                                const int* hist, const int* hist_len, int cap, float penalty,
-                               cudaStream_t stream) {
-    AGV_REQUIRE(penalty > 0.f, "repeat_penalty: penalty must be positive");
+                               const int* dev_params, cudaStream_t stream) {
+    AGV_REQUIRE(dev_params || penalty > 0.f, "repeat_penalty: penalty must be positive");
     AGV_REQUIRE(cap > 0, "repeat_penalty: bad history capacity");
     if (B == 0) return 0;
     dim3 grid((cap + 255) / 256, B);
     agv_launch(repeat_penalty_kernel, grid, 256, 0, stream, logits, row_stride, V, slots, hist, hist_len,
-                                                    cap, penalty);
+                                                    cap, penalty, dev_params);
     AGV_LAUNCH_OK("repeat_penalty_kernel");
     return 0;
 }
@@ -263,9 +272,16 @@ __global__ void __launch_bounds__(SM_THREADS)
 sample_kernel(const float* __restrict__ logits, long long row_stride, int V,
               int* __restrict__ out, float inv_temperature, int top_k, float top_p,
               unsigned long long seed, const long long* __restrict__ seq_ids,
-              const int* __restrict__ steps) {
+              const int* __restrict__ steps, const int* __restrict__ dev_params) {
     pdl_wait();
     pdl_launch_next();
+    if (dev_params) {
+        inv_temperature = __int_as_float(dev_params[SP_INV_TEMPERATURE]);
+        top_k = dev_params[SP_TOP_K];
+        top_p = __int_as_float(dev_params[SP_TOP_P]);
+        seed = (unsigned long long)(unsigned)dev_params[SP_SEED_LO] |
+               ((unsigned long long)(unsigned)dev_params[SP_SEED_HI] << 32);
+    }
     __shared__ SampleShared sh;
     const float* row = logits + (size_t)blockIdx.x * row_stride;
     auto xval = [&](int i) { return row[i] * inv_temperature; };
@@ -344,15 +360,20 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int V,
 
 // One token per row of logits [B, V].  temperature > 0; top_k 0 = off; top_p
 // outside (0, 1) = off.  seq_ids[b] and steps[b] key the draw of row b.
+// dev_params (or null): SP_WORDS ints on the device that replace temperature, top_k,
+// top_p and seed when the kernel runs (a recorded launch then serves every setting).
 AGV_API int agv_sample(const float* logits, long long row_stride, int B, int V, int* out,
                        float temperature, int top_k, float top_p, unsigned long long seed,
-                       const long long* seq_ids, const int* steps, cudaStream_t stream) {
+                       const long long* seq_ids, const int* steps, const int* dev_params,
+                       cudaStream_t stream) {
     AGV_REQUIRE(B >= 0 && V > 0 && row_stride >= V, "sample: bad sizes B=%d V=%d", B, V);
-    AGV_REQUIRE(temperature > 0.f, "sample: temperature must be positive (0 is arg max)");
+    AGV_REQUIRE(dev_params || temperature > 0.f,
+                "sample: temperature must be positive (0 is arg max)");
     AGV_REQUIRE(top_k >= 0, "sample: top_k must be >= 0");
     if (B == 0) return 0;
-    agv_launch(sample_kernel, B, SM_THREADS, 0, stream, logits, row_stride, V, out, 1.0f / temperature,
-                                                top_k, top_p, seed, seq_ids, steps);
+    agv_launch(sample_kernel, B, SM_THREADS, 0, stream, logits, row_stride, V, out,
+               dev_params ? 1.0f : 1.0f / temperature, top_k, top_p, seed, seq_ids, steps,
+               dev_params);
     AGV_LAUNCH_OK("sample_kernel");
     return 0;
 }

@@ -21,10 +21,11 @@ static __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t by
                  "r"(bytes)
                  : "memory");
 }
-// Bounded wait; false when the limit ran out.
-static __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+// Bounded wait; false when the limit (a number of polls) ran out.
+static __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
+                                                 unsigned limit = WAIT_LIMIT) {
     const uint32_t addr = smem_u32(bar);
-    for (unsigned i = 0; i < WAIT_LIMIT; ++i) {
+    for (unsigned i = 0; i < limit; ++i) {
         uint32_t done;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"

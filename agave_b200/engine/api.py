@@ -15,6 +15,7 @@ from __future__ import annotations
 import dataclasses
 import json
 import os
+import threading
 import time
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
@@ -28,7 +29,7 @@ from ..config import load_config, resolve_architecture
 from ..models.decoder import DecoderModel, decoder_param_specs
 from ..sampling import Sampler, SamplingParams
 from ..weights import head_is_stored, load_weights, random_tensors
-from .batch import DECODE, PREFILL, StepContext
+from .batch import DECODE, PREFILL, Cancelled, StepContext
 from .generate import GenerationPlan, RequestState
 from .step import Runner, StepError
 
@@ -47,21 +48,26 @@ def _bucket(n: int) -> int:
 
 
 class _DecodeGraph:
-    """One recorded decode step for a padded batch size and sampling setting."""
+    """One recorded decode step for a padded batch size and a kind of choice (arg
+    max or a draw, with or without the repeat penalty).  The sampling options
+    themselves (temperature, top_k, top_p, seed, penalty) are step inputs on the
+    device, so one recording serves every setting of its kind."""
 
     def __init__(self, engine: "Engine", size: int, params: SamplingParams, seed: int):
         self.size = size
         dev = engine.device
         B = size
         n_int = round_up(3 * B + 3 * B + 1 + B + 1, 2)  # step arrays, sampling steps, flag; even
+        total = n_int + 2 * B + kernels.SAMPLING_WORDS  # + sequence ids (64-bit) + sampling words
         # two pinned staging buffers: the next step's arrays are filled while the
         # copy of this step's may still be in flight
-        self.hosts = [torch.zeros(n_int + 2 * B, dtype=torch.int32, pin_memory=True)
-                      for _ in range(2)]
+        self.hosts = [torch.zeros(total, dtype=torch.int32, pin_memory=True) for _ in range(2)]
         self.hosts_np = [h.numpy() for h in self.hosts]
         self.host, self.host_np = self.hosts[0], self.hosts_np[0]
-        self.dev = torch.zeros(n_int + 2 * B, dtype=torch.int32, device=dev)
+        self.dev = torch.zeros(total, dtype=torch.int32, device=dev)
         d = self.dev
+        self.words_at = n_int + 2 * B
+        self.words = d[self.words_at:]
         o = 3 * B
         self.views = dict(tokens=d[:B], positions=d[B:2 * B], seq_index=d[2 * B:3 * B],
                           cu=d[o:o + B + 1], slots=d[o + B + 1:o + 2 * B + 1],
@@ -69,7 +75,7 @@ class _DecodeGraph:
                           steps=d[o + 3 * B + 1:o + 4 * B + 1],
                           take=d[o + 4 * B + 1:o + 4 * B + 2])
         self.flag_at = o + 4 * B + 1
-        self.seq_ids = d[n_int:].view(torch.int64)
+        self.seq_ids = d[n_int:n_int + 2 * B].view(torch.int64)
         self.n_int = n_int
         self.rows = torch.arange(B, dtype=torch.int32, device=dev)
         self.next_dev = torch.zeros(B, dtype=torch.int32, device=dev)
@@ -82,7 +88,8 @@ class _DecodeGraph:
         self.kernels_per_step = 0
         self._record(engine, params, seed)
 
-    def _body(self, engine: "Engine", params: SamplingParams, seed: int) -> None:
+    def _body(self, engine: "Engine", params: SamplingParams, seed: int,
+              lens_host=None) -> None:
         v = self.views
         runner = engine.runner
         # a step launched ahead takes its token ids from the choices of the step before
@@ -91,12 +98,12 @@ class _DecodeGraph:
                           positions=v["positions"], seq_index=v["seq_index"],
                           cu_seqlens=v["cu"], slots=v["slots"], lens=v["lens"],
                           max_len=runner.cache.max_seq_len, max_new=1, cache=runner.cache,
-                          dtype=runner.dtype, device=runner.device)
+                          dtype=runner.dtype, device=runner.device, lens_host=lens_host)
         h = runner.model.hidden_states(ctx)
         self.logits = runner.model.logits(h, self.rows, ctx)
         engine.sampler.note_inputs(v["tokens"], v["slots"])
         engine.sampler.choose(self.logits, self.next_dev, params, seed, v["slots"], self.seq_ids,
-                              v["steps"], penalise=True)
+                              v["steps"], penalise=True, dev_params=self.words)
 
     def _record(self, engine: "Engine", params: SamplingParams, seed: int) -> None:
         if not engine.use_graphs:
@@ -124,7 +131,13 @@ class _DecodeGraph:
         """Copy staging buffer ``which`` in, run the step, start the copy of the
         chosen tokens out; returns without waiting."""
         self.dev.copy_(self.hosts[which], non_blocking=True)
-        if self.graph is not None:
+        if kernels._perf is not None:
+            # per-operation timing: the step runs launch by launch, lengths known to the host
+            B = self.size
+            lens = self.hosts_np[which][5 * B + 1:6 * B + 1].copy()
+            kernels._perf.n_tokens += int((lens > 0).sum())
+            self._body(engine, params, seed, lens_host=lens)
+        elif self.graph is not None:
             self.graph.replay()
         else:
             self._body(engine, params, seed)
@@ -198,6 +211,8 @@ class Engine:
         self.use_graphs = use_graphs
         self._graphs: Dict[Tuple, _DecodeGraph] = {}
         self.stats: Dict[str, float] = {}
+        self._cancel = threading.Event()
+        self.runner.cancel_flag = self._cancel
 
     @classmethod
     def from_config(cls, raw_config: dict, seed: int = 0, std: float = 0.02,
@@ -222,8 +237,21 @@ class Engine:
 
     def step(self, entries: Sequence[Tuple[int, Sequence[int]]],
              want: Sequence[Sequence[int]]) -> torch.Tensor:
-        """See ``Runner.step``."""
-        return self.runner.step(entries, want)
+        """See ``Runner.step``.  Raises ``Cancelled`` (and runs nothing further) when
+        ``cancel()`` was called; the flag is cleared by that."""
+        try:
+            return self.runner.step(entries, want)
+        except Cancelled:
+            self._cancel.clear()
+            raise
+
+    def cancel(self) -> None:
+        """Stop the running ``generate`` or ``step`` at its next check, from any thread
+        (src/models/model.zig:443-446).  A step that runs launch by launch stops between
+        two blocks (src/models/gemma3.zig:342,435); a recorded step runs to its end, and
+        the generation loop stops before the next one.  ``generate`` then returns what
+        was generated so far, with the finish reason "cancelled" for what it cut."""
+        self._cancel.set()
 
     # ------------------------------------------------------------- generate
     def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: int = 512,
@@ -243,12 +271,20 @@ class Engine:
                               self.max_seq_len)
         stats = dict(prefill_tokens=0, prefill_seconds=0.0, decode_tokens=0, decode_seconds=0.0,
                      decode_steps=0, batches=0)
-        while True:
-            batch = plan.next_batch()
-            if not batch:
-                break
-            stats["batches"] += 1
-            self._run_batch(plan, batch, params, seed_v, stats)
+        try:
+            while True:
+                batch = plan.next_batch()
+                if not batch:
+                    break
+                stats["batches"] += 1
+                try:
+                    self._run_batch(plan, batch, params, seed_v, stats)
+                except Cancelled:
+                    plan.cancel()
+                if self._cancel.is_set():
+                    plan.cancel()
+        finally:
+            self._cancel.clear()
         self.stats = stats
         self.finish_reasons = [r.finish_reason for r in plan.requests]
         return plan.outputs()
@@ -288,8 +324,8 @@ class Engine:
                     r.slot = -1
 
     def _graph_for(self, size: int, params: SamplingParams, seed: int) -> _DecodeGraph:
-        key = (size, params.temperature, params.top_k, params.top_p, params.repeat_penalty,
-               0 if params.greedy else seed)
+        # what is fixed in a recording: the padded batch and which kernels choose the token
+        key = (size, params.greedy, params.repeat_penalty != 1.0)
         g = self._graphs.get(key)
         if g is None:
             if len(self._graphs) >= 64:
@@ -320,9 +356,11 @@ class Engine:
         a[o + 2 * B + 1:o + 2 * B + 1 + n] = lens + 1
         a[o + 3 * B + 1:o + 3 * B + 1 + n] = np.fromiter((len(r.output) + ahead for r in live),
                                                         dtype=np.int32, count=n)
-        ids = a[g.n_int:].view(np.int64)
+        ids = a[g.n_int:g.words_at].view(np.int64)
         ids[:] = 0
         ids[:n] = np.fromiter((r.index for r in live), dtype=np.int64, count=n)
+        a[g.words_at:] = kernels.sampling_words(params.temperature, params.top_k, params.top_p,
+                                                seed, params.repeat_penalty)
         return g
 
     def _decode_loop(self, plan: GenerationPlan, params: SamplingParams, seed: int,
@@ -343,6 +381,12 @@ class Engine:
         inflight = None                    # (graph, staging buffer, requests) launched, not read
         held: List[RequestState] = []      # ended, but a step in flight still uses their slots
         while live or inflight is not None:
+            if self._cancel.is_set() and inflight is None:
+                # between two steps, nothing in flight: the live sequences end here
+                for r in plan.cancel():
+                    self.release(r.slot)
+                    r.slot = -1
+                return
             if inflight is None:
                 n = len(live)
                 g = self._stage_step(live, params, seed, 0, which)
@@ -355,7 +399,8 @@ class Engine:
             g, w, reqs = inflight
             # the step after it, for the same sequences
             ahead = None
-            if all(not r.done and len(r.output) + 1 < r.max_new for r in reqs):
+            if (not self._cancel.is_set() and
+                    all(not r.done and len(r.output) + 1 < r.max_new for r in reqs)):
                 try:
                     g2 = self._stage_step(reqs, params, seed, 1, 1 - w)
                     g2.hosts_np[1 - w][g2.flag_at] = 1

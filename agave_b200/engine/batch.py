@@ -17,6 +17,11 @@ import torch
 PREFILL, DECODE = "prefill", "decode"
 
 
+class Cancelled(RuntimeError):
+    """A step was stopped between two blocks because its cancel flag was set
+    (the reference checks its flag at the same place, src/models/gemma3.zig:342,435)."""
+
+
 @dataclass
 class StepContext:
     mode: str                     # PREFILL or DECODE
@@ -34,6 +39,8 @@ class StepContext:
     dtype: torch.dtype
     device: torch.device
     # per-step scratch shared between layers
+    cancel: object = None         # a threading.Event (or None): set = stop between blocks
+    lens_host: object = None      # the lengths on the host, when per-operation timing wants them
     rope_tables: Dict[Tuple, Tuple[torch.Tensor, torch.Tensor]] = field(default_factory=dict)
     step_kv: Dict[int, Tuple] = field(default_factory=dict)
 

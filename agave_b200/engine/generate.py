@@ -19,7 +19,7 @@ from typing import Dict, List, Optional, Sequence
 
 from ..cache.book import PAGE, round_up
 
-STOP, LENGTH, CONTEXT = "stop", "length", "context"
+STOP, LENGTH, CONTEXT, CANCELLED = "stop", "length", "context", "cancelled"
 
 
 @dataclass
@@ -118,6 +118,16 @@ class GenerationPlan:
                     r.finish_reason = CONTEXT if r.clamped else LENGTH
             if r.done:
                 ended.append(r)
+        return ended
+
+    def cancel(self) -> List[RequestState]:
+        """End every request that has not finished (the running batch and those not
+        yet started) with the reason "cancelled"; returns the live ones of the batch."""
+        ended = self.live()
+        for r in self.requests:
+            if not r.done:
+                r.finish_reason = CANCELLED
+        self._next = len(self.requests)
         return ended
 
     @property

@@ -19,8 +19,9 @@ from typing import List, Optional, Sequence, Tuple
 import numpy as np
 import torch
 
+from .. import kernels
 from ..cache import Cache, CacheError
-from .batch import DECODE, PREFILL, StepContext
+from .batch import DECODE, PREFILL, Cancelled, StepContext
 
 
 class StepError(ValueError):
@@ -53,6 +54,7 @@ class Runner:
         self.device, self.dtype = model.device, model.dtype
         self.cache = Cache(model.cache_requests(), max_tokens, max_seq_len, n_slots,
                            model.dtype, model.device)
+        self.cancel_flag = None        # a threading.Event an eager step checks between blocks
         self.vocab_size = model.spec.vocab_size
 
     # ------------------------------------------------------------- contexts
@@ -91,9 +93,17 @@ class Runner:
         else:
             raise StepError("the sequences of a step must either all start at position 0 or "
                             "all go on by exactly one token")
-        for s, st, c in zip(slots.tolist(), starts.tolist(), counts.tolist()):
-            if s >= 0:
-                self.cache.reserve(s, st + c)
+        reserved = []
+        try:
+            for s, st, c in zip(slots.tolist(), starts.tolist(), counts.tolist()):
+                if s >= 0:
+                    self.cache.reserve(s, st + c)
+                    reserved.append(s)
+        except CacheError:
+            # the step does not run: what its earlier sequences reserved goes back
+            for s in reserved:
+                self.cache.trim(s)
+            raise
         self.cache.flush()
         T = int(counts.sum())
         cu = np.zeros(B + 1, dtype=np.int64)
@@ -180,8 +190,9 @@ class Runner:
         T, B = plan["T"], plan["B"]
         key = (T, B, plan["max_len"], len(rows))
         graph = None
-        if (self.use_graphs and plan["mode"] == PREFILL and 0 < len(rows) <= PROMPT_GRAPH_ROWS
-                and T <= PROMPT_GRAPH_TOKENS):
+        timed = kernels._perf is not None      # operations are timed launch by launch
+        if (self.use_graphs and not timed and plan["mode"] == PREFILL
+                and 0 < len(rows) <= PROMPT_GRAPH_ROWS and T <= PROMPT_GRAPH_TOKENS):
             graph = self._prompt_graphs.get(key)
             if graph is None and self._prompt_seen.get(key, 0) >= 1:
                 try:
@@ -206,7 +217,18 @@ class Runner:
         host = torch.empty(self._packed_size(T, B, len(rows)), dtype=torch.int32, pin_memory=True)
         self._fill(plan, rows, host)
         ctx, rows_dev = self._context_on(plan, host.to(self.device, non_blocking=True))
-        h = self.model.hidden_states(ctx)
+        ctx.cancel = self.cancel_flag
+        if timed:
+            ctx.lens_host = plan["lens"]
+            kernels._perf.n_tokens += T
+        try:
+            h = self.model.hidden_states(ctx)
+        except Cancelled:
+            # nothing is committed: lengths stay, the room reserved for the step goes back
+            for s, _ in entries:
+                if s >= 0:
+                    self.cache.trim(s)
+            raise
         self.commit(entries)
         if not rows:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)

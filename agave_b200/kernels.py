@@ -14,6 +14,7 @@ from typing import Optional
 
 import torch
 
+from . import perf as _perf_mod
 from .csrc import build as _build
 
 F32, BF16 = 0, 1
@@ -70,6 +71,19 @@ def _ptr(t: Optional[torch.Tensor]):
 
 
 _launches = 0
+_perf = None          # an active agave_b200.perf.PerfCounters, or None
+
+
+def _span(op: str, nbytes: int = 0, flops: int = 0):
+    """A timing span around one launch while operations are being timed."""
+    if _perf is None:
+        return _perf_mod.NULL_SPAN
+    return _perf.span(op, nbytes, flops)
+
+
+def _nbytes(*tensors) -> int:
+    return sum(t.numel() * t.element_size() for t in tensors if t is not None)
+
 
 
 _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
@@ -118,8 +132,9 @@ def embed(tokens: torch.Tensor, table: torch.Tensor, scale: float, out: torch.Te
     _i32(tokens, "tokens"); _f32(out, "out"); _dense(table, "table"); _dense(out, "out")
     T, (V, H) = tokens.numel(), table.shape
     assert out.shape == (T, H)
-    _check(library().agv_embed(_ptr(tokens), _ptr(table), dtype_code(table.dtype), _ptr(out),
-                               T, H, V, ctypes.c_float(scale), _stream()))
+    with _span("embed", T * H * table.element_size() + _nbytes(out)):
+        _check(library().agv_embed(_ptr(tokens), _ptr(table), dtype_code(table.dtype), _ptr(out),
+                                   T, H, V, ctypes.c_float(scale), _stream()))
 
 
 def rope_table(positions: torch.Tensor, rotary_dim: int, theta: float, factor: float,
@@ -128,8 +143,9 @@ def rope_table(positions: torch.Tensor, rotary_dim: int, theta: float, factor: f
     _i32(positions, "positions"); _f32(cos, "cos"); _f32(sin, "sin")
     T = positions.numel()
     assert cos.shape == (T, rotary_dim // 2) and sin.shape == cos.shape
-    _check(library().agv_rope_table(_ptr(positions), _ptr(cos), _ptr(sin), T, rotary_dim,
-                                    ctypes.c_double(theta), ctypes.c_double(factor), _stream()))
+    with _span("rope_table", _nbytes(cos, sin)):
+        _check(library().agv_rope_table(_ptr(positions), _ptr(cos), _ptr(sin), T, rotary_dim,
+                                        ctypes.c_double(theta), ctypes.c_double(factor), _stream()))
 
 
 # ---------------------------------------------------------------------- norms
@@ -166,15 +182,27 @@ def norm_residual(h: Optional[torch.Tensor], y: Optional[torch.Tensor],
         _dense(x, "x")
         x_code = dtype_code(x.dtype)
         assert x.shape == (R, H), (x.shape, R, H)
-    _check(library().agv_norm_residual(
-        _ptr(h), _ptr(y), y_code, n_splits, ctypes.c_longlong(split_stride), _ptr(w_post),
-        _ptr(w_next), _ptr(x), x_code, _ptr(rows), R, H, ctypes.c_float(eps_post),
-        ctypes.c_float(eps_next), 1 if (add_residual and y is not None) else 0, _stream()))
+    with _span("norm", _nbytes(y, x) + (R * H * 4 * (2 if y is not None and add_residual else 1)
+                                         if h is not None else 0)):
+        _check(library().agv_norm_residual(
+            _ptr(h), _ptr(y), y_code, n_splits, ctypes.c_longlong(split_stride), _ptr(w_post),
+            _ptr(w_next), _ptr(x), x_code, _ptr(rows), R, H, ctypes.c_float(eps_post),
+            ctypes.c_float(eps_next), 1 if (add_residual and y is not None) else 0, _stream()))
 
 
 # ------------------------------------------------------------ matrix products
+def _linear_cost(x, w, w2, out):
+    """(bytes, flops) of a projection: weights and operands once, 2 T N K flops."""
+    T, K = x.shape
+    N = w.shape[0]
+    n = 2 if w2 is not None else 1
+    return (n * N * K * w.element_size() + T * K * x.element_size() + _nbytes(out),
+            2 * n * T * N * K)
+
+
 def linear_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
-                w2: Optional[torch.Tensor] = None, activation: str = "gelu_tanh") -> None:
+                w2: Optional[torch.Tensor] = None, activation: str = "gelu_tanh",
+                op: str = "linear") -> None:
     """out = x w^T, or act(x w^T) * (x w2^T); FFMA kernel (the 32-bit path)."""
     M, K = x.shape
     N = w.shape[0]
@@ -186,10 +214,11 @@ def linear_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
         assert w2.shape == w.shape and w2.dtype == w.dtype
     if x.dtype != w.dtype:
         raise KernelError(f"linear: input {x.dtype} and weight {w.dtype} differ")
-    _check(library().agv_linear_simt(
-        _ptr(x), _ptr(w), _ptr(w2), _ptr(out), M, N, K, ctypes.c_longlong(x.stride(0)),
-        ctypes.c_longlong(out.stride(0)), dtype_code(x.dtype), dtype_code(out.dtype),
-        ACT[activation], _stream()))
+    with _span(op, *_linear_cost(x, w, w2, out)):
+        _check(library().agv_linear_simt(
+            _ptr(x), _ptr(w), _ptr(w2), _ptr(out), M, N, K, ctypes.c_longlong(x.stride(0)),
+            ctypes.c_longlong(out.stride(0)), dtype_code(x.dtype), dtype_code(out.dtype),
+            ACT[activation], _stream()))
 
 
 # ------------------------------------------------------------------ attention
@@ -231,13 +260,14 @@ def qk_norm_rope_store(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_di
         _dense(vt, "vt"); _i32(cu_seqlens, "cu_seqlens")
         assert vt.dtype == torch.bfloat16 and vt.shape[0] == n_kv_heads * head_dim
         n_seq = cu_seqlens.numel() - 1
-    _check(library().agv_qk_norm_rope_store(
-        _ptr(qkv), dtype_code(qkv.dtype), ctypes.c_longlong(qkv.stride(0)), _ptr(partial),
-        n_splits, T, n_heads, n_kv_heads, head_dim, _ptr(wq), _ptr(wk), ctypes.c_float(eps), _ptr(cos), _ptr(sin),
-        rotary_dim, _ptr(positions), _ptr(k_pool), _ptr(v_pool), _ptr(page_table), _ptr(slots),
-        _ptr(lens), _ptr(seq_index), max_pages, page, cap, _ptr(vt),
-        ctypes.c_longlong(vt.shape[1] if vt is not None else 0), _ptr(cu_seqlens), n_seq, max_len,
-        _stream()))
+    with _span("qk_norm_rope", 2 * _nbytes(qkv) + _nbytes(partial, vt)):
+        _check(library().agv_qk_norm_rope_store(
+            _ptr(qkv), dtype_code(qkv.dtype), ctypes.c_longlong(qkv.stride(0)), _ptr(partial),
+            n_splits, T, n_heads, n_kv_heads, head_dim, _ptr(wq), _ptr(wk), ctypes.c_float(eps),
+            _ptr(cos), _ptr(sin), rotary_dim, _ptr(positions), _ptr(k_pool), _ptr(v_pool),
+            _ptr(page_table), _ptr(slots), _ptr(lens), _ptr(seq_index), max_pages, page, cap,
+            _ptr(vt), ctypes.c_longlong(vt.shape[1] if vt is not None else 0), _ptr(cu_seqlens),
+            n_seq, max_len, _stream()))
 
 
 def attention_prefill_simt(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor,
@@ -282,8 +312,9 @@ def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
     _f32(logits, "logits"); _i32(out, "out")
     B, V = logits.shape
     assert logits.stride(1) == 1
-    _check(library().agv_argmax(_ptr(logits), ctypes.c_longlong(logits.stride(0)), B, V,
-                                _ptr(out), _stream()))
+    with _span("argmax", B * V * 4):
+        _check(library().agv_argmax(_ptr(logits), ctypes.c_longlong(logits.stride(0)), B, V,
+                                    _ptr(out), _stream()))
 
 
 def history_append(tokens: torch.Tensor, slots: torch.Tensor, hist: torch.Tensor,
@@ -306,35 +337,62 @@ def take_tokens(tokens: torch.Tensor, prev: torch.Tensor, take: torch.Tensor,
                                      vocab_size, _stream()))
 
 
+SAMPLING_WORDS = 8
+
+
+def sampling_words(temperature: float, top_k: int, top_p: float, seed: int,
+                   penalty: float):
+    """The sampling options as the int32 words the kernels read from the device
+    (``dev_params``): [1 / temperature, top_k, top_p, seed low, seed high, penalty]."""
+    import numpy as np
+    w = np.zeros(SAMPLING_WORDS, dtype=np.int32)
+    f = w.view(np.float32)
+    f[0] = 1.0 / temperature if temperature > 0 else 1.0
+    w[1] = int(top_k)
+    f[2] = top_p
+    w[3:5] = np.array([seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF], dtype=np.uint32).view(np.int32)
+    f[5] = penalty
+    return w
+
+
 def repeat_penalty(logits: torch.Tensor, slots: torch.Tensor, hist: torch.Tensor,
-                   hist_len: torch.Tensor, penalty: float) -> None:
-    """Penalise, in place, every id in each row's slot history, once per occurrence."""
-    _f32(logits, "logits")
+                   hist_len: torch.Tensor, penalty: float,
+                   dev_params: Optional[torch.Tensor] = None) -> None:
+    """Penalise, in place, every id in each row's slot history, once per occurrence.
+    ``dev_params`` (``sampling_words`` on the device) replaces ``penalty`` at run time."""
+    _f32(logits, "logits"); _i32(dev_params, "dev_params")
     for t, n in ((slots, "slots"), (hist, "hist"), (hist_len, "hist_len")):
         _i32(t, n)
     B, V = logits.shape
     _dense(hist, "hist")
     _check(library().agv_repeat_penalty(_ptr(logits), ctypes.c_longlong(logits.stride(0)), B, V,
                                         _ptr(slots), _ptr(hist), _ptr(hist_len), hist.shape[1],
-                                        ctypes.c_float(penalty), _stream()))
+                                        ctypes.c_float(penalty), _ptr(dev_params), _stream()))
 
 
 def sample(logits: torch.Tensor, out: torch.Tensor, temperature: float, top_k: int, top_p: float,
-           seed: int, seq_ids: torch.Tensor, steps: torch.Tensor) -> None:
-    _f32(logits, "logits"); _i32(out, "out"); _i32(steps, "steps")
+           seed: int, seq_ids: torch.Tensor, steps: torch.Tensor,
+           dev_params: Optional[torch.Tensor] = None) -> None:
+    """out[b] drawn from logits[b]; ``dev_params`` (``sampling_words`` on the device)
+    replaces temperature, top_k, top_p and seed at run time."""
+    _f32(logits, "logits"); _i32(out, "out"); _i32(steps, "steps"); _i32(dev_params, "dev_params")
+    if dev_params is not None:
+        assert dev_params.numel() >= SAMPLING_WORDS
     if seq_ids.dtype != torch.int64:
         raise KernelError("seq_ids must be int64")
     B, V = logits.shape
     assert logits.stride(1) == 1
-    _check(library().agv_sample(_ptr(logits), ctypes.c_longlong(logits.stride(0)), B, V,
-                                _ptr(out), ctypes.c_float(temperature), int(top_k),
-                                ctypes.c_float(top_p), ctypes.c_ulonglong(seed & (2**64 - 1)),
-                                _ptr(seq_ids), _ptr(steps), _stream()))
+    with _span("sample", B * V * 4):
+        _check(library().agv_sample(_ptr(logits), ctypes.c_longlong(logits.stride(0)), B, V,
+                                    _ptr(out), ctypes.c_float(temperature), int(top_k),
+                                    ctypes.c_float(top_p), ctypes.c_ulonglong(seed & (2**64 - 1)),
+                                    _ptr(seq_ids), _ptr(steps), _ptr(dev_params), _stream()))
 
 
 def linear_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
               w2: Optional[torch.Tensor] = None, activation: str = "gelu_tanh",
-              splits: int = 1, token_tile: int = 0, cluster: int = 0) -> None:
+              splits: int = 1, token_tile: int = 0, cluster: int = 0,
+              op: str = "linear") -> None:
     """bfloat16 product on the tensor cores (tcgen05 + TMA).
 
     out [T, N] in bfloat16 or 32-bit.  With splits > 1, K is cut into ranges that
@@ -359,10 +417,11 @@ def linear_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
     else:
         assert out.shape == (T, N) and out.stride(1) == 1
         ldc = out.stride(0)
-    _check(library().agv_linear_tc(
-        _ptr(x), _ptr(w), _ptr(w2), _ptr(out), T, N, K, ctypes.c_longlong(x.stride(0)),
-        ctypes.c_longlong(ldc), dtype_code(out.dtype), ACT[activation], splits, cluster,
-        token_tile, _stream()))
+    with _span(op, *_linear_cost(x, w, w2, out)):
+        _check(library().agv_linear_tc(
+            _ptr(x), _ptr(w), _ptr(w2), _ptr(out), T, N, K, ctypes.c_longlong(x.stride(0)),
+            ctypes.c_longlong(ldc), dtype_code(out.dtype), ACT[activation], splits, cluster,
+            token_tile, _stream()))
 
 
 def linear_tc_splits(K: int, splits: int) -> int:
@@ -382,14 +441,39 @@ def linear_tc_status() -> int:
     return library().agv_linear_tc_status()
 
 
+def selftest_bounded_wait(limit: int = 2000, ctas: int = 4):
+    """Runs the unit kernel whose mbarrier waits all run out after ``limit`` polls;
+    returns (status code, clock cycles the first wait took).  The kernel follows the
+    tensor-core kernels' give-up protocol: record a code, stop, free tensor memory,
+    return."""
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    cycles = torch.zeros(1, dtype=torch.int32, device="cuda")
+    _check(library().agv_selftest_bounded_wait(ctypes.c_uint(limit), ctas, _ptr(status),
+                                               _ptr(cycles), _stream()))
+    torch.cuda.synchronize()
+    return int(status.item()), int(cycles.item()) & 0xFFFFFFFF
+
+
 # ------------------------------------------------------------------ dispatch
-N_SMS = 148
+_n_sms = None
+
+
+def n_sms() -> int:
+    """Streaming multiprocessors of the current device (read once)."""
+    global _n_sms
+    if _n_sms is None:
+        _n_sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+    return _n_sms
+
 _PREFILL_TC = os.environ.get("AGAVE_B200_PREFILL_ATTENTION", "tcgen05") != "mma"
 
 def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
-           w2: Optional[torch.Tensor] = None, activation: str = "gelu_tanh") -> None:
-    """out = x w^T (or the gated pair).  The kernel is chosen from the dtype and
-    the weight's shape only, never from the number of rows of x."""
+           w2: Optional[torch.Tensor] = None, activation: str = "gelu_tanh",
+           op: str = "linear") -> None:
+    """out = x w^T (or the gated pair).  Which kernel runs follows from the dtype and the
+    weight's shape; how K is cut into ranges (and with it the order of the 32-bit sums)
+    also follows from the number of rows of x, so a token's result is the same in any
+    company up to that summation order."""
     if linear_tc_supported(x, w) and (w2 is None or out.dtype == torch.bfloat16):
         c = 0
         if w2 is not None and x.shape[0] <= 64:
@@ -397,10 +481,11 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
             # CTAs per tile, each on a range of K, joined by a cluster
             tiles = (w.shape[0] + 63) // 64
             kb = (w.shape[1] + 63) // 64
-            c = 4 if tiles * 4 <= N_SMS and kb >= 8 else 2 if tiles * 2 <= 2 * N_SMS and kb >= 4 else 0
-        linear_tc(x, w, out, w2, activation, splits=max(c, 1), cluster=c)
+            sms = n_sms()
+            c = 4 if tiles * 4 <= sms and kb >= 8 else 2 if tiles * 2 <= 2 * sms and kb >= 4 else 0
+        linear_tc(x, w, out, w2, activation, splits=max(c, 1), cluster=c, op=op)
     else:
-        linear_simt(x, w, out, w2, activation)
+        linear_simt(x, w, out, w2, activation, op=op)
 
 
 def plan_splits(T: int, N: int, K: int, cheap_sum: bool = False):
@@ -415,13 +500,13 @@ def plan_splits(T: int, N: int, K: int, cheap_sum: bool = False):
         # sums left to the consumer (a cluster's exchange is slow for wide tiles)
         tile = 128 if T <= 128 else 256
         ctas = ((N + 127) // 128) * ((T + tile - 1) // tile)
-        if ctas <= N_SMS // 2 + 6 and (K + 63) // 64 >= 32:
+        if ctas <= n_sms() // 2 + 6 and (K + 63) // 64 >= 32:
             return 2, 0
         return 1, 0
     tile = 16 if T <= 16 else 32 if T <= 32 else 64
     ctas = ((N + 127) // 128) * ((T + tile - 1) // tile)
     kb = (K + 63) // 64
-    want = min(kb, (N_SMS + ctas - 1) // ctas)
+    want = min(kb, (n_sms() + ctas - 1) // ctas)
     if ctas >= 100 or want < 2:
         return 1, 0
     if T > 16:
@@ -438,7 +523,8 @@ def plan_splits(T: int, N: int, K: int, cheap_sum: bool = False):
     return linear_tc_splits(K, min(want, 16)), 0
 
 
-def linear_partial(x: torch.Tensor, w: torch.Tensor, cheap_sum: bool = False) -> torch.Tensor:
+def linear_partial(x: torch.Tensor, w: torch.Tensor, cheap_sum: bool = False,
+                   op: str = "linear") -> torch.Tensor:
     """x w^T in 32-bit for a consumer that adds over a leading axis: [G, T, N] on
     the tensor-core path (G >= 1 groups of ranges of K; the ranges of a group
     are added inside the kernel by a cluster), else [T, N] in x's dtype.
@@ -449,10 +535,10 @@ def linear_partial(x: torch.Tensor, w: torch.Tensor, cheap_sum: bool = False) ->
         groups, csize = plan_splits(T, N, K, cheap_sum)
         out = torch.empty((groups, T, N), dtype=torch.float32, device=x.device)
         linear_tc(x, w, out if groups > 1 else out[0], splits=groups * max(csize, 1),
-                  cluster=csize)
+                  cluster=csize, op=op)
         return out
     out = torch.empty((T, N), dtype=x.dtype, device=x.device)
-    linear_simt(x, w, out)
+    linear_simt(x, w, out, op=op)
     return out
 
 
@@ -536,15 +622,43 @@ def attention_prefill(q, k, v, out, ctx, n_heads, n_kv_heads, head_dim, scale, w
     aligned = (q.dtype == torch.bfloat16 and head_dim <= 256 and
                q.stride(0) % 8 == 0 and k.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and
                k.data_ptr() % 16 == 0 and v.data_ptr() % 16 == 0)
-    if aligned and head_dim % 16 == 0 and _PREFILL_TC:
-        attention_prefill_tc(q, k, v, out, ctx.cu_seqlens, ctx.max_new, n_heads, n_kv_heads,
-                             head_dim, scale, window, vt=vt)
-    elif aligned and head_dim % 8 == 0:
-        attention_prefill_mma(q, k, v, out, ctx.cu_seqlens, ctx.max_new, n_heads, n_kv_heads,
-                              head_dim, scale, window)
-    else:
-        attention_prefill_simt(q, k, v, out, ctx.positions, ctx.seq_index, ctx.cu_seqlens,
-                               n_heads, n_kv_heads, head_dim, scale, window)
+    with _span("attention", *_attention_cost(ctx, q, k, v, out, n_heads, head_dim, window)):
+        if aligned and head_dim % 16 == 0 and _PREFILL_TC:
+            attention_prefill_tc(q, k, v, out, ctx.cu_seqlens, ctx.max_new, n_heads, n_kv_heads,
+                                 head_dim, scale, window, vt=vt)
+        elif aligned and head_dim % 8 == 0:
+            attention_prefill_mma(q, k, v, out, ctx.cu_seqlens, ctx.max_new, n_heads,
+                                  n_kv_heads, head_dim, scale, window)
+        else:
+            attention_prefill_simt(q, k, v, out, ctx.positions, ctx.seq_index, ctx.cu_seqlens,
+                                   n_heads, n_kv_heads, head_dim, scale, window)
+
+
+def _attention_cost(ctx, q, k, v, out, n_heads, head_dim, window, n_kv_heads=0):
+    """(bytes, flops) of one layer's attention, from the lengths the host knows
+    (``ctx.lens_host``; zeros when a step does not carry them)."""
+    if _perf is None:
+        return 0, 0
+    lens = getattr(ctx, "lens_host", None)
+    if lens is None:
+        return _nbytes(q, k, v, out), 0
+    seen = 0                      # (query, key) pairs
+    kv_rows = 0                   # cache rows a decode step reads
+    for n in lens:
+        n = int(n)
+        if n <= 0:
+            continue
+        if ctx.mode == "decode":
+            vis = min(n, window) if window else n
+            seen += vis
+            kv_rows += vis
+        elif window and n > window:
+            seen += window * (window + 1) // 2 + (n - window) * window
+        else:
+            seen += n * (n + 1) // 2
+    esz = out.element_size()
+    nbytes = _nbytes(q, k, v, out) + 2 * kv_rows * n_kv_heads * head_dim * esz
+    return nbytes, 4 * n_heads * head_dim * seen
 
 
 def attention_decode_plan(head_dim: int, dtype: torch.dtype, max_keys: int):
@@ -629,27 +743,35 @@ def attention_decode_fused(partial: torch.Tensor, wq: Optional[torch.Tensor],
         assert cos.shape == (B, head_dim // 2) and sin.shape == cos.shape
     max_keys = max(1, min(window, ctx.max_len) if window else ctx.max_len)
     _, n_splits = attention_decode_plan(head_dim, torch.bfloat16, max_keys)
+    # the tensor-core form leaves at most one partial result per cluster, and at most 16
+    # clusters share a sequence, however long the context may get
+    n_splits = min(n_splits, 16)
     part_acc = torch.empty((B, n_heads, n_splits, head_dim), dtype=torch.float32,
                            device=out.device)
     part_ml = torch.empty((B, n_heads, n_splits, 2), dtype=torch.float32, device=out.device)
     counters = _decode_counters(out.device, B * n_heads)
-    _check(library().agv_attention_decode_fused(
-        _ptr(partial), G, _ptr(wq), _ptr(wk), ctypes.c_float(eps), _ptr(cos), _ptr(sin),
-        1 if store_kv else 0, _ptr(out), _ptr(view.k_pool), _ptr(view.v_pool),
-        _ptr(view.page_table), _ptr(ctx.slots), _ptr(ctx.positions), view.page_table.shape[1],
-        view.page, view.cap, B, n_heads, n_kv_heads, head_dim, ctypes.c_float(scale), window,
-        max_keys, _ptr(part_acc), _ptr(part_ml), _ptr(counters), _stream()))
+    with _span("attention", *_attention_cost(ctx, partial, None, None, out, n_heads, head_dim,
+                                             window, n_kv_heads)):
+        _check(library().agv_attention_decode_fused(
+            _ptr(partial), G, _ptr(wq), _ptr(wk), ctypes.c_float(eps), _ptr(cos), _ptr(sin),
+            1 if store_kv else 0, _ptr(out), _ptr(view.k_pool), _ptr(view.v_pool),
+            _ptr(view.page_table), _ptr(ctx.slots), _ptr(ctx.positions),
+            view.page_table.shape[1], view.page, view.cap, B, n_heads, n_kv_heads, head_dim,
+            ctypes.c_float(scale), window, max_keys, _ptr(part_acc), _ptr(part_ml),
+            _ptr(counters), _stream()))
 
 
 def attention_decode(q, out, view, ctx, n_heads, n_kv_heads, head_dim, scale, window) -> None:
     """Decode attention of one layer: the split kernel for head sizes in steps of
     16 up to 512, else the one-warp-per-head kernel."""
-    if head_dim % 16 == 0 and head_dim <= 512:
-        max_keys = min(window, ctx.max_len) if window else ctx.max_len
-        attention_decode_split(q, out, view.k_pool, view.v_pool, view.page_table, ctx.slots,
-                               ctx.positions, view.page, view.cap, n_heads, n_kv_heads, head_dim,
-                               scale, window, max(1, max_keys))
-    else:
-        attention_paged_simt(q, out, view.k_pool, view.v_pool, view.page_table, ctx.slots,
-                             ctx.positions, ctx.seq_index, view.page, view.cap, n_heads,
-                             n_kv_heads, head_dim, scale, window)
+    with _span("attention", *_attention_cost(ctx, q, None, None, out, n_heads, head_dim, window,
+                                             n_kv_heads)):
+        if head_dim % 16 == 0 and head_dim <= 512:
+            max_keys = min(window, ctx.max_len) if window else ctx.max_len
+            attention_decode_split(q, out, view.k_pool, view.v_pool, view.page_table, ctx.slots,
+                                   ctx.positions, view.page, view.cap, n_heads, n_kv_heads,
+                                   head_dim, scale, window, max(1, max_keys))
+        else:
+            attention_paged_simt(q, out, view.k_pool, view.v_pool, view.page_table, ctx.slots,
+                                 ctx.positions, ctx.seq_index, view.page, view.cap, n_heads,
+                                 n_kv_heads, head_dim, scale, window)

@@ -20,6 +20,7 @@ import torch
 
 from .. import kernels
 from ..config.base import ModelSpec
+from ..engine.batch import Cancelled
 from ..parts.base import ParamSpec, norm_class
 from ..parts.block import Block
 from ..parts.linear import Linear
@@ -86,9 +87,10 @@ class DecoderModel:
             b.load({k[len(p):]: v for k, v in tensors.items() if k.startswith(p)}, dt, dev)
         self.final_norm.load({"weight": tensors["final_norm.weight"]}, dev)
         if self.spec.tie_embeddings:
-            self.head = Linear(self.embed_table)
+            self.head = Linear(self.embed_table, role="lm_head")
         else:
-            self.head = Linear(tensors["lm_head.weight"].to(device=dev, dtype=dt).contiguous())
+            self.head = Linear(tensors["lm_head.weight"].to(device=dev, dtype=dt).contiguous(),
+                               role="lm_head")
 
     def weight_bytes(self) -> int:
         seen, n = set(), 0
@@ -123,6 +125,8 @@ class DecoderModel:
         x = ctx.new(T, spec.hidden_size)
         self.blocks[sched[0].block].pre_mixer_norm.forward(h, x)
         for i, call in enumerate(sched):
+            if ctx.cancel is not None and ctx.cancel.is_set():
+                raise Cancelled(f"cancelled before block {i} of {len(sched)}")
             nxt = self.blocks[sched[i + 1].block].pre_mixer_norm if i + 1 < len(sched) else None
             x = self.blocks[call.block].forward(h, x, ctx, call.cache, call.writes_cache, nxt)
         return h

@@ -69,8 +69,8 @@ class AttentionMixer:
             return tensors[name].to(device=device, dtype=dtype)
         # one product for q | k | v: rows of q first, then k, then v
         self.qkv = Linear(torch.cat([mat("q_proj.weight"), mat("k_proj.weight"),
-                                     mat("v_proj.weight")], dim=0).contiguous())
-        self.out = Linear(mat("o_proj.weight").contiguous())
+                                     mat("v_proj.weight")], dim=0).contiguous(), role="qkv")
+        self.out = Linear(mat("o_proj.weight").contiguous(), role="out_proj")
         if self.spec.qk_norm is not None:
             add = 1.0 if self.spec.qk_norm.zero_centered else 0.0
             self.q_norm_weight = (tensors["q_norm.weight"].to(device=device, dtype=torch.float32)

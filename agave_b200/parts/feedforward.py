@@ -41,7 +41,7 @@ class GatedFeedForward:
             return tensors[name].to(device=device, dtype=dtype).contiguous()
         self.gate_up = GatedLinear(mat("gate_proj.weight"), mat("up_proj.weight"),
                                    self.spec.activation)
-        self.down = Linear(mat("down_proj.weight"))
+        self.down = Linear(mat("down_proj.weight"), role="down")
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         return self.down.partial(self.gate_up(x))

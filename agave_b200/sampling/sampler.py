@@ -68,13 +68,19 @@ class Sampler:
 
     def choose(self, logits: torch.Tensor, out: torch.Tensor, params: SamplingParams, seed: int,
                slots: torch.Tensor, seq_ids: torch.Tensor, steps: torch.Tensor,
-               penalise: bool) -> torch.Tensor:
-        """out[b] = token chosen from logits[b]; logits may be changed in place."""
+               penalise: bool, dev_params: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """out[b] = token chosen from logits[b]; logits may be changed in place.
+
+        With ``dev_params`` (``kernels.sampling_words`` on the device) the
+        temperature, top_k, top_p, seed and penalty are read from there when the
+        kernels run; ``params`` then only says which kernels are launched (greedy
+        or not, penalty or not), so a recording serves every other setting."""
         if penalise and params.repeat_penalty != 1.0:
-            kernels.repeat_penalty(logits, slots, self.hist, self.hist_len, params.repeat_penalty)
+            kernels.repeat_penalty(logits, slots, self.hist, self.hist_len, params.repeat_penalty,
+                                   dev_params)
         if params.greedy:
             kernels.argmax(logits, out)
         else:
             kernels.sample(logits, out, params.temperature, params.top_k, params.top_p, seed,
-                           seq_ids, steps)
+                           seq_ids, steps, dev_params)
         return out

@@ -192,18 +192,33 @@ def decoder_layer(cfg: dict, w: Dict[str, torch.Tensor], l: int, h: torch.Tensor
     return h + rms_norm(d, w[p + "post_feedforward_layernorm.weight"], eps)
 
 
-def forward_logits(cfg: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int]) -> torch.Tensor:
-    """Logits [T, V] of one whole sequence starting at position 0: embedding,
-    the layers in order, final norm, the head tied to the embedding unless the
-    file has lm_head.weight, no soft cap (src/models/gemma3.zig:331-368)."""
+def forward_hidden(cfg: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int]) -> torch.Tensor:
+    """The stream [T, H] after the last layer of one whole sequence starting at
+    position 0: embedding, then the layers in order (src/models/gemma3.zig:331-351)."""
     T = len(tokens)
     positions = torch.arange(T)
     h = embed(tokens, w["embed_tokens.weight"], cfg["hidden_size"])
     for l in range(cfg["num_hidden_layers"]):
         h = decoder_layer(cfg, w, l, h, positions)
+    return h
+
+
+def logits_at(cfg: dict, w: Dict[str, torch.Tensor], h: torch.Tensor,
+              rows: Optional[Sequence[int]] = None) -> torch.Tensor:
+    """Final norm and head on the given rows of the stream (all by default): the
+    head is tied to the embedding unless the file has lm_head.weight; no soft cap
+    (src/models/gemma3.zig:352-367)."""
+    if rows is not None:
+        h = h[torch.as_tensor(list(rows), dtype=torch.long)]
     x = rms_norm(h, w["norm.weight"], cfg.get("rms_norm_eps", 1e-6))
     head = w.get("lm_head.weight", w["embed_tokens.weight"])
     return x @ head.T
+
+
+def forward_logits(cfg: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int]) -> torch.Tensor:
+    """Logits [T, V] of one whole sequence starting at position 0
+    (src/models/gemma3.zig:331-368)."""
+    return logits_at(cfg, w, forward_hidden(cfg, w, tokens))
 
 
 # ----------------------------------------------------------------- generation

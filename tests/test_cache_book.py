@@ -106,3 +106,24 @@ def test_random_lifecycles_conserve_slots_and_pages():
     assert book.slots.n_free == 6 and all(p.n_free == p.n_pages for p in book.pools)
     with pytest.raises(CacheError):
         book.release(0)
+
+
+def test_trim_gives_back_what_a_step_that_did_not_run_reserved():
+    book, groups, where = _book()
+    s = book.acquire()
+    book.reserve(s, 70)
+    book.set_length(s, 70)
+    held = [len(p) for p in book.pages[s]]
+    free = [p.n_free for p in book.pools]
+    book.reserve(s, 400)                       # a step that is then refused
+    assert [p.n_free for p in book.pools] != free
+    book.dirty.clear()
+    book.trim(s)
+    assert [len(p) for p in book.pages[s]] == held and [p.n_free for p in book.pools] == free
+    assert s in book.dirty                     # the table row changed again
+    book.trim(s)                               # nothing more to give back
+    assert [p.n_free for p in book.pools] == free
+    book.release(s)
+    assert all(p.n_free == p.n_pages for p in book.pools)
+    with pytest.raises(CacheError):
+        book.trim(s)

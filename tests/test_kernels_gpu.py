@@ -687,10 +687,34 @@ def test_attention_prefill_tcgen05(nh, nkv, hd, window):
     assert rel_err(out[o:o + n], exact) < 1.2e-2
 
 
+def torch_attention(q, k, v, lens, nh, nkv, hd, scale, window):
+    """softmax(q k^T * scale) v on the GPU in 32-bit, sequence by sequence: a plain
+    statement of the sum with the causal and window masks written out."""
+    out = torch.empty((q.shape[0], nh * hd), dtype=torch.float32, device=q.device)
+    o = 0
+    for n in lens:
+        qs = q[o:o + n].float().reshape(n, nh, hd).transpose(0, 1)             # [nh, n, hd]
+        ks = k[o:o + n].float().reshape(n, nkv, hd).transpose(0, 1)
+        vs = v[o:o + n].float().reshape(n, nkv, hd).transpose(0, 1)
+        ks = ks.repeat_interleave(nh // nkv, dim=0)
+        vs = vs.repeat_interleave(nh // nkv, dim=0)
+        p = torch.arange(n, device=q.device)[:, None]
+        j = torch.arange(n, device=q.device)[None, :]
+        mask = j <= p
+        if window:
+            mask = mask & (j > p - window)
+        sc = (qs @ ks.transpose(1, 2)) * scale
+        sc = sc.masked_fill(~mask, float("-inf"))
+        a = torch.softmax(sc, dim=-1)
+        out[o:o + n] = (a @ vs).transpose(0, 1).reshape(n, nh * hd)
+        o += n
+    return out
+
+
 @pytest.mark.parametrize("window", [0, 512])
 def test_attention_prefill_tcgen05_long_sequences(window):
-    """Thousands of positions, two sequences: the tcgen05 kernel and the mma.sync
-    kernel are two independent implementations of the same sum."""
+    """Thousands of positions, two sequences, at the benchmark's sizes (2,048 positions,
+    four heads of 256, window 512), against the sum written out in torch."""
     from agave_b200 import kernels
     nh, nkv, hd = 4, 1, 256
     lens = [2048, 1500]
@@ -698,15 +722,103 @@ def test_attention_prefill_tcgen05_long_sequences(window):
     qkv = rnd(T, (nh + 2 * nkv) * hd, dtype=torch.bfloat16, seed=5, scale=0.7)
     q, k, v = qkv[:, :nh * hd], qkv[:, nh * hd:(nh + nkv) * hd], qkv[:, (nh + nkv) * hd:]
     cu = torch.tensor([0, lens[0], T], dtype=torch.int32, device=DEV)
-    ref = torch.empty((T, nh * hd), dtype=torch.bfloat16, device=DEV)
-    kernels.attention_prefill_mma(q, k, v, ref, cu, max(lens), nh, nkv, hd, 0.0625, window)
-    out = torch.full_like(ref, float("nan"))
+    ref = torch_attention(q, k, v, lens, nh, nkv, hd, 0.0625, window)
+    out = torch.full((T, nh * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
     kernels.attention_prefill_tc(q, k, v, out, cu, max(lens), nh, nkv, hd, 0.0625, window)
     assert kernels.attention_tc_status() == 0
     assert torch.isfinite(out.float()).all()
     assert rel_err(out, ref) < 1.2e-2
-    for row in (0, 63, 64, 2047, 2048, T - 1):
+    for row in (0, 63, 64, 511, 512, 513, 2047, 2048, T - 1):
         assert rel_err(out[row], ref[row]) < 2e-2, row
+    # the mma.sync kernel is a second implementation of the same sum
+    out2 = torch.full_like(out, float("nan"))
+    kernels.attention_prefill_mma(q, k, v, out2, cu, max(lens), nh, nkv, hd, 0.0625, window)
+    assert rel_err(out2, ref) < 1.2e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("W,nh,nkv,hd", [(128, 4, 1, 64), (64, 6, 2, 128), (128, 4, 1, 256)])
+def test_attention_decode_ring_as_large_as_the_window(dtype, W, nh, nkv, hd):
+    """cap == window: the row that held key p - W holds key p itself, so the oldest key in
+    the window sits in the row right after the newest.  Lengths below, at and past the
+    first wrap (129, 256, 300 for a ring of 128).  The newest key and the oldest key in
+    the window each carry about a third of the weight (their scores stand out by ln(W)),
+    so a kernel that looked one row too far, or counted the newest key twice, would be off
+    by tens of percent; the reference is the sum over the sequence's own history, written
+    out in torch."""
+    from types import SimpleNamespace
+    from agave_b200 import kernels
+    PAGE = 64
+    cap = W
+    max_pages = cap // PAGE
+    lens = [W + 1, 2 * W, 2 * W + 44, W, W - 1, 1, 3 * W + 7]
+    B = len(lens)
+    g = torch.Generator().manual_seed(11)
+    table = torch.randperm(B * max_pages, generator=g).int().reshape(B, max_pages).contiguous().to(DEV)
+    slots = torch.tensor([2, 0, 5, 1, 6, 3, 4], dtype=torch.int32, device=DEV)
+    k_pool = torch.zeros((B * max_pages, PAGE, nkv, hd), dtype=dtype, device=DEV)
+    v_pool = torch.zeros_like(k_pool)
+    q = rnd(B, nh * hd, dtype=dtype, seed=4, scale=0.2)
+    boost = float(torch.log(torch.tensor(float(W))))
+    refs = []
+    for b, n in enumerate(lens):
+        kh = rnd(n, nkv, hd, dtype=dtype, seed=20 + b, scale=0.2)
+        vh = rnd(n, nkv, hd, dtype=dtype, seed=40 + b)
+        p = n - 1
+        lo = max(0, p - W + 1)
+        # dimension 0 carries the marks: q has sqrt(boost) there, the two marked keys too
+        kh[:, :, 0] = 0
+        q.view(B, nh, hd)[b, :, 0] = boost ** 0.5 * 4
+        kh[p, :, 0] = boost ** 0.5 / 4
+        kh[lo, :, 0] = boost ** 0.5 / 4
+        if lo > 0:
+            kh[lo - 1, :, 0] = 3.0          # just outside: would swamp everything if it were seen
+        for j in range(max(0, n - cap), n):                       # what the ring still holds
+            row = j % cap
+            pg = int(table[int(slots[b]), row // PAGE])
+            k_pool[pg, row % PAGE] = kh[j]
+            v_pool[pg, row % PAGE] = vh[j]
+        qs = q[b].float().reshape(nh, hd)
+        ks = kh[lo:].float().repeat_interleave(nh // nkv, dim=1)  # [n_vis, nh, hd]
+        vs = vh[lo:].float().repeat_interleave(nh // nkv, dim=1)
+        a = torch.softmax(torch.einsum("hd,jhd->hj", qs, ks) * 1.0, dim=-1)
+        refs.append(torch.einsum("hj,jhd->hd", a, vs).reshape(nh * hd))
+        if n > 2:
+            assert 0.15 < float(a[0, -1]) < 0.6 and 0.15 < float(a[0, 0]) < 0.6
+    ref = torch.stack(refs)
+    positions = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=DEV)
+    tol = 2e-5 if dtype == torch.float32 else 1e-2
+    out = torch.full((B, nh * hd), float("nan"), dtype=dtype, device=DEV)
+    kernels.attention_decode_split(q, out, k_pool, v_pool, table, slots, positions, PAGE, cap, nh,
+                                   nkv, hd, 1.0, W, W)
+    assert rel_err(out, ref) < tol
+    for b in range(B):
+        assert rel_err(out[b], ref[b]) < 2 * tol, (b, lens[b])
+    seq_index = torch.arange(B, dtype=torch.int32, device=DEV)
+    out1 = torch.full_like(out, float("nan"))
+    kernels.attention_paged_simt(q, out1, k_pool, v_pool, table, slots, positions, seq_index, PAGE,
+                                 cap, nh, nkv, hd, 1.0, W)
+    assert rel_err(out1, ref) < tol
+    if dtype == torch.bfloat16 and kernels.attention_decode_fused_supported(dtype, hd, 0):
+        # the kernel that forms q, k and v of the new position itself: hand it q | k_p | v_p
+        # as one "partial sum" and let it store the row the ring wraps onto
+        part = torch.zeros((1, B, (nh + 2 * nkv) * hd), dtype=torch.float32, device=DEV)
+        for b, n in enumerate(lens):
+            row = (n - 1) % cap
+            pg = int(table[int(slots[b]), row // PAGE])
+            part[0, b, :nh * hd] = q[b].float()
+            part[0, b, nh * hd:(nh + nkv) * hd] = k_pool[pg, row % PAGE].float().reshape(-1)
+            part[0, b, (nh + nkv) * hd:] = v_pool[pg, row % PAGE].float().reshape(-1)
+            k_pool[pg, row % PAGE] = 7.0            # stale contents the kernel must replace
+            v_pool[pg, row % PAGE] = 7.0
+        view = SimpleNamespace(page_table=table, page=PAGE, cap=cap, k_pool=k_pool, v_pool=v_pool)
+        ctx = SimpleNamespace(slots=slots, positions=positions, max_len=max(lens))
+        out2 = torch.full_like(out, float("nan"))
+        kernels.attention_decode_fused(part, None, None, 0.0, None, None, True, out2, view, ctx,
+                                       nh, nkv, hd, 1.0, W)
+        assert rel_err(out2, ref) < tol
+        for b in range(B):
+            assert rel_err(out2[b], ref[b]) < 2 * tol, (b, lens[b])
 
 
 def test_attention_prefill_tcgen05_far_key_window_edge_and_growing_scores():

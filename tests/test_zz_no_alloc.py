@@ -67,6 +67,42 @@ def test_static_scratch_entry_point_matches_the_regular_one(dtype):
         assert err <= tol * ref.double().abs().max().item(), err
 
 
+def test_static_scratch_entry_point_recovers_from_a_call_with_too_small_max_keys():
+    """max_keys sizes the grid.  A call that understates it leaves that entry's arrival
+    count unfinished; the counters live inside the library, where no caller can clear
+    them, so every call clears the ones it uses before its kernel runs and the next call
+    is right again."""
+    from agave_b200 import kernels
+    lib = kernels.library()
+    lib.agv_attention_decode_static.restype = ctypes.c_int
+    dtype = torch.float32
+    PAGE, nh, nkv, hd = 64, 4, 1, 64
+    max_pages, n_pages = 10, 20
+    k_pool = _rnd(n_pages, PAGE, nkv, hd, dtype=dtype, seed=1, scale=0.3)
+    v_pool = _rnd(n_pages, PAGE, nkv, hd, dtype=dtype, seed=2)
+    table = torch.arange(n_pages, dtype=torch.int32).reshape(2, max_pages).contiguous().to(DEV)
+    cap = max_pages * PAGE
+    slots = torch.tensor([0, 1], dtype=torch.int32, device=DEV)
+    positions = torch.tensor([599, 299], dtype=torch.int32, device=DEV)
+    q = _rnd(2, nh * hd, dtype=dtype, seed=5, scale=0.3)
+    ref = torch.empty((2, nh * hd), dtype=dtype, device=DEV)
+    kernels.attention_decode_split(q, ref, k_pool, v_pool, table, slots, positions, PAGE, cap, nh,
+                                   nkv, hd, 0.5, 0, 640)
+    out = torch.zeros_like(ref)
+    # 600 keys announced as at most 128: two chunks run, their count never reaches ten
+    rc = _static(lib, q, out, k_pool, v_pool, table, slots, positions, PAGE, cap, nh, nkv, hd,
+                 0.5, 0, 128)
+    assert rc == 0
+    for _ in range(2):
+        out = torch.full_like(ref, float("nan"))
+        rc = _static(lib, q, out, k_pool, v_pool, table, slots, positions, PAGE, cap, nh, nkv,
+                     hd, 0.5, 0, 640)
+        assert rc == 0, lib.agv_last_error().decode()
+        torch.cuda.synchronize()
+        err = (out.double() - ref.double()).abs().max().item()
+        assert err <= 2e-5 * ref.double().abs().max().item(), err
+
+
 def test_static_scratch_entry_point_refuses_what_does_not_fit():
     from agave_b200 import kernels
     lib = kernels.library()
