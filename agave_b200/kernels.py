@@ -76,8 +76,8 @@ _perf = None          # an active agave_b200.perf.PerfCounters, or None
 
 def _span(op: str, nbytes: int = 0, flops: int = 0):
     """A timing span around one launch while operations are being timed."""
-    if _perf is None:
-        return _perf_mod.NULL_SPAN
+    if _perf is None or torch.cuda.is_current_stream_capturing():
+        return _perf_mod.NULL_SPAN           # (a recording holds no timing events)
     return _perf.span(op, nbytes, flops)
 
 

@@ -46,7 +46,13 @@ def read_weights(folder: str, dtype=torch.float64) -> Dict[str, torch.Tensor]:
     for p in PREFIXES:
         if p + "embed_tokens.weight" in out:
             n = len(p)
-            return {(k[n:] if k.startswith(p) else k): v for k, v in out.items()}
+            named = {(k[n:] if k.startswith(p) else k): v for k, v in out.items()}
+            # a head of its own sits beside the decoder, under the outer part of the
+            # prefix or none (src/format/safetensors.zig:531-540)
+            for k in list(named):
+                if k.endswith("lm_head.weight") and k != "lm_head.weight":
+                    named["lm_head.weight"] = named.pop(k)
+            return named
     raise KeyError("embed_tokens.weight not found under any known prefix")
 
 

@@ -758,11 +758,11 @@ def test_attention_decode_ring_as_large_as_the_window(dtype, W, nh, nkv, hd):
     slots = torch.tensor([2, 0, 5, 1, 6, 3, 4], dtype=torch.int32, device=DEV)
     k_pool = torch.zeros((B * max_pages, PAGE, nkv, hd), dtype=dtype, device=DEV)
     v_pool = torch.zeros_like(k_pool)
-    q = rnd(B, nh * hd, dtype=dtype, seed=4, scale=0.2)
+    q = rnd(B, nh * hd, dtype=dtype, seed=4, scale=0.1)
     boost = float(torch.log(torch.tensor(float(W))))
     refs = []
     for b, n in enumerate(lens):
-        kh = rnd(n, nkv, hd, dtype=dtype, seed=20 + b, scale=0.2)
+        kh = rnd(n, nkv, hd, dtype=dtype, seed=20 + b, scale=0.1)
         vh = rnd(n, nkv, hd, dtype=dtype, seed=40 + b)
         p = n - 1
         lo = max(0, p - W + 1)
@@ -784,7 +784,7 @@ def test_attention_decode_ring_as_large_as_the_window(dtype, W, nh, nkv, hd):
         a = torch.softmax(torch.einsum("hd,jhd->hj", qs, ks) * 1.0, dim=-1)
         refs.append(torch.einsum("hj,jhd->hd", a, vs).reshape(nh * hd))
         if n > 2:
-            assert 0.15 < float(a[0, -1]) < 0.6 and 0.15 < float(a[0, 0]) < 0.6
+            assert 0.2 < float(a[0, -1]) < 0.5 and 0.2 < float(a[0, 0]) < 0.5
     ref = torch.stack(refs)
     positions = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=DEV)
     tol = 2e-5 if dtype == torch.float32 else 1e-2
