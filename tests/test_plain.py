@@ -94,3 +94,86 @@ def test_greedy_generate_stops():
     stop = out[2]
     first = out.index(stop)
     assert P.greedy_generate(cfg, w, [2, 9, 77], 5, stop=[stop]) == out[:first]
+
+
+def _reference_walk():
+    """The reference's whole-model walk (tests/golden/reference_model.npz): its weights
+    under the names and in the form a safetensors checkpoint has (norm weights as w, the
+    file holds 1 + w), a configuration for them, and its stages."""
+    z = np.load(os.path.join(os.path.dirname(__file__), "golden", "reference_model.npz"))
+    E, nh, nkv, hd, ff, L, V, theta, eps = z["meta"]
+    cfg = {"hidden_size": int(E), "num_attention_heads": int(nh), "num_key_value_heads": int(nkv),
+           "head_dim": int(hd), "intermediate_size": int(ff), "num_hidden_layers": int(L),
+           "vocab_size": int(V), "rope_theta": float(theta), "rope_local_base_freq": float(theta),
+           "rms_norm_eps": float(eps), "sliding_window": None, "sliding_window_pattern": 0}
+    names = {"attn_norm": "input_layernorm", "attn_q": "self_attn.q_proj",
+             "attn_k": "self_attn.k_proj", "attn_v": "self_attn.v_proj",
+             "attn_q_norm": "self_attn.q_norm", "attn_k_norm": "self_attn.k_norm",
+             "attn_output": "self_attn.o_proj", "post_attention_norm": "post_attention_layernorm",
+             "ffn_norm": "pre_feedforward_layernorm", "ffn_gate": "mlp.gate_proj",
+             "ffn_up": "mlp.up_proj", "ffn_down": "mlp.down_proj",
+             "post_ffw_norm": "post_feedforward_layernorm"}      # src/format/safetensors.zig:468-481
+    w = {}
+    for key in z.files:
+        if not key.startswith("w:"):
+            continue
+        t = torch.from_numpy(z[key]).double()
+        name = key[2:-len(".weight")]
+        if name == "token_embd":
+            w["embed_tokens.weight"] = t
+        elif name == "output_norm":
+            w["norm.weight"] = t - 1.0
+        else:
+            _, l, short = name.split(".")
+            w[f"layers.{l}.{names[short]}.weight"] = t - 1.0 if short.endswith("norm") else t
+    stages = {k[2:]: torch.from_numpy(z[k]).double() for k in z.files if k.startswith("s:")}
+    return cfg, w, stages
+
+
+def test_whole_model_order_against_the_reference_walk():
+    """research/gemma3_ref.py ran the BOS token through a tiny 32-bit model; the plain
+    implementation must reproduce every stage it printed: the parts of layer 0 one by
+    one, the stream after each layer, the final norm and the logits."""
+    cfg, w, st = _reference_walk()
+    eps, nh, nkv, hd = cfg["rms_norm_eps"], cfg["num_attention_heads"], \
+        cfg["num_key_value_heads"], cfg["head_dim"]
+    tol = dict(rtol=2e-5, atol=2e-6)              # the walk computes in 32-bit
+
+    def same(got, name):
+        assert torch.allclose(got.reshape(-1), st[name], **tol), name
+
+    pos = torch.arange(1)
+    h0 = P.embed([2], w["embed_tokens.weight"], cfg["hidden_size"])
+    same(h0, "embedding")
+    p = "layers.0."
+    x = P.rms_norm(h0, w[p + "input_layernorm.weight"], eps)
+    same(x, "after_norm")
+    q = (x @ w[p + "self_attn.q_proj.weight"].T).reshape(1, nh, hd)
+    k = (x @ w[p + "self_attn.k_proj.weight"].T).reshape(1, nkv, hd)
+    v = (x @ w[p + "self_attn.v_proj.weight"].T).reshape(1, nkv, hd)
+    same(q, "Q"); same(k, "K"); same(v, "V")
+    qn = P.rms_norm(q, w[p + "self_attn.q_norm.weight"], eps)
+    kn = P.rms_norm(k, w[p + "self_attn.k_norm.weight"], eps)
+    same(qn, "Q_normed"); same(kn, "K_normed")
+    ang = P.rope_angles(pos, hd, cfg["rope_theta"], 1.0)
+    same(P.apply_rope(qn, ang), "Q_rope")
+    ao = P.attention(P.apply_rope(qn, ang), P.apply_rope(kn, ang), v, hd ** -0.5, None)
+    same(ao, "attn_out")
+    y = P.attention_block(cfg, w, 0, x, pos)
+    same(y, "out_proj")
+    h = h0 + P.rms_norm(y, w[p + "post_attention_layernorm.weight"], eps)
+    same(h, "hidden_L0_attn")
+    x2 = P.rms_norm(h, w[p + "pre_feedforward_layernorm.weight"], eps)
+    same(x2, "after_ffn_norm")
+    same(P.gelu_tanh(x2 @ w[p + "mlp.gate_proj.weight"].T) * (x2 @ w[p + "mlp.up_proj.weight"].T),
+         "geglu_out")
+    same(P.geglu(x2, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"],
+                 w[p + "mlp.down_proj.weight"]), "ffn_down")
+    # the layer function itself, layer after layer
+    hl = h0
+    for l in range(cfg["num_hidden_layers"]):
+        hl = P.decoder_layer(cfg, w, l, hl, pos)
+        same(hl, "hidden_L0_full" if l == 0 else f"hidden_L{l}")
+    same(P.rms_norm(hl, w["norm.weight"], eps), "final_normed")
+    same(P.forward_logits(cfg, w, [2]), "logits")
+    assert int(P.forward_logits(cfg, w, [2]).argmax()) == int(st["logits"].argmax())
