@@ -42,6 +42,24 @@ constexpr int RED_LD = TILE_M + 4;     // row length of a partial tile in shared
 
 __device__ int g_gemm_status = 0;   // 0 ok; else (role << 8) | stage of the first wait that gave up
 
+// The arg max of a product's rows, taken in its epilogue (the head over the vocabulary
+// when the next token is the greatest logit: the logits themselves are never written).
+// Every CTA reduces its 128 features to one (value, index) per token and folds it into
+// the token's key with a 64-bit atomic maximum; the key orders by value first and by
+// lower index second, so ties go to the first index whatever the order of arrival.  A
+// one-CTA kernel launched behind the product turns the keys into indices and puts them
+// back to zero for the next launch (a CTA of the product that waited to learn whether it
+// is the last would hold its shared memory a memory round trip longer, which costs more
+// than that launch).  Launches that use this must not overlap on the device.
+constexpr int ARGMAX_MAX_TOKENS = 128;
+__device__ unsigned long long g_argmax_keys[ARGMAX_MAX_TOKENS];
+
+__device__ __forceinline__ unsigned long long argmax_key(float v, int idx) {
+    const unsigned u = __float_as_uint(v);
+    const unsigned ord = (u & 0x80000000u) ? ~u : (u | 0x80000000u);   // orders like the floats
+    return ((unsigned long long)ord << 32) | (unsigned long long)(0xFFFFFFFFu - (unsigned)idx);
+}
+
 // The activation of the gated epilogue.  Its result is rounded to bfloat16
 // (relative step 2^-8), so the hardware tanh (relative error about 2^-11) serves.
 __device__ __forceinline__ float gelu_tanh_fast(float t) {
@@ -102,7 +120,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_w2,
                     const __grid_constant__ CUtensorMap map_x, TO* __restrict__ out, int T, int N,
                     int K, long long ldc, long long split_stride, int kb_per_split, int act,
-                    int cluster_reduce) {
+                    int cluster_reduce, int* __restrict__ argmax_out) {
     pdl_launch_next();
     using TL = Tile<BN, MODE>;
     constexpr bool GATED = MODE == 1;          // two accumulators
@@ -335,7 +353,31 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
                 }
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");       // the four epilogue warps
-            if (run) {
+            if (MODE == 0 && sizeof(TO) == 4 && argmax_out != nullptr) {
+                // no logits leave the chip: each warp reduces tokens quarter, quarter + 4,
+                // ... of the tile to (greatest value, first index) over the tile's features
+                if (run) {
+                    const float* ft = reinterpret_cast<const float*>(ctile);
+                    const int rows = min(BN, T - n0);
+                    for (int n = quarter; n < rows; n += 4) {
+                        unsigned long long best = 0ull;
+#pragma unroll
+                        for (int i = 0; i < TILE_M / 32; ++i) {
+                            const int f2 = lane + 32 * i;
+                            if (m0 + f2 < N) {
+                                const unsigned long long k2 = argmax_key(ft[n * TILE_M + f2], m0 + f2);
+                                best = k2 > best ? k2 : best;
+                            }
+                        }
+#pragma unroll
+                        for (int o = 16; o > 0; o >>= 1) {
+                            const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+                            best = other > best ? other : best;
+                        }
+                        if (lane == 0) atomicMax(&g_argmax_keys[n0 + n], best);
+                    }
+                }
+            } else if (run) {
                 constexpr int EPV = 16 / (int)sizeof(TO);          // elements per 16 bytes
                 constexpr int VPR = TILE_M / EPV;                  // 16-byte pieces per row
                 const int et = (warp - 2) * 32 + lane;
@@ -430,6 +472,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
                      "r"((uint32_t)TL::TMEM_COLS)
                      : "memory");
     }
+}
+
+// Keys of the arg max epilogue -> indices; the keys go back to zero.
+__global__ void __launch_bounds__(ARGMAX_MAX_TOKENS)
+argmax_finish_kernel(int* __restrict__ out, int T) {
+    pdl_wait();
+    pdl_launch_next();
+    const int t = threadIdx.x;
+    if (t >= T) return;
+    const unsigned long long key = g_argmax_keys[t];
+    g_argmax_keys[t] = 0ull;
+    out[t] = key ? (int)(0xFFFFFFFFu - (unsigned)(key & 0xFFFFFFFFull)) : 0;
 }
 
 // ------------------------------------------------------------ persistent form
@@ -784,7 +838,7 @@ int make_map(CUtensorMap* out, const void* ptr, long long rows, long long K, lon
 template <int BN, int MODE, typename TO>
 int launch(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx, void* out, int T,
            int N, int K, long long ldc, long long split_stride, int splits, int kb_per_split,
-           int act, int cluster_reduce, cudaStream_t stream) {
+           int act, int cluster_reduce, cudaStream_t stream, int* argmax_out = nullptr) {
     using TL = Tile<BN, MODE>;
     static_assert(MODE != 0 || BN * RED_LD * 4 <= TL::STAGES * TL::STAGE_BYTES,
                   "a partial tile must fit the ring of stages");
@@ -804,10 +858,10 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx,
         agv_launch_cluster(kern, grid, GEMM_THREADS, TL::SMEM, stream,
                            dim3(1, 1, (unsigned)cluster_reduce), mw,
                            mw2, mx, (TO*)out, T, N, K, ldc, split_stride, kb_per_split, act,
-                           cluster_reduce);
+                           cluster_reduce, (int*)nullptr);
     else
         agv_launch(kern, grid, GEMM_THREADS, TL::SMEM, stream, mw, mw2, mx, (TO*)out, T, N, K, ldc,
-                   split_stride, kb_per_split, act, 0);
+                   split_stride, kb_per_split, act, 0, argmax_out);
     AGV_LAUNCH_OK("gemm_tcgen05_kernel");
     return 0;
 }
@@ -978,6 +1032,45 @@ AGV_API int agv_linear_tc(const void* x, const void* w, const void* w2, void* ou
         return launch_bn<0, float>(bn, mw, mw2, mx, out, T, N, K, ldc, split_stride, splits,
                                    kb_per, act, creduce, stream);
     return agv_fail(-1, "linear: unknown output dtype %d", out_dtype);
+}
+
+// out_idx[t] = first index of the greatest element of (x w^T)[t, :], for up to 128 rows
+// of x: the product above (plain form, one range of K) with the arg max taken in its
+// epilogue, so that the [T, N] result is never written (the head over the vocabulary
+// when the next token is the greatest logit).  x: [T, K] bf16 with row stride lda;
+// w: [N, K] bf16 dense.  Ties go to the lowest index.  Two such calls must not overlap
+// on the device (they share a table of keys); calls on one stream do not.
+AGV_API int agv_linear_tc_argmax(const void* x, const void* w, int* out_idx, int T, int N, int K,
+                                 long long lda, cudaStream_t stream) {
+    AGV_REQUIRE(T >= 0 && T <= ARGMAX_MAX_TOKENS && N > 0 && K > 0,
+                "linear_argmax: bad sizes T=%d (at most %d) N=%d K=%d", T, ARGMAX_MAX_TOKENS, N, K);
+    AGV_REQUIRE(K % 8 == 0 && lda % 8 == 0 && lda >= K, "linear_argmax: K (%d) and the row stride "
+                "(%lld) must be multiples of 8", K, lda);
+    AGV_REQUIRE(agv_aligned(x, 16) && agv_aligned(w, 16) && out_idx,
+                "linear_argmax: operands must be 16-byte aligned");
+    if (T == 0) return 0;
+    const int bn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : 128;
+    const int kb_total = (K + TILE_K - 1) / TILE_K;
+    CUtensorMap mw, mx;
+    if (int rc = make_map(&mw, w, N, K, K, TILE_M)) return rc;
+    if (int rc = make_map(&mx, x, T, K, lda, bn)) return rc;
+#define AGV_ARGMAX_CASE(B)                                                                      \
+    case B:                                                                                      \
+        rc = launch<B, 0, float>(mw, mw, mx, nullptr, T, N, K, N, 0, 1, kb_total, 0, 0, stream,  \
+                                 out_idx);                                                       \
+        break
+    int rc = -1;
+    switch (bn) {
+        AGV_ARGMAX_CASE(16);
+        AGV_ARGMAX_CASE(32);
+        AGV_ARGMAX_CASE(64);
+        AGV_ARGMAX_CASE(128);
+    }
+#undef AGV_ARGMAX_CASE
+    if (rc) return rc;
+    agv_launch(argmax_finish_kernel, dim3(1), dim3(ARGMAX_MAX_TOKENS), 0, stream, out_idx, T);
+    AGV_LAUNCH_OK("argmax_finish_kernel");
+    return 0;
 }
 
 // The number of partial sums agv_linear_tc will really write for these sizes.

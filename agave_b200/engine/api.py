@@ -100,8 +100,12 @@ class _DecodeGraph:
                           max_len=runner.cache.max_seq_len, max_new=1, cache=runner.cache,
                           dtype=runner.dtype, device=runner.device, lens_host=lens_host)
         h = runner.model.hidden_states(ctx)
-        self.logits = runner.model.logits(h, self.rows, ctx)
         engine.sampler.note_inputs(v["tokens"], v["slots"])
+        if (params.greedy and params.repeat_penalty == 1.0 and engine.fused_greedy and
+                runner.model.greedy_tokens(h, self.rows, ctx, self.next_dev)):
+            self.logits = None         # the greatest logit was found in the head's epilogue
+            return
+        self.logits = runner.model.logits(h, self.rows, ctx)
         engine.sampler.choose(self.logits, self.next_dev, params, seed, v["slots"], self.seq_ids,
                               v["steps"], penalise=True, dev_params=self.words)
 
@@ -211,6 +215,8 @@ class Engine:
         self.use_graphs = use_graphs
         self._graphs: Dict[Tuple, _DecodeGraph] = {}
         self.stats: Dict[str, float] = {}
+        # greedy decoding takes the arg max in the head product's epilogue
+        self.fused_greedy = os.environ.get("AGAVE_B200_FUSED_GREEDY", "1") != "0"
         self._cancel = threading.Event()
         self.runner.cancel_flag = self._cancel
 

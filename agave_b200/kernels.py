@@ -424,6 +424,30 @@ def linear_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
             token_tile, _stream()))
 
 
+ARGMAX_MAX_ROWS = 128
+
+
+def linear_argmax_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether ``linear_argmax`` takes these operands (else: the product, then ``argmax``)."""
+    return linear_tc_supported(x, w) and x.shape[0] <= ARGMAX_MAX_ROWS
+
+
+def linear_argmax(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t] = first index of the greatest element of (x w^T)[t, :], bfloat16 on the
+    tensor cores; the [T, N] product is never written.  At most 128 rows of x."""
+    T, K = x.shape
+    N = w.shape[0]
+    assert w.shape == (N, K) and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+    assert x.stride(1) == 1 and T <= ARGMAX_MAX_ROWS
+    _dense(w, "w"); _i32(out, "out")
+    assert out.numel() >= T and out.is_contiguous()
+    global _launches
+    with _span("lm_head_argmax", N * K * 2 + T * K * 2, 2 * T * N * K):
+        _check(library().agv_linear_tc_argmax(_ptr(x), _ptr(w), _ptr(out), T, N, K,
+                                              ctypes.c_longlong(x.stride(0)), _stream()))
+    _launches += 1            # the product and the kernel that reads its keys out
+
+
 def linear_tc_splits(K: int, splits: int) -> int:
     return library().agv_linear_tc_splits(K, splits)
 

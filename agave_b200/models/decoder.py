@@ -141,5 +141,19 @@ class DecoderModel:
             out = ctx.new(R, self.spec.vocab_size, dtype=torch.float32)
         return self.head(x, out=out)
 
+    def greedy_tokens(self, h: torch.Tensor, rows: torch.Tensor, ctx,
+                      out: torch.Tensor) -> bool:
+        """out[r] = first index of the greatest logit of stream row rows[r], without the
+        logits ever being written (the head product takes the arg max in its epilogue;
+        the reference chooses in the same place, src/models/gemma3.zig:352-367).
+        Returns False, having done nothing, where the head has no such kernel (32-bit
+        weights, more rows than it takes): the caller then asks for ``logits``."""
+        x = ctx.new(rows.numel(), self.spec.hidden_size)
+        if not kernels.linear_argmax_supported(x, self.head.weight):
+            return False
+        self.final_norm.forward(h, x, rows=rows)
+        kernels.linear_argmax(x, self.head.weight, out)
+        return True
+
     def forward(self, ctx, rows: torch.Tensor) -> torch.Tensor:
         return self.logits(self.hidden_states(ctx), rows, ctx)

@@ -1,19 +1,27 @@
 #!/usr/bin/env python3
-"""Measures decoding and prefill of Gemma 3 1B layer sizes on one B200.
+"""Measures decoding and prefill of Gemma 3 layer sizes on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl ours|reference]
                     [--shapes 1b|4b|27b] [--prompt-lens LO HI] [--prefill-tokens N]
 
 Prints ONE JSON line.  ``value`` is decoded tokens per second of K decode
-steps at batch 8 (context 8,192, prompts of unequal lengths 128..2,048,
-random bfloat16 weights), timed on the device with CUDA events; ``e2e`` is the
-same through ``Engine.generate`` with host token ids in and out every step.
-``prefill`` is one 2,048-token prompt; ``roofline`` relates the decode step to
-the bytes it has to read; ``points`` holds decoding at batch 1 and 64.
-A step's inputs (2 GB of weights) are larger than the 126 MB L2, so every
-timed iteration reads them from HBM; this is said in ``config``.  The last three
-options measure other layer sizes, longer contexts and longer prompts; what they were
-is in the record's ``config`` and ``prefill``.
+steps (random bfloat16 weights, context 8,192), timed on the device with CUDA
+events; ``e2e`` is the same through ``Engine.generate`` with host token ids in
+and out every step.  ``prefill`` is one 2,048-token prompt: ``ms`` for a
+length whose step has been recorded, ``first_seen_ms`` for lengths never run
+before (no recording; the launches come from the host one by one).
+``roofline`` relates the decode step to the bytes it has to read; ``points``
+holds decoding at the other batch sizes of the schedule.
+
+Schedules (``--shapes``; the default, 1b, is the benchmark configuration):
+  1b   batch 8 (and 1, 64), prompts of unequal lengths 128..2,048, K steps
+  4b   batch 8, prompts of unequal lengths 256..4,096, 256 decoded tokens
+  27b  batch 16 (and 1), prompts of 2,048 tokens, 128 decoded tokens (54 GB of weights)
+A step's inputs (the weights, gigabytes) are larger than the 126 MB L2, so
+every timed iteration reads them from HBM; ``config.l2`` says how many bytes.
+``--layers``, ``--prompt-lens`` and ``--prefill-tokens`` measure fewer layers,
+other contexts and other prompts; what they were is in ``config`` and
+``prefill``.
 """
 import argparse
 import json
@@ -46,6 +54,10 @@ CONFIG_27B = dict(CONFIG_4B, num_hidden_layers=62, hidden_size=5376, num_attenti
                   num_key_value_heads=16, head_dim=128, query_pre_attn_scalar=168,
                   intermediate_size=21504)
 SHAPES = {"1b": (CONFIG_1B, 2), "4b": (CONFIG_4B, 3), "27b": (CONFIG_27B, 4)}
+# per shape: headline batch, the other batch sizes, prompt lengths, decode steps (None: --steps)
+SCHEDULES = {"1b": dict(batch=8, others=(1, 64), lens=(128, 2048), steps=None),
+             "4b": dict(batch=8, others=(), lens=(256, 4096), steps=256),
+             "27b": dict(batch=16, others=(1,), lens=(2048, 2048), steps=128)}
 CONTEXT = 8192
 PREFILL_TOKENS = 2048
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
@@ -143,41 +155,38 @@ def run_reference(args):
     return 0
 
 
-def timed_decode(engine, torch, kernels, batch, steps, warmup, seed, lo=128, hi=2048):
-    """K decode steps at one batch size, device-timed; returns (ms/step, lens, launches/step)."""
-    import numpy as np
+def timed_decode(engine, torch, batch, steps, warmup, seed, lo=128, hi=2048):
+    """K decode steps at one batch size, device-timed; returns (ms/step, lens, launches/step).
+
+    The steps are the engine's own: each is staged by ``Engine._stage_step`` (the routine
+    the generation loop stages its steps with), kept in a device array, and replayed
+    through the engine's recorded decode step; only the token ids are this function's."""
+    from agave_b200.engine.generate import RequestState
+    from agave_b200.sampling import SamplingParams
     g = torch.Generator().manual_seed(seed)
     V = engine.spec.vocab_size
     lens = torch.linspace(lo, hi, batch).round().int().tolist() if batch > 1 else [(lo + hi) // 2]
     prompts = [torch.randint(3, V, (n,), generator=g).tolist() for n in lens]
-    slots = [engine.acquire() for _ in prompts]
+    reqs = [RequestState(i, p, 1 << 30, output=[3]) for i, p in enumerate(prompts)]
+    for r in reqs:
+        r.slot = engine.acquire()
     # prompts in chunks of sequences, to bound the prompt step's activations
     for i in range(0, batch, 8):
-        engine.step([(slots[j], prompts[j]) for j in range(i, min(batch, i + 8))],
-                    [[] for _ in range(i, min(batch, i + 8))])
-    from agave_b200.engine.api import _bucket
-    from agave_b200.sampling import SamplingParams
+        part = reqs[i:i + 8]
+        engine.step([(r.slot, r.prompt) for r in part], [[] for _ in part])
     params = SamplingParams()
-    graph = engine._graph_for(_bucket(batch), params, 0)
-    B = graph.size
-    book = engine.runner.cache.book
     total = warmup + steps
-    for s in slots:
-        engine.runner.cache.reserve(s, book.length[s] + total)
-    engine.runner.cache.flush()
-    staged = torch.zeros((total, graph.hosts[0].numel()), dtype=torch.int32)
     toks = torch.randint(3, V, (total, batch), generator=g, dtype=torch.int32)
+    staged = None
     for k in range(total):
-        a = staged[k].numpy()
+        graph = engine._stage_step(reqs, params, 0, k, 0)       # the step k steps ahead
+        a = graph.hosts_np[0]
         a[:batch] = toks[k].numpy()
-        cur = np.array([book.length[s] + k for s in slots], dtype=np.int32)
-        a[B:B + batch] = cur
-        a[2 * B:3 * B] = np.arange(B)
-        o = 3 * B
-        a[o:o + B + 1] = np.arange(B + 1)
-        a[o + B + 1:o + 2 * B + 1] = -1
-        a[o + B + 1:o + B + 1 + batch] = np.array(slots, dtype=np.int32)
-        a[o + 2 * B + 1:o + 2 * B + 1 + batch] = cur + 1
+        a[graph.flag_at] = 0                                    # token ids come from the host
+        if staged is None:
+            staged = torch.zeros((total, a.size), dtype=torch.int32)
+        staged[k] = graph.hosts[0]
+    engine.runner.cache.flush()
     staged_dev = staged.to(engine.device)
     torch.cuda.synchronize()
     per_step = graph.kernels_per_step
@@ -193,9 +202,13 @@ def timed_decode(engine, torch, kernels, batch, steps, warmup, seed, lo=128, hi=
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / steps
-    final_lens = [book.length[s] + total for s in slots]
-    for s in slots:
-        engine.release(s)
+    # the last step's choices are real tokens of the vocabulary (the step ran, on these ids)
+    chosen = graph.next_dev[:batch].cpu()
+    assert int(chosen.min()) >= 0 and int(chosen.max()) < V, "the decode step chose no tokens"
+    book = engine.runner.cache.book
+    final_lens = [book.length[r.slot] + total for r in reqs]
+    for r in reqs:
+        engine.release(r.slot)
     return ms, final_lens, per_step
 
 
@@ -209,16 +222,18 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--shapes", default="1b", choices=sorted(SHAPES),
                     help="layer sizes to run (the default, 1b, is the benchmark configuration)")
-    ap.add_argument("--prompt-lens", type=int, nargs=2, default=[128, 2048], metavar=("LO", "HI"),
+    ap.add_argument("--prompt-lens", type=int, nargs=2, default=None, metavar=("LO", "HI"),
                     help="the decode batches' prompt lengths run from LO to HI (default: the "
-                         "benchmark configuration's 128 to 2,048)")
+                         "schedule's, 128 to 2,048 for the benchmark configuration)")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
                     help="length of the timed prompt (default: the benchmark configuration's)")
     args = ap.parse_args()
-    lo, hi = args.prompt_lens
+    sched = SCHEDULES[args.shapes]
+    lo, hi = args.prompt_lens or sched["lens"]
+    steps = args.steps if sched["steps"] is None else sched["steps"]
     n_pre = args.prefill_tokens
-    if not (0 < lo <= hi and hi + args.steps + max(3, args.warmup) + 1 <= CONTEXT
-            and 0 < n_pre <= CONTEXT):
+    if not (0 < lo <= hi and hi + steps + max(3, args.warmup) + 1 <= CONTEXT
+            and 8 <= n_pre <= CONTEXT):
         print(f"bench.py: prompts and the decoded tokens must fit the context of {CONTEXT}")
         return 2
     if args.impl == "reference":
@@ -229,7 +244,6 @@ def main():
     args.warmup = max(3, args.warmup)
 
     import torch
-    from agave_b200 import kernels
     from agave_b200.engine.api import Engine
 
     base_cfg, seed = SHAPES[args.shapes]
@@ -238,54 +252,62 @@ def main():
     if args.layers:
         cfg["num_hidden_layers"] = args.layers
     pk = peaks()
+    batch = sched["batch"]
+    max_batch = max((batch,) + tuple(sched["others"]))
     engine = Engine.from_config(cfg, seed=seed, std=0.02, norm_std=0.1, dtype="bfloat16",
-                                max_tokens=64 * CONTEXT, ctx_size=CONTEXT, max_batch=64)
+                                max_tokens=max_batch * CONTEXT, ctx_size=CONTEXT,
+                                max_batch=max_batch)
     V = engine.spec.vocab_size
     g = torch.Generator().manual_seed(5)
 
-    # ---- prefill: one prompt (2,048 tokens by default), logits of its last token ----
-    prompt = torch.randint(3, V, (n_pre,), generator=g).tolist()
-    pre_ms = []
-    for it in range(3 + 5):
+    def timed_prompt(tokens):
         s = engine.acquire()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
         e0.record()
-        engine.step([(s, prompt)], [[n_pre - 1]])
+        engine.step([(s, tokens)], [[len(tokens) - 1]])
         e1.record()
         torch.cuda.synchronize()
         engine.release(s)
-        if it >= 3:
-            pre_ms.append(e0.elapsed_time(e1))
+        return e0.elapsed_time(e1)
+
+    # ---- prefill: one prompt (2,048 tokens by default), logits of its last token ----
+    prompt = torch.randint(3, V, (n_pre,), generator=g).tolist()
+    # lengths never run before: no recorded step, the host launches kernel by kernel
+    # (the first of them also pays what a kernel's first use costs, so it is not counted)
+    first_seen = sorted(timed_prompt(prompt[:n_pre - k]) for k in (7, 5, 3, 1))[:3]
+    first_seen_ms = sorted(first_seen)[1]
+    pre_ms = [timed_prompt(prompt) for _ in range(3 + 5)][3:]
     pre_ms = sorted(pre_ms)[len(pre_ms) // 2]
     pflops = prefill_flops(cfg, n_pre, 1)
     prefill = {"value": round(n_pre / pre_ms * 1e3, 1), "tokens": n_pre,
                "ms": round(pre_ms, 3),
-               "frac": round(pflops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+               "frac": round(pflops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+               "first_seen_ms": round(first_seen_ms, 3)}
 
-    # ---- decode at batch 8 (headline), with clocks sampled meanwhile ----
+    # ---- decode at the headline batch, with clocks sampled meanwhile ----
     clocks = ClockSampler()
     clocks.start()
-    ms8, lens8, launches = timed_decode(engine, torch, kernels, 8, args.steps, args.warmup, 8,
-                                        lo, hi)
+    ms_b, lens_b, launches = timed_decode(engine, torch, batch, steps, args.warmup, 8, lo, hi)
     clock_rec = clocks.stop()
-    value = 8 / ms8 * 1e3
-    nbytes = decode_bytes(cfg, lens8)
-    achieved = nbytes / (ms8 * 1e-3) / 1e9
+    value = batch / ms_b * 1e3
+    nbytes = decode_bytes(cfg, lens_b)
+    achieved = nbytes / (ms_b * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"],
                 "unit": "GB/s", "frac": round(achieved / pk["hbm_gbs"], 4),
                 "of": pk["source"], "bytes_per_step": nbytes}
 
     # ---- the other batch sizes ----
-    ms1, _, _ = timed_decode(engine, torch, kernels, 1, args.steps, args.warmup, 1, lo, hi)
-    ms64, _, _ = timed_decode(engine, torch, kernels, 64, max(8, args.steps // 2), args.warmup, 64,
-                              lo, hi)
-    points = {"decode_b1": round(1 / ms1 * 1e3, 1), "decode_b64": round(64 / ms64 * 1e3, 1)}
+    points = {}
+    for b in sched["others"]:
+        k = steps if b <= 16 else max(8, steps // 2)
+        ms, _, _ = timed_decode(engine, torch, b, k, args.warmup, b, lo, hi)
+        points[f"decode_b{b}"] = round(b / ms * 1e3, 1)
 
     # ---- end to end through the Python entry point ----
-    lens = torch.linspace(lo, hi, 8).round().int().tolist()
+    lens = torch.linspace(lo, hi, batch).round().int().tolist()
     prompts = [torch.randint(3, V, (n,), generator=g).tolist() for n in lens]
-    n_new = args.steps + 1
+    n_new = steps + 1
     engine.generate(prompts, max_new_tokens=4, stop_token_ids=[])           # warm-up
     engine.generate(prompts, max_new_tokens=n_new, stop_token_ids=[])
     st = engine.stats
@@ -295,10 +317,12 @@ def main():
            "h2d_bytes_per_step": int(graph.hosts[0].numel() * 4),
            "d2h_bytes_per_step": int(graph.next_hosts[0].numel() * 4)}
 
+    weight_gb = (decode_bytes(cfg, [0]) / 1e9)
     out = {
-        "metric": f"Gemma3-{args.shapes.upper()} bf16 decode tokens/s at batch 8 (context 8192)",
-        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": round(ms8, 4), "higher_is_better": True,
+        "metric": f"Gemma3-{args.shapes.upper()} bf16 decode tokens/s at batch {batch} "
+                  f"(context {CONTEXT})",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps,
+        "warmup": args.warmup, "ms_per_step": round(ms_b, 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {
             "model": f"gemma3-{args.shapes}-shapes-random", "layers": cfg["num_hidden_layers"],
@@ -306,12 +330,12 @@ def main():
             "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
             "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"],
             "vocab": cfg["vocab_size"], "sliding_window": cfg["sliding_window"],
-            "local_per_global": cfg["sliding_window_pattern"] - 1, "global_batch": 8,
-            "seq_len": CONTEXT, "prompt_lens": f"{lo}..{hi} unequal", "seed": seed,
-            "parallelism": "single-gpu", "cache": "paged bf16",
-            "l2": "inputs larger than L2 (2 GB weights per step)"},
+            "local_per_global": cfg["sliding_window_pattern"] - 1, "global_batch": batch,
+            "seq_len": CONTEXT, "prompt_lens": f"{lo}..{hi}" + (" unequal" if lo != hi else ""),
+            "seed": seed, "parallelism": "single-gpu", "cache": "paged bf16",
+            "l2": f"inputs larger than L2 ({weight_gb:.1f} GB weights per step)"},
         "prefill": prefill, "roofline": roofline, "points": points, "e2e": e2e,
-        "gpu_launches": int(launches * args.steps), "clocks": clock_rec,
+        "gpu_launches": int(launches * steps), "clocks": clock_rec,
     }
     print(json.dumps(out))
     return 0

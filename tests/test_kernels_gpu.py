@@ -430,6 +430,38 @@ def test_argmax_first_index_on_ties(V):
     assert out.tolist() == [100, V - 1, 0]
 
 
+@pytest.mark.parametrize("V,T", [(262144 + 64, 8), (5003, 33), (130, 1), (1000, 128), (40000, 64)])
+def test_arg_max_in_the_head_products_epilogue(V, T):
+    """The product whose rows are reduced to the index of their greatest element before
+    anything is written: against torch.argmax of the 32-bit product, with ties inside a
+    tile of 128 features, across tile borders and in the last, partial tile (equal weight
+    rows give equal logits), and twice in a row (the keys go back to zero)."""
+    from agave_b200 import kernels
+    K = 320
+    x = rnd(T, K, dtype=torch.bfloat16, seed=1, scale=0.5)
+    w = rnd(V, K, dtype=torch.bfloat16, seed=2, scale=0.1)
+    # a row that wins for token 0, stored at several places: the first must be chosen
+    big = (x[0].float() * 0.2).to(torch.bfloat16)
+    places = sorted({V - 1, V - 2, min(V - 1, 129), min(V - 1, 127), V // 2})
+    w[places] = big
+    # and a pair of equal rows elsewhere for the last token
+    if T > 1:
+        w[[3, min(V - 1, 700)]] = (x[T - 1].float() * 0.2).to(torch.bfloat16)
+    logits = torch.empty((T, V), dtype=torch.float32, device=DEV)
+    kernels.linear_tc(x, w, logits)
+    want = torch.argmax(logits, dim=1).int()
+    # torch.argmax's tie rule is not promised: the first index of the maximum is
+    first = (logits == logits.max(dim=1, keepdim=True).values).int().argmax(dim=1).int()
+    for _ in range(2):
+        out = torch.full((T,), -7, dtype=torch.int32, device=DEV)
+        kernels.linear_argmax(x, w, out)
+        assert kernels.linear_tc_status() == 0
+        assert torch.equal(out, first), (out[:8], first[:8], want[:8])
+    assert int(out[0]) == places[0]
+    if T > 1:
+        assert int(out[T - 1]) == 3
+
+
 def test_sampling_matches_the_filtered_distribution():
     import sys, os
     from agave_b200 import kernels
