@@ -800,6 +800,289 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w,
     }
 }
 
+// ------------------------------------------------------------- CTA-pair form
+// The gated product for prompts on two SMs per tile (tcgen05 cta_group::2).  The CTAs of
+// a cluster of two share one product of M 256 x N 256 per k-step: each holds 128 of the
+// 256 token rows (the M operand) and half of the N operand in its own shared memory, the
+// even CTA the gate tile's 128 weight rows, the odd CTA the up tile's; each gets the
+// accumulator of its own 128 tokens, columns 0..127 gate and 128..255 up, in its own
+// tensor memory.  A CTA therefore takes 32 KB from L2 per k-block where the one-CTA form
+// takes 48 KB for the same arithmetic, and the L2 feed (about 69 B/clk per SM while all
+// SMs ask) no longer limits the mainloop.
+//
+// One thread of the even CTA issues the products for both.  Both CTAs load their own
+// operands with TMA; all of a stage's bytes are counted on the even CTA's barrier.  The
+// commit that follows a stage's products arrives on the "stage free" barrier of both
+// CTAs, the commit after a tile's last product on both "accumulator full" barriers, and
+// the epilogue warps of both CTAs arrive on the even CTA's "accumulator free" barrier.
+// No load is multicast.  Every wait is bounded as in the other forms; nobody leaves
+// before its partner has passed the final cluster barrier.
+constexpr int PAIR_STAGE_BYTES = 2 * TILE_M * TILE_K * 2;             // 128 token rows + 128 weight rows
+constexpr int PAIR_STAGES = 6;
+constexpr int PAIR_ACC_COLS = 2 * TILE_M;
+constexpr int PAIR_EPI_BYTES = PERSISTENT_EPI_WARPS * 16 * 32 * 4;
+constexpr int PAIR_SMEM = PAIR_STAGES * PAIR_STAGE_BYTES + PAIR_EPI_BYTES + 1024 + 256;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t local, uint32_t rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+    return remote;
+}
+// TMA tile load of a CTA pair: the bytes are counted on a barrier that may lie in the
+// partner CTA (a shared::cluster address).  Not a multicast: one destination.
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, int x, int y,
+                                                 uint32_t bar_cluster_addr) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%2, %3}], [%4];" ::"r"(smem_u32(dst)),
+        "l"(map), "r"(x), "r"(y), "r"(bar_cluster_addr)
+        : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                 uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrives, once the products issued so far are done, on the barrier at this shared-memory
+// offset in both CTAs of the pair.
+__device__ __forceinline__ void tc_commit_pair(uint64_t* bar) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 "
+        "[%0], %1;" ::"r"(smem_u32(bar)),
+        "h"((uint16_t)3)
+        : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr)
+                 : "memory");
+}
+
+__global__ void __launch_bounds__(PERSISTENT_THREADS, 1)
+gemm_tcgen05_pair_gated_kernel(const __grid_constant__ CUtensorMap map_w,
+                               const __grid_constant__ CUtensorMap map_w2,
+                               const __grid_constant__ CUtensorMap map_x,
+                               __nv_bfloat16* __restrict__ out, int T, int N, int K, long long ldc,
+                               int act) {
+    pdl_launch_next();
+    typedef __nv_bfloat16 TO;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* epi = smem + PAIR_STAGES * PAIR_STAGE_BYTES;
+    uint64_t* full = (uint64_t*)(epi + PAIR_EPI_BYTES);     // used in the even CTA
+    uint64_t* empty = full + PAIR_STAGES;                   // one set per CTA
+    uint64_t* acc_full = empty + PAIR_STAGES;               // [2], one set per CTA
+    uint64_t* acc_empty = acc_full + 2;                     // [2], used in the even CTA
+    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();                // 0: issues the products
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    const int f_tiles = (N + TILE_M - 1) / TILE_M;          // tiles of 128 features
+    const int t_tiles = (T + 2 * TILE_M - 1) / (2 * TILE_M); // tiles of 256 tokens
+    const int items = f_tiles * t_tiles;
+    const int n_kb = (K + TILE_K - 1) / TILE_K;
+    constexpr uint32_t STAGE_TX = 2 * PAIR_STAGE_BYTES;     // both CTAs' bytes of a stage
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < PAIR_STAGES; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&acc_full[s], 1);
+            mbar_init(&acc_empty[s], 2 * PERSISTENT_EPI_WARPS);   // the epilogue warps of both CTAs
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         smem_u32(tmem_slot)),
+                     "r"(512u)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();          // the partner's barriers exist before anything is sent to them
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    // item -> (feature tile, token tile); token tiles vary fastest so that the pairs of a
+    // wave share weight tiles in L2
+    auto decode_item = [&](int item, int& m0, int& n0) {
+        m0 = (item / t_tiles) * TILE_M;
+        n0 = (item % t_tiles) * 2 * TILE_M + (int)rank * TILE_M;     // this CTA's first token
+    };
+
+    if (warp == 0 && lane == 0) {
+        // ------------------------------------------------------------ loader (both CTAs)
+        int it = 0;
+        bool waited = false;
+        for (int item = pair; item < items && !*abort_flag; item += n_pairs) {
+            int m0, n0;
+            decode_item(item, m0, n0);
+            for (int i = 0; i < n_kb; ++i, ++it) {
+                const int s = it % PAIR_STAGES;
+                const uint32_t ph = (it / PAIR_STAGES) & 1;
+                if (!mbar_wait(&empty[s], ph ^ 1)) {
+                    atomicCAS(&g_gemm_status, 0, (5 << 8) | s);
+                    *abort_flag = 1;
+                    break;
+                }
+                uint8_t* st = smem + s * PAIR_STAGE_BYTES;
+                const uint32_t bar = mapa_u32(smem_u32(&full[s]), 0);
+                if (rank == 0) mbar_expect_tx(&full[s], STAGE_TX);
+                const int kx = i * TILE_K;
+                // the weights never change: their box is requested before the predecessor
+                // (which produces x) is known to have finished
+                tma_load_2d_pair(st + TILE_M * TILE_K * 2, rank == 0 ? &map_w : &map_w2, kx, m0, bar);
+                if (!waited) {
+                    pdl_wait();
+                    waited = true;
+                }
+                tma_load_2d_pair(st, &map_x, kx, n0, bar);
+            }
+        }
+    } else if (warp == 1 && lane == 0 && rank == 0) {
+        // ------------------------------------------------------------ products (even CTA)
+        constexpr uint32_t idesc = umma_idesc(2 * TILE_M, 2 * TILE_M);
+        int it = 0, li = 0;
+        for (int item = pair; item < items && !*abort_flag; item += n_pairs, ++li) {
+            const int as = li & 1;
+            if (!mbar_wait(&acc_empty[as], ((li >> 1) & 1) ^ 1)) {
+                atomicCAS(&g_gemm_status, 0, (6 << 8) | as);
+                *abort_flag = 1;
+                break;
+            }
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + as * PAIR_ACC_COLS;
+            for (int i = 0; i < n_kb; ++i, ++it) {
+                const int s = it % PAIR_STAGES;
+                const uint32_t ph = (it / PAIR_STAGES) & 1;
+                if (!mbar_wait(&full[s], ph)) {
+                    atomicCAS(&g_gemm_status, 0, (7 << 8) | s);
+                    *abort_flag = 1;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t a_addr = smem_u32(smem + s * PAIR_STAGE_BYTES);      // tokens
+                const uint32_t b_addr = a_addr + TILE_M * TILE_K * 2;               // weight rows
+#pragma unroll
+                for (int k = 0; k < TILE_K / UMMA_K; ++k)
+                    tc_mma_bf16_pair(d_tmem, umma_desc(a_addr + k * UMMA_K * 2),
+                                     umma_desc(b_addr + k * UMMA_K * 2), idesc,
+                                     (i > 0 || k > 0) ? 1u : 0u);
+                tc_commit_pair(&empty[s]);
+            }
+            if (*abort_flag) break;
+            tc_commit_pair(&acc_full[as]);
+        }
+    } else if (warp >= 2) {
+        // ------------------------------------------------------------ epilogue (both CTAs)
+        // lanes are this CTA's tokens, columns 0..127 gate and 128..255 up values of the
+        // tile's features; two warps share each quarter of the lanes, 64 features each
+        pdl_wait();
+        const int quarter = warp & 3, half = (warp - 2) >> 2;
+        constexpr int EPV = 16 / (int)sizeof(TO);
+        const uint32_t acc_empty_leader0 = mapa_u32(smem_u32(&acc_empty[0]), 0);
+        const uint32_t acc_empty_leader1 = mapa_u32(smem_u32(&acc_empty[1]), 0);
+        int li = 0;
+        for (int item = pair; item < items; item += n_pairs, ++li) {
+            int m0, n0;
+            decode_item(item, m0, n0);
+            const int as = li & 1;
+            bool ok = !*abort_flag && mbar_wait(&acc_full[as], (li >> 1) & 1);
+            if (!ok) {
+                if (!*abort_flag) atomicCAS(&g_gemm_status, 0, (8 << 8) | as);
+                *abort_flag = 1;
+                break;
+            }
+            tc_fence_after();
+            const uint32_t lane_base =
+                tmem_base + as * PAIR_ACC_COLS + ((uint32_t)(quarter * 32) << 16);
+            const int tok = n0 + quarter * 32 + lane;
+            TO* grow = out + (size_t)tok * ldc + m0;
+            const bool gfast = m0 + TILE_M <= N && ldc % EPV == 0 && ((uintptr_t)out & 15) == 0;
+            const int c_begin = half * (TILE_M / 2), c_end = c_begin + TILE_M / 2;
+
+            auto release = [&]() {
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(as ? acc_empty_leader1 : acc_empty_leader0);
+            };
+            auto work = [&](const uint32_t (&r)[16], const uint32_t (&u)[16], int c) {
+                float v[16];
+                if (act == 1) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        v[j] = silu_fast(__uint_as_float(r[j])) * __uint_as_float(u[j]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        v[j] = gelu_tanh_fast(__uint_as_float(r[j])) * __uint_as_float(u[j]);
+                }
+                if (tok < T) {
+                    if (gfast) {
+                        TO tmp[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) tmp[j] = __float2bfloat16_rn(v[j]);
+#pragma unroll
+                        for (int q = 0; q < 2; ++q)
+                            reinterpret_cast<uint4*>(grow + c)[q] =
+                                reinterpret_cast<const uint4*>(tmp)[q];
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (m0 + c + j < N) grow[c + j] = __float2bfloat16_rn(v[j]);
+                    }
+                }
+            };
+            uint32_t ra[16], ua[16], rb[16], ub[16];
+            tc_ld16(lane_base + c_begin, ra);
+            tc_ld16(lane_base + TILE_M + c_begin, ua);
+#pragma unroll 1
+            for (int c = c_begin; c < c_end; c += 32) {
+                tc_wait_ld();
+                tc_ld16(lane_base + c + 16, rb);
+                tc_ld16(lane_base + TILE_M + c + 16, ub);
+                work(ra, ua, c);
+                tc_wait_ld();
+                if (c + 32 < c_end) {
+                    tc_ld16(lane_base + c + 32, ra);
+                    tc_ld16(lane_base + TILE_M + c + 32, ua);
+                } else {
+                    release();
+                }
+                work(rb, ub, c + 16);
+            }
+        }
+    }
+    // An abort in one CTA leaves the partner to run into its own bounded waits.  Copies
+    // still in flight into this CTA's shared memory land before the cluster barrier below
+    // lets anybody leave only in a run without an abort; after an abort the result is
+    // void anyway and the status word says so.
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();          // the partner has no product, commit or arrival left for us
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                     "r"(512u)
+                     : "memory");
+    }
+}
+
 // ---------------------------------------------------------------- tensor maps
 // A [rows, K] bf16 matrix with row stride ld (elements), read in boxes of
 // [box_rows x 64]; cached by its geometry (weights are asked for every step).
@@ -888,6 +1171,29 @@ int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mw2, const CUten
     agv_launch(kern, grid, PERSISTENT_THREADS, TL::SMEM, stream, mw, mw2, mx, (TO*)out, T, N, K,
                ldc, split_stride, splits, kb_per_split, act);
     AGV_LAUNCH_OK("gemm_tcgen05_persistent_kernel");
+    return 0;
+}
+
+int launch_pair_gated(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx,
+                      void* out, int T, int N, int K, long long ldc, int act, cudaStream_t stream) {
+    auto kern = gemm_tcgen05_pair_gated_kernel;
+    static bool configured = false;
+    static int sms = 0;
+    if (!configured) {
+        AGV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         PAIR_SMEM));
+        int dev = 0;
+        AGV_CUDA_OK(cudaGetDevice(&dev));
+        AGV_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        configured = true;
+    }
+    const long long items =
+        (long long)((N + TILE_M - 1) / TILE_M) * ((T + 2 * TILE_M - 1) / (2 * TILE_M));
+    long long pairs = sms / 2;
+    if (items < pairs) pairs = items;
+    agv_launch_cluster(kern, dim3((unsigned)(2 * pairs)), PERSISTENT_THREADS, PAIR_SMEM, stream,
+                       dim3(2, 1, 1), mw, mw2, mx, (__nv_bfloat16*)out, T, N, K, ldc, act);
+    AGV_LAUNCH_OK("gemm_tcgen05_pair_gated_kernel");
     return 0;
 }
 
@@ -1000,6 +1306,10 @@ AGV_API int agv_linear_tc(const void* x, const void* w, const void* w2, void* ou
     if (persistent) {
         if (w2) {
             AGV_REQUIRE(out_dtype == AGV_BF16, "linear: the gated form writes bfloat16");
+            static const bool pairs = getenv("AGAVE_B200_CTA_PAIRS") == nullptr ||
+                                      getenv("AGAVE_B200_CTA_PAIRS")[0] != '0';
+            if (pairs && T >= 2 * TILE_M)
+                return launch_pair_gated(mw, mw2, mx, out, T, N, K, ldc, act, stream);
             return launch_persistent<128, 1, __nv_bfloat16>(mw, mw2, mx, out, T, N, K, ldc, 0, 1,
                                                             kb_total, act, stream);
         }
