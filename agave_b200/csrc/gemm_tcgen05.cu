@@ -25,6 +25,7 @@
 // prompts (src/backend/cuda.zig:1569-1570).
 #include "common.cuh"
 #include "tcgen05.cuh"
+#include "cache_write.cuh"
 #include <stdlib.h>
 #include <map>
 #include <mutex>
@@ -497,13 +498,18 @@ argmax_finish_kernel(int* __restrict__ out, int T) {
 // tokens, columns 0..127 gate and 128..255 up values of the same features, and
 // each epilogue thread writes 16 consecutive features of its token.  K may be cut
 // into `splits` ranges whose partial sums go to out + split * split_stride
-// (MODE 0, 32-bit out).
+// (MODE 0, 32-bit out).  q/k/v (MODE 3): tokens on M as in the gated form and 256
+// consecutive rows of the fused q | k | v weight as the N operand, so that an epilogue
+// thread holds whole heads of its token; it norms q and k heads, rotates them, writes q, k
+// and v in bfloat16, stores k and v into the paged cache and writes the values transposed
+// for the prompt attention: what a separate kernel would otherwise do on 32-bit sums that
+// go through global memory in between (see QkvEpilogue).
 constexpr int PERSISTENT_EPI_WARPS = 8;
 constexpr int PERSISTENT_THREADS = 64 + 32 * PERSISTENT_EPI_WARPS;
 
 template <int BN, int MODE>
 struct PTile {
-    static constexpr bool DUAL = MODE == 1;
+    static constexpr bool DUAL = MODE == 1 || MODE == 3;     // two weight boxes per stage
     static constexpr int A_BYTES = TILE_M * TILE_K * 2;
     static constexpr int B_BYTES = BN * TILE_K * 2;
     static constexpr int STAGE_BYTES = A_BYTES * (DUAL ? 2 : 1) + B_BYTES;
@@ -520,16 +526,177 @@ struct PTile {
 };
 
 
+// What the q/k/v form's epilogue does with a token's heads (the order of
+// src/models/gemma3.zig:724-748: norm, then rotation; k stored after both, v as projected,
+// src/backend/kernels/cpu/sdpa.zig:18-21).  Head sizes 64, 128 and 256 (a chunk of 256
+// columns then holds whole heads); the whole head is rotated, or none of it.
+struct QkvEpilogue {
+    __nv_bfloat16* qkv;        // [T, (nh + 2 nkv) * hd], row stride in elements
+    long long row_stride;
+    int nh, nkv, hd;
+    const float* wq;           // [hd] or null: no norm
+    const float* wk;
+    float eps;
+    const float* cosv;         // [T, hd / 2] or null: no rotation
+    const float* sinv;
+    const int* positions;      // [T]
+    CacheWrite cw;
+    VtWrite vw;
+};
+
+__device__ __forceinline__ void st_bf16x16(__nv_bfloat16* dst, const float (&v)[16]) {
+    __nv_bfloat16 tmp[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) tmp[j] = __float2bfloat16_rn(v[j]);
+    reinterpret_cast<uint4*>(dst)[0] = reinterpret_cast<const uint4*>(tmp)[0];
+    reinterpret_cast<uint4*>(dst)[1] = reinterpret_cast<const uint4*>(tmp)[1];
+}
+
+// One epilogue warp's share of one accumulator [128 tokens x 256 columns]: lanes are tokens
+// (tok), the columns are rows m0 .. m0 + 255 of the fused weight.  The two warps that share
+// the lanes (half 0 and 1) each take half of every head's rotation pairs (i, i + hd / 2);
+// both add up the whole head's squares, which costs a few tensor-memory loads and saves an
+// exchange.
+__device__ __forceinline__ void qkv_epilogue(uint32_t lane_base, int m0, int tok, int half, int T,
+                                             const QkvEpilogue& qe) {
+    const int hd = qe.hd, H2 = hd / 2, heads = qe.nh + 2 * qe.nkv;
+    const bool live = tok < T;
+    const int share = H2 / 2;                       // pairs per warp and head: 16, 32 or 64
+    // where this token's key and value go: looked up when the first k or v head comes
+    bool looked = false;
+    int c_page = -1, c_row = 0;
+    long long vt_col = -1;
+    int vt_pad = 0;
+    for (int hh = 0; hh * hd < 2 * TILE_M; ++hh) {
+        const int head = m0 / hd + hh;
+        if (head >= heads) break;
+        const uint32_t base = lane_base + hh * hd;
+        const bool is_q = head < qe.nh, is_k = !is_q && head < qe.nh + qe.nkv;
+        const bool is_v = !is_q && !is_k;
+        const float* w = is_q ? qe.wq : (is_k ? qe.wk : nullptr);
+        float rs = 1.f;
+        if (w) {
+            float ss = 0.f;
+#pragma unroll 1
+            for (int c = 0; c < hd; c += 32) {
+                uint32_t a[16], b[16];
+                tc_ld16(base + c, a);
+                tc_ld16(base + c + 16, b);
+                tc_wait_ld();
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const float x = __uint_as_float(a[j]), y = __uint_as_float(b[j]);
+                    ss = fmaf(x, x, ss);
+                    ss = fmaf(y, y, ss);
+                }
+            }
+            rs = 1.0f / sqrtf(ss / (float)hd + qe.eps);
+        }
+        if (!is_q && !looked && live) {
+            looked = true;
+            const int b = qe.cw.seq_index ? qe.cw.seq_index[tok] : qe.vw.seq_index[tok];
+            const int p = qe.positions[tok];
+            if (qe.cw.k_pool) {
+                const int slot = qe.cw.slots[b], len = qe.cw.lens[b];
+                if (slot >= 0 && p >= len - qe.cw.cap) {
+                    c_row = p % qe.cw.cap;
+                    c_page = qe.cw.page_table[(size_t)slot * qe.cw.max_pages + c_row / qe.cw.page];
+                }
+            }
+            if (qe.vw.vt) {
+                int start = 0;
+                for (int i = 0; i < b; ++i) start += (qe.vw.cu[i + 1] - qe.vw.cu[i] + 63) & ~63;
+                vt_col = start + p;
+                const int len = qe.vw.cu[b + 1] - qe.vw.cu[b];
+                if (p == len - 1) vt_pad = ((len + 63) & ~63) - len;
+            }
+        }
+        const int g = is_k ? head - qe.nh : head - qe.nh - qe.nkv;
+        __nv_bfloat16* row_dst = qe.qkv + (size_t)tok * qe.row_stride + (size_t)head * hd;
+        __nv_bfloat16* pool_dst = nullptr;
+        if (!is_q && c_page >= 0)
+            pool_dst = (__nv_bfloat16*)(is_k ? qe.cw.k_pool : qe.cw.v_pool) +
+                       (((size_t)c_page * qe.cw.page + c_row % qe.cw.page) * qe.nkv + g) * hd;
+        const bool rotate = qe.cosv && !is_v;
+#pragma unroll 1
+        for (int i = half * share; i < (half + 1) * share; i += 16) {
+            uint32_t a[16], b[16];
+            tc_ld16(base + i, a);
+            tc_ld16(base + H2 + i, b);
+            tc_wait_ld();
+            if (!live) continue;
+            float x[16], y[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                x[j] = __uint_as_float(a[j]);
+                y[j] = __uint_as_float(b[j]);
+            }
+            if (w) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float4 wa = *reinterpret_cast<const float4*>(w + i + 4 * q);
+                    const float4 wb = *reinterpret_cast<const float4*>(w + H2 + i + 4 * q);
+                    x[4 * q] *= rs * wa.x, x[4 * q + 1] *= rs * wa.y;
+                    x[4 * q + 2] *= rs * wa.z, x[4 * q + 3] *= rs * wa.w;
+                    y[4 * q] *= rs * wb.x, y[4 * q + 1] *= rs * wb.y;
+                    y[4 * q + 2] *= rs * wb.z, y[4 * q + 3] *= rs * wb.w;
+                }
+            }
+            if (rotate) {
+                const float* cs = qe.cosv + (size_t)tok * H2 + i;
+                const float* sn = qe.sinv + (size_t)tok * H2 + i;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float4 c4 = *reinterpret_cast<const float4*>(cs + 4 * q);
+                    const float4 s4 = *reinterpret_cast<const float4*>(sn + 4 * q);
+                    const float cc[4] = {c4.x, c4.y, c4.z, c4.w}, sv[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float re = x[4 * q + e], im = y[4 * q + e];
+                        x[4 * q + e] = re * cc[e] - im * sv[e];
+                        y[4 * q + e] = re * sv[e] + im * cc[e];
+                    }
+                }
+            }
+            st_bf16x16(row_dst + i, x);
+            st_bf16x16(row_dst + H2 + i, y);
+            if (pool_dst) {
+                st_bf16x16(pool_dst + i, x);
+                st_bf16x16(pool_dst + H2 + i, y);
+            }
+            if (is_v && vt_col >= 0) {
+                __nv_bfloat16* v0 = qe.vw.vt + (size_t)(g * hd + i) * qe.vw.ld + vt_col;
+                __nv_bfloat16* v1 = qe.vw.vt + (size_t)(g * hd + H2 + i) * qe.vw.ld + vt_col;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    v0[(size_t)j * qe.vw.ld] = __float2bfloat16_rn(x[j]);
+                    v1[(size_t)j * qe.vw.ld] = __float2bfloat16_rn(y[j]);
+                }
+                for (int pc = 1; pc <= vt_pad; ++pc)        // the sequence's last token: zero padding
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        v0[(size_t)j * qe.vw.ld + pc] = __float2bfloat16_rn(0.f);
+                        v1[(size_t)j * qe.vw.ld + pc] = __float2bfloat16_rn(0.f);
+                    }
+            }
+        }
+    }
+}
+
 template <int BN, int MODE, typename TO>
 __global__ void __launch_bounds__(PERSISTENT_THREADS, 1)
 gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w,
                                const __grid_constant__ CUtensorMap map_w2,
                                const __grid_constant__ CUtensorMap map_x, TO* __restrict__ out,
                                int T, int N, int K, long long ldc, long long split_stride,
-                               int splits, int kb_per_split, int act) {
+                               int splits, int kb_per_split, int act,
+                               const __grid_constant__ QkvEpilogue qe) {
     pdl_launch_next();
     using TL = PTile<BN, MODE>;
     constexpr bool GATED = MODE == 1;
+    constexpr bool QKV = MODE == 3;
+    constexpr bool TOKM = GATED || QKV;                    // the token tile is the M operand
+    constexpr int M_STEP = QKV ? 2 * TILE_M : TILE_M;      // weight rows per item
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* epi = smem + TL::STAGES * TL::STAGE_BYTES;
@@ -541,7 +708,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w,
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m_tiles = (N + TILE_M - 1) / TILE_M, n_tiles = (T + BN - 1) / BN;
+    const int m_tiles = (N + M_STEP - 1) / M_STEP, n_tiles = (T + BN - 1) / BN;
     const int tiles = m_tiles * n_tiles, items = tiles * splits;
     const int kb_total = (K + TILE_K - 1) / TILE_K;
 
@@ -574,7 +741,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w,
     auto decode_item = [&](int item, int& m0, int& n0, int& kb_begin, int& n_kb, int& split) {
         split = item / tiles;
         const int t = item % tiles;
-        m0 = (t / n_tiles) * TILE_M;
+        m0 = (t / n_tiles) * M_STEP;
         n0 = (t % n_tiles) * BN;
         kb_begin = split * kb_per_split;
         n_kb = min(kb_total, kb_begin + kb_per_split) - kb_begin;
@@ -600,13 +767,14 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w,
                 const int kx = (kb_begin + i) * TILE_K;
                 tma_load_2d(st, &map_w, kx, m0, &full[s]);
                 if (GATED) tma_load_2d(st + TL::A_BYTES, &map_w2, kx, m0, &full[s]);
+                if (QKV) tma_load_2d(st + TL::A_BYTES, &map_w, kx, m0 + TILE_M, &full[s]);
                 if (!waited) {
                     // the weights never change: the first box is requested before the
                     // predecessor (which produces x) is known to have finished
                     pdl_wait();
                     waited = true;
                 }
-                tma_load_2d(st + TL::A_BYTES * (GATED ? 2 : 1), &map_x, kx, n0, &full[s]);
+                tma_load_2d(st + TL::A_BYTES * (TOKM ? 2 : 1), &map_x, kx, n0, &full[s]);
             }
         }
         if (*abort_flag) {
@@ -615,7 +783,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w,
         }
     } else if (warp == 1 && lane == 0) {
         // ------------------------------------------------------------ products
-        constexpr uint32_t idesc = GATED ? umma_idesc(BN, 2 * TILE_M) : umma_idesc(TILE_M, BN);
+        constexpr uint32_t idesc = TOKM ? umma_idesc(BN, 2 * TILE_M) : umma_idesc(TILE_M, BN);
         int it = 0, li = 0;
         for (int item = blockIdx.x; item < items && !*abort_flag; item += gridDim.x, ++li) {
             int m0, n0, kb_begin, n_kb, split;
@@ -638,13 +806,14 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w,
                 }
                 tc_fence_after();
                 const uint32_t a_addr = smem_u32(smem + s * TL::STAGE_BYTES);
-                const uint32_t b_addr = a_addr + TL::A_BYTES * (GATED ? 2 : 1);
+                const uint32_t b_addr = a_addr + TL::A_BYTES * (TOKM ? 2 : 1);
 #pragma unroll
                 for (int k = 0; k < TILE_K / UMMA_K; ++k) {
                     const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
-                    if (GATED)
-                        // the token tile is the M operand; the gate tile and the up tile,
-                        // one after the other in the stage, are one N operand of 256 rows
+                    if (TOKM)
+                        // the token tile is the M operand; the two weight tiles (gate and up,
+                        // or 256 consecutive rows of q | k | v), one after the other in the
+                        // stage, are one N operand of 256 rows
                         tc_mma_bf16(d_tmem, umma_desc(b_addr + k * UMMA_K * 2),
                                     umma_desc(a_addr + k * UMMA_K * 2), idesc, acc);
                     else
@@ -669,7 +838,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w,
         constexpr int HALF_COLS = (GATED ? TILE_M : BN) / 2;
         constexpr int UP_COL = GATED ? TILE_M : BN;
         static_assert(HALF_COLS % 32 == 0, "the column loop works in pairs of 16");
-        static_assert(!GATED || BN == 128, "the gated form puts a tile of 128 tokens on M");
+        static_assert(!TOKM || BN == 128, "these forms put a tile of 128 tokens on M");
         int li = 0;
         for (int item = blockIdx.x; item < items; item += gridDim.x, ++li) {
             int m0, n0, kb_begin, n_kb, split;
@@ -767,6 +936,11 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w,
             };
 
             if (n_kb <= 0) {
+                release();
+                continue;
+            }
+            if constexpr (QKV) {
+                qkv_epilogue(lane_base, m0, tok, half, T, qe);
                 release();
                 continue;
             }
@@ -1152,7 +1326,8 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx,
 template <int BN, int MODE, typename TO>
 int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx,
                       void* out, int T, int N, int K, long long ldc, long long split_stride,
-                      int splits, int kb_per_split, int act, cudaStream_t stream) {
+                      int splits, int kb_per_split, int act, cudaStream_t stream,
+                      const QkvEpilogue& qe = QkvEpilogue{}) {
     using TL = PTile<BN, MODE>;
     auto kern = gemm_tcgen05_persistent_kernel<BN, MODE, TO>;
     static bool configured = false;
@@ -1165,11 +1340,12 @@ int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mw2, const CUten
         AGV_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
         configured = true;
     }
+    constexpr int m_step = MODE == 3 ? 2 * TILE_M : TILE_M;
     const long long items =
-        (long long)((N + TILE_M - 1) / TILE_M) * ((T + BN - 1) / BN) * splits;
+        (long long)((N + m_step - 1) / m_step) * ((T + BN - 1) / BN) * splits;
     const int grid = (int)(items < sms ? items : sms);
     agv_launch(kern, grid, PERSISTENT_THREADS, TL::SMEM, stream, mw, mw2, mx, (TO*)out, T, N, K,
-               ldc, split_stride, splits, kb_per_split, act);
+               ldc, split_stride, splits, kb_per_split, act, qe);
     AGV_LAUNCH_OK("gemm_tcgen05_persistent_kernel");
     return 0;
 }
@@ -1381,6 +1557,53 @@ AGV_API int agv_linear_tc_argmax(const void* x, const void* w, int* out_idx, int
     agv_launch(argmax_finish_kernel, dim3(1), dim3(ARGMAX_MAX_TOKENS), 0, stream, out_idx, T);
     AGV_LAUNCH_OK("argmax_finish_kernel");
     return 0;
+}
+
+// Whether agv_qkv_prefill_tc takes a layer of these sizes.
+AGV_API int agv_qkv_prefill_tc_supported(int hd, int rotary_dim, int K, long long lda,
+                                         long long row_stride) {
+    return ((hd == 64 || hd == 128 || hd == 256) && (rotary_dim == 0 || rotary_dim == hd) &&
+            K % 8 == 0 && lda % 8 == 0 && row_stride % 8 == 0) ? 1 : 0;
+}
+
+// The q | k | v projection of a prompt step with everything that follows it up to the
+// attention in its epilogue: qkv [T, (nh + 2 nkv) * hd] (bfloat16, row stride in elements)
+// receives q and k normed (wq / wk, [hd], or null) and rotated (cos / sin, [T, hd / 2], or
+// null) and v as projected; k and v also go to the layer's cache pools (unless k_pool is
+// null) and the values, transposed, to vt (unless null; see VtWrite).  x: [T, K] bf16 with
+// row stride lda; w: [(nh + 2 nkv) * hd, K] bf16 dense, rows q | k | v.
+AGV_API int agv_qkv_prefill_tc(const void* x, const void* w, int T, int K, long long lda, void* qkv,
+                               long long row_stride, int nh, int nkv, int hd, const float* wq,
+                               const float* wk, float eps, const float* cosv, const float* sinv,
+                               const int* positions, void* k_pool, void* v_pool,
+                               const int* page_table, const int* slots, const int* lens,
+                               const int* seq_index, int max_pages, int page, int cap, void* vt,
+                               long long vt_ld, const int* cu_seqlens, cudaStream_t stream) {
+    AGV_REQUIRE(T >= 0 && K > 0 && nh > 0 && nkv > 0, "qkv_prefill: bad sizes");
+    AGV_REQUIRE(agv_qkv_prefill_tc_supported(hd, cosv ? hd : 0, K, lda, row_stride),
+                "qkv_prefill: head_dim %d, K %d or a row stride is not supported", hd, K);
+    const int N = (nh + 2 * nkv) * hd;
+    AGV_REQUIRE(row_stride >= N && lda >= K, "qkv_prefill: row strides shorter than rows");
+    AGV_REQUIRE(agv_aligned(x, 16) && agv_aligned(w, 16) && agv_aligned(qkv, 16) &&
+                agv_aligned(wq, 16) && agv_aligned(wk, 16) && agv_aligned(cosv, 16) &&
+                agv_aligned(sinv, 16) && agv_aligned(k_pool, 16) && agv_aligned(v_pool, 16),
+                "qkv_prefill: operands must be 16-byte aligned");
+    AGV_REQUIRE(!cosv || sinv, "qkv_prefill: cos without sin");
+    AGV_REQUIRE(!k_pool || (v_pool && page_table && slots && lens && seq_index && positions &&
+                            page > 0 && cap > 0 && max_pages > 0),
+                "qkv_prefill: incomplete cache arguments");
+    AGV_REQUIRE(!vt || (seq_index && positions && cu_seqlens && vt_ld % 64 == 0),
+                "qkv_prefill: the transposed values need seq_index, positions and cu_seqlens");
+    if (T == 0) return 0;
+    CUtensorMap mw, mx;
+    if (int rc = make_map(&mw, w, N, K, K, TILE_M)) return rc;
+    if (int rc = make_map(&mx, x, T, K, lda, TILE_M)) return rc;
+    QkvEpilogue qe{(__nv_bfloat16*)qkv, row_stride, nh, nkv, hd, wq, wk, eps, cosv, sinv, positions,
+                   CacheWrite{k_pool, v_pool, page_table, slots, lens, seq_index, max_pages, page, cap},
+                   VtWrite{(__nv_bfloat16*)vt, vt_ld, cu_seqlens, seq_index}};
+    const int kb_total = (K + TILE_K - 1) / TILE_K;
+    return launch_persistent<128, 3, __nv_bfloat16>(mw, mw, mx, nullptr, T, N, K, 0, 0, 1, kb_total,
+                                                    0, stream, qe);
 }
 
 // The number of partial sums agv_linear_tc will really write for these sizes.

@@ -270,6 +270,69 @@ def qk_norm_rope_store(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_di
             n_seq, max_len, _stream()))
 
 
+_FUSED_QKV = os.environ.get("AGAVE_B200_FUSED_QKV_PREFILL", "1") != "0"
+
+
+def qkv_prefill_supported(x: torch.Tensor, w: torch.Tensor, head_dim: int, rotary_dim: int) -> bool:
+    """Whether ``qkv_prefill`` takes a prompt step of these sizes: bfloat16 on the tensor
+    cores, head sizes 64, 128 or 256 rotated whole or not at all, and enough tiles (128
+    tokens x 256 weight rows) that a CTA works on several: the epilogue of one tile then
+    runs under the products of the next.  With about one tile per CTA it is exposed, and
+    the plain product followed by the norm / rotation / store kernel, whose thousands of
+    warps hide their memory trips, is faster (1B sizes, 2,048 tokens: 149 against 156 us a
+    layer; 4B: 441 against 433; 27B: 1,624 against 1,612).  ``AGAVE_B200_FUSED_QKV_PREFILL``
+    = 0 turns it off, = 2 takes it whenever the sizes allow."""
+    if not _FUSED_QKV or x.shape[0] <= 128 or not linear_tc_supported(x, w):
+        return False
+    tiles = ((w.shape[0] + 255) // 256) * ((x.shape[0] + 127) // 128)
+    if tiles * 2 < 3 * n_sms() and os.environ.get("AGAVE_B200_FUSED_QKV_PREFILL") != "2":
+        return False
+    return (bool(
+        library().agv_qkv_prefill_tc_supported(head_dim, rotary_dim, w.shape[1],
+                                               ctypes.c_longlong(x.stride(0)),
+                                               ctypes.c_longlong(w.shape[0]))))
+
+
+def qkv_prefill(x: torch.Tensor, w: torch.Tensor, qkv: torch.Tensor, n_heads: int, n_kv_heads: int,
+                head_dim: int, wq: Optional[torch.Tensor], wk: Optional[torch.Tensor], eps: float,
+                cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
+                positions: torch.Tensor, seq_index: torch.Tensor,
+                k_pool: Optional[torch.Tensor] = None, v_pool: Optional[torch.Tensor] = None,
+                page_table: Optional[torch.Tensor] = None, slots: Optional[torch.Tensor] = None,
+                lens: Optional[torch.Tensor] = None, page: int = 0, cap: int = 0,
+                vt: Optional[torch.Tensor] = None, cu_seqlens: Optional[torch.Tensor] = None) -> None:
+    """qkv [T, (nh + 2 nkv) * hd] = x w^T with the per-head norm of q and k, the rotation, the
+    store of k and v into the paged cache (if pools are given) and the transposed copy of
+    the values (if ``vt`` is given) all done in the product's epilogue."""
+    T, K = x.shape
+    N = (n_heads + 2 * n_kv_heads) * head_dim
+    assert w.shape == (N, K) and qkv.shape == (T, N) and qkv.dtype == torch.bfloat16
+    assert x.stride(1) == 1 and qkv.stride(1) == 1
+    _dense(w, "w")
+    _f32(wq, "wq"); _f32(wk, "wk"); _f32(cos, "cos"); _f32(sin, "sin")
+    for t, n in ((positions, "positions"), (page_table, "page_table"), (slots, "slots"),
+                 (lens, "lens"), (seq_index, "seq_index"), (cu_seqlens, "cu_seqlens")):
+        _i32(t, n)
+    if cos is not None:
+        _dense(cos, "cos"); _dense(sin, "sin")
+        assert cos.shape == (T, head_dim // 2)
+    if k_pool is not None:
+        _dense(k_pool, "k_pool"); _dense(v_pool, "v_pool")
+        assert k_pool.dtype == torch.bfloat16 and v_pool.dtype == torch.bfloat16
+    if vt is not None:
+        _dense(vt, "vt")
+        assert vt.dtype == torch.bfloat16 and vt.shape[0] == n_kv_heads * head_dim
+    max_pages = page_table.shape[1] if page_table is not None else 0
+    with _span("qkv", *_linear_cost(x, w, None, qkv)):
+        _check(library().agv_qkv_prefill_tc(
+            _ptr(x), _ptr(w), T, K, ctypes.c_longlong(x.stride(0)), _ptr(qkv),
+            ctypes.c_longlong(qkv.stride(0)), n_heads, n_kv_heads, head_dim, _ptr(wq), _ptr(wk),
+            ctypes.c_float(eps), _ptr(cos), _ptr(sin), _ptr(positions), _ptr(k_pool), _ptr(v_pool),
+            _ptr(page_table), _ptr(slots), _ptr(lens), _ptr(seq_index), max_pages, page, cap,
+            _ptr(vt), ctypes.c_longlong(vt.shape[1] if vt is not None else 0), _ptr(cu_seqlens),
+            _stream()))
+
+
 def attention_prefill_simt(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor,
                            positions: torch.Tensor, seq_index: torch.Tensor,
                            cu_seqlens: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,

@@ -82,8 +82,6 @@ class AttentionMixer:
         s = self.spec
         nh, nkv, hd = s.n_heads, s.n_kv_heads, s.head_dim
         T = x.shape[0]
-        proj = self.qkv.partial(x, cheap_sum=True)
-        part = proj if proj.dim() == 3 else None
         cos = sin = None
         rotary_dim = 0
         if self.position is not None:
@@ -92,6 +90,23 @@ class AttentionMixer:
         view = ctx.cache.kv_view(cache_entry)
         eps = s.qk_norm.eps if s.qk_norm is not None else 0.0
         window = s.window or 0
+        if ctx.mode == PREFILL and kernels.qkv_prefill_supported(x, self.qkv.weight, hd,
+                                                                 rotary_dim):
+            # a prompt step on the tensor cores: norm, rotation, the cache store and the
+            # transposed values are the epilogue of the q/k/v product
+            qkv = ctx.new(T, (nh + 2 * nkv) * hd)
+            vt = None
+            if writes_cache and kernels.attention_prefill_wants_transposed_values(qkv, hd):
+                vt = kernels.prefill_values_scratch(T, ctx.batch, nkv, hd, qkv.device)
+            pools = dict(k_pool=view.k_pool, v_pool=view.v_pool, page_table=view.page_table,
+                         slots=ctx.slots, lens=ctx.lens, page=view.page,
+                         cap=view.cap) if writes_cache else {}
+            kernels.qkv_prefill(x, self.qkv.weight, qkv, nh, nkv, hd, self.q_norm_weight,
+                                self.k_norm_weight, eps, cos, sin, ctx.positions, ctx.seq_index,
+                                vt=vt, cu_seqlens=ctx.cu_seqlens, **pools)
+            return self._attend_prompt(qkv, vt, ctx, cache_entry, writes_cache, window)
+        proj = self.qkv.partial(x, cheap_sum=True)
+        part = proj if proj.dim() == 3 else None
         if (ctx.mode == DECODE and part is not None and
                 kernels.attention_decode_fused_supported(self.dtype, hd, rotary_dim)):
             # decoding: norm, rotation and the store of the new key and value happen inside
@@ -116,18 +131,27 @@ class AttentionMixer:
         else:
             kernels.qk_norm_rope_store(qkv, nh, nkv, hd, self.q_norm_weight, self.k_norm_weight,
                                        eps, cos, sin, rotary_dim, ctx.positions, partial=part)
-        q = qkv[:, :nh * hd]
-        out = ctx.new(T, nh * hd)
         if ctx.mode == PREFILL:
-            if writes_cache:
-                k = qkv[:, nh * hd:(nh + nkv) * hd]
-                v = qkv[:, (nh + nkv) * hd:]
-                ctx.step_kv[cache_entry] = (k, v, vt)
-            else:
-                k, v, vt = ctx.step_kv[cache_entry]
-            kernels.attention_prefill(q, k, v, out, ctx, nh, nkv, hd, s.scale, window, vt=vt)
+            return self._attend_prompt(qkv, vt if writes_cache else None, ctx, cache_entry,
+                                       writes_cache, window)
+        out = ctx.new(T, nh * hd)
+        kernels.attention_decode(qkv[:, :nh * hd], out, view, ctx, nh, nkv, hd, s.scale, window)
+        return self.out.partial(out)
+
+    def _attend_prompt(self, qkv: torch.Tensor, vt, ctx, cache_entry: int, writes_cache: bool,
+                       window: int) -> torch.Tensor:
+        """Prompt attention from the step's own keys and values, then the output projection."""
+        s = self.spec
+        nh, nkv, hd = s.n_heads, s.n_kv_heads, s.head_dim
+        if writes_cache:
+            k = qkv[:, nh * hd:(nh + nkv) * hd]
+            v = qkv[:, (nh + nkv) * hd:]
+            ctx.step_kv[cache_entry] = (k, v, vt)
         else:
-            kernels.attention_decode(q, out, view, ctx, nh, nkv, hd, s.scale, window)
+            k, v, vt = ctx.step_kv[cache_entry]
+        out = ctx.new(qkv.shape[0], nh * hd)
+        kernels.attention_prefill(qkv[:, :nh * hd], k, v, out, ctx, nh, nkv, hd, s.scale, window,
+                                  vt=vt)
         return self.out.partial(out)
 
 

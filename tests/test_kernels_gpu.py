@@ -288,6 +288,75 @@ def test_qk_norm_rope_store(dtype, nh, nkv, hd, rd):
 
 
 # ------------------------------------------------------------------ attention
+@pytest.mark.parametrize("nh,nkv,hd,norm,rotate", [(4, 1, 256, True, True), (6, 2, 128, True, True),
+                                                   (3, 2, 64, False, True), (8, 4, 128, True, False),
+                                                   (2, 1, 64, True, True)])
+def test_qkv_product_with_norm_rotation_and_stores_in_its_epilogue(nh, nkv, hd, norm, rotate):
+    """The prompt step's q/k/v product whose epilogue norms and rotates q and k, writes the
+    cache rows and the transposed values, against the plain product followed by the
+    separate norm / rotation / store kernel: three sequences of unequal lengths, one
+    longer than its ring (its early rows are not stored), a padding slot in between,
+    token counts that end inside a tile, a projection whose rows do not fill the last
+    chunk of 256."""
+    from agave_b200 import kernels
+    K, PAGE, cap = 320, 64, 256
+    lens = [300, 70, 197]
+    T, B = sum(lens), 3
+    width = (nh + 2 * nkv) * hd
+    x = rnd(T, K, dtype=torch.bfloat16, seed=1, scale=0.5)
+    w = rnd(width, K, dtype=torch.bfloat16, seed=2, scale=0.1)
+    wq = (1.0 + 0.3 * rnd(hd, seed=5)) if norm else None
+    wk = (1.0 + 0.3 * rnd(hd, seed=6)) if norm else None
+    positions = torch.cat([torch.arange(n) for n in lens]).int().to(DEV)
+    seq_index = torch.cat([torch.full((n,), i) for i, n in enumerate(lens)]).int().to(DEV)
+    cu = torch.tensor([0, 300, 370, 567], dtype=torch.int32, device=DEV)
+    lens_t = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    slots = torch.tensor([2, 0, 3], dtype=torch.int32, device=DEV)
+    max_pages = cap // PAGE
+    g = torch.Generator().manual_seed(3)
+    table = torch.randperm(4 * max_pages, generator=g).int().reshape(4, max_pages).contiguous().to(DEV)
+    cos = sin = None
+    if rotate:
+        cos = torch.empty((T, hd // 2), dtype=torch.float32, device=DEV)
+        sin = torch.empty_like(cos)
+        kernels.rope_table(positions, hd, 10000.0, 1.0, cos, sin)
+    import ctypes
+    assert kernels.library().agv_qkv_prefill_tc_supported(
+        hd, hd if rotate else 0, K, ctypes.c_longlong(K), ctypes.c_longlong(width))
+    # the separate path
+    part = torch.empty((1, T, width), dtype=torch.float32, device=DEV)
+    kernels.linear_tc(x, w, part[0])
+    k_ref = torch.zeros((4 * max_pages, PAGE, nkv, hd), dtype=torch.bfloat16, device=DEV)
+    v_ref = torch.zeros_like(k_ref)
+    qkv_ref = torch.empty((T, width), dtype=torch.bfloat16, device=DEV)
+    vt_ref = kernels.prefill_values_scratch(T, B, nkv, hd, torch.device(DEV))
+    vt_ref.fill_(7.0)
+    kernels.qk_norm_rope_store(qkv_ref, nh, nkv, hd, wq, wk, 1e-5, cos, sin, hd if rotate else 0,
+                               positions, k_ref, v_ref, table, slots, lens_t, seq_index, PAGE, cap,
+                               partial=part, vt=vt_ref, cu_seqlens=cu, max_len=max(lens))
+    # the product with the epilogue
+    k_got, v_got = torch.zeros_like(k_ref), torch.zeros_like(v_ref)
+    qkv = torch.full((T, width), float("nan"), dtype=torch.bfloat16, device=DEV)
+    vt = torch.full_like(vt_ref, 7.0)
+    kernels.qkv_prefill(x, w, qkv, nh, nkv, hd, wq, wk, 1e-5, cos, sin, positions, seq_index,
+                        k_pool=k_got, v_pool=v_got, page_table=table, slots=slots, lens=lens_t,
+                        page=PAGE, cap=cap, vt=vt, cu_seqlens=cu)
+    assert kernels.linear_tc_status() == 0
+    assert torch.isfinite(qkv.float()).all()
+    assert rel_err(qkv, qkv_ref) < 6e-3
+    for lo in range(0, width, hd):                       # head by head
+        assert rel_err(qkv[:, lo:lo + hd], qkv_ref[:, lo:lo + hd]) < 8e-3, lo // hd
+    assert rel_err(k_got, k_ref) < 8e-3 and rel_err(v_got, v_ref) < 8e-3
+    # the same rows and no others were written (sequence 0 is longer than its ring)
+    assert torch.equal(k_got.abs().sum(dim=(2, 3)) > 0, k_ref.abs().sum(dim=(2, 3)) > 0)
+    assert torch.equal(vt == 7.0, vt_ref == 7.0)         # the same columns, the same zero padding
+    assert rel_err(vt, vt_ref) < 8e-3
+    # without a cache and without the transposed copy: only qkv
+    qkv2 = torch.full_like(qkv, float("nan"))
+    kernels.qkv_prefill(x, w, qkv2, nh, nkv, hd, wq, wk, 1e-5, cos, sin, positions, seq_index)
+    assert torch.equal(qkv2, qkv)
+
+
 def ref_attention(q, k, v, scale, window):
     """q [Tq, nh, hd] at positions pos (last Tq of the keys), k/v [Tk, nkv, hd]."""
     Tq, nh, hd = q.shape

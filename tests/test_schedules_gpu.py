@@ -240,6 +240,37 @@ def test_windows_as_large_as_their_ring(name, dtype):
     _all_back(eng)
 
 
+def test_prompt_steps_with_the_qkv_epilogue(monkeypatch):
+    """The q/k/v product that norms, rotates and stores in its epilogue is chosen only when
+    a CTA gets several tiles (the larger models); here it is forced on a small model so
+    that a whole prompt step and the decoding that follows from its cache run through it:
+    two prompts, one longer than its ring."""
+    from agave_b200.engine.api import Engine
+    from agave_b200.weights import write_model_folder
+    monkeypatch.setenv("AGAVE_B200_FUSED_QKV_PREFILL", "2")
+    cfg = WINDOWED["W128"]
+    V = cfg["vocab_size"]
+    with tempfile.TemporaryDirectory() as d:
+        write_model_folder(d, cfg, seed=22, std=0.05, norm_std=0.2, dtype=torch.bfloat16)
+        eng = Engine(d, dtype="bfloat16", max_tokens=2048, max_batch=4)
+        seqs = [random_tokens(n, V, 90 + n) for n in (230, 150)]
+        starts = [222, 141]
+        refs = [plain_logits(d, s) for s in seqs]
+    slots = [eng.acquire() for _ in seqs]
+    out = eng.step([(slots[i], seqs[i][:starts[i]]) for i in range(2)],
+                   [list(range(starts[i])) for i in range(2)])
+    got = [[out[:starts[0]]], [out[starts[0]:]]]
+    for k in range(9):
+        live = [i for i in range(2) if starts[i] + k < len(seqs[i])]
+        res = eng.step([(slots[i], [seqs[i][starts[i] + k]]) for i in live], [[0]] * len(live))
+        for j, i in enumerate(live):
+            got[i].append(res[j:j + 1])
+    for i in range(2):
+        close(torch.cat(got[i]), refs[i], TOL["bfloat16"])
+        eng.release(slots[i])
+    _all_back(eng)
+
+
 # --------------------------------------------------------- the 1B layer sizes
 CFG_1B_TWO_LAYERS = {
     "architectures": ["Gemma3ForCausalLM"], "model_type": "gemma3_text",
