@@ -22,10 +22,6 @@
 // (src/backend/kernels/cpu/sdpa.zig:36-37,58); window start sl - W
 // (src/models/gemma4.zig:1153-1155).  No value row is skipped for a small weight.
 #include "common.cuh"
-#include "tcgen05.cuh"
-#include <map>
-#include <mutex>
-#include <tuple>
 
 namespace {
 
@@ -82,7 +78,6 @@ struct DecodeArgs {
     int* counters;             // [B * gridDim.y], zero before and after a launch
     int max_pages, page, cap, nh, nkv, hd, window, n_splits, chunk;
     float scale;
-    int pool_pages;            // pages in k_pool / v_pool (0: not known to this call)
 };
 
 // The decode step's q/k norm, rotation and cache store done by the attention kernel
@@ -386,13 +381,6 @@ template <int W>
 __device__ __forceinline__ int dm_swz(int row, int chunk) {
     return row * W + (((chunk & ~7) | ((chunk ^ row) & 7)) << 3);
 }
-// The layout TMA leaves a [64 keys][W] tile in when it is fetched as W / 64 boxes of
-// [64 rows x 128 bytes] with the 128-byte swizzle: box after box, inside a box row after
-// row, the 16-byte chunk c of row r at c ^ (r & 7).
-template <int W>
-__device__ __forceinline__ int tm_swz(int row, int chunk) {
-    return (chunk >> 3) * (DM_KEYS * 64) + row * 64 + (((chunk & 7) ^ (row & 7)) << 3);
-}
 
 __device__ __forceinline__ void dm_cluster_sync() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n"
@@ -428,7 +416,7 @@ __device__ __forceinline__ void dm_ld_run(const float* p, float* dst) {
 // hd / 2).  The result goes, as bfloat16, to a row of a swizzled [rows][HDP] tile in
 // shared memory and, if gdst is given, to global memory.  Weights and angles are
 // requested before the sums, so that all loads are in flight together.
-template <int HDP, bool TMA_LAYOUT = false>
+template <int HDP>
 __device__ __forceinline__ void dm_head_from_partials(const float* __restrict__ src, int G,
                                                       size_t split_stride,
                                                       const float* __restrict__ w, float eps,
@@ -486,7 +474,7 @@ __device__ __forceinline__ void dm_head_from_partials(const float* __restrict__ 
     for (int i = 0; i < 2 * HALF; ++i) {
         const int e = (i < HALF ? e0 + i : H2 + e0 + i - HALF);
         const __nv_bfloat16 x = __float2bfloat16_rn(v[i]);
-        tile[(TMA_LAYOUT ? tm_swz<HDP>(row, e >> 3) : dm_swz<HDP>(row, e >> 3)) + (e & 7)] = x;
+        tile[dm_swz<HDP>(row, e >> 3) + (e & 7)] = x;
         if (gdst) gdst[e] = x;
     }
 }
@@ -886,443 +874,6 @@ int launch_decode_mma(const DecodeArgs& a0, int B, cudaStream_t stream, const Fu
     return 0;
 }
 
-// ------------------------------------------------- tensor-core variant, tiles by TMA
-// The same arithmetic with the key and value tiles brought in by TMA through a ring of
-// shared-memory stages: the loads of the next tiles are in flight while a tile is worked
-// on, so a CTA that walks several tiles pays one trip to memory, not one per tile.  That
-// is the form for many sequences (each then gets few CTAs and each CTA many tiles) and for
-// long contexts; with a few short sequences, where every tile has a CTA of its own, the
-// form above is as fast and keeps two CTAs on an SM.
-//
-// A tile is one cache page of 64 positions (a.page must be 64): position 64 k .. 64 k + 63
-// of the sequence, ring row (64 k) % cap, physical page from the page table.  One box of
-// [64 rows x 64 elements] per 128 bytes of head width lands with the 128-byte swizzle
-// (tm_swz).  The first page of a window and the last page of the sequence are masked by
-// position; value rows beyond position p are zeroed in shared memory, since what a page
-// holds there is left over from its last user.  In the fused form the new position's key
-// and value are formed from the projection's partial sums into the tile after it has
-// landed.  Waits on the stage barriers are bounded; a wait that gives up records a code
-// that agv_attention_decode_status returns and the kernel goes on (its result is void).
-__device__ int g_decode_status = 0;
-
-template <int HDP>
-struct TmShape {
-    static constexpr int STAGES = HDP >= 256 ? 3 : 4;
-    static constexpr int TILE = DM_KEYS * HDP;                   // elements of a key or value tile
-    static constexpr int STAGE_BYTES = 2 * TILE * 2;             // keys + values
-    static constexpr int BOXES = HDP / 64;                       // per tile
-    static constexpr int SMEM = STAGES * STAGE_BYTES + DM_HEADS * HDP * 2 +
-                                DM_HEADS * DM_KEYS * (2 + 4) + DM_HEADS * 3 * 4 + STAGES * 8 +
-                                1024 /* alignment */ + 64;
-};
-
-template <int HDP>
-__global__ void __launch_bounds__(DmShape<HDP>::NT, 1)
-attention_decode_tma_kernel(DecodeArgs a, int cs, FuseQK fq,
-                            const __grid_constant__ CUtensorMap map_k,
-                            const __grid_constant__ CUtensorMap map_v) {
-    typedef DmShape<HDP> Sh;
-    typedef TmShape<HDP> Tm;
-    constexpr int DM_THREADS = Sh::NT;
-    constexpr int STAGES = Tm::STAGES;
-    pdl_launch_next();
-    typedef __nv_bfloat16 T;
-    extern __shared__ unsigned char smem_raw0[];
-    unsigned char* smem_raw = (unsigned char*)(((uintptr_t)smem_raw0 + 1023) & ~(uintptr_t)1023);
-    __shared__ int s_last;
-    T* kv = reinterpret_cast<T*>(smem_raw);                 // [STAGES][keys | values][64][HDP]
-    T* Qs = kv + STAGES * 2 * Tm::TILE;                     // [16][HDP]
-    T* Ps = Qs + DM_HEADS * HDP;                            // [16][64]
-    float* Ss = reinterpret_cast<float*>(Ps + DM_HEADS * DM_KEYS);   // [16][64]
-    float* stat = Ss + DM_HEADS * DM_KEYS;                  // [16][2] running maximum and sum
-    float* fac = stat + DM_HEADS * 2;                       // [16] what a new maximum scales O by
-    uint64_t* full = reinterpret_cast<uint64_t*>(fac + DM_HEADS);    // [STAGES]
-
-    const int W = gridDim.x;
-    const int b = blockIdx.z, split = blockIdx.x;
-    const int G = a.nh / a.nkv;
-    const int groups_per_kv = (G + DM_HEADS - 1) / DM_HEADS;
-    const int g = blockIdx.y / groups_per_kv;
-    const int h0 = g * G + (blockIdx.y % groups_per_kv) * DM_HEADS;
-    const int gc = min(DM_HEADS, g * G + G - h0);
-    const int hd = a.hd;                                    // == HDP here
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int gid = lane >> 2, tig = lane & 3;
-    T* outp = (T*)a.out + ((size_t)b * a.nh + h0) * hd;
-    const int slot = a.slots[b];
-    if (slot < 0) {
-        pdl_wait();
-        if (split == 0)
-            for (int i = tid; i < gc * hd; i += DM_THREADS) outp[i] = __float2bfloat16_rn(0.f);
-        return;
-    }
-    const int p = a.positions[b];
-    const int lo = a.window > 0 ? max(0, p - a.window + 1) : 0;
-    const int k0 = lo / DM_KEYS, k_last = p / DM_KEYS;        // first and last page of the sequence
-    const int all_tiles = k_last - k0 + 1;
-    const int used = min(W, all_tiles);
-    const int cid = split / cs, crank = split % cs;
-    const int used_clusters = (used + cs - 1) / cs;
-    if (cid >= used_clusters) {
-        pdl_wait();
-        return;
-    }
-    const bool has = split < all_tiles;
-    const int n_tiles = has ? (all_tiles - 1 - split) / W + 1 : 0;
-    const int* table = a.page_table + (size_t)slot * a.max_pages;
-    const bool fused = fq.part != nullptr;
-    float* Osm = reinterpret_cast<float*>(kv);               // [16][HDP], after the last tile
-
-    if (tid == 0) {
-        for (int s = 0; s < STAGES; ++s) tc5::mbar_init(&full[s], 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    __syncthreads();
-    // tile tt of this CTA -> stage tt % STAGES (one thread issues; everybody waits on the barrier)
-    auto issue = [&](int tt) {
-        const int k = k0 + split + tt * W;
-        const int row0 = (k * DM_KEYS) % a.cap;
-        const int page = table[row0 / DM_KEYS];
-        const int s = tt % STAGES;
-        T* Ks = kv + (size_t)s * 2 * Tm::TILE;
-        T* Vs = Ks + Tm::TILE;
-        tc5::mbar_expect_tx(&full[s], Tm::STAGE_BYTES);
-#pragma unroll
-        for (int x = 0; x < Tm::BOXES; ++x) {
-            tc5::tma_load_3d(Ks + x * DM_KEYS * 64, &map_k, x * 64, g, page * DM_KEYS, &full[s]);
-            tc5::tma_load_3d(Vs + x * DM_KEYS * 64, &map_v, x * 64, g, page * DM_KEYS, &full[s]);
-        }
-    };
-    // Pages of earlier positions were written by earlier steps: in the fused form (where the
-    // new position's row is formed here and not read from the cache) their loads start
-    // before the wait for the predecessor.
-    int issued = 0;
-    if (has && fused && tid == 0)
-        for (; issued < min(n_tiles, STAGES); ++issued) issue(issued);
-    pdl_wait();
-    if (has) {
-    if (!fused && tid == 0)
-        for (; issued < min(n_tiles, STAGES); ++issued) issue(issued);
-    const size_t f_width = (size_t)(a.nh + 2 * a.nkv) * hd;
-    const size_t f_stride = (size_t)gridDim.z * f_width;
-    const float* f_cos = fused && fq.cosv ? fq.cosv + (size_t)b * (hd / 2) : nullptr;
-    const float* f_sin = fused && fq.cosv ? fq.sinv + (size_t)b * (hd / 2) : nullptr;
-    constexpr int CPR = HDP / 8;
-    // queries of the group: rows beyond the group's heads are zero
-    for (int i = tid; i < DM_HEADS * CPR; i += DM_THREADS) {
-        const int r = i / CPR, c = i % CPR;
-        T* dst = Qs + dm_swz<HDP>(r, c);
-        if (r < gc) {
-            if (!fused)
-                cp_async16(dst, (const T*)a.q + (size_t)b * a.q_stride + (size_t)(h0 + r) * hd +
-                                    c * 8);
-        } else {
-            *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
-        }
-    }
-    if (fused)
-        for (int r = warp; r < gc; r += DM_THREADS / 32)
-            dm_head_from_partials<HDP>(fq.part + (size_t)b * f_width + (size_t)(h0 + r) * hd, fq.G,
-                                       f_stride, fq.wq, fq.eps, f_cos, f_sin, Qs, r, nullptr, lane);
-    cp_async_wait_all();
-    constexpr int NP = Sh::NP;
-    float o[NP * 2][4] = {};
-    for (int tt = 0; tt < n_tiles; ++tt) {
-    const int s = tt % STAGES;
-    T* Ks = kv + (size_t)s * 2 * Tm::TILE;
-    T* Vs = Ks + Tm::TILE;
-    const int k = k0 + split + tt * W;
-    const int jt = k * DM_KEYS;                              // position of the tile's first row
-    if (!tc5::mbar_wait(&full[s], (tt / STAGES) & 1)) atomicCAS(&g_decode_status, 0, (1 << 8) | s);
-    if (k == k_last) {
-        // the sequence's newest page: the new position's row, and nothing after it
-        const int r_new = p - jt;
-        if (fused && fq.store_kv) {
-            const int row = p % a.cap;
-            const int cache_row = table[row / DM_KEYS] * DM_KEYS + row % DM_KEYS;
-            const bool writer = blockIdx.y % groups_per_kv == 0;
-            T* kd = writer ? (T*)a.k_pool + ((size_t)cache_row * a.nkv + g) * hd : nullptr;
-            T* vd = writer ? (T*)a.v_pool + ((size_t)cache_row * a.nkv + g) * hd : nullptr;
-            const float* src = fq.part + (size_t)b * f_width;
-            if (warp == gc % Sh::NW)
-                dm_head_from_partials<HDP, true>(src + (size_t)(a.nh + g) * hd, fq.G, f_stride,
-                                                 fq.wk, fq.eps, f_cos, f_sin, Ks, r_new, kd, lane);
-            else if (warp == (gc + 1) % Sh::NW)
-                dm_head_from_partials<HDP, true>(src + (size_t)(a.nh + a.nkv + g) * hd, fq.G,
-                                                 f_stride, nullptr, 0.f, nullptr, nullptr, Vs,
-                                                 r_new, vd, lane);
-        }
-        for (int i = tid; i < (DM_KEYS - 1 - r_new) * CPR; i += DM_THREADS) {
-            const int r = r_new + 1 + i / CPR, c = i % CPR;
-            *reinterpret_cast<uint4*>(Vs + tm_swz<HDP>(r, c)) = make_uint4(0, 0, 0, 0);
-        }
-    }
-    __syncthreads();
-    // ---- scores of 16 heads x this warp's keys; keys outside lo .. p count for nothing
-    if constexpr (Sh::KW == 16) {
-        float sc[2][4] = {};
-#pragma unroll
-        for (int kk = 0; kk < HDP / 16; ++kk) {
-            unsigned af[4], bf[4];
-            dm_ldsm4(dm_smem(Qs + dm_swz<HDP>(lane & 15, kk * 2 + (lane >> 4))), af);
-            const int mat = lane >> 3, r = lane & 7;
-            dm_ldsm4(dm_smem(Ks + tm_swz<HDP>(warp * 16 + r + (mat >> 1) * 8, kk * 2 + (mat & 1))),
-                     bf);
-            dm_mma(sc[0], af, bf[0], bf[1]);
-            dm_mma(sc[1], af, bf[2], bf[3]);
-        }
-#pragma unroll
-        for (int i = 0; i < 2; ++i)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int key = warp * 16 + i * 8 + tig * 2 + (e & 1);
-                const int row = gid + (e >> 1) * 8;
-                const int j = jt + key;
-                Ss[row * DM_KEYS + key] = (j >= lo && j <= p) ? sc[i][e] * a.scale : -INFINITY;
-            }
-    } else {
-        float sc[2][4] = {};
-#pragma unroll
-        for (int k2 = 0; k2 < HDP / 32; ++k2) {
-            unsigned a0[4], a1[4], bf[4];
-            dm_ldsm4(dm_smem(Qs + dm_swz<HDP>(lane & 15, k2 * 4 + (lane >> 4))), a0);
-            dm_ldsm4(dm_smem(Qs + dm_swz<HDP>(lane & 15, k2 * 4 + 2 + (lane >> 4))), a1);
-            dm_ldsm4(dm_smem(Ks + tm_swz<HDP>(warp * 8 + (lane & 7), k2 * 4 + (lane >> 3))), bf);
-            dm_mma(sc[0], a0, bf[0], bf[1]);
-            dm_mma(sc[1], a1, bf[2], bf[3]);
-        }
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const int key = warp * 8 + tig * 2 + (e & 1);
-            const int row = gid + (e >> 1) * 8;
-            const int j = jt + key;
-            Ss[row * DM_KEYS + key] =
-                (j >= lo && j <= p) ? (sc[0][e] + sc[1][e]) * a.scale : -INFINITY;
-        }
-    }
-    __syncthreads();
-    // ---- softmax weights relative to the running maximum: a warp's rows.  (A tile always
-    // holds a key that counts: the first page holds lo, the last holds p.)
-#pragma unroll
-    for (int rr = 0; rr < Sh::RW; ++rr) {
-        const int row = warp * Sh::RW + rr;
-        const float s0 = Ss[row * DM_KEYS + lane], s1 = Ss[row * DM_KEYS + lane + 32];
-        const float m_old = tt > 0 ? stat[row * 2] : -INFINITY;
-        const float l_old = tt > 0 ? stat[row * 2 + 1] : 0.f;
-        const float m = fmaxf(m_old, warp_max(fmaxf(s0, s1)));
-        const float alpha = tt > 0 ? expf(m_old - m) : 0.f;
-        const float w0 = expf(s0 - m), w1 = expf(s1 - m);
-        const float l = fmaf(l_old, alpha, warp_sum(w0 + w1));
-        Ps[dm_swz<DM_KEYS>(row, lane >> 3) + (lane & 7)] = __float2bfloat16_rn(w0);
-        Ps[dm_swz<DM_KEYS>(row, (lane >> 3) + 4) + (lane & 7)] = __float2bfloat16_rn(w1);
-        __syncwarp();
-        if (lane == 0) {
-            stat[row * 2] = m;
-            stat[row * 2 + 1] = l;
-            fac[row] = alpha;
-        }
-    }
-    __syncthreads();
-    // ---- weighted values: this warp's share of the head dimension
-    {
-        if (tt > 0) {
-            const float f0 = fac[gid], f1 = fac[gid + 8];
-#pragma unroll
-            for (int i = 0; i < NP * 2; ++i) {
-                o[i][0] *= f0, o[i][1] *= f0;
-                o[i][2] *= f1, o[i][3] *= f1;
-            }
-        }
-#pragma unroll
-        for (int kk = 0; kk < DM_KEYS / 16; ++kk) {
-            unsigned af[4];
-            dm_ldsm4(dm_smem(Ps + dm_swz<DM_KEYS>(lane & 15, kk * 2 + (lane >> 4))), af);
-#pragma unroll
-            for (int nn = 0; nn < NP; ++nn) {
-                unsigned bf[4];
-                const int mat = lane >> 3, r = lane & 7;
-                dm_ldsm4t(dm_smem(Vs + tm_swz<HDP>(kk * 16 + r + (mat & 1) * 8,
-                                                   warp * (Sh::DW / 8) + nn * 2 + (mat >> 1))), bf);
-                dm_mma(o[nn * 2], af, bf[0], bf[1]);
-                dm_mma(o[nn * 2 + 1], af, bf[2], bf[3]);
-            }
-        }
-    }
-    if (tt + STAGES < n_tiles) {
-        // everybody is done with this stage (what was written into it by hand is ordered
-        // before the copy that overwrites it); its next tile is requested
-        tc5::fence_async_shared();
-        __syncthreads();
-        if (tid == 0) issue(tt + STAGES);
-    }
-    }   // tiles
-    {
-        if (cs > 1 && used > 1) __syncthreads();   // Osm lies over the first stage
-#pragma unroll
-        for (int i = 0; i < NP * 2; ++i) {
-            const int d = warp * Sh::DW + i * 8 + tig * 2;
-#pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                const int row = gid + half * 8;
-                if (row >= gc) continue;
-                const float v0 = o[i][half * 2], v1 = o[i][half * 2 + 1];
-                if (used == 1) {
-                    const float inv = 1.0f / stat[row * 2 + 1];
-                    outp[row * hd + d] = __float2bfloat16_rn(v0 * inv);
-                    outp[row * hd + d + 1] = __float2bfloat16_rn(v1 * inv);
-                } else if (cs > 1) {
-                    Osm[row * HDP + d] = v0;
-                    Osm[row * HDP + d + 1] = v1;
-                } else {
-                    float* dst = a.part_acc +
-                                 (((size_t)b * a.nh + h0 + row) * a.n_splits + split) * hd + d;
-                    dst[0] = v0;
-                    dst[1] = v1;
-                }
-            }
-        }
-    }
-    } else if (tid < DM_HEADS) {
-        // a CTA past the sequence's pages inside a live cluster contributes nothing
-        stat[tid * 2] = -INFINITY;
-        stat[tid * 2 + 1] = 0.f;
-    }
-    if (used == 1) return;
-    const int wcap = (int)((size_t)2 * DM_KEYS * HDP * sizeof(T) / sizeof(float));
-    if (cs == 1) {
-        finish_split<T>(a, b, h0, gc, used, split, stat, reinterpret_cast<float*>(smem_raw), wcap,
-                        &s_last, outp);
-        return;
-    }
-    // ---- merge inside the cluster: rank r owns a slice of the head dimension
-    dm_cluster_sync();
-    {
-        const int DS = HDP / cs;
-        for (int item = tid; item < gc * DS; item += DM_THREADS) {
-            const int row = item / DS, d = crank * DS + item % DS;
-            float mq[8], lq[8], oq[8];
-#pragma unroll
-            for (int q = 0; q < 8; ++q) {
-                const unsigned qq = q < cs ? q : 0;
-                mq[q] = dm_ld_peer(stat + row * 2, qq);
-                lq[q] = dm_ld_peer(stat + row * 2 + 1, qq);
-                oq[q] = dm_ld_peer(Osm + row * HDP + d, qq);
-            }
-            float M = -INFINITY;
-#pragma unroll
-            for (int q = 0; q < 8; ++q)
-                if (q < cs) M = fmaxf(M, mq[q]);
-            float L = 0.f, O = 0.f;
-#pragma unroll
-            for (int q = 0; q < 8; ++q) {
-                if (q < cs && lq[q] > 0.f) {
-                    const float w = expf(mq[q] - M);
-                    L = fmaf(w, lq[q], L);
-                    O = fmaf(w, oq[q], O);
-                }
-            }
-            if (used_clusters == 1) {
-                outp[row * hd + d] = __float2bfloat16_rn(O / L);
-            } else {
-                a.part_acc[(((size_t)b * a.nh + h0 + row) * a.n_splits + cid) * hd + d] = O;
-                if (d == 0) {
-                    float* ml = a.part_ml + (((size_t)b * a.nh + h0 + row) * a.n_splits + cid) * 2;
-                    ml[0] = M;
-                    ml[1] = L;
-                }
-            }
-        }
-    }
-    dm_cluster_sync();
-    if (used_clusters == 1) return;
-    finish_split<T>(a, b, h0, gc, used_clusters, cid, stat, reinterpret_cast<float*>(smem_raw), wcap,
-                    &s_last, outp, used_clusters * cs, false);
-}
-
-// A pool [pages * 64, nkv, hd] bf16 as a 3-D tensor map read in boxes of [64 rows, 1 head, 64
-// elements]; cached by its geometry.
-int make_pool_map(CUtensorMap* out, const void* pool, long long pages, int nkv, int hd) {
-    typedef std::tuple<const void*, long long, int, int> Key;
-    static std::map<Key, CUtensorMap> cache;
-    static std::mutex mu;
-    Key key(pool, pages, nkv, hd);
-    {
-        std::lock_guard<std::mutex> gl(mu);
-        auto it = cache.find(key);
-        if (it != cache.end()) {
-            *out = it->second;
-            return 0;
-        }
-    }
-    tc5::EncodeTiledFn fn = tc5::encode_fn();
-    if (!fn) return agv_fail(-4, "attention_decode: the driver does not export cuTensorMapEncodeTiled");
-    cuuint64_t dims[3] = {(cuuint64_t)hd, (cuuint64_t)nkv, (cuuint64_t)pages * DM_KEYS};
-    cuuint64_t strides[2] = {(cuuint64_t)hd * 2, (cuuint64_t)nkv * hd * 2};
-    cuuint32_t box[3] = {64, 1, (cuuint32_t)DM_KEYS};
-    cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(pool), dims, strides,
-                    box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS)
-        return agv_fail(-4, "attention_decode: cuTensorMapEncodeTiled failed with code %d (pages "
-                        "%lld, kv heads %d, head_dim %d)", (int)r, pages, nkv, hd);
-    std::lock_guard<std::mutex> gl(mu);
-    if (cache.size() > 4096) cache.clear();
-    cache[key] = *out;
-    return 0;
-}
-
-// 0 auto, 1 always the cp.async form, 2 the TMA form wherever its sizes allow
-int g_decode_form = 0;
-
-template <int HDP>
-int launch_decode_tma(const DecodeArgs& a0, int B, cudaStream_t stream, const FuseQK& fq,
-                      bool* taken) {
-    typedef TmShape<HDP> Tm;
-    auto kern = attention_decode_tma_kernel<HDP>;
-    constexpr int DM_THREADS = DmShape<HDP>::NT;
-    static bool configured = false;
-    static int resident = 0, resident_cp = 0;
-    if (!configured) {
-        AGV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Tm::SMEM));
-        int dev = 0, sms = 0, per_sm = 0;
-        AGV_CUDA_OK(cudaGetDevice(&dev));
-        AGV_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-        AGV_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, DM_THREADS, Tm::SMEM));
-        resident = sms * (per_sm > 0 ? per_sm : 1);
-        resident_cp = sms * (DM_THREADS == 256 ? 2 : 3);
-        configured = true;
-    }
-    DecodeArgs a = a0;
-    const int G = a.nh / a.nkv;
-    const int groups = a.nkv * ((G + DM_HEADS - 1) / DM_HEADS);
-    // Taken when the other form would give a sequence so few CTAs that each walks tiles one
-    // after the other: its tiles (a.n_splits on entry bounds them) against its CTAs there.
-    const int tiles = a.n_splits + 1;                   // pages a window or context can touch
-    const int per_seq_cp = resident_cp / (groups * B) > 0 ? resident_cp / (groups * B) : 1;
-    *taken = g_decode_form == 2 || (g_decode_form == 0 && per_seq_cp <= 8 && tiles > per_seq_cp);
-    if (!*taken) return 0;
-    CUtensorMap mk, mv;
-    if (int rc = make_pool_map(&mk, a.k_pool, a.pool_pages, a.nkv, a.hd)) return rc;
-    if (int rc = make_pool_map(&mv, a.v_pool, a.pool_pages, a.nkv, a.hd)) return rc;
-    int per_seq = resident / (groups * B);
-    if (per_seq > tiles) per_seq = tiles;
-    if (per_seq < 1) per_seq = 1;
-    int cs = 1;
-    while (cs < 8 && cs * 2 <= per_seq) cs *= 2;
-    int clusters = per_seq / cs;
-    if (clusters < 1) clusters = 1;
-    if (clusters > 16) clusters = 16;
-    a.n_splits = clusters;
-    dim3 grid(clusters * cs, groups, B);
-    if (cs > 1)
-        agv_launch_cluster(kern, grid, DM_THREADS, Tm::SMEM, stream, dim3(cs, 1, 1), a, cs, fq, mk, mv);
-    else
-        agv_launch(kern, grid, DM_THREADS, Tm::SMEM, stream, a, 1, fq, mk, mv);
-    AGV_LAUNCH_OK("attention_decode_tma_kernel");
-    return 0;
-}
-
 int pick_chunk(int hd, int elem) {
     int ch = 64;
     while (ch > 8 && (size_t)2 * ch * hd * elem > 128 * 1024) ch /= 2;
@@ -1362,7 +913,7 @@ static int attention_decode_impl(const void* q, long long q_stride, void* out, i
                                  const int* slots, const int* positions, int max_pages, int page,
                                  int cap, int B, int nh, int nkv, int hd, float scale, int window,
                                  int max_keys, float* part_acc, float* part_ml, int* counters,
-                                 cudaStream_t stream, const FuseQK& fq, int pool_pages = 0) {
+                                 cudaStream_t stream, const FuseQK& fq) {
     AGV_REQUIRE(B >= 0 && nh > 0 && nkv > 0 && hd > 0, "attention_decode: bad sizes");
     AGV_REQUIRE(nh % nkv == 0, "attention_decode: %d heads are not a multiple of %d kv heads", nh,
                 nkv);
@@ -1385,20 +936,9 @@ static int attention_decode_impl(const void* q, long long q_stride, void* out, i
     AGV_REQUIRE(smem <= (size_t)AD_MAX_SMEM, "attention_decode: %zu bytes of shared memory needed",
                 smem);
     DecodeArgs a{q, q_stride, out, k_pool, v_pool, page_table, slots, positions, part_acc, part_ml,
-                 counters, max_pages, page, cap, nh, nkv, hd, window, n_splits, ch, scale,
-                 pool_pages};
+                 counters, max_pages, page, cap, nh, nkv, hd, window, n_splits, ch, scale};
     if (dtype == AGV_BF16 && hd % 8 == 0 && hd <= 256 && ch == DM_KEYS &&
         (fq.part || (q_stride % 8 == 0 && agv_aligned(q, 16)))) {
-        if (pool_pages > 0 && page == DM_KEYS && cap % DM_KEYS == 0 && g_decode_form != 1 &&
-            (hd == 64 || hd == 128 || hd == 256) && agv_aligned(k_pool, 128) &&
-            agv_aligned(v_pool, 128)) {
-            // many sequences or long contexts: the form whose tiles come by TMA
-            bool taken = false;
-            int rc = hd == 64    ? launch_decode_tma<64>(a, B, stream, fq, &taken)
-                     : hd == 128 ? launch_decode_tma<128>(a, B, stream, fq, &taken)
-                                 : launch_decode_tma<256>(a, B, stream, fq, &taken);
-            if (rc || taken) return rc;
-        }
         if (hd <= 64) return launch_decode_mma<64>(a, B, stream, fq);
         if (hd <= 128) return launch_decode_mma<128>(a, B, stream, fq);
         return launch_decode_mma<256>(a, B, stream, fq);
@@ -1440,38 +980,6 @@ AGV_API int agv_attention_decode(const void* q, long long q_stride, void* out, i
                                  max_keys, part_acc, part_ml, counters, stream, FuseQK{});
 }
 
-// The same with the number of pages the pools hold (pool_pages > 0), which lets the call
-// take the form whose tiles come by TMA when many sequences or long contexts make a CTA
-// walk several tiles.
-AGV_API int agv_attention_decode_paged(const void* q, long long q_stride, void* out, int dtype,
-                                       const void* k_pool, const void* v_pool,
-                                       const int* page_table, const int* slots,
-                                       const int* positions, int max_pages, int page, int cap,
-                                       int B, int nh, int nkv, int hd, float scale, int window,
-                                       int max_keys, float* part_acc, float* part_ml,
-                                       int* counters, int pool_pages, cudaStream_t stream) {
-    return attention_decode_impl(q, q_stride, out, dtype, k_pool, v_pool, page_table, slots,
-                                 positions, max_pages, page, cap, B, nh, nkv, hd, scale, window,
-                                 max_keys, part_acc, part_ml, counters, stream, FuseQK{}, pool_pages);
-}
-
-// Which tensor-core form the decode attention takes: 0 chosen from the sizes, 1 always the
-// cp.async form, 2 the TMA form wherever its sizes allow (for tests and measurements).
-AGV_API int agv_attention_decode_set_form(int form) {
-    AGV_REQUIRE(form >= 0 && form <= 2, "attention_decode_set_form: 0, 1 or 2");
-    g_decode_form = form;
-    return 0;
-}
-
-// Reads and clears the status word of the TMA form: 0, or (1 << 8 | stage) of the first
-// bounded wait on a stage barrier that gave up.
-AGV_API int agv_attention_decode_status() {
-    int v = 0, zero = 0;
-    if (cudaMemcpyFromSymbol(&v, g_decode_status, sizeof(int)) != cudaSuccess) return -1;
-    if (v != 0) cudaMemcpyToSymbol(g_decode_status, &zero, sizeof(int));
-    return v;
-}
-
 // Whether agv_attention_decode_fused takes these sizes: bfloat16, head sizes 64, 128,
 // 256, the whole head rotated (or none of it).
 AGV_API int agv_attention_decode_fused_supported(int dtype, int hd, int rotary_dim) {
@@ -1484,8 +992,7 @@ AGV_API int agv_attention_decode_fused_supported(int dtype, int hd, int rotary_d
 // 32-bit partial sums; wq, wk [hd] or null; cos, sin [B, hd / 2] or null; store_kv 0
 // for a layer that reads another layer's cache entry (then only q is formed here and
 // the new position's key and value must be in the cache already).  The pools are
-// written, so they are not const.  pool_pages: the pages the pools hold (0: not known,
-// which keeps the call off the form whose tiles come by TMA).
+// written, so they are not const.
 AGV_API int agv_attention_decode_fused(const float* part, int G, const float* wq, const float* wk,
                                        float eps, const float* cosv, const float* sinv,
                                        int store_kv, void* out, void* k_pool, void* v_pool,
@@ -1493,7 +1000,7 @@ AGV_API int agv_attention_decode_fused(const float* part, int G, const float* wq
                                        const int* positions, int max_pages, int page, int cap,
                                        int B, int nh, int nkv, int hd, float scale, int window,
                                        int max_keys, float* part_acc, float* part_ml,
-                                       int* counters, int pool_pages, cudaStream_t stream) {
+                                       int* counters, cudaStream_t stream) {
     AGV_REQUIRE(part && G >= 1, "attention_decode_fused: no partial sums");
     AGV_REQUIRE(agv_attention_decode_fused_supported(AGV_BF16, hd, cosv ? hd : 0),
                 "attention_decode_fused: head_dim %d is not 64, 128 or 256", hd);
@@ -1502,7 +1009,7 @@ AGV_API int agv_attention_decode_fused(const float* part, int G, const float* wq
     FuseQK fq{part, G, wq, wk, eps, cosv, sinv, store_kv};
     return attention_decode_impl(nullptr, 0, out, AGV_BF16, k_pool, v_pool, page_table, slots,
                                  positions, max_pages, page, cap, B, nh, nkv, hd, scale, window,
-                                 max_keys, part_acc, part_ml, counters, stream, fq, pool_pages);
+                                 max_keys, part_acc, part_ml, counters, stream, fq);
 }
 
 // ------------------------------------------------------- no-allocation variant

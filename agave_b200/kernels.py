@@ -45,10 +45,6 @@ def library() -> ctypes.CDLL:
                     # kernels then start only after the one before has ended, which
                     # makes per-kernel durations in a profiler additive
                     lib.agv_set_dependent_launch(0)
-                form = os.environ.get("AGAVE_B200_DECODE_ATTENTION_FORM")
-                if form in ("1", "2"):
-                    # 1: tiles by cp.async always; 2: tiles by TMA wherever the sizes allow
-                    lib.agv_attention_decode_set_form(int(form))
                 _lib = lib
     return _lib
 
@@ -800,27 +796,14 @@ def attention_decode_split(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Ten
     assert part_ml.numel() >= B * n_heads * n_splits * 2
     _f32(part_acc, "part_acc"); _f32(part_ml, "part_ml")
     counters = _decode_counters(q.device, B * n_heads)
-    _check(library().agv_attention_decode_paged(
+    _check(library().agv_attention_decode(
         _ptr(q), ctypes.c_longlong(q.stride(0)), _ptr(out), dtype_code(q.dtype), _ptr(k_pool),
         _ptr(v_pool), _ptr(page_table), _ptr(slots), _ptr(positions), page_table.shape[1], page,
         cap, B, n_heads, n_kv_heads, head_dim, ctypes.c_float(scale), window, max_keys,
-        _ptr(part_acc), _ptr(part_ml), _ptr(counters), int(k_pool.shape[0]), _stream()))
+        _ptr(part_acc), _ptr(part_ml), _ptr(counters), _stream()))
 
 
 _FUSED_DECODE = os.environ.get("AGAVE_B200_FUSED_DECODE_ATTENTION", "1") != "0"
-
-
-def attention_decode_form(form: int) -> None:
-    """Which tensor-core decode attention runs: 0 chosen from the sizes (the default),
-    1 always the form with cp.async tiles, 2 the form with TMA tiles wherever it can."""
-    _check(library().agv_attention_decode_set_form(int(form)))
-
-
-def attention_decode_status() -> int:
-    """0, or the code of the first bounded wait of the TMA decode attention that gave up
-    since the last call (this call synchronises the device)."""
-    torch.cuda.synchronize()
-    return library().agv_attention_decode_status()
 
 
 def attention_decode_fused_supported(dtype: torch.dtype, head_dim: int, rotary_dim: int) -> bool:
@@ -862,7 +845,7 @@ def attention_decode_fused(partial: torch.Tensor, wq: Optional[torch.Tensor],
             _ptr(view.page_table), _ptr(ctx.slots), _ptr(ctx.positions),
             view.page_table.shape[1], view.page, view.cap, B, n_heads, n_kv_heads, head_dim,
             ctypes.c_float(scale), window, max_keys, _ptr(part_acc), _ptr(part_ml),
-            _ptr(counters), int(view.k_pool.shape[0]), _stream()))
+            _ptr(counters), _stream()))
 
 
 def attention_decode(q, out, view, ctx, n_heads, n_kv_heads, head_dim, scale, window) -> None:

@@ -583,23 +583,10 @@ def test_repeat_penalty_per_occurrence_and_history():
     assert logits[0, 6].item() == 1.0 and (logits[1] == torch.where(torch.arange(V, device=DEV) == 7, -2.0, 1.0)).all()
 
 
-@pytest.fixture(params=["cp.async tiles", "TMA tiles"])
-def decode_form(request):
-    """Runs a test with each tensor-core form of the decode attention: the one chosen for
-    few sequences (tiles by cp.async, two CTAs on an SM) and the one for many sequences
-    and long contexts (tiles by TMA through a ring of stages), which takes head sizes 64,
-    128 and 256 and otherwise leaves the call to the first."""
-    from agave_b200 import kernels
-    kernels.attention_decode_form(1 if request.param == "cp.async tiles" else 2)
-    yield request.param
-    kernels.attention_decode_form(0)
-    assert kernels.attention_decode_status() == 0
-
-
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("nh,nkv,hd", [(4, 1, 256), (16, 2, 128), (5, 5, 80), (12, 2, 512),
-                                       (3, 1, 208), (2, 2, 48), (34, 2, 112), (6, 3, 64)])
-def test_attention_decode_split_long_sequences(dtype, nh, nkv, hd, decode_form):
+                                       (3, 1, 208), (2, 2, 48), (34, 2, 112)])
+def test_attention_decode_split_long_sequences(dtype, nh, nkv, hd):
     """Several chunks per sequence, groups wider than the kernel's head tile,
     a far key that must win, and a window edge in the middle of a chunk."""
     from agave_b200 import kernels
@@ -636,7 +623,7 @@ def test_attention_decode_split_long_sequences(dtype, nh, nkv, hd, decode_form):
 
 
 @pytest.mark.parametrize("B,nh,nkv,hd", [(64, 8, 4, 256), (96, 4, 1, 128), (200, 4, 2, 64)])
-def test_attention_decode_many_sequences_walk_several_tiles(B, nh, nkv, hd, decode_form):
+def test_attention_decode_many_sequences_walk_several_tiles(B, nh, nkv, hd):
     """With many sequences a sequence gets few CTAs, each of which walks several key
     tiles with a running softmax (and, with fewer still, a single CTA the whole
     sequence): unequal lengths up to a dozen tiles, padding entries in between, a
@@ -676,8 +663,7 @@ def test_attention_decode_many_sequences_walk_several_tiles(B, nh, nkv, hd, deco
                                                 (8, 8, 64, 70, 9), (6, 3, 128, 64, 16),
                                                 (32, 2, 256, 0, 2), (20, 1, 128, 0, 4)])
 @pytest.mark.parametrize("norm,rotate", [(True, True), (False, False)])
-def test_attention_decode_with_norm_rotation_and_store_inside(nh, nkv, hd, window, G, norm, rotate,
-                                                              decode_form):
+def test_attention_decode_with_norm_rotation_and_store_inside(nh, nkv, hd, window, G, norm, rotate):
     """The decode attention that forms q, k and v of the new position from the
     projection's partial sums, against the separate norm / rotation / store launch
     followed by the plain decode attention: the outputs, the cache rows it writes, and
@@ -856,7 +842,7 @@ def test_attention_prefill_tcgen05_long_sequences(window):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("W,nh,nkv,hd", [(128, 4, 1, 64), (64, 6, 2, 128), (128, 4, 1, 256)])
-def test_attention_decode_ring_as_large_as_the_window(dtype, W, nh, nkv, hd, decode_form):
+def test_attention_decode_ring_as_large_as_the_window(dtype, W, nh, nkv, hd):
     """cap == window: the row that held key p - W holds key p itself, so the oldest key in
     the window sits in the row right after the newest.  Lengths below, at and past the
     first wrap (129, 256, 300 for a ring of 128).  The newest key and the oldest key in
