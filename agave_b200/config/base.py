@@ -79,11 +79,17 @@ class BlockSpec:
     arrangement "sandwich": h += post(mixer(pre(h))); h += post(ffn(pre(h)))
     (src/models/gemma3.zig:708-709,824-826,835-836,876-878);
     arrangement "pre": the same without the two post norms.
+    ``kind`` names the block class in the block registry; "sequential" is the
+    class that runs the mixer and then the feed-forward, as above.  Another
+    arrangement of parts (both branches from one norm, no feed-forward at all)
+    is another block class under another kind, with a spec of its own if it
+    needs other fields.
     """
     mixer: object = None
     feed_forward: object = None
     norm: NormSpec = NormSpec()
     arrangement: str = "sandwich"
+    kind: str = "sequential"
 
 
 @dataclass(frozen=True)
@@ -112,6 +118,9 @@ class ModelSpec:
     max_positions: int = 0
     bos_token_id: Optional[int] = None
     eos_token_ids: Tuple[int, ...] = ()
+    # a position encoding that is added to the stream after the embedding (a learned
+    # table, say), by its kind in the stream-position registry; None: there is none
+    stream_position: Optional[object] = None
 
     def n_cache_entries(self) -> int:
         return 1 + max(c.cache for c in self.schedule) if self.schedule else 0

@@ -21,8 +21,8 @@ import torch
 from .. import kernels
 from ..config.base import ModelSpec
 from ..engine.batch import Cancelled
-from ..parts.base import ParamSpec, norm_class
-from ..parts.block import Block
+from ..parts import block as _block      # registers the "sequential" block
+from ..parts.base import ParamSpec, block_class, norm_class, stream_position_class
 from ..parts.linear import Linear
 
 
@@ -30,8 +30,13 @@ def decoder_param_specs(spec: ModelSpec) -> Dict[str, ParamSpec]:
     out: Dict[str, ParamSpec] = {
         "embed.weight": ParamSpec((spec.vocab_size, spec.hidden_size), "embedding")}
     for i, b in enumerate(spec.blocks):
-        for k, v in Block.param_specs(b, spec.hidden_size).items():
+        B = block_class(getattr(b, "kind", "sequential"))
+        for k, v in B.param_specs(b, spec.hidden_size).items():
             out[f"blocks.{i}.{k}"] = v
+    if spec.stream_position is not None:
+        S = stream_position_class(spec.stream_position.kind)
+        for k, v in S.param_specs(spec.stream_position, spec.hidden_size).items():
+            out[f"stream_position.{k}"] = v
     N = norm_class(spec.final_norm.kind)
     for k, v in N.param_specs(spec.final_norm, spec.hidden_size).items():
         out[f"final_norm.{k}"] = v
@@ -45,8 +50,13 @@ class DecoderModel:
         if dtype not in (torch.float32, torch.bfloat16):
             raise ValueError(f"compute dtype {dtype} is not supported (float32, bfloat16)")
         self.spec, self.dtype, self.device = spec, dtype, device
-        self.blocks: List[Block] = [Block(b, spec.hidden_size, dtype, device)
-                                    for b in spec.blocks]
+        self.blocks: List[object] = [
+            block_class(getattr(b, "kind", "sequential"))(b, spec.hidden_size, dtype, device)
+            for b in spec.blocks]
+        self.stream_position = None
+        if spec.stream_position is not None:
+            self.stream_position = stream_position_class(spec.stream_position.kind)(
+                spec.stream_position, spec.hidden_size, dtype, device)
         self.final_norm = norm_class(spec.final_norm.kind)(spec.final_norm, spec.hidden_size,
                                                            dtype, device)
         self.embed_table: Optional[torch.Tensor] = None
@@ -71,7 +81,7 @@ class DecoderModel:
         n = self.spec.n_cache_entries()
         out: List[object] = [None] * n
         for entry, block in self._writers.items():
-            out[entry] = self.blocks[block].mixer.cache_request()
+            out[entry] = self.blocks[block].cache_request()
         return out
 
     # --------------------------------------------------------------- weights
@@ -85,6 +95,10 @@ class DecoderModel:
         for i, b in enumerate(self.blocks):
             p = f"blocks.{i}."
             b.load({k[len(p):]: v for k, v in tensors.items() if k.startswith(p)}, dt, dev)
+        if self.stream_position is not None:
+            p = "stream_position."
+            self.stream_position.load({k[len(p):]: v for k, v in tensors.items()
+                                       if k.startswith(p)}, dev)
         self.final_norm.load({"weight": tensors["final_norm.weight"]}, dev)
         if self.spec.tie_embeddings:
             self.head = Linear(self.embed_table, role="lm_head")
@@ -110,6 +124,7 @@ class DecoderModel:
                 for v in vars(o).values():
                     visit(v)
         visit(self.blocks); visit(self.final_norm); visit(self.embed_table); visit(self.head)
+        visit(self.stream_position)
         return n
 
     # --------------------------------------------------------------- forward
@@ -119,15 +134,17 @@ class DecoderModel:
         T = ctx.n_tokens
         h = ctx.new(T, spec.hidden_size, dtype=torch.float32)
         kernels.embed(ctx.tokens, self.embed_table, spec.embed_scale, h)
+        if self.stream_position is not None:
+            self.stream_position.forward(h, ctx)
         sched = spec.schedule
         if not sched:
             return h
         x = ctx.new(T, spec.hidden_size)
-        self.blocks[sched[0].block].pre_mixer_norm.forward(h, x)
+        self.blocks[sched[0].block].entry_norm.forward(h, x)
         for i, call in enumerate(sched):
             if ctx.cancel is not None and ctx.cancel.is_set():
                 raise Cancelled(f"cancelled before block {i} of {len(sched)}")
-            nxt = self.blocks[sched[i + 1].block].pre_mixer_norm if i + 1 < len(sched) else None
+            nxt = self.blocks[sched[i + 1].block].entry_norm if i + 1 < len(sched) else None
             x = self.blocks[call.block].forward(h, x, ctx, call.cache, call.writes_cache, nxt)
         return h
 

@@ -10,6 +10,12 @@ size; it never learns which model it sits in.  Each part class gives
 * an instance with ``load(tensors)`` and ``forward(...)`` (see the part kinds
   below for the exact ``forward`` signature of each kind).
 
+A block is the arrangement of such parts in one layer; it has a registry of
+its own (``register_block``), so that an arrangement the library does not
+have is added like a part.  A stream position is a position encoding that is
+added to the residual stream right after the embedding (as opposed to one
+that rotates q and k inside a mixer); it too is registered by kind.
+
 Registries map ``spec.kind`` to the part class; registering under a new kind
 is all that a new part needs.
 """
@@ -55,6 +61,8 @@ _MIXERS: Dict[str, type] = {}
 _FEED_FORWARDS: Dict[str, type] = {}
 _NORMS: Dict[str, type] = {}
 _POSITIONS: Dict[str, type] = {}
+_BLOCKS: Dict[str, type] = {}
+_STREAM_POSITIONS: Dict[str, type] = {}
 
 
 def register_mixer(kind: str, cls: type) -> None:
@@ -71,6 +79,26 @@ def register_norm(kind: str, cls: type) -> None:
 
 def register_position(kind: str, cls: type) -> None:
     _POSITIONS[kind] = cls
+
+
+def register_block(kind: str, cls: type) -> None:
+    """A block class: ``param_specs(spec, hidden) -> {name: ParamSpec}`` (class method),
+    ``__init__(spec, hidden, dtype, device)``, ``load(tensors, dtype, device)``,
+    ``entry_norm`` (the norm part that feeds its first branch; the block before it
+    applies that norm in the launch that also adds its own last branch),
+    ``cache_request()`` and
+    ``forward(h, x, ctx, cache_entry, writes_cache, next_norm) -> x_next``: h is the
+    32-bit stream [T, H], updated in place; x = entry_norm(h); x_next = next_norm(h)
+    after the update, or None when next_norm is None."""
+    _BLOCKS[kind] = cls
+
+
+def register_stream_position(kind: str, cls: type) -> None:
+    """A position encoding added to the stream after the embedding:
+    ``param_specs(spec, hidden)`` (class method), ``__init__(spec, hidden, dtype,
+    device)``, ``load(tensors, device)`` and ``forward(h, ctx)``, which adds to the
+    32-bit stream h [T, H] in place from ``ctx.positions``."""
+    _STREAM_POSITIONS[kind] = cls
 
 
 def _lookup(table: Dict[str, type], what: str, kind: str) -> type:
@@ -94,3 +122,11 @@ def norm_class(kind: str) -> type:
 
 def position_class(kind: str) -> type:
     return _lookup(_POSITIONS, "position encoding", kind)
+
+
+def block_class(kind: str) -> type:
+    return _lookup(_BLOCKS, "block", kind)
+
+
+def stream_position_class(kind: str) -> type:
+    return _lookup(_STREAM_POSITIONS, "stream position", kind)

@@ -17,7 +17,7 @@ from typing import Dict, Optional
 import torch
 
 from ..config.base import BlockSpec
-from .base import ParamSpec, feed_forward_class, mixer_class, norm_class
+from .base import ParamSpec, feed_forward_class, mixer_class, norm_class, register_block
 from .norm import fused_residual
 
 
@@ -54,6 +54,14 @@ class Block:
             out[f"ffn.{k}"] = v
         return out
 
+    @property
+    def entry_norm(self):
+        """The norm that feeds this block's first branch."""
+        return self.pre_mixer_norm
+
+    def cache_request(self):
+        return self.mixer.cache_request()
+
     def load(self, tensors: Dict[str, torch.Tensor], dtype: torch.dtype,
              device: torch.device) -> None:
         def sub(prefix):
@@ -76,6 +84,9 @@ class Block:
         x3 = ctx.new(*x.shape) if next_norm is not None else None
         _join(h, d, self.post_ffn_norm, next_norm, x3)
         return x3
+
+
+register_block("sequential", Block)
 
 
 def _join(h, y, post, nxt, x_out) -> None:

@@ -1,8 +1,10 @@
 """Each part alone against the plain functions, and the generality of the
 assembly: a toy mixer with state of its own, another arrangement, activation
 and norm flavour, a block called twice and a layer that reads another layer's
-cache, a feed-forward with routing and a position encoding of another formula.  The toy parts live here and are registered from here; no file of the
-library changes for them."""
+cache, a feed-forward with routing and a position encoding of another formula,
+a block of another shape (both branches from one norm) and a learned position
+table added to the stream.  The toy parts live here and are registered from
+here; no file of the library changes for them."""
 import dataclasses
 import json
 import math
@@ -478,3 +480,173 @@ def test_toy_routed_feed_forward_and_toy_position_encoding():
         got.append(eng.step([(s, [t])], [[0]]))
     eng.release(s)
     close(torch.cat(got), ref, 2e-4)
+
+
+# ------- a block of another shape and a position table added to the stream, both toys
+class ParallelBlockSpec:
+    """h += mixer(norm(h)) + ffn(norm(h)): one norm, both branches from it."""
+    kind = "toy_parallel"
+
+    def __init__(self, mixer, feed_forward, norm):
+        self.mixer, self.feed_forward, self.norm = mixer, feed_forward, norm
+
+
+class ParallelBlock:
+    def __init__(self, spec, hidden_size, dtype, device):
+        from agave_b200.parts import feed_forward_class, mixer_class, norm_class
+        self.norm = norm_class(spec.norm.kind)(spec.norm, hidden_size, dtype, device)
+        self.mixer = mixer_class(spec.mixer.kind)(spec.mixer, hidden_size, dtype, device)
+        self.ffn = feed_forward_class(spec.feed_forward.kind)(spec.feed_forward, hidden_size,
+                                                              dtype, device)
+
+    @classmethod
+    def param_specs(cls, spec, hidden_size):
+        from agave_b200.parts import feed_forward_class, mixer_class, norm_class
+        out = {f"norm.{k}": v
+               for k, v in norm_class(spec.norm.kind).param_specs(spec.norm, hidden_size).items()}
+        out.update({f"mixer.{k}": v for k, v in
+                    mixer_class(spec.mixer.kind).param_specs(spec.mixer, hidden_size).items()})
+        out.update({f"ffn.{k}": v for k, v in feed_forward_class(spec.feed_forward.kind)
+                    .param_specs(spec.feed_forward, hidden_size).items()})
+        return out
+
+    @property
+    def entry_norm(self):
+        return self.norm
+
+    def cache_request(self):
+        return self.mixer.cache_request()
+
+    def load(self, tensors, dtype, device):
+        sub = lambda p: {k[len(p) + 1:]: v for k, v in tensors.items() if k.startswith(p + ".")}
+        self.norm.load(sub("norm"), device)
+        self.mixer.load(sub("mixer"), dtype, device)
+        self.ffn.load(sub("ffn"), dtype, device)
+
+    def forward(self, h, x, ctx, cache_entry, writes_cache, next_norm):
+        y = self.mixer.forward(x, ctx, cache_entry, writes_cache)
+        d = self.ffn.forward(x, ctx)
+        for branch in (y, d):                        # (partial sums over ranges of K are added)
+            h += branch.float().sum(0) if branch.dim() == 3 else branch.float()
+        if next_norm is None:
+            return None
+        x_next = ctx.new(*x.shape)
+        next_norm.forward(h, x_next)
+        return x_next
+
+
+class LearnedPositionsSpec:
+    kind = "toy_learned_positions"
+
+    def __init__(self, n_positions):
+        self.n_positions = n_positions
+
+
+class LearnedPositions:
+    """h[t] += table[position of t]: a position encoding with no seat inside a mixer."""
+
+    def __init__(self, spec, hidden_size, dtype, device):
+        self.spec = spec
+
+    @classmethod
+    def param_specs(cls, spec, hidden_size):
+        from agave_b200.parts import ParamSpec
+        return {"table.weight": ParamSpec((spec.n_positions, hidden_size), "float32")}
+
+    def load(self, tensors, device):
+        self.table = tensors["table.weight"].to(device=device, dtype=torch.float32).contiguous()
+
+    def forward(self, h, ctx):
+        from agave_b200 import kernels
+        add = torch.empty_like(h)
+        kernels.embed(ctx.positions, self.table, 1.0, add)      # the library's own gather
+        h += add
+
+
+class ParallelConfig:
+    def __init__(self, raw):
+        self.raw = raw
+
+    @classmethod
+    def from_dict(cls, raw):
+        return cls(raw)
+
+    def to_model_spec(self):
+        from agave_b200.config import (AttentionSpec, GatedFeedForwardSpec, ModelSpec, NormSpec,
+                                       default_schedule)
+        r = self.raw
+        norm = NormSpec(eps=r["eps"], zero_centered=False)
+        att = AttentionSpec(n_heads=r["heads"], n_kv_heads=r["kv_heads"], head_dim=r["head_dim"],
+                            scale=r["head_dim"] ** -0.5, window=r["window"], qk_norm=None,
+                            position=None)
+        ffn = GatedFeedForwardSpec(intermediate_size=r["inter"], activation="gelu_tanh")
+        blocks = tuple(ParallelBlockSpec(att, ffn, norm) for _ in range(r["layers"]))
+        return ModelSpec(hidden_size=r["hidden"], vocab_size=r["vocab"], embed_scale=1.0,
+                         blocks=blocks, schedule=default_schedule(len(blocks)), final_norm=norm,
+                         tie_embeddings=True, max_positions=r["positions"],
+                         stream_position=LearnedPositionsSpec(r["positions"]))
+
+
+def parallel_plain(raw, w, tokens):
+    T = len(tokens)
+    nh, nkv, hd = raw["heads"], raw["kv_heads"], raw["head_dim"]
+    h = w["toy.embed.weight"][torch.tensor(tokens)] + w["toy.stream_position.table.weight"][:T]
+    for l in range(raw["layers"]):
+        p = f"toy.blocks.{l}."
+        x = P.rms_norm(h, w[p + "norm.weight"], raw["eps"], add_one=False)
+        q = (x @ w[p + "mixer.q_proj.weight"].T).reshape(T, nh, hd)
+        k = (x @ w[p + "mixer.k_proj.weight"].T).reshape(T, nkv, hd)
+        v = (x @ w[p + "mixer.v_proj.weight"].T).reshape(T, nkv, hd)
+        y = P.attention(q, k, v, hd ** -0.5, raw["window"]) @ w[p + "mixer.o_proj.weight"].T
+        d = P.geglu(x, w[p + "ffn.gate_proj.weight"], w[p + "ffn.up_proj.weight"],
+                    w[p + "ffn.down_proj.weight"])
+        h = h + y + d
+    return P.rms_norm(h, w["toy.final_norm.weight"], raw["eps"], add_one=False) \
+        @ w["toy.embed.weight"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_block_of_another_shape_and_positions_added_to_the_stream(dtype):
+    """A block that is not "norm, mixer, add, norm, feed-forward, add" and a position
+    encoding that is not a rotation inside a mixer: registered here, built through the
+    block and stream-position registries, loaded by name, stepped whole, token by token
+    and through the generation loop (whose steps are recorded, these parts being
+    launches only)."""
+    from safetensors.torch import load_file
+    from agave_b200.config import register_architecture
+    from agave_b200.engine.api import Engine
+    from agave_b200.parts import register_block, register_stream_position
+    from agave_b200.weights import write_model_folder
+    register_block("toy_parallel", ParallelBlock)
+    register_stream_position("toy_learned_positions", LearnedPositions)
+    register_architecture("ToyParallelLM", ParallelConfig, lambda c: ToyNames())
+    raw = {"architectures": ["ToyParallelLM"], "hidden": 96, "vocab": 260, "layers": 3,
+           "heads": 4, "kv_heads": 2, "head_dim": 32, "window": 11, "inter": 160, "eps": 1e-5,
+           "positions": 128}
+    store = torch.float32 if dtype == "float32" else torch.bfloat16
+    with tempfile.TemporaryDirectory() as d:
+        write_model_folder(d, raw, seed=13, std=0.06, norm_std=0.1, dtype=store)
+        w = {k: v.double() for k, v in load_file(os.path.join(d, "model.safetensors")).items()}
+        eng = Engine(d, dtype=dtype, max_tokens=512, max_batch=4)
+    seqs = [random_tokens(n, 260, 30 + n) for n in (37, 12)]
+    refs = [parallel_plain(raw, w, s) for s in seqs]
+    slots = [eng.acquire() for _ in seqs]
+    starts = [29, 5]
+    out = eng.step([(slots[i], seqs[i][:starts[i]]) for i in range(2)],
+                   [list(range(starts[i])) for i in range(2)])
+    got = [[out[:starts[0]]], [out[starts[0]:]]]
+    for k in range(8):
+        live = [i for i in range(2) if starts[i] + k < len(seqs[i])]
+        res = eng.step([(slots[i], [seqs[i][starts[i] + k]]) for i in live], [[0]] * len(live))
+        for j, i in enumerate(live):
+            got[i].append(res[j:j + 1])
+    for i in range(2):
+        close(torch.cat(got[i]), refs[i], 2e-4 if dtype == "float32" else 3e-2)
+        eng.release(slots[i])
+    prompts = [s[:6] for s in seqs]
+    outs = eng.generate(prompts, max_new_tokens=5, stop_token_ids=[])
+    for pr, o in zip(prompts, outs):
+        ref = parallel_plain(raw, w, pr + o)
+        for k, t in enumerate(o):
+            row = ref[len(pr) - 1 + k]
+            assert row[t] >= row.max() - (1e-3 if dtype == "float32" else 6e-2) * row.abs().max()
