@@ -99,13 +99,12 @@ class _DecodeGraph:
                           cu_seqlens=v["cu"], slots=v["slots"], lens=v["lens"],
                           max_len=runner.cache.max_seq_len, max_new=1, cache=runner.cache,
                           dtype=runner.dtype, device=runner.device, lens_host=lens_host)
-        h = runner.model.hidden_states(ctx)
         engine.sampler.note_inputs(v["tokens"], v["slots"])
-        if (params.greedy and params.repeat_penalty == 1.0 and engine.fused_greedy and
-                runner.model.greedy_tokens(h, self.rows, ctx, self.next_dev)):
-            self.logits = None         # the greatest logit was found in the head's epilogue
-            return
-        self.logits = runner.model.logits(h, self.rows, ctx)
+        fused = params.greedy and params.repeat_penalty == 1.0 and engine.fused_greedy
+        self.logits = runner.model.run_step(ctx, self.rows,
+                                            choose_into=self.next_dev if fused else None)
+        if self.logits is None:
+            return                     # the greatest logit was found in the head's epilogue
         engine.sampler.choose(self.logits, self.next_dev, params, seed, v["slots"], self.seq_ids,
                               v["steps"], penalise=True, dev_params=self.words)
 

@@ -222,7 +222,7 @@ class Runner:
             ctx.lens_host = plan["lens"]
             kernels._perf.n_tokens += T
         try:
-            h = self.model.hidden_states(ctx)
+            logits = self.model.run_step(ctx, rows_dev if rows else None)
         except Cancelled:
             # nothing is committed: lengths stay, the room reserved for the step goes back
             for s, _ in entries:
@@ -232,7 +232,7 @@ class Runner:
         self.commit(entries)
         if not rows:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
-        return self.model.logits(h, rows_dev, ctx)
+        return logits
 
     def _record_prompt(self, plan, rows: Sequence[int], key) -> "_PromptGraph":
         """Record the prompt step of these sizes.  Recording runs nothing; the caller
@@ -249,8 +249,7 @@ class Runner:
         g.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g.graph):
             ctx, rows_dev = self._context_on(plan, g.dev)
-            h = self.model.hidden_states(ctx)
-            g.logits = self.model.logits(h, rows_dev, ctx)
+            g.logits = self.model.run_step(ctx, rows_dev)
         while len(self._prompt_graphs) >= PROMPT_GRAPHS:
             self._prompt_graphs.popitem(last=False)
         self._prompt_graphs[key] = g

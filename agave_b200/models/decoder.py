@@ -61,6 +61,7 @@ class DecoderModel:
                                                            dtype, device)
         self.embed_table: Optional[torch.Tensor] = None
         self.head: Optional[Linear] = None
+        self.native = None             # the C++ host side of a step, if the model allows it
         for call in spec.schedule:
             if not 0 <= call.block < len(self.blocks):
                 raise ValueError(f"the run order names block {call.block}, which does not exist")
@@ -105,6 +106,8 @@ class DecoderModel:
         else:
             self.head = Linear(tensors["lm_head.weight"].to(device=dev, dtype=dt).contiguous(),
                                role="lm_head")
+        from .native import NativeStep
+        self.native = NativeStep.build(self)
 
     def weight_bytes(self) -> int:
         seen, n = set(), 0
@@ -174,3 +177,37 @@ class DecoderModel:
 
     def forward(self, ctx, rows: torch.Tensor) -> torch.Tensor:
         return self.logits(self.hidden_states(ctx), rows, ctx)
+
+    def run_step(self, ctx, rows: Optional[torch.Tensor],
+                 choose_into: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+        """A whole step: 32-bit logits [len(rows), V] of the stream rows ``rows`` (None:
+        the step only fills the cache and nothing is returned); or, with ``choose_into``
+        (int32, len(rows)), the index of each row's greatest logit goes there without the
+        logits being written, where the head has that kernel (else the logits are
+        returned and nothing is chosen).
+
+        Models of standard blocks take the C++ host path (one call into the library for
+        the whole step); others, and any step whose operations are being timed, run
+        through the Python parts launch by launch."""
+        n_rows = rows.numel() if rows is not None else 0
+        if ctx.cancel is not None and ctx.cancel.is_set():
+            raise Cancelled("cancelled before the step")
+        greedy = (choose_into is not None and n_rows > 0 and self.dtype == torch.bfloat16 and
+                  n_rows <= kernels.ARGMAX_MAX_ROWS and self.spec.hidden_size % 8 == 0 and
+                  self.head.weight.data_ptr() % 16 == 0)
+        if self.native is not None and kernels._perf is None:
+            if n_rows == 0:
+                self.native.run(ctx, None)
+                return None
+            if greedy:
+                self.native.run(ctx, rows, argmax_out=choose_into)
+                return None
+            out = ctx.new(n_rows, self.spec.vocab_size, dtype=torch.float32)
+            self.native.run(ctx, rows, logits=out)
+            return out
+        h = self.hidden_states(ctx)
+        if n_rows == 0:
+            return None
+        if greedy and self.greedy_tokens(h, rows, ctx, choose_into):
+            return None
+        return self.logits(h, rows, ctx)

@@ -9,7 +9,9 @@ steps (random bfloat16 weights, context 8,192), timed on the device with CUDA
 events; ``e2e`` is the same through ``Engine.generate`` with host token ids in
 and out every step.  ``prefill`` is one 2,048-token prompt: ``ms`` for a
 length whose step has been recorded, ``first_seen_ms`` for lengths never run
-before (no recording; the launches come from the host one by one).
+before (no recording: the host launches the step, through the library's C++
+step function), ``first_seen_128_tokens_ms`` the same for prompts of about 128
+tokens.
 ``roofline`` relates the decode step to the bytes it has to read; ``points``
 holds decoding at the other batch sizes of the schedule.
 
@@ -277,13 +279,18 @@ def main():
     # (the first of them also pays what a kernel's first use costs, so it is not counted)
     first_seen = sorted(timed_prompt(prompt[:n_pre - k]) for k in (7, 5, 3, 1))[:3]
     first_seen_ms = sorted(first_seen)[1]
+    # the same for short prompts (time to the first token of a chat turn): what the host
+    # needs to launch a step bounds these
+    short = sorted(timed_prompt(prompt[:128 - k]) for k in (7, 5, 3, 1))[:3]
+    short_ms = sorted(short)[1]
     pre_ms = [timed_prompt(prompt) for _ in range(3 + 5)][3:]
     pre_ms = sorted(pre_ms)[len(pre_ms) // 2]
     pflops = prefill_flops(cfg, n_pre, 1)
     prefill = {"value": round(n_pre / pre_ms * 1e3, 1), "tokens": n_pre,
                "ms": round(pre_ms, 3),
                "frac": round(pflops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
-               "first_seen_ms": round(first_seen_ms, 3)}
+               "first_seen_ms": round(first_seen_ms, 3),
+               "first_seen_128_tokens_ms": round(short_ms, 3)}
 
     # ---- decode at the headline batch, with clocks sampled meanwhile ----
     clocks = ClockSampler()

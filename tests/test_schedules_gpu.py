@@ -405,6 +405,51 @@ def test_a_multimodal_folder_runs_as_its_text_decoder(dtype):
     close(torch.cat(got), ref, TOL[dtype])
 
 
+# ----------------------------------------------- the two host sides of a step
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["B", "C"])
+def test_the_cpp_host_step_launches_what_the_python_parts_launch(name, dtype):
+    """A model of standard blocks runs its steps through one call into the library, which
+    makes the dispatch decisions itself; the Python parts make them launch by launch for
+    every other model.  Both must launch the same kernels with the same arguments: the
+    logits of a prompt step, of decode steps and of a batch are equal bit for bit."""
+    eng, folder = _engine(name, dtype, max_tokens=4096)
+    assert eng.model.native is not None
+    V = TINY[name][0]["vocab_size"]
+    seqs = [random_tokens(n, V, 400 + n) for n in (150, 7, 41)]
+
+    def run():
+        slots = [eng.acquire() for _ in seqs]
+        outs = [eng.step([(slots[i], seqs[i][:-4]) for i in range(3)],
+                         [list(range(len(seqs[i]) - 4)) for i in range(3)])]
+        for k in range(4, 0, -1):
+            outs.append(eng.step([(slots[i], [seqs[i][-k]]) for i in range(3)], [[0]] * 3))
+        outs.append(eng.step([(slots[0], [7])], [[0]]))
+        for s in slots:
+            eng.release(s)
+        return torch.cat(outs)
+
+    native = run()
+    close(native[:146], plain_logits(folder, seqs[0])[:146], TOL[dtype])
+    keep, eng.model.native = eng.model.native, None
+    try:
+        python = run()
+    finally:
+        eng.model.native = keep
+    assert torch.equal(native, python)
+    # and through the generation loop (recorded decode steps, arg max in the head's epilogue)
+    prompts = [s[:9] for s in seqs]
+    a = eng.generate(prompts, max_new_tokens=8, stop_token_ids=[])
+    keep, eng.model.native = eng.model.native, None
+    eng._graphs.clear()
+    try:
+        b = eng.generate(prompts, max_new_tokens=8, stop_token_ids=[])
+    finally:
+        eng.model.native = keep
+        eng._graphs.clear()
+    assert a == b
+
+
 # ------------------------------------------------------------------ cancelling
 def test_cancel_from_another_thread():
     """``Engine.cancel`` stops an eager step between two blocks (nothing is committed, the
