@@ -9,6 +9,10 @@ Cases (Gemma 3 1B layer sizes, random bfloat16 data):
   gemm_gated_decode    gate/up product, 8 tokens
   gemm_down_decode     down projection, 8 tokens (K split over a cluster or partial sums)
   gemm_lm_head_decode  the head over a 262,144-row table, 8 tokens
+  gemm_lm_head_argmax_decode   the same with the arg max taken in the epilogue (no logits written)
+  gemm_qkv_fused_prefill_4b    q/k/v product with norm, rotation, cache store and transposed
+                       values in its epilogue, 4B layer sizes (width 2,560, 8 + 4 + 4 heads
+                       of 256), 2,048 tokens
   gemm_qkv_prefill     q/k/v projection (32-bit output), 2,048 tokens
   qk_norm_rope_prefill q/k norm + rotation + cache store + transposed values, 2,048 tokens
   norm_prefill         residual sum + two RMS norms over 2,048 rows
@@ -152,6 +156,43 @@ def case_lm_head():
     return (lambda i: kernels.linear_tc(x, w, out)), 2 * 8 * V * H, V * H * 2 + 8 * V * 4, 1
 
 
+def case_lm_head_argmax():
+    from . import kernels
+    x, w = _rnd(8, H), _rnd(V, H, scale=0.02)
+    out = torch.empty(8, dtype=torch.int32, device=DEV)
+    return (lambda i: kernels.linear_argmax(x, w, out)), 2 * 8 * V * H, V * H * 2, 1
+
+
+def case_qkv_fused_prefill_4b(T=2048):
+    from . import kernels
+    Hq, nh, nkv, hd, PAGE = 2560, 8, 4, 256, 64
+    width = (nh + 2 * nkv) * hd
+    c = 6
+    xs = [_rnd(T, Hq) for _ in range(c)]
+    w = _rnd(width, Hq, scale=0.02)
+    qkvs = [torch.empty(T, width, dtype=torch.bfloat16, device=DEV) for _ in range(c)]
+    n_pages = T // PAGE
+    kp = [torch.empty(n_pages, PAGE, nkv, hd, dtype=torch.bfloat16, device=DEV) for _ in range(c)]
+    vp = [torch.empty(n_pages, PAGE, nkv, hd, dtype=torch.bfloat16, device=DEV) for _ in range(c)]
+    table = torch.arange(n_pages, dtype=torch.int32, device=DEV).reshape(1, n_pages)
+    slots = torch.zeros(1, dtype=torch.int32, device=DEV)
+    lens = torch.tensor([T], dtype=torch.int32, device=DEV)
+    seq_index = torch.zeros(T, dtype=torch.int32, device=DEV)
+    positions = torch.arange(T, dtype=torch.int32, device=DEV)
+    cu = torch.tensor([0, T], dtype=torch.int32, device=DEV)
+    cos = torch.empty(T, hd // 2, device=DEV)
+    sin = torch.empty_like(cos)
+    kernels.rope_table(positions, hd, 10000.0, 1.0, cos, sin)
+    wn = torch.ones(hd, device=DEV)
+    vt = kernels.prefill_values_scratch(T, 1, nkv, hd, torch.device(DEV))
+
+    def fn(i):
+        kernels.qkv_prefill(xs[i], w, qkvs[i], nh, nkv, hd, wn, wn, 1e-6, cos, sin, positions,
+                            seq_index, k_pool=kp[i], v_pool=vp[i], page_table=table, slots=slots,
+                            lens=lens, page=PAGE, cap=T, vt=vt, cu_seqlens=cu)
+    return fn, 2 * T * width * Hq, (width * Hq + T * Hq + 2 * T * width) * 2, c
+
+
 def case_attention_prefill(window=0, legacy=False):
     from . import kernels
     T = 2048
@@ -252,6 +293,8 @@ CASES = {
     "gemm_gated_decode": lambda: case_gemm_gated(8),
     "gemm_down_decode": lambda: case_gemm_down(8),
     "gemm_lm_head_decode": case_lm_head,
+    "gemm_lm_head_argmax_decode": case_lm_head_argmax,
+    "gemm_qkv_fused_prefill_4b": case_qkv_fused_prefill_4b,
     "gemm_qkv_prefill": lambda: case_gemm_qkv(2048),
     "qk_norm_rope_prefill": case_qk_norm_rope_prefill,
     "norm_prefill": case_norm_prefill,
