@@ -70,6 +70,7 @@ def _ptr(t: Optional[torch.Tensor]):
     return ctypes.c_void_p(t.data_ptr())
 
 
+NVTX = os.environ.get("AGAVE_B200_NVTX", "0") == "1"     # name every launch for a profiler
 _launches = 0
 _perf = None          # an active agave_b200.perf.PerfCounters, or None
 
@@ -77,7 +78,8 @@ _perf = None          # an active agave_b200.perf.PerfCounters, or None
 def _span(op: str, nbytes: int = 0, flops: int = 0):
     """A timing span around one launch while operations are being timed."""
     if _perf is None or torch.cuda.is_current_stream_capturing():
-        return _perf_mod.NULL_SPAN           # (a recording holds no timing events)
+        # (a recording holds no timing events)
+        return _perf_mod.NvtxSpan(op) if NVTX else _perf_mod.NULL_SPAN
     return _perf.span(op, nbytes, flops)
 
 

@@ -195,7 +195,7 @@ class DecoderModel:
         greedy = (choose_into is not None and n_rows > 0 and self.dtype == torch.bfloat16 and
                   n_rows <= kernels.ARGMAX_MAX_ROWS and self.spec.hidden_size % 8 == 0 and
                   self.head.weight.data_ptr() % 16 == 0)
-        if self.native is not None and kernels._perf is None:
+        if self.native is not None and kernels._perf is None and not kernels.NVTX:
             if n_rows == 0:
                 self.native.run(ctx, None)
                 return None

@@ -34,6 +34,24 @@ class _Null:
 NULL_SPAN = _Null()
 
 
+class NvtxSpan:
+    """An NVTX range around one launch: with ``AGAVE_B200_NVTX=1`` every operation is
+    named on a profiler's timeline (steps then run launch by launch through the Python
+    parts, also while a CUDA graph is recorded: a range is a host-side mark)."""
+    __slots__ = ("op",)
+
+    def __init__(self, op: str):
+        self.op = op
+
+    def __enter__(self):
+        torch.cuda.nvtx.range_push(self.op)
+        return self
+
+    def __exit__(self, *a):
+        torch.cuda.nvtx.range_pop()
+        return False
+
+
 class _Span:
     __slots__ = ("owner", "op", "nbytes", "flops", "e0")
 

@@ -48,9 +48,10 @@ def test_simple_tokenizer_round_trip():
     assert [PIECES[i] for i in tok.encode("at")] == ["at"]
 
 
-def _run(cmd):
+def _run(cmd, env=None):
     return subprocess.run([sys.executable, "-m", "agave_b200"] + cmd, capture_output=True,
-                          text=True, cwd=ROOT, timeout=900)
+                          text=True, cwd=ROOT, timeout=900,
+                          env=dict(os.environ, **env) if env else None)
 
 
 @pytest.mark.gpu
@@ -91,5 +92,10 @@ def test_text_prompt_random_weights_and_profile():
             assert r.returncode == 0, r.stderr[-2000:]
             outs.append(json.loads(r.stdout.strip().splitlines()[-1])["output_ids"])
         assert outs[0] == outs[1] and len(outs[0]) <= 8
+        # every launch named by an NVTX range (steps then go through the Python parts):
+        # the same tokens
+        r = _run([d, "--tokens", "2,9,30,77,5", "-n", "8", "--json"], env={"AGAVE_B200_NVTX": "1"})
+        assert r.returncode == 0, r.stderr[-2000:]
+        assert json.loads(r.stdout.strip().splitlines()[-1])["output_ids"] == outs[0]
         r = _run([d, "--tokens", "2,9", "-n", "2"])
         assert r.returncode != 0 and "safetensors" in r.stderr
