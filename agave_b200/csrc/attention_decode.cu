@@ -560,6 +560,7 @@ attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq) {
     const int r_new = p - j0;                                 // in [0, 64): the first tile holds p
     if (has) {
         // (the first tile; the others are loaded inside the walk below, after the wait)
+#pragma unroll 2
         for (int i = tid; i < DM_KEYS * CPR; i += DM_THREADS) {
             const int r = i / CPR, c = i % CPR;
             const int off = dm_swz<HDP>(r, c);
@@ -574,24 +575,32 @@ attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq) {
             }
         }
     }
+    const bool fused = fq.part != nullptr;                  // (then hd == HDP)
+    if (has && fused) {
+        // rows of the query tile beyond the group's heads are zero: nothing of the
+        // predecessor's, so they are written before the wait
+        for (int i = tid; i < (DM_HEADS - gc) * CPR; i += DM_THREADS)
+            *reinterpret_cast<uint4*>(Qs + dm_swz<HDP>(gc + i / CPR, i % CPR)) = make_uint4(0, 0, 0, 0);
+    }
     pdl_wait();
     if (has) {
-    const bool fused = fq.part != nullptr;                  // (then hd == HDP)
     const size_t f_width = (size_t)(a.nh + 2 * a.nkv) * hd;  // a row of the projection
     const size_t f_stride = (size_t)gridDim.z * f_width;     // one partial sum of the batch
     const float* f_cos = fused && fq.cosv ? fq.cosv + (size_t)b * (hd / 2) : nullptr;
     const float* f_sin = fused && fq.cosv ? fq.sinv + (size_t)b * (hd / 2) : nullptr;
     // queries of the group: rows beyond the group's heads and dims beyond hd are zero
+    if (!fused) {
+#pragma unroll 1
     for (int i = tid; i < DM_HEADS * CPR; i += DM_THREADS) {
         const int r = i / CPR, c = i % CPR;
         T* dst = Qs + dm_swz<HDP>(r, c);
         if (r < gc && c * 8 < hd) {
-            if (!fused)
-                cp_async16(dst, (const T*)a.q + (size_t)b * a.q_stride + (size_t)(h0 + r) * hd +
-                                    c * 8);
+            cp_async16(dst, (const T*)a.q + (size_t)b * a.q_stride + (size_t)(h0 + r) * hd +
+                                c * 8);
         } else {
             *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
         }
+    }
     }
     if (fused)
         for (int r = warp; r < gc; r += DM_THREADS / 32)
@@ -639,6 +648,7 @@ attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq) {
         __syncthreads();
         const int* ro = rowoff + (tt & 1) * DM_KEYS;
         const int rn = p - jt;                               // the new position's row, if in this tile
+#pragma unroll 2
         for (int i = tid; i < DM_KEYS * CPR; i += DM_THREADS) {
             const int r = i / CPR, c = i % CPR;
             const int off = dm_swz<HDP>(r, c);

@@ -94,7 +94,8 @@ def test_text_prompt_random_weights_and_profile():
         assert outs[0] == outs[1] and len(outs[0]) <= 8
         # every launch named by an NVTX range (steps then go through the Python parts):
         # the same tokens
-        r = _run([d, "--tokens", "2,9,30,77,5", "-n", "8", "--json"], env={"AGAVE_B200_NVTX": "1"})
+        r = _run([d, "--random-weights", "3", "--tokens", "2,9,30,77,5", "-n", "8", "--json"],
+                 env={"AGAVE_B200_NVTX": "1"})
         assert r.returncode == 0, r.stderr[-2000:]
         assert json.loads(r.stdout.strip().splitlines()[-1])["output_ids"] == outs[0]
         r = _run([d, "--tokens", "2,9", "-n", "2"])
