@@ -165,6 +165,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // A cluster of token tiles of 16 writes into its peers' shared memory: every CTA of the
+    // cluster must have started by then.  All arrive here without waiting (the loader goes
+    // on to request weights) and wait just before the first such write, or, the two warps
+    // that write nothing, before the cluster's second barrier.
+    if (TL::PUSH && cluster_reduce)
+        asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
 
     if (warp == 0 && lane == 0) {
         // ------------------------------------------------------------ loader
@@ -245,6 +251,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
         // up rows of the features whose gate rows lanes 0-63 hold)
         const int f = HALF ? m0 + (quarter & 1) * 32 + lane : m0 + quarter * 32 + lane;
         pdl_wait();          // this warp writes global memory: not before the predecessor is done
+        // (the peers run: asked here, where the answer comes while the products are under way)
+        if (TL::PUSH && cluster_reduce) asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
         bool ok = mbar_wait(acc_full, 0);
         if (!ok) {
             atomicCAS(&g_gemm_status, 0, (3 << 8));
@@ -403,6 +411,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
     }
     __syncwarp();
     if (cluster_reduce) {
+        if (TL::PUSH && warp < 2) asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
         pdl_wait();
         // The gridDim.z CTAs of a cluster hold partial sums of one tile over
         // consecutive ranges of K.  Each adds, in rank order, a slice of the tile's
