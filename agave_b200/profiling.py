@@ -26,6 +26,8 @@ Cases (Gemma 3 1B layer sizes, random bfloat16 data):
   norm_decode          residual sum + two RMS norms over 8 rows of 16 partial sums
   decode_step          whole decode steps of a 6-layer model (vocabulary 32,768), batch 8
   decode_step_b64      the same at batch 64
+  decode_step_4b, decode_step_27b   the same with the layer sizes of the 4B model (batch 8,
+                       256..4,096 positions) and the 27B model (batch 16, 2,048 positions)
   prefill_step         whole prompt steps of the same model, one prompt of 2,048 tokens
 
 Each case prints the mean time per call: the calls run back to back from a CUDA
@@ -252,13 +254,19 @@ def case_norm_decode():
         y.numel() * 4 + 3 * 8 * H * 4, 1
 
 
-def _six_layer_engine(max_batch=16):
+# layer sizes of the larger family members: hidden, heads, kv heads, head_dim, scalar, ff, window
+SIZES = {"1b": (H, NH, NKV, HD, HD, FF, 512), "4b": (2560, 8, 4, 256, 256, 10240, 1024),
+         "27b": (5376, 32, 16, 128, 168, 21504, 1024)}
+
+
+def _six_layer_engine(max_batch=16, sizes="1b"):
     from .engine.api import Engine
+    h, nh, nkv, hd, scalar, ff, window = SIZES[sizes]
     cfg = {
         "architectures": ["Gemma3ForCausalLM"], "model_type": "gemma3_text",
-        "num_hidden_layers": 6, "hidden_size": H, "num_attention_heads": NH,
-        "num_key_value_heads": NKV, "head_dim": HD, "query_pre_attn_scalar": HD,
-        "intermediate_size": FF, "vocab_size": 32768, "sliding_window": 512,
+        "num_hidden_layers": 6, "hidden_size": h, "num_attention_heads": nh,
+        "num_key_value_heads": nkv, "head_dim": hd, "query_pre_attn_scalar": scalar,
+        "intermediate_size": ff, "vocab_size": 32768, "sliding_window": window,
         "sliding_window_pattern": 6, "rope_local_base_freq": 10000.0, "rope_theta": 1000000.0,
         "rms_norm_eps": 1e-6, "max_position_embeddings": 8192, "eos_token_id": 1}
     return Engine.from_config(cfg, seed=2, dtype="bfloat16", max_tokens=max_batch * 8192,
@@ -277,10 +285,10 @@ def case_prefill_step():
     return fn, 0, 0, 0
 
 
-def case_decode_step(batch=8):
-    eng = _six_layer_engine(max_batch=max(16, batch))
+def case_decode_step(batch=8, sizes="1b", lo=128, hi=2048):
+    eng = _six_layer_engine(max_batch=max(16, batch), sizes=sizes)
     g = torch.Generator().manual_seed(0)
-    lens = torch.linspace(128, 2048, batch).round().int().tolist()
+    lens = torch.linspace(lo, hi, batch).round().int().tolist()
     prompts = [torch.randint(3, 32768, (n,), generator=g).tolist() for n in lens]
     slots = [eng.acquire() for _ in prompts]
     eng.step([(s, p) for s, p in zip(slots, prompts)], [[] for _ in prompts])
@@ -309,6 +317,8 @@ CASES = {
     "norm_decode": case_norm_decode,
     "decode_step": case_decode_step,
     "decode_step_b64": lambda: case_decode_step(64),
+    "decode_step_4b": lambda: case_decode_step(8, "4b", 256, 4096),
+    "decode_step_27b": lambda: case_decode_step(16, "27b", 2048, 2048),
     "prefill_step": case_prefill_step,
 }
 
