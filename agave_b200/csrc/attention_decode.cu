@@ -38,6 +38,13 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
 }
+__device__ __forceinline__ void cp_async_commit() {
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+// waits until at most one group of copies, the one committed last, is still in flight
+__device__ __forceinline__ void cp_async_wait_but_one() {
+    asm volatile("cp.async.wait_group 1;" ::: "memory");
+}
 __device__ __forceinline__ void cp_async_wait_all() {
     asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
 }
@@ -352,6 +359,10 @@ struct DmShape {
     static constexpr int RW = DM_HEADS / NW;            // rows per warp in the softmax
     static constexpr int DW = HDP / NW;                 // dims per warp in the weighted sum
     static constexpr int NP = DW / 16;                  // pairs of 8-wide column tiles per warp
+    // Tiles of keys and values in shared memory: head sizes up to 128 leave room for a
+    // second one, so that a CTA that walks several tiles has the next one under way while it
+    // works on this one (at 256 a second tile would cost the second CTA of the SM)
+    static constexpr int NBUF = HDP <= 128 ? 2 : 1;
     static_assert(DW % 16 == 0 && (KW == 16 || KW == 8), "unsupported split of a tile over warps");
 };
 
@@ -507,6 +518,9 @@ attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq) {
     float* stat = Ss + DM_HEADS * DM_KEYS;                  // [16][2] running maximum and sum
     float* fac = stat + DM_HEADS * 2;                       // [16] what a new maximum scales O by
     int* rowoff = reinterpret_cast<int*>(fac + DM_HEADS);   // [2][64]: this tile's and the next
+    T* Ks1 = reinterpret_cast<T*>(rowoff + 2 * DM_KEYS);    // the second tile (NBUF == 2)
+    T* Vs1 = Ks1 + DM_KEYS * HDP;
+    constexpr int NBUF = Sh::NBUF;
 
     // The W = gridDim.x CTAs of a sequence share its tiles of 64 keys: CTA w walks the
     // tiles w, w + W, w + 2 W, ... with a running softmax.  W is chosen from the batch
@@ -552,28 +566,41 @@ attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq) {
         const int row = key % a.cap;
         return key <= p ? table[row / a.page] * a.page + row % a.page : -1;
     };
-    if (has && tid < DM_KEYS) rowoff[tid] = row_of(j0);
+    if (has && tid < DM_KEYS) {
+        rowoff[tid] = row_of(j0);
+        if (NBUF == 2 && n_tiles > 1) rowoff[DM_KEYS + tid] = row_of(j0 + W * DM_KEYS);
+    }
     __syncthreads();
     constexpr int CPR = HDP / 8;
     // Keys and values of earlier positions were stored by earlier steps: their copies
     // start before the wait too.  Only the row of position p is the predecessor's.
     const int r_new = p - j0;                                 // in [0, 64): the first tile holds p
-    if (has) {
-        // (the first tile; the others are loaded inside the walk below, after the wait)
+    // One tile's keys and values into shared memory as one group of copies.  ro: the
+    // tile's cache rows (-1 beyond position p); skip: the row of the new position, which is
+    // not in the cache yet (or out of the tile).
+    auto request_tile = [&](T* kd, T* vd, const int* ro, int skip) {
 #pragma unroll 2
         for (int i = tid; i < DM_KEYS * CPR; i += DM_THREADS) {
             const int r = i / CPR, c = i % CPR;
             const int off = dm_swz<HDP>(r, c);
-            if (r == r_new) continue;
-            if (rowoff[r] >= 0 && c * 8 < hd) {
-                const size_t src = ((size_t)rowoff[r] * a.nkv + g) * hd + c * 8;
-                cp_async16(Ks + off, (const T*)a.k_pool + src);
-                cp_async16(Vs + off, (const T*)a.v_pool + src);
+            if (r == skip) continue;
+            if (ro[r] >= 0 && c * 8 < hd) {
+                const size_t src = ((size_t)ro[r] * a.nkv + g) * hd + c * 8;
+                cp_async16(kd + off, (const T*)a.k_pool + src);
+                cp_async16(vd + off, (const T*)a.v_pool + src);
             } else {
-                *reinterpret_cast<uint4*>(Ks + off) = make_uint4(0, 0, 0, 0);
-                *reinterpret_cast<uint4*>(Vs + off) = make_uint4(0, 0, 0, 0);
+                *reinterpret_cast<uint4*>(kd + off) = make_uint4(0, 0, 0, 0);
+                *reinterpret_cast<uint4*>(vd + off) = make_uint4(0, 0, 0, 0);
             }
         }
+        cp_async_commit();
+    };
+    if (has) {
+        // the first tile (and the second, where there is room for it); the others are
+        // requested inside the walk below
+        request_tile(Ks, Vs, rowoff, r_new);
+        if (NBUF == 2 && n_tiles > 1)
+            request_tile(Ks1, Vs1, rowoff + DM_KEYS, p - (j0 + W * DM_KEYS));
     }
     const bool fused = fq.part != nullptr;                  // (then hd == HDP)
     if (has && fused) {
@@ -607,7 +634,7 @@ attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq) {
             dm_head_from_partials<HDP>(fq.part + (size_t)b * f_width + (size_t)(h0 + r) * hd, fq.G,
                                        f_stride, fq.wq, fq.eps, f_cos, f_sin, Qs, r, nullptr, lane);
     // the new position's key and value: from the cache, or formed here and stored
-    auto new_row = [&](int r, int cache_row) {
+    auto new_row = [&](T* Ks, T* Vs, int r, int cache_row) {
         if (fused && fq.store_kv) {
             const bool writer = blockIdx.y % groups_per_kv == 0 && cache_row >= 0;
             T* kd = writer ? (T*)a.k_pool + ((size_t)cache_row * a.nkv + g) * hd : nullptr;
@@ -634,37 +661,35 @@ attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq) {
             }
         }
     };
-    if (r_new >= 0 && r_new < DM_KEYS) new_row(r_new, rowoff[r_new]);
+    if (r_new >= 0 && r_new < DM_KEYS) new_row(Ks, Vs, r_new, rowoff[r_new]);
     constexpr int NP = Sh::NP;
     float o[NP * 2][4] = {};
     for (int tt = 0; tt < n_tiles; ++tt) {
     const int jt = j0 + tt * W * DM_KEYS;                   // first key of this tile
     const int n = min(DM_KEYS, p - jt + 1);                 // its keys
-    // the rows of the next tile: the lookup runs beside this tile's work
+    const bool last = tt + 1 == n_tiles;
+    // this tile's buffers (the tiles alternate between two where there are two)
+    T* const Kt = (NBUF == 2 && (tt & 1)) ? Ks1 : Ks;
+    T* const Vt = (NBUF == 2 && (tt & 1)) ? Vs1 : Vs;
+    // the rows of the tile that is requested next (the next one; with two buffers the one
+    // after it): the lookup runs beside this tile's work
+    const int ahead = NBUF * W * DM_KEYS;
     int next_row = -1;
-    if (tt + 1 < n_tiles && tid < DM_KEYS) next_row = row_of(jt + W * DM_KEYS);
+    if (tt + NBUF < n_tiles && tid < DM_KEYS) next_row = row_of(jt + ahead);
     if (tt > 0) {
-        // the tile before has been used up: this one replaces it
-        __syncthreads();
         const int* ro = rowoff + (tt & 1) * DM_KEYS;
         const int rn = p - jt;                               // the new position's row, if in this tile
-#pragma unroll 2
-        for (int i = tid; i < DM_KEYS * CPR; i += DM_THREADS) {
-            const int r = i / CPR, c = i % CPR;
-            const int off = dm_swz<HDP>(r, c);
-            if (r == rn) continue;
-            if (ro[r] >= 0 && c * 8 < hd) {
-                const size_t src = ((size_t)ro[r] * a.nkv + g) * hd + c * 8;
-                cp_async16(Ks + off, (const T*)a.k_pool + src);
-                cp_async16(Vs + off, (const T*)a.v_pool + src);
-            } else {
-                *reinterpret_cast<uint4*>(Ks + off) = make_uint4(0, 0, 0, 0);
-                *reinterpret_cast<uint4*>(Vs + off) = make_uint4(0, 0, 0, 0);
-            }
+        if (NBUF == 1) {
+            // the tile before has been used up: this one replaces it
+            __syncthreads();
+            request_tile(Kt, Vt, ro, rn);
         }
-        if (rn >= 0 && rn < DM_KEYS) new_row(rn, ro[rn]);
+        if (rn >= 0 && rn < DM_KEYS) new_row(Kt, Vt, rn, ro[rn]);
     }
-    cp_async_wait_all();
+    // (with two buffers the tile after this one stays in flight; the first tile waits for
+    // everything because the queries' copies, made after the dependency wait, are among it,
+    // and so does a CTA's last tile, which may hold the new position)
+    if (NBUF == 2 && !last && tt > 0) cp_async_wait_but_one(); else cp_async_wait_all();
     __syncthreads();
     // ---- scores of 16 heads x this warp's keys
     if constexpr (Sh::KW == 16) {
@@ -674,7 +699,7 @@ attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq) {
             unsigned af[4], bf[4];
             dm_ldsm4(dm_smem(Qs + dm_swz<HDP>(lane & 15, kk * 2 + (lane >> 4))), af);
             const int mat = lane >> 3, r = lane & 7;
-            dm_ldsm4(dm_smem(Ks + dm_swz<HDP>(warp * 16 + r + (mat >> 1) * 8, kk * 2 + (mat & 1))),
+            dm_ldsm4(dm_smem(Kt + dm_swz<HDP>(warp * 16 + r + (mat >> 1) * 8, kk * 2 + (mat & 1))),
                      bf);
             dm_mma(s[0], af, bf[0], bf[1]);
             dm_mma(s[1], af, bf[2], bf[3]);
@@ -696,7 +721,7 @@ attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq) {
             unsigned a0[4], a1[4], bf[4];
             dm_ldsm4(dm_smem(Qs + dm_swz<HDP>(lane & 15, k2 * 4 + (lane >> 4))), a0);
             dm_ldsm4(dm_smem(Qs + dm_swz<HDP>(lane & 15, k2 * 4 + 2 + (lane >> 4))), a1);
-            dm_ldsm4(dm_smem(Ks + dm_swz<HDP>(warp * 8 + (lane & 7), k2 * 4 + (lane >> 3))), bf);
+            dm_ldsm4(dm_smem(Kt + dm_swz<HDP>(warp * 8 + (lane & 7), k2 * 4 + (lane >> 3))), bf);
             dm_mma(s[0], a0, bf[0], bf[1]);
             dm_mma(s[1], a1, bf[2], bf[3]);
         }
@@ -747,14 +772,23 @@ attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq) {
             for (int nn = 0; nn < NP; ++nn) {
                 unsigned bf[4];
                 const int mat = lane >> 3, r = lane & 7;
-                dm_ldsm4t(dm_smem(Vs + dm_swz<HDP>(kk * 16 + r + (mat & 1) * 8,
+                dm_ldsm4t(dm_smem(Vt + dm_swz<HDP>(kk * 16 + r + (mat & 1) * 8,
                                                    warp * (Sh::DW / 8) + nn * 2 + (mat >> 1))), bf);
                 dm_mma(o[nn * 2], af, bf[0], bf[1]);
                 dm_mma(o[nn * 2 + 1], af, bf[2], bf[3]);
             }
         }
     }
-    if (tt + 1 < n_tiles && tid < DM_KEYS) rowoff[((tt + 1) & 1) * DM_KEYS + tid] = next_row;
+    if (NBUF == 2) {
+        if (tt + 2 < n_tiles) {
+            // this tile's buffers are used up: the tile after the next goes there
+            if (tid < DM_KEYS) rowoff[(tt & 1) * DM_KEYS + tid] = next_row;
+            __syncthreads();
+            request_tile(Kt, Vt, rowoff + (tt & 1) * DM_KEYS, p - (jt + ahead));
+        }
+    } else if (!last && tid < DM_KEYS) {
+        rowoff[((tt + 1) & 1) * DM_KEYS + tid] = next_row;
+    }
     }   // tiles
     {
         if (cs > 1 && used > 1) __syncthreads();   // Osm lies over the last key tile
@@ -848,7 +882,8 @@ int launch_decode_mma(const DecodeArgs& a0, int B, cudaStream_t stream, const Fu
     auto kern = attention_decode_mma_kernel<HDP>;
     constexpr int DM_THREADS = DmShape<HDP>::NT;
     constexpr int smem = (2 * DM_KEYS + DM_HEADS) * HDP * 2 + DM_HEADS * DM_KEYS * (2 + 4) +
-                         DM_HEADS * 3 * 4 + 2 * DM_KEYS * 4;
+                         DM_HEADS * 3 * 4 + 2 * DM_KEYS * 4 +
+                         (DmShape<HDP>::NBUF - 1) * 2 * DM_KEYS * HDP * 2;
     static bool configured = false;
     static int resident = 0;
     if (!configured) {

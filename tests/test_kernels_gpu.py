@@ -622,7 +622,8 @@ def test_attention_decode_split_long_sequences(dtype, nh, nkv, hd):
             assert (out[0, :hd].float() - v_pool[page5, 5, 0].float()).abs().max() > 0.1
 
 
-@pytest.mark.parametrize("B,nh,nkv,hd", [(64, 8, 4, 256), (96, 4, 1, 128), (200, 4, 2, 64)])
+@pytest.mark.parametrize("B,nh,nkv,hd", [(64, 8, 4, 256), (96, 4, 1, 128), (200, 4, 2, 64),
+                                        (700, 4, 2, 64), (300, 2, 2, 128)])
 def test_attention_decode_many_sequences_walk_several_tiles(B, nh, nkv, hd):
     """With many sequences a sequence gets few CTAs, each of which walks several key
     tiles with a running softmax (and, with fewer still, a single CTA the whole
