@@ -76,7 +76,7 @@ __device__ __forceinline__ float silu_fast(float t) { return __fdividef(t, 1.0f 
 // rows of the same features share one 128-row tile and one accumulator, and the
 // epilogue warps exchange the halves through shared memory (decoding: twice as
 // many CTAs stream the weights).
-template <int BN, int MODE>
+template <int BN, int MODE, int SLIM = 0>
 struct Tile {
     static constexpr bool DUAL = MODE == 1;
     static constexpr bool HALF = MODE == 2;
@@ -91,8 +91,12 @@ struct Tile {
     // stages, which a slower CTA still reads while faster peers already push.
     static constexpr bool PUSH = BN == 16 && !DUAL;
     static constexpr int INBOX_BYTES = PUSH ? BN * 144 * 4 : 0;
+    // SLIM: a ring of three stages, so that three CTAs share an SM: for a weight whose
+    // tiles number between two and three times the SMs, which would otherwise run as one
+    // full round and a second, nearly empty one
     static constexpr int BUDGET =
-        DUAL ? 196 * 1024 : (BN >= 128 ? 196 * 1024 : (PUSH ? 96 * 1024 : 108 * 1024));
+        SLIM ? 56 * 1024
+             : (DUAL ? 196 * 1024 : (BN >= 128 ? 196 * 1024 : (PUSH ? 96 * 1024 : 108 * 1024)));
     static constexpr int STAGES_RAW = (BUDGET - XCHG_BYTES) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : (STAGES_RAW < 2 ? 2 : STAGES_RAW);
     static constexpr int TMEM_COLS_RAW = DUAL ? 2 * BN : BN;
@@ -115,7 +119,7 @@ template <> __device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat
     *p = __float2bfloat16_rn(v);
 }
 
-template <int BN, int MODE, typename TO>
+template <int BN, int MODE, typename TO, int SLIM = 0>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_w2,
@@ -123,7 +127,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
                     int K, long long ldc, long long split_stride, int kb_per_split, int act,
                     int cluster_reduce, int* __restrict__ argmax_out) {
     pdl_launch_next();
-    using TL = Tile<BN, MODE>;
+    using TL = Tile<BN, MODE, SLIM>;
     constexpr bool GATED = MODE == 1;          // two accumulators
     constexpr bool HALF = MODE == 2;           // gate and up rows in one tile
     extern __shared__ uint8_t smem_raw[];
@@ -1301,16 +1305,16 @@ int make_map(CUtensorMap* out, const void* ptr, long long rows, long long K, lon
     return 0;
 }
 
-template <int BN, int MODE, typename TO>
+template <int BN, int MODE, typename TO, int SLIM = 0>
 int launch(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx, void* out, int T,
            int N, int K, long long ldc, long long split_stride, int splits, int kb_per_split,
            int act, int cluster_reduce, cudaStream_t stream, int* argmax_out = nullptr) {
-    using TL = Tile<BN, MODE>;
+    using TL = Tile<BN, MODE, SLIM>;
     static_assert(MODE != 0 || BN * RED_LD * 4 <= TL::STAGES * TL::STAGE_BYTES,
                   "a partial tile must fit the ring of stages");
     AGV_REQUIRE(!cluster_reduce || BN * RED_LD * 4 <= TL::STAGES * TL::STAGE_BYTES,
                 "linear: a partial tile of %d tokens does not fit the ring of stages", BN);
-    auto kern = gemm_tcgen05_kernel<BN, MODE, TO>;
+    auto kern = gemm_tcgen05_kernel<BN, MODE, TO, SLIM>;
     static bool configured = false;
     if (!configured) {
         AGV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -1512,6 +1516,18 @@ AGV_API int agv_linear_tc(const void* x, const void* w, const void* w2, void* ou
     }
     if (w2) {
         AGV_REQUIRE(out_dtype == AGV_BF16, "linear: the gated form writes bfloat16");
+        if (half && bn == 16) {
+            // between two and three CTAs per SM: the form of which three fit (see Tile)
+            int sms = 148;
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
+            const long long ctas =
+                (long long)((N + TILE_M / 2 - 1) / (TILE_M / 2)) * (creduce ? splits : 1);
+            if (ctas > 2LL * sms && ctas <= 3LL * sms)
+                return launch<16, 2, __nv_bfloat16, 1>(mw, mw2, mx, out, T, N, K, ldc, 0,
+                                                       creduce ? splits : 1,
+                                                       creduce ? kb_per : kb_total, act, creduce,
+                                                       stream);
+        }
         if (half)
             return launch_bn<2, __nv_bfloat16>(bn, mw, mw2, mx, out, T, N, K, ldc, 0,
                                                creduce ? splits : 1, creduce ? kb_per : kb_total,

@@ -87,10 +87,13 @@ def test_linear_tensor_cores_row_strided_input_and_output():
 
 @pytest.mark.parametrize("T,N,K,act", [(3, 224, 96, "gelu_tanh"), (40, 130, 320, "silu"),
                                        (150, 256, 64, "gelu_tanh"), (256, 128, 64, "gelu_tanh"),
-                                       (600, 390, 448, "silu"), (2049, 1000, 1152, "gelu_tanh")])
+                                       (600, 390, 448, "silu"), (2049, 1000, 1152, "gelu_tanh"),
+                                       (9, 19230, 448, "gelu_tanh")])
 def test_linear_tensor_cores_gated(T, N, K, act):
     """From 256 tokens on, the gated product runs on pairs of CTAs (cta_group::2): one
-    pair and one k-block, token and feature counts that end inside a tile, many rounds."""
+    pair and one k-block, token and feature counts that end inside a tile, many rounds.
+    A few tokens over a weight with between two and three tiles per SM run with three
+    CTAs to the SM and a ring of three stages (more k-blocks than stages)."""
     from agave_b200 import kernels
     x = rnd(T, K, dtype=torch.bfloat16, seed=7)
     wg, wu = rnd(N, K, dtype=torch.bfloat16, seed=8, scale=0.3), rnd(N, K, dtype=torch.bfloat16, seed=9, scale=0.3)
