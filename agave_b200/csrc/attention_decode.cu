@@ -733,10 +733,13 @@ attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq) {
         }
     }
     __syncthreads();
-    // ---- softmax weights relative to the running maximum: a warp's rows
+    // ---- softmax weights relative to the running maximum.  Rows are dealt round the
+    // warps, so that the few heads of a small group get a warp each; rows beyond the
+    // group's heads are padding whose products nobody reads, and are left as they are.
 #pragma unroll
     for (int rr = 0; rr < Sh::RW; ++rr) {
-        const int row = warp * Sh::RW + rr;
+        const int row = rr * Sh::NW + warp;
+        if (row >= gc) break;
         const float s0 = Ss[row * DM_KEYS + lane], s1 = Ss[row * DM_KEYS + lane + 32];
         const float m_old = tt > 0 ? stat[row * 2] : -INFINITY;
         const float l_old = tt > 0 ? stat[row * 2 + 1] : 0.f;
