@@ -714,22 +714,24 @@ attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq) {
             }
     } else {
         // 8 keys: one load brings their chunks of 32 dims, two products into sums of
-        // their own (no chain between them), added at the end
-        float s[2][4] = {};
+        // their own; four such sums in turn, so that a product waits for the one two loads
+        // back and not for its neighbour, added at the end
+        float s[4][4] = {};
 #pragma unroll
         for (int k2 = 0; k2 < HDP / 32; ++k2) {
             unsigned a0[4], a1[4], bf[4];
             dm_ldsm4(dm_smem(Qs + dm_swz<HDP>(lane & 15, k2 * 4 + (lane >> 4))), a0);
             dm_ldsm4(dm_smem(Qs + dm_swz<HDP>(lane & 15, k2 * 4 + 2 + (lane >> 4))), a1);
             dm_ldsm4(dm_smem(Kt + dm_swz<HDP>(warp * 8 + (lane & 7), k2 * 4 + (lane >> 3))), bf);
-            dm_mma(s[0], a0, bf[0], bf[1]);
-            dm_mma(s[1], a1, bf[2], bf[3]);
+            dm_mma(s[(k2 & 1) * 2], a0, bf[0], bf[1]);
+            dm_mma(s[(k2 & 1) * 2 + 1], a1, bf[2], bf[3]);
         }
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             const int key = warp * 8 + tig * 2 + (e & 1);
             const int row = gid + (e >> 1) * 8;
-            Ss[row * DM_KEYS + key] = key < n ? (s[0][e] + s[1][e]) * a.scale : -INFINITY;
+            Ss[row * DM_KEYS + key] =
+                key < n ? ((s[0][e] + s[1][e]) + (s[2][e] + s[3][e])) * a.scale : -INFINITY;
         }
     }
     __syncthreads();
