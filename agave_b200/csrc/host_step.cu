@@ -23,6 +23,7 @@
 #include "common.cuh"
 #include <stdlib.h>
 #include <string.h>
+#include <utility>
 #include <vector>
 
 // ---- the launchers of the other files (all return 0 or a negative code)
@@ -36,6 +37,10 @@ int agv_linear_simt(const void*, const void*, const void*, void*, int, int, int,
 int agv_linear_tc(const void*, const void*, const void*, void*, int, int, int, long long, long long,
                   int, int, int, int, int, cudaStream_t);
 int agv_linear_tc_splits(int, int);
+int agv_gemv_few_supported(int, int, int, long long, int);
+int agv_gemv_few(const void*, const void*, int, int, int, const void*, long long, const float*, float*,
+                 const float*, const float*, const float*, float, float, void*, long long, int,
+                 cudaStream_t);
 int agv_linear_tc_argmax(const void*, const void*, int*, int, int, int, long long, cudaStream_t);
 int agv_qkv_prefill_tc_supported(int, int, int, long long, long long);
 int agv_qkv_prefill_tc(const void*, const void*, int, int, long long, void*, long long, int, int,
@@ -379,6 +384,88 @@ struct Run {
         return linear_partial(z, b.ff, b.w_down, H, b.ff, T, false);
     }
 
+    // Whether a decode step of this few tokens runs as dot products with the joins in the
+    // projections' prologues (gemv_few.cu): five kernels a layer instead of seven.
+    bool few_tokens() const {
+        static const int most = [] {
+            const char* v = getenv("AGAVE_B200_FEW_TOKENS");
+            return v ? atoi(v) : 1;
+        }();
+        static const bool fused_decode = env_on("AGAVE_B200_FUSED_DECODE_ATTENTION", true);
+        if (s.mode != 1 || s.T > most || s.T < 1 || m.dtype != AGV_BF16 || !fused_decode) return false;
+        for (int ci : m.call_block) {
+            const AgvBlockDesc& b = m.blocks[ci];
+            const int width = (b.nh + 2 * b.nkv) * b.hd;
+            const int rotary_dim = b.rope_slot >= 0 ? b.rotary_dim : 0;
+            if (!b.w_pre_mixer || !b.w_pre_ffn) return false;
+            if (!agv_attention_decode_fused_supported(AGV_BF16, b.hd, rotary_dim)) return false;
+            if (!agv_gemv_few_supported(s.T, width, m.H, 8, 1) ||
+                !agv_gemv_few_supported(s.T, m.H, b.nh * b.hd, b.nh * b.hd, 0) ||
+                !agv_gemv_few_supported(s.T, b.ff, m.H, 8, 1) ||
+                !agv_gemv_few_supported(s.T, m.H, b.ff, b.ff, 0))
+                return false;
+        }
+        return !m.call_block.empty();
+    }
+
+    // The blocks of such a step.  The stream alternates between two buffers, because the
+    // CTAs of a projection all read it while one of them writes the joined stream.  Returns
+    // the buffer that holds the stream after the last block.
+    float* few_blocks(float* h, float* const* cosv, float* const* sinv) {
+        const int T = s.T, H = m.H;
+        const int n_calls = (int)m.call_block.size();
+        float* cur = h;
+        float* other = (float*)ar.take((size_t)T * H * 4);
+        float* y_down = (float*)ar.take((size_t)T * H * 4);
+        const float* pend_y = nullptr;           // the branch the next join adds
+        const float* pend_w = nullptr;
+        float pend_eps = 0.f;
+        const size_t mark = ar.top;
+        for (int ci = 0; ci < n_calls; ++ci) {
+            ar.top = mark;
+            const AgvBlockDesc& b = m.blocks[m.call_block[ci]];
+            const AgvCacheDesc& c = m.caches[m.call_cache[ci]];
+            const int width = (b.nh + 2 * b.nkv) * b.hd;
+            const float* cs = b.rope_slot >= 0 ? cosv[b.rope_slot] : nullptr;
+            const float* sn = b.rope_slot >= 0 ? sinv[b.rope_slot] : nullptr;
+            float* qkv = (float*)ar.take((size_t)T * width * 4);
+            void* att = ar.take((size_t)T * b.nh * b.hd * 2);
+            float* y_out = (float*)ar.take((size_t)T * H * 4);
+            void* z = ar.take((size_t)T * b.ff * 2);
+            const int max_keys_raw = b.window ? (b.window < s.max_len ? b.window : s.max_len) : s.max_len;
+            const int max_keys = max_keys_raw > 1 ? max_keys_raw : 1;
+            int chunk = 0, n_splits = 0;
+            agv_attention_decode_plan(b.hd, AGV_BF16, max_keys, &chunk, &n_splits);
+            if (n_splits > 16) n_splits = 16;
+            float* acc = (float*)ar.take((size_t)s.B * b.nh * n_splits * b.hd * 4);
+            float* ml = (float*)ar.take((size_t)s.B * b.nh * n_splits * 2 * 4);
+            if (dry()) continue;
+            // q/k/v of the stream joined with the block before (or the stream as embedded)
+            did(agv_gemv_few(b.w_qkv, nullptr, width, H, T, nullptr, 0, cur, pend_y ? other : nullptr,
+                             pend_y, pend_w, b.w_pre_mixer, pend_eps, b.eps, qkv, width, 0, stream));
+            if (pend_y) std::swap(cur, other);
+            did(agv_attention_decode_fused(qkv, 1, b.wq_norm, b.wk_norm, b.qk_eps, cs, sn, 1, att,
+                                           c.k_pool, c.v_pool, c.page_table, s.slots, s.positions,
+                                           c.max_pages, c.page, c.cap, s.B, b.nh, b.nkv, b.hd, b.scale,
+                                           b.window, max_keys, acc, ml, s.decode_counters, stream));
+            did(agv_gemv_few(b.w_out, nullptr, H, b.nh * b.hd, T, att, (long long)b.nh * b.hd, nullptr,
+                             nullptr, nullptr, nullptr, nullptr, 0.f, 0.f, y_out, H, 0, stream));
+            did(agv_gemv_few(b.w_gate, b.w_up, b.ff, H, T, nullptr, 0, cur, other, y_out,
+                             b.w_post_mixer, b.w_pre_ffn, b.eps, b.eps, z, b.ff, b.act, stream));
+            std::swap(cur, other);
+            did(agv_gemv_few(b.w_down, nullptr, H, b.ff, T, z, b.ff, nullptr, nullptr, nullptr, nullptr,
+                             nullptr, 0.f, 0.f, y_down, H, 0, stream));
+            pend_y = y_down;
+            pend_w = b.w_post_ffn;
+            pend_eps = b.eps;
+        }
+        ar.top = mark;
+        if (!dry() && pend_y)                    // the last block's branch joins the stream
+            did(agv_norm_residual(cur, pend_y, AGV_F32, 1, 0, pend_w, nullptr, nullptr, m.dtype, nullptr,
+                                  T, H, pend_w ? pend_eps : 0.f, 0.f, 1, stream));
+        return cur;
+    }
+
     int step() {
         const int T = s.T, H = m.H, e = esz();
         const int n_calls = (int)m.call_block.size();
@@ -399,13 +486,15 @@ struct Run {
                                        r.factor, stream));
             }
         }
-        if (n_calls > 0 && !dry()) {
+        const bool few = few_tokens();
+        if (few) h = few_blocks(h, cosv.data(), sinv.data());
+        if (!few && n_calls > 0 && !dry()) {
             const AgvBlockDesc& b0 = m.blocks[m.call_block[0]];
             did(agv_norm_residual(h, nullptr, AGV_F32, 1, 0, nullptr, b0.w_pre_mixer, xa, m.dtype,
                                   nullptr, T, H, 0.f, b0.eps, 0, stream));
         }
         const size_t mark = ar.top;
-        for (int ci = 0; ci < n_calls; ++ci) {
+        for (int ci = 0; !few && ci < n_calls; ++ci) {
             ar.top = mark;                    // a layer's buffers are reused by the next
             const AgvBlockDesc& b = m.blocks[m.call_block[ci]];
             const AgvCacheDesc& c = m.caches[m.call_cache[ci]];

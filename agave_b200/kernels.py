@@ -631,6 +631,58 @@ def linear_partial(x: torch.Tensor, w: torch.Tensor, cheap_sum: bool = False,
     return out
 
 
+GEMV_FEW_MAX_ROWS = 4
+# Decode steps of at most this many tokens run their projections as dot products with the
+# joins in their prologues (five kernels a layer instead of seven); measured: one token
+# gains 13 %, two lose 3 %.
+FEW_TOKENS = int(os.environ.get("AGAVE_B200_FEW_TOKENS", "1"))
+
+
+def gemv_few_supported(T: int, N: int, K: int, ldx: int = 8, join: bool = False) -> bool:
+    """Whether ``gemv_few`` takes these sizes (one to four rows; see the kernel)."""
+    return bool(library().agv_gemv_few_supported(T, N, K, ctypes.c_longlong(ldx), 1 if join else 0))
+
+
+def gemv_few(w: torch.Tensor, out: torch.Tensor, x: Optional[torch.Tensor] = None,
+             w2: Optional[torch.Tensor] = None, activation: str = "gelu_tanh",
+             h_in: Optional[torch.Tensor] = None, h_out: Optional[torch.Tensor] = None,
+             y: Optional[torch.Tensor] = None, w_post: Optional[torch.Tensor] = None,
+             w_next: Optional[torch.Tensor] = None, eps_post: float = 0.0, eps_next: float = 0.0,
+             op: str = "linear") -> None:
+    """A projection of one to four tokens, one dot product per warp and output row:
+    out [T, N] = x w^T in 32-bit, or with w2 the gated pair in bfloat16.  x [T, K]
+    bfloat16, or None: then x = bfloat16(norm(h_out; w_next)) with
+    h_out = h_in + norm(y; w_post) (or h_in + y, or h_in itself without y) formed in the
+    kernel's prologue; h_out (another buffer than h_in) receives the joined stream."""
+    N, K = w.shape
+    _dense(w, "w")
+    assert w.dtype == torch.bfloat16 and out.stride(-1) == 1
+    T = out.shape[0]
+    if x is not None:
+        assert x.shape == (T, K) and x.dtype == torch.bfloat16 and x.stride(1) == 1
+    else:
+        assert h_in is not None and h_in.shape == (T, K) and w_next is not None
+        _f32(h_in, "h_in"); _f32(h_out, "h_out"); _f32(y, "y"); _f32(w_post, "w_post")
+        _f32(w_next, "w_next"); _dense(h_in, "h_in")
+        for t in (h_out, y):
+            if t is not None:
+                _dense(t, "join operand")
+                assert t.shape == (T, K)
+    if w2 is not None:
+        _dense(w2, "w2")
+        assert w2.shape == w.shape and out.dtype == torch.bfloat16
+    else:
+        assert out.dtype == torch.float32
+    assert out.shape == (T, N)
+    nbytes = (2 if w2 is not None else 1) * N * K * 2 + _nbytes(x, h_in, y, out)
+    with _span(op, nbytes, 2 * T * N * K * (2 if w2 is not None else 1)):
+        _check(library().agv_gemv_few(
+            _ptr(w), _ptr(w2), N, K, T, _ptr(x), ctypes.c_longlong(x.stride(0) if x is not None else 0),
+            _ptr(h_in), _ptr(h_out), _ptr(y), _ptr(w_post), _ptr(w_next), ctypes.c_float(eps_post),
+            ctypes.c_float(eps_next), _ptr(out), ctypes.c_longlong(out.stride(0)), ACT[activation],
+            _stream()))
+
+
 def attention_prefill_mma(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor,
                           cu_seqlens: torch.Tensor, max_len: int, n_heads: int, n_kv_heads: int,
                           head_dim: int, scale: float, window: int) -> None:

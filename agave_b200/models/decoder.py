@@ -20,7 +20,7 @@ import torch
 
 from .. import kernels
 from ..config.base import ModelSpec
-from ..engine.batch import Cancelled
+from ..engine.batch import DECODE, Cancelled
 from ..parts import block as _block      # registers the "sequential" block
 from ..parts.base import ParamSpec, block_class, norm_class, stream_position_class
 from ..parts.linear import Linear
@@ -62,6 +62,7 @@ class DecoderModel:
         self.embed_table: Optional[torch.Tensor] = None
         self.head: Optional[Linear] = None
         self.native = None             # the C++ host side of a step, if the model allows it
+        self.standard = False          # every block the standard arrangement of the library's parts
         for call in spec.schedule:
             if not 0 <= call.block < len(self.blocks):
                 raise ValueError(f"the run order names block {call.block}, which does not exist")
@@ -106,7 +107,8 @@ class DecoderModel:
         else:
             self.head = Linear(tensors["lm_head.weight"].to(device=dev, dtype=dt).contiguous(),
                                role="lm_head")
-        from .native import NativeStep
+        from .native import NativeStep, standard_blocks
+        self.standard = standard_blocks(self)
         self.native = NativeStep.build(self)
 
     def weight_bytes(self) -> int:
@@ -131,6 +133,81 @@ class DecoderModel:
         return n
 
     # --------------------------------------------------------------- forward
+    def _few_tokens(self, ctx) -> bool:
+        """Whether this step is a decode step of so few tokens that its projections run as
+        dot products with the joins in their prologues (``kernels.gemv_few``)."""
+        T = ctx.n_tokens
+        if ctx.mode != DECODE or not self.standard or self.dtype != torch.bfloat16 or \
+                not 1 <= T <= kernels.FEW_TOKENS or not self.spec.schedule:
+            return False
+        H = self.spec.hidden_size
+        for call in self.spec.schedule:
+            b = self.blocks[call.block]
+            s = b.mixer.spec
+            width = (s.n_heads + 2 * s.n_kv_heads) * s.head_dim
+            rd = b.mixer.position.rotary_dim if b.mixer.position is not None else 0
+            ff = b.ffn.spec.intermediate_size
+            if not (kernels.attention_decode_fused_supported(self.dtype, s.head_dim, rd) and
+                    kernels.gemv_few_supported(T, width, H, join=True) and
+                    kernels.gemv_few_supported(T, H, s.n_heads * s.head_dim, s.n_heads * s.head_dim) and
+                    kernels.gemv_few_supported(T, ff, H, join=True) and
+                    kernels.gemv_few_supported(T, H, ff, ff)):
+                return False
+        return True
+
+    def _blocks_few_tokens(self, h: torch.Tensor, ctx) -> torch.Tensor:
+        """The blocks of such a step; returns the buffer that holds the stream afterwards
+        (it alternates between two, because all CTAs of a projection read the stream while
+        one of them writes the joined one)."""
+        T, H = h.shape
+        cur, other = h, ctx.new(T, H, dtype=torch.float32)
+        y_down = ctx.new(T, H, dtype=torch.float32)
+        pend = None                                    # (branch output, its norm) the next join adds
+        sched = self.spec.schedule
+        for i, call in enumerate(sched):
+            if ctx.cancel is not None and ctx.cancel.is_set():
+                raise Cancelled(f"cancelled before block {i} of {len(sched)}")
+            b = self.blocks[call.block]
+            m, s = b.mixer, b.mixer.spec
+            nh, nkv, hd = s.n_heads, s.n_kv_heads, s.head_dim
+            width = (nh + 2 * nkv) * hd
+            cos = sin = None
+            if m.position is not None:
+                cos, sin = m.position.tables(ctx)
+            view = ctx.cache.kv_view(call.cache)
+            qkv = ctx.new(T, width, dtype=torch.float32)
+            post = pend[1] if pend is not None else None
+            kernels.gemv_few(m.qkv.weight, qkv, h_in=cur, h_out=other if pend is not None else None,
+                             y=pend[0] if pend is not None else None,
+                             w_post=post.weight if post is not None else None,
+                             w_next=b.pre_mixer_norm.weight,
+                             eps_post=post.eps if post is not None else 0.0,
+                             eps_next=b.pre_mixer_norm.eps, op="qkv")
+            if pend is not None:
+                cur, other = other, cur
+            att = ctx.new(T, nh * hd)
+            kernels.attention_decode_fused(
+                qkv.view(1, T, width), m.q_norm_weight, m.k_norm_weight,
+                s.qk_norm.eps if s.qk_norm is not None else 0.0, cos, sin, True, att, view, ctx, nh,
+                nkv, hd, s.scale, s.window or 0)
+            y_out = ctx.new(T, H, dtype=torch.float32)
+            kernels.gemv_few(m.out.weight, y_out, x=att, op="out_proj")
+            z = ctx.new(T, b.ffn.spec.intermediate_size)
+            pm = b.post_mixer_norm
+            kernels.gemv_few(b.ffn.gate_up.w_gate, z, w2=b.ffn.gate_up.w_up,
+                             activation=b.ffn.spec.activation, h_in=cur, h_out=other, y=y_out,
+                             w_post=pm.weight if pm is not None else None,
+                             w_next=b.pre_ffn_norm.weight, eps_post=pm.eps if pm is not None else 0.0,
+                             eps_next=b.pre_ffn_norm.eps, op="gate_up")
+            cur, other = other, cur
+            kernels.gemv_few(b.ffn.down.weight, y_down, x=z, op="down")
+            pend = (y_down, b.post_ffn_norm)
+        if pend is not None:                           # the last block's branch joins the stream
+            post = pend[1]
+            kernels.norm_residual(cur, pend[0], post.weight if post is not None else None, None, None,
+                                  eps_post=post.eps if post is not None else 0.0)
+        return cur
+
     def hidden_states(self, ctx) -> torch.Tensor:
         """The 32-bit stream [T, H] after the last block (before the final norm)."""
         spec = self.spec
@@ -142,6 +219,8 @@ class DecoderModel:
         sched = spec.schedule
         if not sched:
             return h
+        if self._few_tokens(ctx):
+            return self._blocks_few_tokens(h, ctx)
         x = ctx.new(T, spec.hidden_size)
         self.blocks[sched[0].block].entry_norm.forward(h, x)
         for i, call in enumerate(sched):

@@ -61,6 +61,30 @@ def _ptr(t: Optional[torch.Tensor]):
 ENABLED = os.environ.get("AGAVE_B200_NATIVE_STEP", "1") != "0"
 
 
+def standard_blocks(model) -> bool:
+    """Whether every block of the model is the standard arrangement of the library's own
+    parts (RMS norms, attention mixer with or without rotation, gated feed-forward), every
+    call writes its own cache entry and nothing is added to the stream: what the C++ step
+    function and the few-token decode path know how to run."""
+    if model.head is None or model.stream_position is not None:
+        return False
+    if any(not c.writes_cache for c in model.spec.schedule):
+        return False
+    for b in model.blocks:
+        if type(b) is not Block or type(b.mixer) is not AttentionMixer or \
+                type(b.ffn) is not GatedFeedForward:
+            return False
+        if not isinstance(b.mixer.spec, AttentionSpec) or \
+                not isinstance(b.ffn.spec, GatedFeedForwardSpec):
+            return False
+        for n in (b.pre_mixer_norm, b.pre_ffn_norm, b.post_mixer_norm, b.post_ffn_norm):
+            if n is not None and type(n) is not RMSNorm:
+                return False
+        if b.mixer.position is not None and type(b.mixer.position) is not RotaryEmbedding:
+            return False
+    return type(model.final_norm) is RMSNorm
+
+
 class NativeStep:
     def __init__(self, handle, lib, model, keep):
         self._handle, self._lib, self.model = handle, lib, model
@@ -77,25 +101,9 @@ class NativeStep:
     # ----------------------------------------------------------------- build
     @classmethod
     def build(cls, model) -> Optional["NativeStep"]:
-        if not ENABLED or model.head is None or model.stream_position is not None:
+        if not ENABLED or not standard_blocks(model):
             return None
         spec = model.spec
-        if any(not c.writes_cache for c in spec.schedule):
-            return None
-        for b in model.blocks:
-            if type(b) is not Block or type(b.mixer) is not AttentionMixer or \
-                    type(b.ffn) is not GatedFeedForward:
-                return None
-            if not isinstance(b.mixer.spec, AttentionSpec) or \
-                    not isinstance(b.ffn.spec, GatedFeedForwardSpec):
-                return None
-            for n in (b.pre_mixer_norm, b.pre_ffn_norm, b.post_mixer_norm, b.post_ffn_norm):
-                if n is not None and type(n) is not RMSNorm:
-                    return None
-            if b.mixer.position is not None and type(b.mixer.position) is not RotaryEmbedding:
-                return None
-        if type(model.final_norm) is not RMSNorm:
-            return None
         lib = kernels.library()
         lib.agv_model_create.restype = ctypes.c_void_p
         lib.agv_model_workspace_bytes.restype = ctypes.c_longlong

@@ -150,6 +150,58 @@ def test_linear_tensor_cores_cluster_reduction(splits, T, tile):
     assert rel_err(out, small.float() @ wsm.float().T) < 1e-5
 
 
+@pytest.mark.parametrize("T", [1, 2, 3, 4])
+@pytest.mark.parametrize("N,K", [(1152, 1024), (1536, 1152), (200, 6912), (6912, 1152), (50, 72),
+                                 (1000, 5376)])
+def test_projection_of_a_few_tokens_with_the_join_in_its_prologue(T, N, K):
+    """One dot product per warp and row: plain and gated, x given; and x formed in the
+    prologue from the stream, a branch and both norms (every combination), with the stream
+    written to another buffer."""
+    from agave_b200 import kernels
+    assert kernels.gemv_few_supported(T, N, K, K) and not kernels.gemv_few_supported(5, N, K, K)
+    x = rnd(T + 1, K + 8, dtype=torch.bfloat16, seed=31)[:T, :K]           # a row-strided view
+    w = rnd(N, K, dtype=torch.bfloat16, seed=32, scale=0.05)
+    w2 = rnd(N, K, dtype=torch.bfloat16, seed=33, scale=0.05)
+    out = torch.full((T, N), float("nan"), dtype=torch.float32, device=DEV)
+    kernels.gemv_few(w, out, x=x)
+    assert rel_err(out, x.float() @ w.float().T) < 1e-5
+    for act in ("gelu_tanh", "silu"):
+        g, u = x.float() @ w.float().T, x.float() @ w2.float().T
+        a = torch.nn.functional.gelu(g, approximate="tanh") if act == "gelu_tanh" \
+            else torch.nn.functional.silu(g)
+        outb = torch.full((T, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+        kernels.gemv_few(w, outb, x=x, w2=w2, activation=act)
+        assert rel_err(outb, a * u) < 6e-3
+    if not kernels.gemv_few_supported(T, N, K, join=True):
+        assert T * K * 8 + K * 8 > 200 * 1024
+        return
+    h = rnd(T, K, seed=34)
+    y = rnd(T, K, seed=35)
+    wp, wn = rnd(K, seed=36) * 0.2 + 1, rnd(K, seed=37) * 0.2 + 1
+
+    def norm(v, wt, eps):
+        return v * torch.rsqrt((v * v).mean(-1, keepdim=True) + eps) * wt
+
+    for yy, post in ((y, wp), (y, None), (None, None)):
+        h_out = torch.full_like(h, float("nan"))
+        out = torch.full((T, N), float("nan"), dtype=torch.float32, device=DEV)
+        kernels.gemv_few(w, out, h_in=h, h_out=h_out if yy is not None else None, y=yy, w_post=post,
+                         w_next=wn, eps_post=1e-5, eps_next=1e-6)
+        href = h if yy is None else h + (norm(yy, post, 1e-5) if post is not None else yy)
+        if yy is not None:
+            assert rel_err(h_out, href) < 1e-6
+        xr = norm(href, wn, 1e-6).to(torch.bfloat16).float()
+        assert rel_err(out, xr @ w.float().T) < 2e-3      # (x is rounded to bfloat16 in both)
+    outb = torch.full((T, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    h_out = torch.full_like(h, float("nan"))
+    kernels.gemv_few(w, outb, w2=w2, h_in=h, h_out=h_out, y=y, w_post=wp, w_next=wn, eps_post=1e-5,
+                     eps_next=1e-6)
+    href = h + norm(y, wp, 1e-5)
+    xr = norm(href, wn, 1e-6).to(torch.bfloat16).float()
+    ref = torch.nn.functional.gelu(xr @ w.float().T, approximate="tanh") * (xr @ w2.float().T)
+    assert rel_err(outb, ref) < 8e-3 and rel_err(h_out, href) < 1e-6
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_linear_simt_plain_and_gated(dtype):
     from agave_b200 import kernels
