@@ -137,7 +137,7 @@ gemv_few_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __rest
     const int rpr = GF_WARPS / ks, slice = warp % ks, rl = warp / ks;
     const int per_slice = (K8 + ks - 1) / ks;
     const int c_lo = slice * per_slice, c_hi = min(K8, c_lo + per_slice);
-    constexpr int U = GATED ? 4 : 8;          // 16-byte pieces of a row per lane and batch
+    constexpr int U = GATED ? 5 : 8;          // 16-byte pieces of a row per lane and batch
     const int bpr = max(1, (c_hi - c_lo + 32 * U - 1) / (32 * U));       // batches per row
     const int my_rows = r0 + rl < r1 ? (int)((r1 - r0 - rl + rpr - 1) / rpr) : 0;
     const int n_batches = my_rows * bpr;

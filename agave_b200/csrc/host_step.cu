@@ -389,7 +389,7 @@ struct Run {
     bool few_tokens() const {
         static const int most = [] {
             const char* v = getenv("AGAVE_B200_FEW_TOKENS");
-            return v ? atoi(v) : 1;
+            return v ? atoi(v) : 2;
         }();
         static const bool fused_decode = env_on("AGAVE_B200_FUSED_DECODE_ATTENTION", true);
         if (s.mode != 1 || s.T > most || s.T < 1 || m.dtype != AGV_BF16 || !fused_decode) return false;

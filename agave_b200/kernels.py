@@ -633,9 +633,9 @@ def linear_partial(x: torch.Tensor, w: torch.Tensor, cheap_sum: bool = False,
 
 GEMV_FEW_MAX_ROWS = 4
 # Decode steps of at most this many tokens run their projections as dot products with the
-# joins in their prologues (five kernels a layer instead of seven); measured: one token
-# gains 13 %, two lose 3 %.
-FEW_TOKENS = int(os.environ.get("AGAVE_B200_FEW_TOKENS", "1"))
+# joins in their prologues (five kernels a layer instead of seven); measured at the 1B
+# sizes: one token gains 18 %, two gain 3 %, four lose 22 %.
+FEW_TOKENS = int(os.environ.get("AGAVE_B200_FEW_TOKENS", "2"))
 
 
 def gemv_few_supported(T: int, N: int, K: int, ldx: int = 8, join: bool = False) -> bool:
