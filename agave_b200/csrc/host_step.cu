@@ -398,6 +398,11 @@ struct Run {
             const int width = (b.nh + 2 * b.nkv) * b.hd;
             const int rotary_dim = b.rope_slot >= 0 ? b.rotary_dim : 0;
             if (!b.w_pre_mixer || !b.w_pre_ffn) return false;
+            // (a layer of more than 96 MB is bound by how fast its weights stream, and there
+            // the tensor-core products, fed by TMA, are ahead: measured at the 4B and 27B sizes)
+            const long long weights = 2LL * ((long long)width * m.H + (long long)m.H * b.nh * b.hd +
+                                             3LL * b.ff * m.H);
+            if (weights > 96LL * 1024 * 1024) return false;
             if (!agv_attention_decode_fused_supported(AGV_BF16, b.hd, rotary_dim)) return false;
             if (!agv_gemv_few_supported(s.T, width, m.H, 8, 1) ||
                 !agv_gemv_few_supported(s.T, m.H, b.nh * b.hd, b.nh * b.hd, 0) ||

@@ -147,6 +147,10 @@ class DecoderModel:
             width = (s.n_heads + 2 * s.n_kv_heads) * s.head_dim
             rd = b.mixer.position.rotary_dim if b.mixer.position is not None else 0
             ff = b.ffn.spec.intermediate_size
+            # (a layer of more than 96 MB is bound by how fast its weights stream, and there
+            # the tensor-core products, fed by TMA, are ahead)
+            if 2 * (width * H + H * s.n_heads * s.head_dim + 3 * ff * H) > 96 * 1024 * 1024:
+                return False
             if not (kernels.attention_decode_fused_supported(self.dtype, s.head_dim, rd) and
                     kernels.gemv_few_supported(T, width, H, join=True) and
                     kernels.gemv_few_supported(T, H, s.n_heads * s.head_dim, s.n_heads * s.head_dim) and
