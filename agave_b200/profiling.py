@@ -24,6 +24,8 @@ Cases (Gemma 3 1B layer sizes, random bfloat16 data):
   attention_decode_window_b64, attention_decode_full_b64   the same for 64 sequences (the
                        second with a grid sized for a context of 8,192)
   norm_decode          residual sum + two RMS norms over 8 rows of 16 partial sums
+  gemv_gated_join_one_token, gemv_down_one_token   the gate/up (with the join in its prologue)
+                       and down projections of one token as dot products (gemv_few.cu)
   decode_step          whole decode steps of a 6-layer model (vocabulary 32,768), batch 8
   decode_step_b64      the same at batch 64
   decode_step_4b, decode_step_27b   the same with the layer sizes of the 4B model (batch 8,
@@ -91,6 +93,30 @@ def case_gemm_gated(T):
     wu = [_rnd(FF, H, scale=0.02) for _ in range(c)]
     out = torch.empty(T, FF, dtype=torch.bfloat16, device=DEV)
     return (lambda i: kernels.linear_tc(x, wg[i], out, w2=wu[i])), 4 * T * FF * H, nbytes, c
+
+
+def case_gemv_gated_join():
+    """Gate/up of one token as dot products, the join (residual sum, both norms) in the prologue."""
+    from . import kernels
+    c = _copies(2 * FF * H * 2)
+    wg = [_rnd(FF, H, scale=0.02) for _ in range(c)]
+    wu = [_rnd(FF, H, scale=0.02) for _ in range(c)]
+    h, y = torch.randn(1, H, device=DEV), torch.randn(1, H, device=DEV)
+    h2 = torch.empty_like(h)
+    w = torch.ones(H, device=DEV)
+    out = torch.empty(1, FF, dtype=torch.bfloat16, device=DEV)
+    return (lambda i: kernels.gemv_few(wg[i], out, w2=wu[i], h_in=h, h_out=h2, y=y, w_post=w, w_next=w,
+                                       eps_post=1e-6, eps_next=1e-6)), 4 * FF * H, \
+        2 * FF * H * 2 + FF * 2 + 3 * H * 4, c
+
+
+def case_gemv_down():
+    from . import kernels
+    c = _copies(FF * H * 2)
+    x = _rnd(1, FF)
+    w = [_rnd(H, FF, scale=0.02) for _ in range(c)]
+    out = torch.empty(1, H, dtype=torch.float32, device=DEV)
+    return (lambda i: kernels.gemv_few(w[i], out, x=x)), 2 * FF * H, FF * H * 2 + FF * 2 + H * 4, c
 
 
 def case_gemm_down(T):
@@ -300,6 +326,8 @@ CASES = {
     "gemm_down_prefill": lambda: case_gemm_down(2048),
     "gemm_gated_decode": lambda: case_gemm_gated(8),
     "gemm_down_decode": lambda: case_gemm_down(8),
+    "gemv_gated_join_one_token": case_gemv_gated_join,
+    "gemv_down_one_token": case_gemv_down,
     "gemm_lm_head_decode": case_lm_head,
     "gemm_lm_head_argmax_decode": case_lm_head_argmax,
     "gemm_qkv_fused_prefill_4b": case_qkv_fused_prefill_4b,
