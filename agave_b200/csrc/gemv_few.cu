@@ -52,7 +52,7 @@ __device__ __forceinline__ void gf_ask_l2(const void* p) {
 }
 
 // Block-wide sums of T values per thread; every thread gets all T results.  scratch:
-// GF_WARPS * T floats; it may be used again after the call.
+// GF_WARPS * T floats that nobody writes again in this launch (one barrier suffices then).
 template <int T>
 __device__ __forceinline__ void gf_block_sums(float (&v)[T], float* scratch) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -69,7 +69,6 @@ __device__ __forceinline__ void gf_block_sums(float (&v)[T], float* scratch) {
         for (int w = 0; w < GF_WARPS; ++w) s += scratch[w * T + t];      // in warp order
         v[t] = s;
     }
-    __syncthreads();
 }
 
 // eight bfloat16 times eight bfloat16, added to acc in 32-bit
@@ -99,7 +98,7 @@ gemv_few_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __rest
                 int part_off) {
     pdl_launch_next();
     extern __shared__ __align__(16) unsigned char smem[];
-    __shared__ float scratch[GF_WARPS * T];
+    __shared__ float scratch[2][GF_WARPS * T];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const long long r0 = (long long)blockIdx.x * rows_per_cta;
     const long long r1 = r0 + rows_per_cta < N ? r0 + rows_per_cta : N;
@@ -187,7 +186,7 @@ gemv_few_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __rest
                     ss[t] = fmaf(v, v, ss[t]);
                 }
             }
-            gf_block_sums<T>(ss, scratch);
+            gf_block_sums<T>(ss, scratch[0]);
 #pragma unroll
             for (int t = 0; t < T; ++t) rs[t] = 1.0f / sqrtf(ss[t] / (float)K + j.eps_post);
         }
@@ -205,7 +204,7 @@ gemv_few_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __rest
                 ss2[t] = fmaf(v, v, ss2[t]);
             }
         }
-        gf_block_sums<T>(ss2, scratch);          // (its barriers: h is read, x may go there)
+        gf_block_sums<T>(ss2, scratch[1]);       // (its barrier: h is read, x may go there)
 #pragma unroll
         for (int t = 0; t < T; ++t) {
             const float r2 = 1.0f / sqrtf(ss2[t] / (float)K + j.eps_next);
