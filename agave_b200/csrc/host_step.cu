@@ -184,7 +184,18 @@ struct Run {
         if (T > 64) {
             const int tile = T <= 128 ? 128 : 256;
             const long long ctas = (long long)((N + 127) / 128) * ((T + tile - 1) / tile);
-            if (ctas <= sms / 2 + 6 && (K + 63) / 64 >= 32) *groups = 2;
+            const int kb = (K + 63) / 64;
+            if (T <= 512) {
+                // short prompts: one or two token tiles, so a narrow weight is cut into
+                // ranges of K whose partial sums the consumer adds
+                const int most = T <= 128 ? 16 : T <= 256 ? 8 : 4;
+                long long want = kb / 2;
+                if (sms / ctas < want) want = sms / ctas;
+                if (most < want) want = most;
+                if (want >= 2) *groups = agv_linear_tc_splits(K, (int)want);
+                return;
+            }
+            if (ctas <= sms / 2 + 6 && kb >= 32) *groups = 2;
             return;
         }
         const int tile = T <= 16 ? 16 : T <= 32 ? 32 : 64;

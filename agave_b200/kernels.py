@@ -585,11 +585,19 @@ def plan_splits(T: int, N: int, K: int, cheap_sum: bool = False):
     loads it makes anyway (the q/k norm kernel), so up to eight groups are better
     than a cluster, whose exchange costs about 2 us.  Prompts are not cut."""
     if T > 64:
-        # prompts: only a long K over few tiles is cut, in two, with the partial
-        # sums left to the consumer (a cluster's exchange is slow for wide tiles)
         tile = 128 if T <= 128 else 256
         ctas = ((N + 127) // 128) * ((T + tile - 1) // tile)
-        if ctas <= n_sms() // 2 + 6 and (K + 63) // 64 >= 32:
+        kb = (K + 63) // 64
+        if T <= 512:
+            # short prompts have one or two token tiles: without a cut a narrow weight
+            # would run on a dozen CTAs; the partial sums (fewer, the more tokens there
+            # are to write them for) are left to the consumer
+            most = 16 if T <= 128 else 8 if T <= 256 else 4
+            want = min(kb // 2, n_sms() // ctas, most)
+            return (linear_tc_splits(K, want), 0) if want >= 2 else (1, 0)
+        # long prompts: only a long K over few tiles is cut, in two, with the partial
+        # sums left to the consumer (a cluster's exchange is slow for wide tiles)
+        if ctas <= n_sms() // 2 + 6 and kb >= 32:
             return 2, 0
         return 1, 0
     tile = 16 if T <= 16 else 32 if T <= 32 else 64
