@@ -132,6 +132,10 @@ struct Model {
     std::vector<int> call_block, call_cache;
 };
 
+// a prompt step of at most this many tokens runs the mma.sync attention (a short prompt gives
+// the tcgen05 kernel, 128 query rows a CTA, a handful of CTAs with a long set-up each)
+constexpr int PREFILL_TC_MIN_TOKENS = 192;
+
 struct Arena {
     char* base;
     size_t cap, top = 0, peak = 0;
@@ -256,7 +260,7 @@ struct Run {
             return !(v2 && strcmp(v2, "mma") == 0);
         }();
         if (!dry()) {
-            if (aligned && b.hd % 16 == 0 && prefill_tc)
+            if (aligned && b.hd % 16 == 0 && prefill_tc && T > PREFILL_TC_MIN_TOKENS)
                 did(agv_attention_prefill_tc(q, width, k, v, width, out, vt, vt_cols, 1, s.cu_seqlens,
                                              s.B, T, s.max_new, b.nh, b.nkv, b.hd, b.scale,
                                              b.window, stream));
@@ -279,7 +283,8 @@ struct Run {
             return !(v2 && strcmp(v2, "mma") == 0);
         }();
         const long long width = (long long)(b.nh + 2 * b.nkv) * b.hd;
-        return prefill_tc && m.dtype == AGV_BF16 && b.hd % 16 == 0 && b.hd <= 256 &&
+        return prefill_tc && s.T > PREFILL_TC_MIN_TOKENS && m.dtype == AGV_BF16 && b.hd % 16 == 0 &&
+               b.hd <= 256 &&
                width % 8 == 0 && agv_aligned(qkv, 16);
     }
 

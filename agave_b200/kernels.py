@@ -756,11 +756,19 @@ def attention_tc_status() -> int:
     return library().agv_attention_tc_status()
 
 
+# A prompt step of at most this many tokens runs the mma.sync attention: the tcgen05
+# kernel's CTAs take 128 query rows each, so a short prompt gives it a handful of CTAs with
+# a long set-up each (a 128-token step: 586 against 624 us over six layers; from 256 tokens
+# on the tcgen05 kernel is ahead).
+PREFILL_TC_MIN_TOKENS = 192
+
+
 def attention_prefill_wants_transposed_values(qkv: torch.Tensor, head_dim: int) -> bool:
     """Whether ``attention_prefill`` on views of this projection output will take the
     tcgen05 kernel, which reads the values transposed."""
-    return (_PREFILL_TC and qkv.dtype == torch.bfloat16 and head_dim % 16 == 0 and
-            head_dim <= 256 and qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0)
+    return (_PREFILL_TC and qkv.shape[0] > PREFILL_TC_MIN_TOKENS and qkv.dtype == torch.bfloat16 and
+            head_dim % 16 == 0 and head_dim <= 256 and qkv.stride(0) % 8 == 0 and
+            qkv.data_ptr() % 16 == 0)
 
 
 def attention_prefill(q, k, v, out, ctx, n_heads, n_kv_heads, head_dim, scale, window,
@@ -772,7 +780,7 @@ def attention_prefill(q, k, v, out, ctx, n_heads, n_kv_heads, head_dim, scale, w
                q.stride(0) % 8 == 0 and k.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and
                k.data_ptr() % 16 == 0 and v.data_ptr() % 16 == 0)
     with _span("attention", *_attention_cost(ctx, q, k, v, out, n_heads, head_dim, window)):
-        if aligned and head_dim % 16 == 0 and _PREFILL_TC:
+        if aligned and head_dim % 16 == 0 and _PREFILL_TC and q.shape[0] > PREFILL_TC_MIN_TOKENS:
             attention_prefill_tc(q, k, v, out, ctx.cu_seqlens, ctx.max_new, n_heads, n_kv_heads,
                                  head_dim, scale, window, vt=vt)
         elif aligned and head_dim % 8 == 0:
