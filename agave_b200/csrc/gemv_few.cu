@@ -13,9 +13,10 @@
 // read h_in.  A layer then is five kernels instead of seven: q/k/v (join of the layer
 // before), attention, output, gate/up (join), down.
 //
-// Before the dependency wait a warp asks the L2 cache for the weight rows it will read
-// and the CTA copies the two norm weights into shared memory; after it the token rows
-// come in as one group of copies.  x is rounded to bfloat16 before it is multiplied, as
+// Before the dependency wait a warp loads its first two batches of weight rows and the CTA
+// copies the two norm weights into shared memory; after it the token rows come in as one
+// group of copies.  (Asking the L2 cache for all of a CTA's rows up front as well,
+// prefetch.global.L2, made the stream slower: 100 against 72 us for the 27B gate/up.)  x is rounded to bfloat16 before it is multiplied, as
 // the tensor-core products round it, so a token decoded alone and one decoded in a
 // larger batch see the same operands.
 //
@@ -46,9 +47,6 @@ __device__ __forceinline__ void gf_copy16(void* smem_dst, const void* gmem_src) 
 }
 __device__ __forceinline__ void gf_copies_done() {
     asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
-}
-__device__ __forceinline__ void gf_ask_l2(const void* p) {
-    asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
 }
 
 // Block-wide sums of T values per thread; every thread gets all T results.  scratch:
@@ -103,18 +101,7 @@ gemv_few_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __rest
     const long long r0 = (long long)blockIdx.x * rows_per_cta;
     const long long r1 = r0 + rows_per_cta < N ? r0 + rows_per_cta : N;
 
-    // ---- before the wait: this CTA's weight rows towards L2, the norm weights in
-    if (r0 < N) {
-        const long long bytes = (r1 - r0) * K * 2;
-        const char* p = reinterpret_cast<const char*>(W + r0 * K);
-        for (long long off = (long long)tid * 128; off < bytes; off += GF_THREADS * 128)
-            gf_ask_l2(p + off);
-        if (GATED) {
-            const char* p2 = reinterpret_cast<const char*>(W2 + r0 * K);
-            for (long long off = (long long)tid * 128; off < bytes; off += GF_THREADS * 128)
-                gf_ask_l2(p2 + off);
-        }
-    }
+    // ---- before the wait: the norm weights into shared memory, the first weight batches
     // join:   [v: T x K 32-bit][h: T x K 32-bit, afterwards x in bfloat16][w_post, w_next: 2 K]
     // direct: [x: T x K bfloat16]
     // (x as 32-bit values in shared memory, with nothing to unpack per use, was slower: it
