@@ -27,7 +27,7 @@ Cases (Gemma 3 1B layer sizes, random bfloat16 data):
   gemv_gated_join_one_token, gemv_down_one_token   the gate/up (with the join in its prologue)
                        and down projections of one token as dot products (gemv_few.cu)
   decode_step          whole decode steps of a 6-layer model (vocabulary 32,768), batch 8
-  decode_step_b64      the same at batch 64
+  decode_step_b1, decode_step_b64   the same at batch 1 (dot-product projections) and 64
   decode_step_4b, decode_step_27b   the same with the layer sizes of the 4B model (batch 8,
                        256..4,096 positions) and the 27B model (batch 16, 2,048 positions)
   prefill_step         whole prompt steps of the same model, one prompt of 2,048 tokens
@@ -344,6 +344,7 @@ CASES = {
     "attention_decode_full_b64_tight": lambda: case_attention_decode(0, 2048, 64, 2048),
     "norm_decode": case_norm_decode,
     "decode_step": case_decode_step,
+    "decode_step_b1": lambda: case_decode_step(1),
     "decode_step_b64": lambda: case_decode_step(64),
     "decode_step_4b": lambda: case_decode_step(8, "4b", 256, 4096),
     "decode_step_27b": lambda: case_decode_step(16, "27b", 2048, 2048),
