@@ -92,6 +92,12 @@ def test_text_prompt_random_weights_and_profile():
             assert r.returncode == 0, r.stderr[-2000:]
             outs.append(json.loads(r.stdout.strip().splitlines()[-1])["output_ids"])
         assert outs[0] == outs[1] and len(outs[0]) <= 8
+        # one sequence decoded through the tensor-core products instead of the dot products
+        # that steps of one and two tokens take by default: the same tokens
+        r = _run([d, "--random-weights", "3", "--tokens", "2,9,30,77,5", "-n", "8", "--json"],
+                 env={"AGAVE_B200_FEW_TOKENS": "0"})
+        assert r.returncode == 0, r.stderr[-2000:]
+        assert json.loads(r.stdout.strip().splitlines()[-1])["output_ids"] == outs[0]
         # every launch named by an NVTX range (steps then go through the Python parts):
         # the same tokens
         r = _run([d, "--random-weights", "3", "--tokens", "2,9,30,77,5", "-n", "8", "--json"],
