@@ -141,9 +141,16 @@ gemv_few_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __rest
             if (GATED) u[i] = c < c_hi ? __ldg(ur + c) : make_uint4(0, 0, 0, 0);
         }
     };
-    // (the weights are nobody's output: the first two batches are asked for before the wait)
+    // (the weights are nobody's output: the first two batches are asked for before the wait;
+    // so are the join's arguments, whose first read from the parameter bank is a slow one)
     if (n_batches > 0) ask(0, wa, ua);
     if (n_batches > 1) ask(1, wb, ub);
+    const float* const jy = j.y;
+    const float* const jh = j.h_in;
+    float* const jho = j.h_out;
+    const float* const jwp = j.w_post;
+    const float eps_post = j.eps_post, eps_next = j.eps_next;
+    const bool add = jy != nullptr;
     pdl_wait();
     if (x_direct) {
         for (int i = tid * 8; i < T * K; i += GF_THREADS * 8) {
@@ -153,50 +160,72 @@ gemv_few_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __rest
         gf_copies_done();
         __syncthreads();
     } else {
-        const bool add = j.y != nullptr;
         for (int i = tid * 4; i < T * K; i += GF_THREADS * 4) {
-            if (add) gf_copy16(vs + i, j.y + i);
-            gf_copy16(hs + i, j.h_in + i);
+            if (add) gf_copy16(vs + i, jy + i);
+            gf_copy16(hs + i, jh + i);
         }
         gf_copies_done();
         __syncthreads();
+        // three passes over the rows, four values of a row per thread and access (the loops
+        // are short chains of shared-memory trips: wide accesses and several of them in
+        // flight, or a pass costs a microsecond)
+        const int K4 = K >> 2;
         float rs[T];
 #pragma unroll
         for (int t = 0; t < T; ++t) rs[t] = 1.f;
-        if (add && j.w_post) {
+        if (add && jwp) {
             float ss[T];
 #pragma unroll
             for (int t = 0; t < T; ++t) {
                 ss[t] = 0.f;
-                for (int c = tid; c < K; c += GF_THREADS) {
-                    const float v = vs[(size_t)t * K + c];
-                    ss[t] = fmaf(v, v, ss[t]);
+#pragma unroll 2
+                for (int c = tid; c < K4; c += GF_THREADS) {
+                    const float4 v = reinterpret_cast<const float4*>(vs + (size_t)t * K)[c];
+                    ss[t] += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
                 }
             }
             gf_block_sums<T>(ss, scratch[0]);
 #pragma unroll
-            for (int t = 0; t < T; ++t) rs[t] = 1.0f / sqrtf(ss[t] / (float)K + j.eps_post);
+            for (int t = 0; t < T; ++t) rs[t] = 1.0f / sqrtf(ss[t] / (float)K + eps_post);
         }
         float ss2[T];
-        const bool writer = blockIdx.x == 0 && j.h_out != nullptr;
+        const bool writer = blockIdx.x == 0 && jho != nullptr;
 #pragma unroll
         for (int t = 0; t < T; ++t) {
             ss2[t] = 0.f;
-            for (int c = tid; c < K; c += GF_THREADS) {
-                const size_t i = (size_t)t * K + c;
-                float v = hs[i];
-                if (add) v += j.w_post ? vs[i] * rs[t] * wp[c] : vs[i];
-                vs[i] = v;
-                if (writer) j.h_out[i] = v;
-                ss2[t] = fmaf(v, v, ss2[t]);
+#pragma unroll 2
+            for (int c = tid; c < K4; c += GF_THREADS) {
+                float4 v = reinterpret_cast<const float4*>(hs + (size_t)t * K)[c];
+                if (add) {
+                    const float4 y4 = reinterpret_cast<const float4*>(vs + (size_t)t * K)[c];
+                    if (jwp) {
+                        const float4 w4 = reinterpret_cast<const float4*>(wp)[c];
+                        v.x += y4.x * rs[t] * w4.x; v.y += y4.y * rs[t] * w4.y;
+                        v.z += y4.z * rs[t] * w4.z; v.w += y4.w * rs[t] * w4.w;
+                    } else {
+                        v.x += y4.x; v.y += y4.y; v.z += y4.z; v.w += y4.w;
+                    }
+                }
+                reinterpret_cast<float4*>(vs + (size_t)t * K)[c] = v;
+                if (writer) reinterpret_cast<float4*>(jho + (size_t)t * K)[c] = v;
+                ss2[t] += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
             }
         }
         gf_block_sums<T>(ss2, scratch[1]);       // (its barrier: h is read, x may go there)
 #pragma unroll
         for (int t = 0; t < T; ++t) {
-            const float r2 = 1.0f / sqrtf(ss2[t] / (float)K + j.eps_next);
-            for (int c = tid; c < K; c += GF_THREADS)
-                xs[(size_t)t * K + c] = __float2bfloat16_rn(vs[(size_t)t * K + c] * r2 * wn[c]);
+            const float r2 = 1.0f / sqrtf(ss2[t] / (float)K + eps_next);
+#pragma unroll 2
+            for (int c = tid; c < K4; c += GF_THREADS) {
+                const float4 v = reinterpret_cast<const float4*>(vs + (size_t)t * K)[c];
+                const float4 w4 = reinterpret_cast<const float4*>(wn)[c];
+                const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x * r2 * w4.x, v.y * r2 * w4.y);
+                const __nv_bfloat162 hi = __floats2bfloat162_rn(v.z * r2 * w4.z, v.w * r2 * w4.w);
+                uint2 pk;
+                pk.x = *reinterpret_cast<const unsigned*>(&lo);
+                pk.y = *reinterpret_cast<const unsigned*>(&hi);
+                reinterpret_cast<uint2*>(xs + (size_t)t * K)[c] = pk;
+            }
         }
         __syncthreads();
     }
