@@ -145,6 +145,10 @@ norm_residual_small_kernel(float* __restrict__ h, const TY* __restrict__ y, int 
                            const float* __restrict__ w_next, TX* __restrict__ x,
                            const int* __restrict__ rows, int H, float eps_post, float eps_next,
                            int add_residual) {
+    // (the arguments are read before the wait: their first read from the parameter bank
+    // is a slow one, and here nothing else hides it)
+    asm volatile("" ::"l"(h), "l"(y), "l"(w_post), "l"(w_next), "l"(x), "l"(rows), "r"(H),
+                 "r"(n_splits), "l"(split_stride), "f"(eps_post), "f"(eps_next), "r"(add_residual));
     pdl_wait();
     pdl_launch_next();
     __shared__ float red[33];
