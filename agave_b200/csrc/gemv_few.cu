@@ -16,9 +16,9 @@
 // Before the dependency wait a warp loads its first two batches of weight rows and the CTA
 // copies the two norm weights into shared memory; after it the token rows come in as one
 // group of copies.  (Asking the L2 cache for all of a CTA's rows up front as well,
-// prefetch.global.L2, made the stream slower: 100 against 72 us for the 27B gate/up.)  x is rounded to bfloat16 before it is multiplied, as
-// the tensor-core products round it, so a token decoded alone and one decoded in a
-// larger batch see the same operands.
+// prefetch.global.L2, made the stream slower: 100 against 72 us for the 27B gate/up.)
+// x is rounded to bfloat16 before it is multiplied, as the tensor-core products round it,
+// so a token decoded alone and one decoded in a larger batch see the same operands.
 //
 // Reference: one dot product per output row with 32-bit accumulation, bfloat16 weights
 // converted in the loop (src/backend/kernels/cuda/gemv_bf16.zig:6-24); the norms as
