@@ -126,6 +126,32 @@ def build_parser() -> argparse.ArgumentParser:
                         "reading tensors.")
     g.add_argument("--strict", action="store_true",
                    help="Refuse a folder that holds tensors the decoder does not ask for.")
+    g = p.add_argument_group(
+        "OPTIONS OF THE REFERENCE WITHOUT A COUNTERPART HERE",
+        "Accepted where they name what this library does anyway, refused with the reason where "
+        "they ask for what it does not have.")
+    g.add_argument("--backend", default="auto",
+                   help="Compute backend: only auto and cuda exist here [default: auto].")
+    g.add_argument("--color", default="auto", help="Color mode (output here is plain; ignored).")
+    g.add_argument("--no-color", action="store_true", help="Same as --color=never (ignored).")
+    g.add_argument("--mmap", action="store_true",
+                   help="Lazy weight mapping (weights are read straight to the GPU; ignored).")
+    g.add_argument("--prefill-batch-size", type=int, default=None,
+                   help="Prefill chunk size (a prompt runs as one step here; ignored).")
+    g.add_argument("--allow-cpu-fallback", action="store_true", help="Refused: there is no CPU path.")
+    g.add_argument("--kv-type", default=None,
+                   help="Cache element type: bf16 (f16 is read as bf16) with --dtype bfloat16, f32 "
+                        "with --dtype float32; quantised caches are refused.")
+    for name in ("--kv-type-k", "--kv-type-v", "--cache-type-k", "--cache-type-v"):
+        g.add_argument(name, default=None, help="As --kv-type.")
+    for name, why in (("--kv-tiers", "tiered caches"), ("--kv-eviction", "cache eviction"),
+                      ("--grammar", "constrained decoding"), ("--grammar-string", "constrained decoding"),
+                      ("--draft-model", "speculative decoding"), ("--mmproj", "vision input"),
+                      ("--image", "vision input")):
+        g.add_argument(name, default=None, help=f"Refused: no {why} here.")
+    for name, why in (("--json-output", "constrained decoding"), ("--serve", "server"),
+                      ("--megakernel", "quantised single-launch kernels")):
+        g.add_argument(name, action="store_true", help=f"Refused: no {why} here.")
     g = p.add_argument_group("DIAGNOSTICS")
     g.add_argument("-V", "--verbose", action="store_true",
                    help="Show technical details (params, load times, EOG).")
@@ -160,6 +186,30 @@ def _fail(msg: str) -> int:
     return 1
 
 
+def _unsupported(args) -> Optional[str]:
+    """Why an option of the reference's command line cannot be honoured here, or None."""
+    if args.backend not in ("auto", "cuda"):
+        return f"--backend {args.backend}: this library runs on CUDA (sm_100a) only"
+    if args.allow_cpu_fallback:
+        return "--allow-cpu-fallback: there is no CPU path"
+    want = {"bfloat16": ("bf16", "f16", "fp16", "bfloat16", "float16"),
+            "float32": ("f32", "fp32", "float32")}[args.dtype]
+    for name in ("kv_type", "kv_type_k", "kv_type_v", "cache_type_k", "cache_type_v"):
+        v = getattr(args, name)
+        if v is not None and v.lower() not in want:
+            return (f"--{name.replace('_', '-')} {v}: the cache holds {args.dtype} with --dtype "
+                    f"{args.dtype}; there are no quantised or mixed caches")
+    for name, why in (("kv_tiers", "tiered caches"), ("kv_eviction", "cache eviction"),
+                      ("grammar", "constrained decoding"), ("grammar_string", "constrained decoding"),
+                      ("json_output", "constrained decoding"), ("draft_model", "speculative decoding"),
+                      ("mmproj", "vision input"), ("image", "vision input"), ("serve", "a server"),
+                      ("megakernel", "quantised single-launch kernels")):
+        v = getattr(args, name)
+        if v not in (None, False) and not (name == "kv_eviction" and v == "none"):
+            return f"--{name.replace('_', '-')}: this library has no {why}"
+    return None
+
+
 def main(argv: Optional[List[str]] = None) -> int:
     args = build_parser().parse_args(argv)
     if args.version:
@@ -172,6 +222,9 @@ def main(argv: Optional[List[str]] = None) -> int:
         return _fail(f"'{args.model}' is not a model folder")
     if args.random_weights is not None and args.strict:
         return _fail("--strict is about tensors in files; --random-weights reads none")
+    refusal = _unsupported(args)
+    if refusal:
+        return _fail(refusal)
     # the reference's own validation (src/main.zig:555-573)
     if args.temperature < 0:
         return _fail("--temperature must be >= 0")

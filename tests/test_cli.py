@@ -48,6 +48,25 @@ def test_simple_tokenizer_round_trip():
     assert [PIECES[i] for i in tok.encode("at")] == ["at"]
 
 
+def test_options_of_the_reference_without_a_counterpart():
+    """Accepted where they name what happens anyway, refused with the reason otherwise;
+    none ends in a usage error."""
+    from agave_b200.cli import build_parser, _unsupported
+    p = build_parser()
+    ok = p.parse_args(["m", "--backend", "cuda", "--no-color", "--color", "never", "--mmap",
+                       "--prefill-batch-size", "512", "--kv-type", "f16", "--kv-eviction", "none"])
+    assert _unsupported(ok) is None
+    for argv, word in ((["--backend", "vulkan"], "CUDA"), (["--allow-cpu-fallback"], "CPU"),
+                       (["--kv-type", "q8_0"], "quantised"), (["--kv-type-k", "f32"], "bfloat16"),
+                       (["--kv-tiers", "vram+ram"], "tiered"), (["--grammar", "g.gbnf"], "constrained"),
+                       (["--json-output"], "constrained"), (["--draft-model", "d"], "speculative"),
+                       (["--image", "a.png"], "vision"), (["--serve"], "server"),
+                       (["--megakernel"], "single-launch"), (["--kv-eviction", "norm"], "eviction")):
+        msg = _unsupported(p.parse_args(["m"] + argv))
+        assert msg is not None and word in msg, (argv, msg)
+    assert _unsupported(p.parse_args(["m", "--dtype", "float32", "--kv-type", "f32"])) is None
+
+
 def _run(cmd, env=None):
     return subprocess.run([sys.executable, "-m", "agave_b200"] + cmd, capture_output=True,
                           text=True, cwd=ROOT, timeout=900,
