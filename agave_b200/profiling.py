@@ -21,6 +21,8 @@ Cases (Gemma 3 1B layer sizes, random bfloat16 data):
   attention_prefill_mma      the mma.sync kernel on the first workload
   attention_decode_window   decode attention, 8 sequences of 128..2,048 positions, window 512
   attention_decode_full     the same without a window
+  attention_decode_window_27b   16 sequences of 2,048 positions, window 1,024, with the 27B
+                       model's heads (32 query, 16 kv, 128 wide: 256 pairs of sequence and kv head)
   attention_decode_window_b64, attention_decode_full_b64   the same for 64 sequences (the
                        second with a grid sized for a context of 8,192)
   norm_decode          residual sum + two RMS norms over 8 rows of 16 partial sums
@@ -248,15 +250,16 @@ def case_attention_prefill(window=0, legacy=False):
     return fn, flops, qkv[0].numel() * 2 + out.numel() * 2, c
 
 
-def case_attention_decode(window, max_keys, B=8, grid_keys=0):
+def case_attention_decode(window, max_keys, B=8, grid_keys=0, heads=None, lo=128, hi=2048):
     from . import kernels
+    NH, NKV, HD = heads or (globals()["NH"], globals()["NKV"], globals()["HD"])
     PAGE, max_pages = 64, 40
     c = 16 if B <= 8 else 4
     pools = [(_rnd(B * max_pages, PAGE, NKV, HD), _rnd(B * max_pages, PAGE, NKV, HD))
              for _ in range(c)]
     table = torch.arange(B * max_pages, dtype=torch.int32, device=DEV).reshape(B, max_pages)
     slots = torch.arange(B, dtype=torch.int32, device=DEV)
-    lens = torch.linspace(128, 2048, B).round().int().tolist()
+    lens = torch.linspace(lo, hi, B).round().int().tolist()
     positions = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=DEV)
     q = _rnd(B, NH * HD)
     out = torch.empty_like(q)
@@ -342,6 +345,8 @@ CASES = {
     "attention_decode_window_b64": lambda: case_attention_decode(512, 512, 64),
     "attention_decode_full_b64": lambda: case_attention_decode(0, 2048, 64, 8192),
     "attention_decode_full_b64_tight": lambda: case_attention_decode(0, 2048, 64, 2048),
+    "attention_decode_window_27b": lambda: case_attention_decode(1024, 1024, 16, heads=(32, 16, 128),
+                                                                lo=2048, hi=2048),
     "norm_decode": case_norm_decode,
     "decode_step": case_decode_step,
     "decode_step_b1": lambda: case_decode_step(1),
