@@ -1,0 +1,137 @@
+"""Configurations drawn at random (every size and option of the architecture,
+from a seed) through the engine against the plain implementation, in 32-bit
+and in bfloat16: a request cut into a prompt and single tokens, two batches
+of unequal prompts whose shorter requests end earlier (the second reuses the
+slots of the first), and greedy generation through the entry point.
+
+The sizes no hand-picked configuration has come up here: head sizes in steps
+of 16 up to 256, one to eight query heads per kv head, widths and
+vocabularies that are no power of two, every layer pattern, tied and untied
+heads; the larger class also takes the products with several tiles and
+splits, the tcgen05 prompt attention and decode attention over several key
+tiles.  The score scale stays within a factor of sqrt(2) of 1/sqrt(head
+size): a far larger one (tried: 1/sqrt(24) with heads of 256) makes the
+model itself amplify rounding from layer to layer, in 32-bit by the same
+factor as in bfloat16, and says nothing about the kernels.
+"""
+import random
+import shutil
+import tempfile
+
+import pytest
+import torch
+
+from util import TOL, close, plain_logits, random_tokens
+
+pytestmark = pytest.mark.gpu
+
+
+def random_config(seed: int, larger: bool) -> dict:
+    rng = random.Random(seed)
+    hd = rng.choice([16, 32, 48, 64, 64, 80, 96, 128, 128, 160, 256, 256])
+    nkv = rng.choice([1, 1, 2, 3, 4])
+    group = rng.choice([1, 2, 2, 3, 4, 5, 8])
+    if larger:
+        hidden, ff = 8 * rng.randint(40, 200), 8 * rng.randint(80, 800)
+        layers = rng.randint(2, 3)
+        window = rng.choice([64, 100, 130, 200, 256, 300])
+        vocab = rng.randint(2000, 20000)
+    else:
+        hidden, ff = 8 * rng.randint(4, 48), 8 * rng.randint(6, 90)
+        layers = rng.randint(1, 5)
+        window = rng.choice([4, 7, 16, 24, 40, 64, 100, 130])
+        vocab = rng.randint(90, 900)
+    return {
+        "architectures": ["Gemma3ForCausalLM"], "model_type": "gemma3_text",
+        "num_hidden_layers": layers, "hidden_size": hidden,
+        "num_attention_heads": nkv * group, "num_key_value_heads": nkv, "head_dim": hd,
+        "query_pre_attn_scalar": rng.choice([hd, hd // 2, 2 * hd]),
+        "intermediate_size": ff, "vocab_size": vocab, "sliding_window": window,
+        "sliding_window_pattern": rng.choice([0, 1, 2, 3, 6]),
+        "rope_local_base_freq": rng.choice([10000.0, 5000.0, 777.0]),
+        "rope_theta": rng.choice([1000000.0, 200000.0, 10000.0]),
+        "rope_scaling": rng.choice([None, {"rope_type": "linear", "factor": 2.0},
+                                    {"rope_type": "linear", "factor": 8.0}]),
+        "rms_norm_eps": rng.choice([1e-6, 1e-5, 3e-6]),
+        "tie_word_embeddings": rng.choice([True, True, False]),
+        "max_position_embeddings": 4096, "hidden_activation": "gelu_pytorch_tanh",
+        "bos_token_id": 2, "eos_token_id": 1,
+    }
+
+
+def run_schedules(cfg: dict, seed: int, dtype: str, larger: bool) -> None:
+    from agave_b200.engine.api import Engine
+    from agave_b200.weights import write_model_folder
+    store = torch.float32 if dtype == "float32" else torch.bfloat16
+    folder = tempfile.mkdtemp(prefix="agave_random_")
+    try:
+        write_model_folder(folder, cfg, seed, 0.6 / cfg["hidden_size"] ** 0.5, 0.15, store)
+        eng = Engine(folder, dtype=dtype, max_tokens=4096)
+        V = cfg["vocab_size"]
+        rng = random.Random(seed * 7 + 1)
+
+        # one request: a prompt, then the rest token by token
+        n = rng.randint(300, 800) if larger else rng.randint(40, 260)
+        head = max(rng.randint(1, n - 1), n - (40 if larger else 70))
+        toks = random_tokens(n, V, seed + 5)
+        s = eng.acquire()
+        got = [eng.step([(s, toks[:head])], [list(range(head))])]
+        for i in range(head, n):
+            got.append(eng.step([(s, [toks[i]])], [[0]]))
+        eng.release(s)
+        close(torch.cat(got), plain_logits(folder, toks), TOL[dtype])
+
+        # two batches of unequal prompts; shorter requests end earlier; slots are reused
+        free_before = eng.runner.cache.book.slots.n_free
+        for batch in range(2):
+            B = rng.randint(2, 6)
+            lengths = [rng.randint(1, 500 if larger else 150) for _ in range(B)]
+            decode = [rng.randint(1, 12 if larger else 24) for _ in range(B)]
+            seqs = [random_tokens(L + decode[i], V, seed * 31 + 100 * batch + i)
+                    for i, L in enumerate(lengths)]
+            slots = [eng.acquire() for _ in seqs]
+            out = eng.step([(slots[i], seqs[i][:L]) for i, L in enumerate(lengths)],
+                           [list(range(L)) for L in lengths])
+            got = [[] for _ in seqs]
+            o = 0
+            for i, L in enumerate(lengths):
+                got[i].append(out[o:o + L])
+                o += L
+            live = list(range(B))
+            pos = dict(enumerate(lengths))
+            while live:
+                out = eng.step([(slots[i], [seqs[i][pos[i]]]) for i in live], [[0]] * len(live))
+                for j, i in enumerate(live):
+                    got[i].append(out[j:j + 1])
+                    pos[i] += 1
+                for i in [i for i in live if pos[i] == len(seqs[i])]:
+                    eng.release(slots[i])
+                    live.remove(i)
+            for i in range(B):
+                close(torch.cat(got[i]), plain_logits(folder, seqs[i]), TOL[dtype])
+        assert eng.runner.cache.book.slots.n_free == free_before
+
+        # greedy generation (32-bit: in bfloat16 two near-equal logits may change places)
+        if dtype == "float32":
+            prompts = [random_tokens(rng.randint(1, 40), V, seed + 900 + i) for i in range(3)]
+            outs = eng.generate(prompts, max_new_tokens=5, stop_token_ids=())
+            for prompt, out in zip(prompts, outs):
+                cur, want = list(prompt), []
+                for _ in range(5):
+                    want.append(int(torch.argmax(plain_logits(folder, cur)[-1])))
+                    cur.append(want[-1])
+                assert list(out) == want
+    finally:
+        shutil.rmtree(folder, ignore_errors=True)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("seed", range(200, 216))
+def test_small_random_configuration(seed, dtype):
+    run_schedules(random_config(seed, larger=False), seed, dtype, larger=False)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("seed", range(4))
+def test_larger_random_configuration(seed, dtype):
+    run_schedules(random_config(seed, larger=True), seed, dtype, larger=True)
