@@ -2,7 +2,10 @@
 from a seed) through the engine against the plain implementation, in 32-bit
 and in bfloat16: a request cut into a prompt and single tokens, two batches
 of unequal prompts whose shorter requests end earlier (the second reuses the
-slots of the first), and greedy generation through the entry point.
+slots of the first), and greedy generation through the entry point; and
+`generate` with a random number of requests, slot limit and token budget (one
+to twenty batches) and stop tokens taken from the plain run's own output, so
+that requests end at different steps.
 
 The sizes no hand-picked configuration has come up here: head sizes in steps
 of 16 up to 256, one to eight query heads per kv head, widths and
@@ -135,3 +138,44 @@ def test_small_random_configuration(seed, dtype):
 @pytest.mark.parametrize("seed", range(4))
 def test_larger_random_configuration(seed, dtype):
     run_schedules(random_config(seed, larger=True), seed, dtype, larger=True)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("seed", range(300, 310))
+def test_generation_in_a_random_configuration(seed, dtype):
+    """32-bit: the tokens of the plain greedy run, cut at the first stop token.
+    bfloat16 (no stop tokens): every token generated is, by the plain logits of
+    the sequence generated, within twice the tolerance of the greatest."""
+    from agave_b200.engine.api import Engine
+    from agave_b200.weights import write_model_folder
+    from plain import gemma3_plain as P
+    cfg = random_config(seed, larger=False)
+    store = torch.float32 if dtype == "float32" else torch.bfloat16
+    folder = tempfile.mkdtemp(prefix="agave_random_")
+    try:
+        write_model_folder(folder, cfg, seed, 0.6 / cfg["hidden_size"] ** 0.5, 0.15, store)
+        rng = random.Random(seed * 13 + 5)
+        eng = Engine(folder, dtype=dtype, max_tokens=rng.choice([256, 512, 1024, 4096]),
+                     max_batch=rng.choice([1, 2, 3, 5, 8, 16, None]))
+        pc, pw = P.read_config(folder), P.read_weights(folder, torch.float64)
+        n_requests, new = rng.randint(1, 20), rng.randint(1, 20)
+        prompts = [random_tokens(rng.randint(1, 100), cfg["vocab_size"], seed * 77 + i)
+                   for i in range(n_requests)]
+        if dtype == "float32":
+            whole = [P.greedy_generate(pc, pw, p, new) for p in prompts]
+            stops = {o[rng.randrange(len(o))] for o in whole if rng.random() < 0.4}
+            want = [o[:next((i for i, t in enumerate(o) if t in stops), len(o))] for o in whole]
+            got = eng.generate(prompts, max_new_tokens=new, stop_token_ids=tuple(stops))
+            assert [list(g) for g in got] == want
+        else:
+            got = eng.generate(prompts, max_new_tokens=new, stop_token_ids=())
+            for p, g in zip(prompts, got):
+                assert len(g) == new
+                logits = P.forward_logits(pc, pw, list(p) + list(g))
+                rows = logits[len(p) - 1:len(p) - 1 + new]
+                gap = rows.max(dim=1).values - rows[torch.arange(new), torch.tensor(list(g))]
+                assert gap.max().item() <= 2 * TOL[dtype] * logits.abs().max().item()
+        slots = eng.runner.cache.book.slots
+        assert slots.n_free == slots.n_slots
+    finally:
+        shutil.rmtree(folder, ignore_errors=True)
