@@ -5,7 +5,8 @@ of unequal prompts whose shorter requests end earlier (the second reuses the
 slots of the first), and greedy generation through the entry point; and
 `generate` with a random number of requests, slot limit and token budget (one
 to twenty batches) and stop tokens taken from the plain run's own output, so
-that requests end at different steps.
+that requests end at different steps; and batches of 8 to 48 sequences of up
+to 2,500 tokens (the plain implementation then runs in 64-bit on the GPU).
 
 The sizes no hand-picked configuration has come up here: head sizes in steps
 of 16 up to 256, one to eight query heads per kv head, widths and
@@ -177,5 +178,61 @@ def test_generation_in_a_random_configuration(seed, dtype):
                 assert gap.max().item() <= 2 * TOL[dtype] * logits.abs().max().item()
         slots = eng.runner.cache.book.slots
         assert slots.n_free == slots.n_slots
+    finally:
+        shutil.rmtree(folder, ignore_errors=True)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("seed", [0, 3, 11, 16, 26, 51, 54, 73])
+def test_large_batches_of_long_unequal_sequences(seed, dtype):
+    """8 to 48 prompts of 1 to 2,500 tokens in one step, then three tokens each: decode
+    attention with few CTAs per sequence that walk several tiles, windows from 128 to
+    1,500 as rings, wide heads; the logits at each prompt's end and of the decoded tokens."""
+    from agave_b200.engine.api import Engine
+    from agave_b200.weights import write_model_folder
+    from plain import gemma3_plain as P
+    rng = random.Random(seed)
+    hd = rng.choice([64, 128, 256, 256, 48, 96, 160])
+    nkv, group = rng.choice([1, 2, 4]), rng.choice([1, 2, 4, 8])
+    cfg = {
+        "architectures": ["Gemma3ForCausalLM"], "model_type": "gemma3_text",
+        "num_hidden_layers": rng.randint(1, 2), "hidden_size": 8 * rng.randint(16, 64),
+        "num_attention_heads": nkv * group, "num_key_value_heads": nkv, "head_dim": hd,
+        "query_pre_attn_scalar": hd, "intermediate_size": 8 * rng.randint(16, 64),
+        "vocab_size": rng.randint(200, 900),
+        "sliding_window": rng.choice([128, 512, 700, 1024, 1500]),
+        "sliding_window_pattern": rng.choice([0, 1, 2]),
+        "rope_local_base_freq": 10000.0, "rope_theta": 1000000.0,
+        "rope_scaling": rng.choice([None, {"rope_type": "linear", "factor": 8.0}]),
+        "rms_norm_eps": 1e-6, "tie_word_embeddings": True, "max_position_embeddings": 8192,
+        "hidden_activation": "gelu_pytorch_tanh", "bos_token_id": 2, "eos_token_id": 1,
+    }
+    store = torch.float32 if dtype == "float32" else torch.bfloat16
+    folder = tempfile.mkdtemp(prefix="agave_random_")
+    try:
+        write_model_folder(folder, cfg, seed, 0.6 / cfg["hidden_size"] ** 0.5, 0.15, store)
+        B = rng.randint(8, 48)
+        longest = rng.choice([300, 1000, 2500])
+        lengths = [rng.randint(1, longest) for _ in range(B)]
+        decoded = 3
+        eng = Engine(folder, dtype=dtype, max_tokens=B * (longest + 128), max_batch=B)
+        pc = P.read_config(folder)
+        pw = {k: v.cuda() for k, v in P.read_weights(folder, torch.float64).items()}
+        seqs = [random_tokens(L + decoded, cfg["vocab_size"], seed * 131 + i)
+                for i, L in enumerate(lengths)]
+        slots = [eng.acquire() for _ in seqs]
+        out = eng.step([(slots[i], seqs[i][:L]) for i, L in enumerate(lengths)],
+                       [[L - 1] for L in lengths])
+        got = [[out[i:i + 1]] for i in range(B)]
+        for k in range(decoded):
+            out = eng.step([(slots[i], [seqs[i][lengths[i] + k]]) for i in range(B)], [[0]] * B)
+            for i in range(B):
+                got[i].append(out[i:i + 1])
+        for slot in slots:
+            eng.release(slot)
+        for i, L in enumerate(lengths):
+            with torch.device("cuda"):
+                ref = P.forward_logits(pc, pw, seqs[i])[L - 1:]
+            close(torch.cat(got[i]), ref, TOL[dtype])
     finally:
         shutil.rmtree(folder, ignore_errors=True)
