@@ -8,6 +8,8 @@ Cases (Gemma 3 1B layer sizes, random bfloat16 data):
   gemm_down_prefill    down projection, 2,048 tokens
   gemm_gated_decode    gate/up product, 8 tokens
   gemm_down_decode     down projection, 8 tokens (K split over a cluster or partial sums)
+  gemm_gated_decode_4b, gemm_gated_decode_27b   gate/up product with the 4B model's sizes
+                       (2,560 x 10,240, 8 tokens) and the 27B model's (5,376 x 21,504, 16 tokens)
   gemm_lm_head_decode  the head over a 262,144-row table, 8 tokens
   gemm_lm_head_argmax_decode   the same with the arg max taken in the epilogue (no logits written)
   gemm_qkv_fused_prefill_4b    q/k/v product with norm, rotation, cache store and transposed
@@ -86,15 +88,19 @@ def _run(fn, copies: int, iters: int) -> float:
     return total / iters / n * 1e3
 
 
-def case_gemm_gated(T):
+def case_gemm_gated(T, sizes=None):
+    """Gate/up product; ``sizes`` = (hidden, intermediate) of a larger model: then through
+    ``kernels.linear``, which picks the tiles and the cut of K as a decode step does."""
     from . import kernels
-    nbytes = (2 * FF * H + T * H + T * FF) * 2
-    c = _copies(2 * FF * H * 2)
-    x = _rnd(T, H)
-    wg = [_rnd(FF, H, scale=0.02) for _ in range(c)]
-    wu = [_rnd(FF, H, scale=0.02) for _ in range(c)]
-    out = torch.empty(T, FF, dtype=torch.bfloat16, device=DEV)
-    return (lambda i: kernels.linear_tc(x, wg[i], out, w2=wu[i])), 4 * T * FF * H, nbytes, c
+    h, ff = sizes or (H, FF)
+    nbytes = (2 * ff * h + T * h + T * ff) * 2
+    c = _copies(2 * ff * h * 2)
+    x = _rnd(T, h)
+    wg = [_rnd(ff, h, scale=0.02) for _ in range(c)]
+    wu = [_rnd(ff, h, scale=0.02) for _ in range(c)]
+    out = torch.empty(T, ff, dtype=torch.bfloat16, device=DEV)
+    product = kernels.linear if sizes else kernels.linear_tc
+    return (lambda i: product(x, wg[i], out, w2=wu[i])), 4 * T * ff * h, nbytes, c
 
 
 def case_gemv_gated_join():
@@ -329,6 +335,8 @@ CASES = {
     "gemm_down_prefill": lambda: case_gemm_down(2048),
     "gemm_gated_decode": lambda: case_gemm_gated(8),
     "gemm_down_decode": lambda: case_gemm_down(8),
+    "gemm_gated_decode_4b": lambda: case_gemm_gated(8, (SIZES["4b"][0], SIZES["4b"][5])),
+    "gemm_gated_decode_27b": lambda: case_gemm_gated(16, (SIZES["27b"][0], SIZES["27b"][5])),
     "gemv_gated_join_one_token": case_gemv_gated_join,
     "gemv_down_one_token": case_gemv_down,
     "gemm_lm_head_decode": case_lm_head,
