@@ -22,6 +22,9 @@
 // (src/backend/kernels/cpu/sdpa.zig:36-37,58); window start sl - W
 // (src/models/gemma4.zig:1153-1155).  No value row is skipped for a small weight.
 #include "common.cuh"
+#include "tcgen05.cuh"
+#include <map>
+#include <tuple>
 
 namespace {
 
@@ -363,6 +366,9 @@ struct DmShape {
     // second one, so that a CTA that walks several tiles has the next one under way while it
     // works on this one (at 256 a second tile would cost the second CTA of the SM)
     static constexpr int NBUF = HDP <= 128 ? 2 : 1;
+    // By TMA a request costs the threads next to nothing, so a third tile goes where the
+    // one before this one was as soon as everybody is past it, with no barrier of its own.
+    static constexpr int NBUF_TMA = HDP <= 128 ? 3 : 1;
     static_assert(DW % 16 == 0 && (KW == 16 || KW == 8), "unsupported split of a tile over warps");
 };
 
@@ -392,6 +398,19 @@ template <int W>
 __device__ __forceinline__ int dm_swz(int row, int chunk) {
     return row * W + (((chunk & ~7) | ((chunk ^ row) & 7)) << 3);
 }
+// The layout TMA leaves a [64 keys][W] tile in when it comes as W / 64 boxes of [64 rows x
+// 128 bytes] with the 128-byte swizzle: box after box, inside a box row after row, the
+// 16-byte chunk c of row r at c ^ (r & 7).  (The tile starts on a 1024-byte boundary.)
+template <int W>
+__device__ __forceinline__ int tm_swz(int row, int chunk) {
+    return (chunk >> 3) * (DM_KEYS * 64) + row * 64 + (((chunk & 7) ^ (row & 7)) << 3);
+}
+// A key / value tile's layout: as the 16-byte copies write it, or as TMA does.
+template <int W, bool TMA>
+__device__ __forceinline__ int kv_swz(int row, int chunk) {
+    return TMA ? tm_swz<W>(row, chunk) : dm_swz<W>(row, chunk);
+}
+__device__ int g_decode_status = 0;   // 0, or 1 + the tile whose bounded wait gave up first
 
 __device__ __forceinline__ void dm_cluster_sync() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n"
@@ -425,9 +444,10 @@ __device__ __forceinline__ void dm_ld_run(const float* p, float* dst) {
 // a lane holds the runs [lane * HALF, +HALF) of both halves of the head, so that the
 // partners of the rotation are its own.  Optional norm (w) and rotation (cs / sn rows of
 // hd / 2).  The result goes, as bfloat16, to a row of a swizzled [rows][HDP] tile in
-// shared memory and, if gdst is given, to global memory.  Weights and angles are
+// shared memory (TMA_TILE: a key / value tile in the layout TMA writes) and, if gdst is
+// given, to global memory.  Weights and angles are
 // requested before the sums, so that all loads are in flight together.
-template <int HDP>
+template <int HDP, bool TMA_TILE = false>
 __device__ __forceinline__ void dm_head_from_partials(const float* __restrict__ src, int G,
                                                       size_t split_stride,
                                                       const float* __restrict__ w, float eps,
@@ -485,7 +505,7 @@ __device__ __forceinline__ void dm_head_from_partials(const float* __restrict__ 
     for (int i = 0; i < 2 * HALF; ++i) {
         const int e = (i < HALF ? e0 + i : H2 + e0 + i - HALF);
         const __nv_bfloat16 x = __float2bfloat16_rn(v[i]);
-        tile[dm_swz<HDP>(row, e >> 3) + (e & 7)] = x;
+        tile[kv_swz<HDP, TMA_TILE>(row, e >> 3) + (e & 7)] = x;
         if (gdst) gdst[e] = x;
     }
 }
@@ -497,9 +517,28 @@ __device__ __forceinline__ void dm_head_from_partials(const float* __restrict__ 
 // sequence each cluster leaves one partial result in global scratch and the last
 // CTA to arrive merges them.  cs = 1 with several CTAs: every CTA's partial result
 // goes through scratch.
-template <int HDP>
+//
+// TMA: the tiles are the cache's pages (page and tile are 64 positions, hd == HDP, the ring
+// a whole number of pages): tile k holds positions 64 k .. 64 k + 63, and one thread asks
+// for it with a box of [64 rows x 128 bytes] per 128 bytes of head width and operand (maps
+// over the pools as [rows, kv heads, hd]) instead of all threads with 16 bytes each, whose
+// issue alone took a third of a tile's time.  The first page of a window and the last of
+// the sequence are masked by position, and value rows outside lo .. p are zeroed in shared
+// memory, since what a page holds there is left over from an earlier user.  The waits for
+// a tile are bounded; one that gives up leaves a code for agv_attention_decode_status and
+// the kernel goes on (its result is void).
+// The pools' tensor maps are a kernel argument of the TMA form only.
+template <bool TMA>
+struct PoolMaps {
+    CUtensorMap k, v;
+};
+template <>
+struct PoolMaps<false> {};
+
+template <int HDP, bool TMA>
 __global__ void __launch_bounds__(DmShape<HDP>::NT, DmShape<HDP>::NT == 256 ? 2 : 3)
-attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq) {
+attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq,
+                            const __grid_constant__ PoolMaps<TMA> maps) {
     typedef DmShape<HDP> Sh;
     constexpr int DM_THREADS = Sh::NT;
     // Slots, positions and page tables are written by copies at the start of the step,
@@ -508,19 +547,24 @@ attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq) {
     // memory leave the chain.
     pdl_launch_next();
     typedef __nv_bfloat16 T;
-    extern __shared__ __align__(128) unsigned char smem_raw[];
+    extern __shared__ __align__(128) unsigned char smem_raw0[];
     __shared__ int s_last;
+    __shared__ uint64_t kv_bar[3];                          // TMA: a tile's bytes have arrived
+    constexpr int NBUF = TMA ? Sh::NBUF_TMA : Sh::NBUF;
+    constexpr int TILE = DM_KEYS * HDP;
+    // (tiles that TMA writes with the 128-byte swizzle start on 1024-byte boundaries)
+    unsigned char* smem_raw =
+        TMA ? (unsigned char*)(((uintptr_t)smem_raw0 + 1023) & ~(uintptr_t)1023) : smem_raw0;
     T* Ks = reinterpret_cast<T*>(smem_raw);                 // [64][HDP]
     T* Vs = Ks + DM_KEYS * HDP;                             // [64][HDP]
-    T* Qs = Vs + DM_KEYS * HDP;                             // [16][HDP]
+    T* Ks1 = Vs + DM_KEYS * HDP;                            // the second tile (and the third after it)
+    T* Vs1 = Ks1 + DM_KEYS * HDP;
+    T* Qs = Ks + 2 * NBUF * TILE;                           // [16][HDP]
     T* Ps = Qs + DM_HEADS * HDP;                            // [16][64]
     float* Ss = reinterpret_cast<float*>(Ps + DM_HEADS * DM_KEYS);   // [16][64]
     float* stat = Ss + DM_HEADS * DM_KEYS;                  // [16][2] running maximum and sum
     float* fac = stat + DM_HEADS * 2;                       // [16] what a new maximum scales O by
     int* rowoff = reinterpret_cast<int*>(fac + DM_HEADS);   // [2][64]: this tile's and the next
-    T* Ks1 = reinterpret_cast<T*>(rowoff + 2 * DM_KEYS);    // the second tile (NBUF == 2)
-    T* Vs1 = Ks1 + DM_KEYS * HDP;
-    constexpr int NBUF = Sh::NBUF;
 
     // The W = gridDim.x CTAs of a sequence share its tiles of 64 keys: CTA w walks the
     // tiles w, w + W, w + 2 W, ... with a running softmax.  W is chosen from the batch
@@ -547,7 +591,9 @@ attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq) {
     }
     const int p = a.positions[b];
     const int lo = a.window > 0 ? max(0, p - a.window + 1) : 0;
-    const int all_tiles = (p - lo) / DM_KEYS + 1;             // tiles this sequence has
+    // tiles this sequence has: from its first key on, or (TMA) the cache pages it touches
+    const int k0 = TMA ? lo / DM_KEYS : 0;
+    const int all_tiles = TMA ? p / DM_KEYS - k0 + 1 : (p - lo) / DM_KEYS + 1;
     const int used = min(W, all_tiles);                       // CTAs of it with work
     const int cid = split / cs, crank = split % cs;
     const int used_clusters = (used + cs - 1) / cs;
@@ -557,7 +603,8 @@ attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq) {
     }
     const bool has = split < all_tiles;                       // (always true when cs == 1)
     const int n_tiles = has ? (all_tiles - 1 - split) / W + 1 : 0;    // tiles this CTA walks
-    const int j0 = lo + split * DM_KEYS;                      // first key of its first tile
+    // first key of its first tile
+    const int j0 = TMA ? (k0 + split) * DM_KEYS : lo + split * DM_KEYS;
     float* Osm = reinterpret_cast<float*>(Ks);                // [16][HDP], after the scores are done
     const int* table = a.page_table + (size_t)slot * a.max_pages;
     // cache row of key (first + tid), or -1 beyond position p
@@ -566,12 +613,67 @@ attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq) {
         const int row = key % a.cap;
         return key <= p ? table[row / a.page] * a.page + row % a.page : -1;
     };
-    if (has && tid < DM_KEYS) {
+    if (!TMA && has && tid < DM_KEYS) {
         rowoff[tid] = row_of(j0);
         if (NBUF == 2 && n_tiles > 1) rowoff[DM_KEYS + tid] = row_of(j0 + W * DM_KEYS);
     }
+    // A CTA that walks more tiles than it has buffers looks their rows up inside the walk,
+    // between two barriers, where a division by a runtime value (a hundred cycles) shows:
+    // thread t keeps the key it looks up next and that key's place in the ring and steps
+    // both by a tile's distance.  (Set up only for such a CTA: a CTA with a single tile,
+    // the common case of a short batch, is better off without the set-up; and only where
+    // the registers are there for it: with heads of 256 they are not.)
+    constexpr bool WALK = !TMA && HDP <= 128;
+    const int pshift = (a.page & (a.page - 1)) == 0 ? 31 - __clz(a.page) : -1;
+    int look_key = 0, look_ring = 0, step_ring = 0;
+    if (WALK && n_tiles > NBUF && tid < DM_KEYS) {
+        look_key = j0 + NBUF * W * DM_KEYS + tid;
+        look_ring = look_key % a.cap;
+        step_ring = (W * DM_KEYS) % a.cap;
+    }
+    // cache row of this thread's key of the next tile, or -1 beyond position p
+    auto next_lookup = [&]() {
+        int r = -1;
+        if (look_key <= p)
+            r = pshift >= 0 ? (table[look_ring >> pshift] << pshift) + (look_ring & (a.page - 1))
+                            : table[look_ring / a.page] * a.page + look_ring % a.page;
+        look_key += W * DM_KEYS;
+        look_ring += step_ring;
+        if (look_ring >= a.cap) look_ring -= a.cap;
+        return r;
+    };
+    if (TMA && tid == 0) {
+        tc5::mbar_init(&kv_bar[0], 1);
+        tc5::mbar_init(&kv_bar[1], 1);
+        tc5::mbar_init(&kv_bar[2], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
     __syncthreads();
     constexpr int CPR = HDP / 8;
+    // TMA: a tile is asked for box by box, each box by the first lane of a warp of its own
+    // (a request holds its thread for a hundred cycles, and every warp is needed at the
+    // next barrier).  Those lanes step tile and ring place as above (look_key is the
+    // tile's first position there, a multiple of 64; the ring holds whole pages).  The
+    // barrier of the tile's buffer counts its bytes in.
+    const bool asks = TMA && lane == 0 && warp < 2 * (HDP / 64);
+    if (asks) {
+        look_ring = j0 % a.cap;
+        step_ring = (W * DM_KEYS) % a.cap;
+    }
+    auto next_page = [&]() {                                   // its first cache row
+        const int row0 = table[look_ring >> 6] << 6;
+        look_ring += step_ring;
+        if (look_ring >= a.cap) look_ring -= a.cap;
+        return row0;
+    };
+    auto request_page = [&](int buf, int row0) {               // (only where asks)
+        uint64_t* bar = &kv_bar[buf];
+        if (warp == 0) tc5::mbar_expect_tx(bar, 2 * TILE * (unsigned)sizeof(T));
+        const int x = warp >> 1;
+        if constexpr (TMA)
+            tc5::tma_load_3d(Ks + (buf * 2 + (warp & 1)) * TILE + x * DM_KEYS * 64,
+                             warp & 1 ? &maps.v : &maps.k, x * 64, g, row0, bar);
+    };
     // Keys and values of earlier positions were stored by earlier steps: their copies
     // start before the wait too.  Only the row of position p is the predecessor's.
     const int r_new = p - j0;                                 // in [0, 64): the first tile holds p
@@ -595,12 +697,20 @@ attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq) {
         }
         cp_async_commit();
     };
-    if (has) {
+    if (TMA) {
+        if (has && asks)
+            for (int t = 0; t < min(n_tiles, NBUF); ++t) request_page(t, next_page());
+    } else if (has) {
         // the first tile (and the second, where there is room for it); the others are
         // requested inside the walk below
         request_tile(Ks, Vs, rowoff, r_new);
         if (NBUF == 2 && n_tiles > 1)
             request_tile(Ks1, Vs1, rowoff + DM_KEYS, p - (j0 + W * DM_KEYS));
+    }
+    int p_row = -1;                                         // TMA: the cache row of position p
+    if (TMA) {
+        const int pr = p % a.cap;
+        p_row = (table[pr >> 6] << 6) + (pr & 63);
     }
     const bool fused = fq.part != nullptr;                  // (then hd == HDP)
     if (has && fused) {
@@ -642,15 +752,16 @@ attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq) {
             const float* src = fq.part + (size_t)b * f_width;
             // (by the warps after those that form the queries, if there are any)
             if (warp == gc % Sh::NW)
-                dm_head_from_partials<HDP>(src + (size_t)(a.nh + g) * hd, fq.G, f_stride, fq.wk,
-                                           fq.eps, f_cos, f_sin, Ks, r, kd, lane);
+                dm_head_from_partials<HDP, TMA>(src + (size_t)(a.nh + g) * hd, fq.G, f_stride,
+                                                fq.wk, fq.eps, f_cos, f_sin, Ks, r, kd, lane);
             else if (warp == (gc + 1) % Sh::NW)
-                dm_head_from_partials<HDP>(src + (size_t)(a.nh + a.nkv + g) * hd, fq.G, f_stride,
-                                           nullptr, 0.f, nullptr, nullptr, Vs, r, vd, lane);
+                dm_head_from_partials<HDP, TMA>(src + (size_t)(a.nh + a.nkv + g) * hd, fq.G,
+                                                f_stride, nullptr, 0.f, nullptr, nullptr, Vs, r,
+                                                vd, lane);
             return;
         }
         for (int c = tid; c < CPR; c += DM_THREADS) {
-            const int off = dm_swz<HDP>(r, c);
+            const int off = kv_swz<HDP, TMA>(r, c);
             if (cache_row >= 0 && c * 8 < hd) {
                 const size_t src = ((size_t)cache_row * a.nkv + g) * hd + c * 8;
                 cp_async16(Ks + off, (const T*)a.k_pool + src);
@@ -661,22 +772,55 @@ attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq) {
             }
         }
     };
-    if (r_new >= 0 && r_new < DM_KEYS) new_row(Ks, Vs, r_new, rowoff[r_new]);
+    if (!TMA && r_new >= 0 && r_new < DM_KEYS) new_row(Ks, Vs, r_new, rowoff[r_new]);
     constexpr int NP = Sh::NP;
     float o[NP * 2][4] = {};
+    int ahead_row0 = -1;                                    // TMA: first cache row of the page asked for next
     for (int tt = 0; tt < n_tiles; ++tt) {
     const int jt = j0 + tt * W * DM_KEYS;                   // first key of this tile
-    const int n = min(DM_KEYS, p - jt + 1);                 // its keys
+    const int n = min(DM_KEYS, p - jt + 1);                 // its keys: rows nlo .. n - 1
+    const int nlo = TMA ? max(0, lo - jt) : 0;
     const bool last = tt + 1 == n_tiles;
-    // this tile's buffers (the tiles alternate between two where there are two)
-    T* const Kt = (NBUF == 2 && (tt & 1)) ? Ks1 : Ks;
-    T* const Vt = (NBUF == 2 && (tt & 1)) ? Vs1 : Vs;
+    // this tile's buffers (the tiles take turns where there are two or three)
+    const int buf = NBUF == 1 ? 0 : NBUF == 2 ? tt & 1 : tt % NBUF;
+    T* const Kt = Ks + buf * 2 * TILE;
+    T* const Vt = Kt + TILE;
+    bool top_barrier = true;
     // the rows of the tile that is requested next (the next one; with two buffers the one
     // after it): the lookup runs beside this tile's work
     const int ahead = NBUF * W * DM_KEYS;
     int next_row = -1;
-    if (tt + NBUF < n_tiles && tid < DM_KEYS) next_row = row_of(jt + ahead);
-    if (tt > 0) {
+    if (!TMA && tt + NBUF < n_tiles && tid < DM_KEYS)
+        next_row = WALK ? next_lookup() : row_of(jt + ahead);
+    if constexpr (TMA) {
+        if (NBUF == 1 && tt > 0) {
+            // the tile before has been used up: this one replaces it
+            __syncthreads();
+            if (asks) request_page(0, ahead_row0);
+        }
+        // The page that is asked for next is looked up beside this tile's work: with one
+        // buffer the next tile's, asked for at the top of the next round; with three the
+        // tile after the next, asked for below as soon as everybody is past the tile before
+        // this one, whose buffer it takes (tiles 0 to 2 were asked for at the start).
+        if (asks && (NBUF == 1 ? tt + 1 < n_tiles : tt >= 1 && tt + 2 < n_tiles))
+            ahead_row0 = next_page();
+        if (!tc5::mbar_wait(&kv_bar[buf], (tt / NBUF) & 1) && tid == 0)
+            atomicCAS(&g_decode_status, 0, 1 + tt);
+        // the tile has landed: the new position's row goes over what the page held there,
+        // and the value rows of positions that do not count are zeroed (written by hand,
+        // so ordered here before the copy that may overwrite the buffer later)
+        const int rn = p - jt;
+        const int dead = nlo + (DM_KEYS - n);                 // rows 0 .. nlo - 1 and n .. 63
+        if (rn < DM_KEYS) new_row(Kt, Vt, rn, p_row);
+        for (int i = tid; i < dead * CPR; i += DM_THREADS) {
+            const int q = i / CPR, r = q < nlo ? q : n + q - nlo;
+            *reinterpret_cast<uint4*>(Vt + tm_swz<HDP>(r, i % CPR)) = make_uint4(0, 0, 0, 0);
+        }
+        if (rn < DM_KEYS || dead > 0) tc5::fence_async_shared();
+        // between two tiles that came whole nobody has written anything the others read
+        // before the next barrier, so the walk goes on without one
+        top_barrier = NBUF == 1 || tt == 0 || rn < DM_KEYS || dead > 0;
+    } else if (tt > 0) {
         const int* ro = rowoff + (tt & 1) * DM_KEYS;
         const int rn = p - jt;                               // the new position's row, if in this tile
         if (NBUF == 1) {
@@ -689,8 +833,8 @@ attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq) {
     // (with two buffers the tile after this one stays in flight; the first tile waits for
     // everything because the queries' copies, made after the dependency wait, are among it,
     // and so does a CTA's last tile, which may hold the new position)
-    if (NBUF == 2 && !last && tt > 0) cp_async_wait_but_one(); else cp_async_wait_all();
-    __syncthreads();
+    if (!TMA && NBUF == 2 && !last && tt > 0) cp_async_wait_but_one(); else cp_async_wait_all();
+    if (top_barrier) __syncthreads();
     // ---- scores of 16 heads x this warp's keys
     if constexpr (Sh::KW == 16) {
         float s[2][4] = {};
@@ -699,8 +843,8 @@ attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq) {
             unsigned af[4], bf[4];
             dm_ldsm4(dm_smem(Qs + dm_swz<HDP>(lane & 15, kk * 2 + (lane >> 4))), af);
             const int mat = lane >> 3, r = lane & 7;
-            dm_ldsm4(dm_smem(Kt + dm_swz<HDP>(warp * 16 + r + (mat >> 1) * 8, kk * 2 + (mat & 1))),
-                     bf);
+            dm_ldsm4(dm_smem(Kt + kv_swz<HDP, TMA>(warp * 16 + r + (mat >> 1) * 8,
+                                                   kk * 2 + (mat & 1))), bf);
             dm_mma(s[0], af, bf[0], bf[1]);
             dm_mma(s[1], af, bf[2], bf[3]);
         }
@@ -710,7 +854,8 @@ attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq) {
             for (int e = 0; e < 4; ++e) {
                 const int key = warp * 16 + i * 8 + tig * 2 + (e & 1);
                 const int row = gid + (e >> 1) * 8;
-                Ss[row * DM_KEYS + key] = key < n ? s[i][e] * a.scale : -INFINITY;
+                Ss[row * DM_KEYS + key] =
+                    key >= nlo && key < n ? s[i][e] * a.scale : -INFINITY;
             }
     } else {
         // 8 keys: one load brings their chunks of 32 dims, two products into sums of
@@ -722,7 +867,8 @@ attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq) {
             unsigned a0[4], a1[4], bf[4];
             dm_ldsm4(dm_smem(Qs + dm_swz<HDP>(lane & 15, k2 * 4 + (lane >> 4))), a0);
             dm_ldsm4(dm_smem(Qs + dm_swz<HDP>(lane & 15, k2 * 4 + 2 + (lane >> 4))), a1);
-            dm_ldsm4(dm_smem(Kt + dm_swz<HDP>(warp * 8 + (lane & 7), k2 * 4 + (lane >> 3))), bf);
+            dm_ldsm4(dm_smem(Kt + kv_swz<HDP, TMA>(warp * 8 + (lane & 7), k2 * 4 + (lane >> 3))),
+                     bf);
             dm_mma(s[(k2 & 1) * 2], a0, bf[0], bf[1]);
             dm_mma(s[(k2 & 1) * 2 + 1], a1, bf[2], bf[3]);
         }
@@ -730,11 +876,13 @@ attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq) {
         for (int e = 0; e < 4; ++e) {
             const int key = warp * 8 + tig * 2 + (e & 1);
             const int row = gid + (e >> 1) * 8;
-            Ss[row * DM_KEYS + key] =
-                key < n ? ((s[0][e] + s[1][e]) + (s[2][e] + s[3][e])) * a.scale : -INFINITY;
+            Ss[row * DM_KEYS + key] = key >= nlo && key < n
+                ? ((s[0][e] + s[1][e]) + (s[2][e] + s[3][e])) * a.scale : -INFINITY;
         }
     }
     __syncthreads();
+    if (TMA && NBUF == 3 && asks && tt >= 1 && tt + 2 < n_tiles)
+        request_page((tt + 2) % NBUF, ahead_row0);      // everybody is past the tile before this one
     // ---- softmax weights relative to the running maximum.  Rows are dealt round the
     // warps, so that the few heads of a small group get a warp each; rows beyond the
     // group's heads are padding whose products nobody reads, and are left as they are.
@@ -777,14 +925,17 @@ attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq) {
             for (int nn = 0; nn < NP; ++nn) {
                 unsigned bf[4];
                 const int mat = lane >> 3, r = lane & 7;
-                dm_ldsm4t(dm_smem(Vt + dm_swz<HDP>(kk * 16 + r + (mat & 1) * 8,
-                                                   warp * (Sh::DW / 8) + nn * 2 + (mat >> 1))), bf);
+                dm_ldsm4t(dm_smem(Vt + kv_swz<HDP, TMA>(kk * 16 + r + (mat & 1) * 8,
+                                                        warp * (Sh::DW / 8) + nn * 2 + (mat >> 1))),
+                          bf);
                 dm_mma(o[nn * 2], af, bf[0], bf[1]);
                 dm_mma(o[nn * 2 + 1], af, bf[2], bf[3]);
             }
         }
     }
-    if (NBUF == 2) {
+    if (TMA) {
+        // (asked for above, or at the top of the next round)
+    } else if (NBUF == 2) {
         if (tt + 2 < n_tiles) {
             // this tile's buffers are used up: the tile after the next goes there
             if (tid < DM_KEYS) rowoff[(tt & 1) * DM_KEYS + tid] = next_row;
@@ -882,13 +1033,85 @@ attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq) {
                     &s_last, outp, used_clusters * cs, false);
 }
 
-template <int HDP>
+// A pool [rows, nkv, hd] bfloat16 as a 3-D tensor map read in boxes of [64 rows, 1 head, 64
+// elements]; kept per (pool, nkv, hd).  The number of rows a pool holds is not known
+// here: the map is given more than any pool has, and the rows asked for come from the
+// page table.
+int make_pool_map(CUtensorMap* out, const void* pool, int nkv, int hd) {
+    typedef std::tuple<const void*, int, int> Key;
+    static std::map<Key, CUtensorMap> cache;
+    static std::mutex mu;
+    Key key(pool, nkv, hd);
+    {
+        std::lock_guard<std::mutex> gl(mu);
+        auto it = cache.find(key);
+        if (it != cache.end()) {
+            *out = it->second;
+            return 0;
+        }
+    }
+    tc5::EncodeTiledFn fn = tc5::encode_fn();
+    if (!fn) return agv_fail(-4, "attention_decode: the driver does not export cuTensorMapEncodeTiled");
+    cuuint64_t dims[3] = {(cuuint64_t)hd, (cuuint64_t)nkv, (cuuint64_t)1 << 31};
+    cuuint64_t strides[2] = {(cuuint64_t)hd * 2, (cuuint64_t)nkv * hd * 2};
+    cuuint32_t box[3] = {64, 1, (cuuint32_t)DM_KEYS};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(pool), dims, strides,
+                    box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return agv_fail(-4, "attention_decode: cuTensorMapEncodeTiled failed with code %d (kv heads "
+                        "%d, head_dim %d)", (int)r, nkv, hd);
+    std::lock_guard<std::mutex> gl(mu);
+    if (cache.size() > 4096) cache.clear();
+    cache[key] = *out;
+    return 0;
+}
+
+// Which way the tensor-core form brings its tiles: 0 chosen from the sizes, 1 always 16-byte
+// copies, 2 TMA wherever its sizes allow (AGAVE_B200_DECODE_TILES=copies|tma, or
+// agv_attention_decode_set_tiles; for tests and measurements).
+int g_decode_tiles = -1;
+int decode_tiles_form() {
+    if (g_decode_tiles < 0) {
+        const char* e = getenv("AGAVE_B200_DECODE_TILES");
+        g_decode_tiles = !e ? 0 : !strcmp(e, "copies") ? 1 : !strcmp(e, "tma") ? 2 : 0;
+    }
+    return g_decode_tiles;
+}
+
+int decode_sms() {
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+            sms = 148;
+    }
+    return sms;
+}
+
+// CTAs per sequence: as many as stay resident together over the whole batch, at most one
+// per tile of the longest sequence a launch may see; up to eight form a cluster, more
+// clusters leave one partial result each.
+void ctas_per_sequence(int resident, int pairs, int most, int* cs, int* clusters) {
+    int per_seq = resident / pairs;
+    if (per_seq > most) per_seq = most;
+    if (per_seq < 1) per_seq = 1;
+    *cs = 1;
+    while (*cs < 8 && *cs * 2 <= per_seq) *cs *= 2;
+    *clusters = per_seq / *cs;
+    if (*clusters < 1) *clusters = 1;
+    if (*clusters > 16) *clusters = 16;
+}
+
+template <int HDP, bool TMA>
 int launch_decode_mma(const DecodeArgs& a0, int B, cudaStream_t stream, const FuseQK& fq) {
-    auto kern = attention_decode_mma_kernel<HDP>;
+    auto kern = attention_decode_mma_kernel<HDP, TMA>;
     constexpr int DM_THREADS = DmShape<HDP>::NT;
-    constexpr int smem = (2 * DM_KEYS + DM_HEADS) * HDP * 2 + DM_HEADS * DM_KEYS * (2 + 4) +
-                         DM_HEADS * 3 * 4 + 2 * DM_KEYS * 4 +
-                         (DmShape<HDP>::NBUF - 1) * 2 * DM_KEYS * HDP * 2;
+    constexpr int NBUF = TMA ? DmShape<HDP>::NBUF_TMA : DmShape<HDP>::NBUF;
+    constexpr int smem = (2 * NBUF * DM_KEYS + DM_HEADS) * HDP * 2 + DM_HEADS * DM_KEYS * (2 + 4) +
+                         DM_HEADS * 3 * 4 + 2 * DM_KEYS * 4 + (TMA ? 1024 : 0);
     static bool configured = false;
     static int resident = 0;
     if (!configured) {
@@ -901,27 +1124,50 @@ int launch_decode_mma(const DecodeArgs& a0, int B, cudaStream_t stream, const Fu
         configured = true;
     }
     DecodeArgs a = a0;
+    PoolMaps<TMA> maps;
+    if constexpr (TMA) {
+        if (int rc = make_pool_map(&maps.k, a.k_pool, a.nkv, a.hd)) return rc;
+        if (int rc = make_pool_map(&maps.v, a.v_pool, a.nkv, a.hd)) return rc;
+    }
     const int G = a.nh / a.nkv;
     const int groups = a.nkv * ((G + DM_HEADS - 1) / DM_HEADS);
-    // CTAs per sequence: as many as stay resident together over the whole batch, at
-    // most one per tile of the longest sequence this launch may see (a.n_splits on
-    // entry); up to eight form a cluster, more clusters leave one partial result each
-    int per_seq = resident / (groups * B);
-    if (per_seq > a.n_splits) per_seq = a.n_splits;
-    if (per_seq < 1) per_seq = 1;
-    int cs = 1;
-    while (cs < 8 && cs * 2 <= per_seq) cs *= 2;
-    int clusters = per_seq / cs;
-    if (clusters < 1) clusters = 1;
-    if (clusters > 16) clusters = 16;
+    // (a.n_splits on entry: the tiles of the longest sequence this launch may see; a window
+    // or context that does not start on a page touches one page more)
+    int cs, clusters;
+    ctas_per_sequence(resident, groups * B, a.n_splits + (TMA ? 1 : 0), &cs, &clusters);
     a.n_splits = clusters;                         // partial results per (sequence, head)
     dim3 grid(clusters * cs, groups, B);
     if (cs > 1)
-        agv_launch_cluster(kern, grid, DM_THREADS, smem, stream, dim3(cs, 1, 1), a, cs, fq);
+        agv_launch_cluster(kern, grid, DM_THREADS, smem, stream, dim3(cs, 1, 1), a, cs, fq, maps);
     else
-        agv_launch(kern, grid, DM_THREADS, smem, stream, a, 1, fq);
+        agv_launch(kern, grid, DM_THREADS, smem, stream, a, 1, fq, maps);
     AGV_LAUNCH_OK("attention_decode_mma_kernel");
     return 0;
+}
+
+// The tensor-core form for a head size, its tiles by TMA where the cache's geometry is the
+// tiles' (pages of 64 positions, a ring of whole pages, a head as wide as its tile).
+template <int HDP>
+int launch_decode_form(const DecodeArgs& a, int B, cudaStream_t stream, const FuseQK& fq) {
+    const bool can = a.page == DM_KEYS && a.cap % DM_KEYS == 0 && a.hd == HDP &&
+                     agv_aligned(a.k_pool, 128) && agv_aligned(a.v_pool, 128);
+    const int form = decode_tiles_form();
+    // Pages cost a tile more than tiles that start at the window's first key, and a request
+    // by TMA saves its time per tile: taken where a CTA may walk six tiles or more
+    // (measured: 16 sequences with the 27B model's heads and a window of 1,024, one CTA a
+    // pair, 34.8 -> 27.1 us; 64 sequences of up to 2,048 with heads of 256, four CTAs a
+    // sequence, 31.2 -> 28.0; with a window of 512 there, nine pages for eight tiles, 13.2
+    // -> 15.5, and one tile per CTA at 8 sequences 5.5 -> 8.1)
+    bool tma = can && form == 2;
+    if (can && form == 0) {
+        const int G = a.nh / a.nkv, groups = a.nkv * ((G + DM_HEADS - 1) / DM_HEADS);
+        int cs, clusters;
+        ctas_per_sequence(decode_sms() * (DmShape<HDP>::NT == 256 ? 2 : 3), groups * B,
+                          a.n_splits + 1, &cs, &clusters);
+        tma = a.n_splits + 1 >= 6 * cs * clusters;
+    }
+    if (tma) return launch_decode_mma<HDP, true>(a, B, stream, fq);
+    return launch_decode_mma<HDP, false>(a, B, stream, fq);
 }
 
 int pick_chunk(int hd, int elem) {
@@ -989,9 +1235,9 @@ static int attention_decode_impl(const void* q, long long q_stride, void* out, i
                  counters, max_pages, page, cap, nh, nkv, hd, window, n_splits, ch, scale};
     if (dtype == AGV_BF16 && hd % 8 == 0 && hd <= 256 && ch == DM_KEYS &&
         (fq.part || (q_stride % 8 == 0 && agv_aligned(q, 16)))) {
-        if (hd <= 64) return launch_decode_mma<64>(a, B, stream, fq);
-        if (hd <= 128) return launch_decode_mma<128>(a, B, stream, fq);
-        return launch_decode_mma<256>(a, B, stream, fq);
+        if (hd <= 64) return launch_decode_form<64>(a, B, stream, fq);
+        if (hd <= 128) return launch_decode_form<128>(a, B, stream, fq);
+        return launch_decode_form<256>(a, B, stream, fq);
     }
     AGV_REQUIRE(!fq.part, "attention_decode: the fused form needs the tensor-core kernel");
     const int G = nh / nkv;
@@ -1127,4 +1373,23 @@ AGV_API int agv_attention_decode_static(const void* q, long long q_stride, void*
     return agv_attention_decode(q, q_stride, out, dtype, k_pool, v_pool, page_table, slots,
                                 positions, max_pages, page, cap, B, nh, nkv, hd, scale, window,
                                 max_keys, base, base + acc_floats, counters, stream);
+}
+
+// 0, or 1 + the tile at which a bounded wait of the TMA form for a key / value tile gave up
+// first since the last call (this call synchronises the device and clears the word).
+AGV_API int agv_attention_decode_status() {
+    int v = 0, zero = 0;
+    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+    if (cudaMemcpyFromSymbol(&v, g_decode_status, sizeof(int)) != cudaSuccess) return -1;
+    if (v) cudaMemcpyToSymbol(g_decode_status, &zero, sizeof(int));
+    return v;
+}
+
+// 0: the way the tiles come is chosen from the sizes; 1: always 16-byte copies; 2: TMA
+// wherever the cache's geometry allows it.  Returns the setting before.
+AGV_API int agv_attention_decode_set_tiles(int form) {
+    AGV_REQUIRE(form >= 0 && form <= 2, "attention_decode_set_tiles: 0, 1 or 2");
+    const int before = decode_tiles_form();
+    g_decode_tiles = form;
+    return before;
 }

@@ -838,6 +838,25 @@ def _decode_counters(device: torch.device, n: int) -> torch.Tensor:
     return t
 
 
+def attention_decode_status() -> int:
+    """0, or 1 + the tile at which a bounded wait of the decode attention for a tile of keys
+    and values gave up first since the last call (this call synchronises the device)."""
+    return library().agv_attention_decode_status()
+
+
+DECODE_TILES = {"auto": 0, "copies": 1, "tma": 2}
+
+
+def attention_decode_tiles(form: str) -> str:
+    """How the tensor-core decode attention brings its key / value tiles: "auto" (from the
+    sizes), "copies" (16-byte copies by all threads) or "tma" (the cache's pages as TMA
+    boxes, wherever the cache's geometry allows).  Returns the setting before."""
+    before = library().agv_attention_decode_set_tiles(DECODE_TILES[form])
+    if before < 0:
+        raise KernelError("attention_decode_set_tiles failed")
+    return {v: k for k, v in DECODE_TILES.items()}[before]
+
+
 def prepare_device(device: torch.device) -> None:
     """Allocate what the kernels share on a device before any graph is recorded."""
     _decode_counters(device, 65536)

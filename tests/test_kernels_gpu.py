@@ -16,6 +16,17 @@ def rnd(*shape, dtype=torch.float32, seed=0, scale=1.0):
     return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
 
 
+@pytest.fixture(params=["copies", "tma"])
+def decode_tiles(request):
+    """Both ways the tensor-core decode attention brings its key / value tiles (TMA wherever
+    the sizes allow it); afterwards no bounded wait of the TMA form may have given up."""
+    from agave_b200 import kernels
+    before = kernels.attention_decode_tiles(request.param)
+    yield request.param
+    kernels.attention_decode_tiles(before)
+    assert kernels.attention_decode_status() == 0
+
+
 def rel_err(got, ref):
     got, ref = got.double().cpu(), ref.double().cpu()
     return ((got - ref).abs().max() / ref.abs().max().clamp_min(1e-30)).item()
@@ -641,7 +652,7 @@ def test_repeat_penalty_per_occurrence_and_history():
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("nh,nkv,hd", [(4, 1, 256), (16, 2, 128), (5, 5, 80), (12, 2, 512),
                                        (3, 1, 208), (2, 2, 48), (34, 2, 112)])
-def test_attention_decode_split_long_sequences(dtype, nh, nkv, hd):
+def test_attention_decode_split_long_sequences(dtype, nh, nkv, hd, decode_tiles):
     """Several chunks per sequence, groups wider than the kernel's head tile,
     a far key that must win, and a window edge in the middle of a chunk."""
     from agave_b200 import kernels
@@ -679,11 +690,13 @@ def test_attention_decode_split_long_sequences(dtype, nh, nkv, hd):
 
 @pytest.mark.parametrize("B,nh,nkv,hd", [(64, 8, 4, 256), (96, 4, 1, 128), (200, 4, 2, 64),
                                         (700, 4, 2, 64), (300, 2, 2, 128)])
-def test_attention_decode_many_sequences_walk_several_tiles(B, nh, nkv, hd):
+def test_attention_decode_many_sequences_walk_several_tiles(B, nh, nkv, hd, decode_tiles):
     """With many sequences a sequence gets few CTAs, each of which walks several key
     tiles with a running softmax (and, with fewer still, a single CTA the whole
     sequence): unequal lengths up to a dozen tiles, padding entries in between, a
-    window, against the one-warp kernel."""
+    window, against the one-warp kernel.  What the last page of a sequence holds beyond
+    its newest position is not a number: a kernel that brings whole pages must not let
+    it through."""
     from agave_b200 import kernels
     PAGE, max_pages = 64, 12
     g = torch.Generator().manual_seed(7)
@@ -699,6 +712,11 @@ def test_attention_decode_many_sequences_walk_several_tiles(B, nh, nkv, hd):
     positions = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=DEV)
     seq_index = torch.arange(B, dtype=torch.int32, device=DEV)
     cap = max_pages * PAGE
+    for b in range(0, B, 3):
+        if int(slots[b]) >= 0 and lens[b] % PAGE:
+            pg = int(table[int(slots[b]), (lens[b] - 1) // PAGE])
+            k_pool[pg, lens[b] % PAGE:] = float("nan")
+            v_pool[pg, lens[b] % PAGE:] = float("nan")
     for window in (0, 200):
         ref = torch.empty((B, nh * hd), dtype=torch.bfloat16, device=DEV)
         live = (slots >= 0).nonzero().flatten()
@@ -719,7 +737,8 @@ def test_attention_decode_many_sequences_walk_several_tiles(B, nh, nkv, hd):
                                                 (8, 8, 64, 70, 9), (6, 3, 128, 64, 16),
                                                 (32, 2, 256, 0, 2), (20, 1, 128, 0, 4)])
 @pytest.mark.parametrize("norm,rotate", [(True, True), (False, False)])
-def test_attention_decode_with_norm_rotation_and_store_inside(nh, nkv, hd, window, G, norm, rotate):
+def test_attention_decode_with_norm_rotation_and_store_inside(nh, nkv, hd, window, G, norm, rotate,
+                                                              decode_tiles):
     """The decode attention that forms q, k and v of the new position from the
     projection's partial sums, against the separate norm / rotation / store launch
     followed by the plain decode attention: the outputs, the cache rows it writes, and
@@ -898,7 +917,7 @@ def test_attention_prefill_tcgen05_long_sequences(window):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("W,nh,nkv,hd", [(128, 4, 1, 64), (64, 6, 2, 128), (128, 4, 1, 256)])
-def test_attention_decode_ring_as_large_as_the_window(dtype, W, nh, nkv, hd):
+def test_attention_decode_ring_as_large_as_the_window(dtype, W, nh, nkv, hd, decode_tiles):
     """cap == window: the row that held key p - W holds key p itself, so the oldest key in
     the window sits in the row right after the newest.  Lengths below, at and past the
     first wrap (129, 256, 300 for a ring of 128).  The newest key and the oldest key in

@@ -182,12 +182,24 @@ def test_generation_in_a_random_configuration(seed, dtype):
         shutil.rmtree(folder, ignore_errors=True)
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("dtype,tiles", [("float32", "auto"), ("bfloat16", "auto"),
+                                         ("bfloat16", "tma")])
 @pytest.mark.parametrize("seed", [0, 3, 11, 16, 26, 51, 54, 73])
-def test_large_batches_of_long_unequal_sequences(seed, dtype):
+def test_large_batches_of_long_unequal_sequences(seed, dtype, tiles):
     """8 to 48 prompts of 1 to 2,500 tokens in one step, then three tokens each: decode
     attention with few CTAs per sequence that walk several tiles, windows from 128 to
-    1,500 as rings, wide heads; the logits at each prompt's end and of the decoded tokens."""
+    1,500 as rings, wide heads; the logits at each prompt's end and of the decoded tokens.
+    In bfloat16 also with the key / value tiles brought by TMA wherever the sizes allow."""
+    from agave_b200 import kernels
+    before = kernels.attention_decode_tiles(tiles)
+    try:
+        _large_batch(seed, dtype)
+    finally:
+        kernels.attention_decode_tiles(before)
+    assert kernels.attention_decode_status() == 0
+
+
+def _large_batch(seed, dtype):
     from agave_b200.engine.api import Engine
     from agave_b200.weights import write_model_folder
     from plain import gemma3_plain as P
