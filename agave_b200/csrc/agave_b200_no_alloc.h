@@ -29,6 +29,9 @@
  *   - The first call on a device looks up the array's device address
  *     (cudaGetSymbolAddress, with that device current).  Make that first call
  *     before any stream capture begins on that device.
+ *   - Where many sequences or long contexts make the kernel fetch the cache's pages by
+ *     TMA, the first call for a pair of pools encodes two tensor maps and keeps them in
+ *     host memory (a host-side table; nothing on the device).
  *   - max_keys must be at least the number of keys any entry attends to
  *     (position + 1, or the window if that is smaller): it sizes the grid.  An
  *     entry with more keys gets no output from that call.  The call clears the
