@@ -1153,7 +1153,8 @@ int launch_decode_form(const DecodeArgs& a, int B, cudaStream_t stream, const Fu
                      agv_aligned(a.k_pool, 128) && agv_aligned(a.v_pool, 128);
     const int form = decode_tiles_form();
     // Pages cost a tile more than tiles that start at the window's first key, and a request
-    // by TMA saves its time per tile: taken where a CTA may walk six tiles or more
+    // by TMA saves its time per tile: taken where a CTA may walk six tiles or more (four
+    // with heads of up to 128)
     // (measured: 16 sequences with the 27B model's heads and a window of 1,024, one CTA a
     // pair, 34.8 -> 27.1 us; 64 sequences of up to 2,048 with heads of 256, four CTAs a
     // sequence, 31.2 -> 28.0; with a window of 512 there, nine pages for eight tiles, 13.2
@@ -1164,7 +1165,9 @@ int launch_decode_form(const DecodeArgs& a, int B, cudaStream_t stream, const Fu
         int cs, clusters;
         ctas_per_sequence(decode_sms() * (DmShape<HDP>::NT == 256 ? 2 : 3), groups * B,
                           a.n_splits + 1, &cs, &clusters);
-        tma = a.n_splits + 1 >= 6 * cs * clusters;
+        // (with three pages in flight, head sizes up to 128, four tiles are enough: four
+        // sequences with the 27B model's heads and a window of 1,024 13.4 -> 11.5 us)
+        tma = a.n_splits + 1 >= (DmShape<HDP>::NBUF_TMA == 3 ? 4 : 6) * cs * clusters;
     }
     if (tma) return launch_decode_mma<HDP, true>(a, B, stream, fq);
     return launch_decode_mma<HDP, false>(a, B, stream, fq);
