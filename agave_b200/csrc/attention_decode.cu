@@ -591,9 +591,15 @@ attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq,
     }
     const int p = a.positions[b];
     const int lo = a.window > 0 ? max(0, p - a.window + 1) : 0;
-    // tiles this sequence has: from its first key on, or (TMA) the cache pages it touches
-    const int k0 = TMA ? lo / DM_KEYS : 0;
-    const int all_tiles = TMA ? p / DM_KEYS - k0 + 1 : (p - lo) / DM_KEYS + 1;
+    // Tiles this sequence has: from its first key on, or (TMA) the cache pages it touches.
+    // A full window in a ring of its own size is the ring's pages, every row of them: the
+    // tiles are then counted in ring rows (tile k is the ring's page k), which saves the
+    // page that a window's two ragged ends would otherwise cost.
+    const bool ringed = TMA && a.window > 0 && a.cap == a.window && p >= a.window - 1;
+    const int pt = ringed ? p % a.cap : p;                    // p on the scale the tiles are counted in
+    const int k0 = TMA && !ringed ? lo / DM_KEYS : 0;
+    const int all_tiles = ringed ? a.cap / DM_KEYS
+                          : TMA  ? p / DM_KEYS - k0 + 1 : (p - lo) / DM_KEYS + 1;
     const int used = min(W, all_tiles);                       // CTAs of it with work
     const int cid = split / cs, crank = split % cs;
     const int used_clusters = (used + cs - 1) / cs;
@@ -778,8 +784,8 @@ attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq,
     int ahead_row0 = -1;                                    // TMA: first cache row of the page asked for next
     for (int tt = 0; tt < n_tiles; ++tt) {
     const int jt = j0 + tt * W * DM_KEYS;                   // first key of this tile
-    const int n = min(DM_KEYS, p - jt + 1);                 // its keys: rows nlo .. n - 1
-    const int nlo = TMA ? max(0, lo - jt) : 0;
+    const int n = ringed ? DM_KEYS : min(DM_KEYS, p - jt + 1);    // its keys: rows nlo .. n - 1
+    const int nlo = TMA && !ringed ? max(0, lo - jt) : 0;
     const bool last = tt + 1 == n_tiles;
     // this tile's buffers (the tiles take turns where there are two or three)
     const int buf = NBUF == 1 ? 0 : NBUF == 2 ? tt & 1 : tt % NBUF;
@@ -809,17 +815,18 @@ attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq,
         // the tile has landed: the new position's row goes over what the page held there,
         // and the value rows of positions that do not count are zeroed (written by hand,
         // so ordered here before the copy that may overwrite the buffer later)
-        const int rn = p - jt;
+        const int rn = pt - jt;
         const int dead = nlo + (DM_KEYS - n);                 // rows 0 .. nlo - 1 and n .. 63
-        if (rn < DM_KEYS) new_row(Kt, Vt, rn, p_row);
+        const bool holds_new = rn >= 0 && rn < DM_KEYS;
+        if (holds_new) new_row(Kt, Vt, rn, p_row);
         for (int i = tid; i < dead * CPR; i += DM_THREADS) {
             const int q = i / CPR, r = q < nlo ? q : n + q - nlo;
             *reinterpret_cast<uint4*>(Vt + tm_swz<HDP>(r, i % CPR)) = make_uint4(0, 0, 0, 0);
         }
-        if (rn < DM_KEYS || dead > 0) tc5::fence_async_shared();
+        if (holds_new || dead > 0) tc5::fence_async_shared();
         // between two tiles that came whole nobody has written anything the others read
         // before the next barrier, so the walk goes on without one
-        top_barrier = NBUF == 1 || tt == 0 || rn < DM_KEYS || dead > 0;
+        top_barrier = NBUF == 1 || tt == 0 || holds_new || dead > 0;
     } else if (tt > 0) {
         const int* ro = rowoff + (tt & 1) * DM_KEYS;
         const int rn = p - jt;                               // the new position's row, if in this tile
@@ -1105,6 +1112,13 @@ void ctas_per_sequence(int resident, int pairs, int most, int* cs, int* clusters
     if (*clusters > 16) *clusters = 16;
 }
 
+// The tiles of the longest sequence a launch may see (a.n_splits on entry): as pages, a
+// window that does not start on one touches one page more, unless it is a ring of its own
+// size.
+int most_tiles(const DecodeArgs& a, bool pages) {
+    return a.n_splits + (pages && a.window > 0 && a.cap != a.window ? 1 : 0);
+}
+
 template <int HDP, bool TMA>
 int launch_decode_mma(const DecodeArgs& a0, int B, cudaStream_t stream, const FuseQK& fq) {
     auto kern = attention_decode_mma_kernel<HDP, TMA>;
@@ -1131,10 +1145,8 @@ int launch_decode_mma(const DecodeArgs& a0, int B, cudaStream_t stream, const Fu
     }
     const int G = a.nh / a.nkv;
     const int groups = a.nkv * ((G + DM_HEADS - 1) / DM_HEADS);
-    // (a.n_splits on entry: the tiles of the longest sequence this launch may see; a window
-    // or context that does not start on a page touches one page more)
     int cs, clusters;
-    ctas_per_sequence(resident, groups * B, a.n_splits + (TMA ? 1 : 0), &cs, &clusters);
+    ctas_per_sequence(resident, groups * B, most_tiles(a, TMA), &cs, &clusters);
     a.n_splits = clusters;                         // partial results per (sequence, head)
     dim3 grid(clusters * cs, groups, B);
     if (cs > 1)
@@ -1163,11 +1175,15 @@ int launch_decode_form(const DecodeArgs& a, int B, cudaStream_t stream, const Fu
     if (can && form == 0) {
         const int G = a.nh / a.nkv, groups = a.nkv * ((G + DM_HEADS - 1) / DM_HEADS);
         int cs, clusters;
-        ctas_per_sequence(decode_sms() * (DmShape<HDP>::NT == 256 ? 2 : 3), groups * B,
-                          a.n_splits + 1, &cs, &clusters);
+        const int most = most_tiles(a, true);
+        ctas_per_sequence(decode_sms() * (DmShape<HDP>::NT == 256 ? 2 : 3), groups * B, most, &cs,
+                          &clusters);
         // (with three pages in flight, head sizes up to 128, four tiles are enough: four
-        // sequences with the 27B model's heads and a window of 1,024 13.4 -> 11.5 us)
-        tma = a.n_splits + 1 >= (DmShape<HDP>::NBUF_TMA == 3 ? 4 : 6) * cs * clusters;
+        // sequences with the 27B model's heads and a window of 1,024 13.4 -> 11.5 us.  Where
+        // a window is a ring of its own size, whose pages are its tiles exactly, two tiles a
+        // CTA are enough alone, 64 sequences with heads of 256 and a window of 512 12.5 ->
+        // 11.8 us, but a step shows no gain from it, so the rule is the same there)
+        tma = most >= (DmShape<HDP>::NBUF_TMA == 3 ? 4 : 6) * cs * clusters;
     }
     if (tma) return launch_decode_mma<HDP, true>(a, B, stream, fq);
     return launch_decode_mma<HDP, false>(a, B, stream, fq);
