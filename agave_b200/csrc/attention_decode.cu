@@ -680,6 +680,21 @@ attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq,
             tc5::tma_load_3d(Ks + (buf * 2 + (warp & 1)) * TILE + x * DM_KEYS * 64,
                              warp & 1 ? &maps.v : &maps.k, x * 64, g, row0, bar);
     };
+    // With a single buffer (head size 256) keys and values are asked for apart, each as soon
+    // as its half of the buffer is free: the next tile's keys when everybody has this tile's
+    // scores, its values when everybody has this tile's weighted sum (kv_bar[0] counts the
+    // keys in, kv_bar[1] the values), so that a trip to memory runs beside half a tile's work
+    // instead of beside none.
+    constexpr bool APART = TMA && NBUF == 1;
+    auto request_half = [&](int which, int row0) {             // (only where asks)
+        if ((warp & 1) != which) return;
+        uint64_t* bar = &kv_bar[which];
+        if (warp == which) tc5::mbar_expect_tx(bar, TILE * (unsigned)sizeof(T));
+        const int x = warp >> 1;
+        if constexpr (TMA)
+            tc5::tma_load_3d(Ks + which * TILE + x * DM_KEYS * 64, which ? &maps.v : &maps.k,
+                             x * 64, g, row0, bar);
+    };
     // Keys and values of earlier positions were stored by earlier steps: their copies
     // start before the wait too.  Only the row of position p is the predecessor's.
     const int r_new = p - j0;                                 // in [0, 64): the first tile holds p
@@ -704,8 +719,15 @@ attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq,
         cp_async_commit();
     };
     if (TMA) {
-        if (has && asks)
-            for (int t = 0; t < min(n_tiles, NBUF); ++t) request_page(t, next_page());
+        if (has && asks) {
+            if (APART) {
+                const int row0 = next_page();
+                request_half(0, row0);
+                request_half(1, row0);
+            } else {
+                for (int t = 0; t < min(n_tiles, NBUF); ++t) request_page(t, next_page());
+            }
+        }
     } else if (has) {
         // the first tile (and the second, where there is room for it); the others are
         // requested inside the walk below
@@ -791,7 +813,7 @@ attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq,
     const int buf = NBUF == 1 ? 0 : NBUF == 2 ? tt & 1 : tt % NBUF;
     T* const Kt = Ks + buf * 2 * TILE;
     T* const Vt = Kt + TILE;
-    bool top_barrier = true;
+    bool top_barrier = true, values_here = true;
     // the rows of the tile that is requested next (the next one; with two buffers the one
     // after it): the lookup runs beside this tile's work
     const int ahead = NBUF * W * DM_KEYS;
@@ -800,9 +822,10 @@ attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq,
         next_row = WALK ? next_lookup() : row_of(jt + ahead);
     if constexpr (TMA) {
         if (NBUF == 1 && tt > 0) {
-            // the tile before has been used up: this one replaces it
+            // the tile before has been used up: this one's values replace its values (this
+            // one's keys were asked for when the scores of the tile before were done)
             __syncthreads();
-            if (asks) request_page(0, ahead_row0);
+            if (asks) request_half(1, ahead_row0);
         }
         // The page that is asked for next is looked up beside this tile's work: with one
         // buffer the next tile's, asked for at the top of the next round; with three the
@@ -812,6 +835,14 @@ attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq,
             ahead_row0 = next_page();
         if (!tc5::mbar_wait(&kv_bar[buf], (tt / NBUF) & 1) && tid == 0)
             atomicCAS(&g_decode_status, 0, 1 + tt);
+        const int rn0 = pt - jt;
+        values_here = !APART;
+        if (APART && ((rn0 >= 0 && rn0 < DM_KEYS) || nlo > 0 || n < DM_KEYS)) {
+            // a tile that is written into by hand: its values have to be there as well
+            if (!tc5::mbar_wait(&kv_bar[1], tt & 1) && tid == 0)
+                atomicCAS(&g_decode_status, 0, 1 + tt);
+            values_here = true;
+        }
         // the tile has landed: the new position's row goes over what the page held there,
         // and the value rows of positions that do not count are zeroed (written by hand,
         // so ordered here before the copy that may overwrite the buffer later)
@@ -826,7 +857,7 @@ attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq,
         if (holds_new || dead > 0) tc5::fence_async_shared();
         // between two tiles that came whole nobody has written anything the others read
         // before the next barrier, so the walk goes on without one
-        top_barrier = NBUF == 1 || tt == 0 || holds_new || dead > 0;
+        top_barrier = tt == 0 || holds_new || dead > 0;
     } else if (tt > 0) {
         const int* ro = rowoff + (tt & 1) * DM_KEYS;
         const int rn = p - jt;                               // the new position's row, if in this tile
@@ -890,6 +921,8 @@ attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq,
     __syncthreads();
     if (TMA && NBUF == 3 && asks && tt >= 1 && tt + 2 < n_tiles)
         request_page((tt + 2) % NBUF, ahead_row0);      // everybody is past the tile before this one
+    if (APART && asks && tt + 1 < n_tiles)
+        request_half(0, ahead_row0);                    // everybody is past this tile's keys
     // ---- softmax weights relative to the running maximum.  Rows are dealt round the
     // warps, so that the few heads of a small group get a warp each; rows beyond the
     // group's heads are padding whose products nobody reads, and are left as they are.
@@ -914,6 +947,8 @@ attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq,
         }
     }
     __syncthreads();
+    if (APART && !values_here && !tc5::mbar_wait(&kv_bar[1], tt & 1) && tid == 0)
+        atomicCAS(&g_decode_status, 0, 1 + tt);
     // ---- weighted values: this warp's share of the head dimension
     {
         if (tt > 0) {
@@ -1164,13 +1199,17 @@ int launch_decode_form(const DecodeArgs& a, int B, cudaStream_t stream, const Fu
     const bool can = a.page == DM_KEYS && a.cap % DM_KEYS == 0 && a.hd == HDP &&
                      agv_aligned(a.k_pool, 128) && agv_aligned(a.v_pool, 128);
     const int form = decode_tiles_form();
-    // Pages cost a tile more than tiles that start at the window's first key, and a request
-    // by TMA saves its time per tile: taken where a CTA may walk six tiles or more (four
-    // with heads of up to 128)
-    // (measured: 16 sequences with the 27B model's heads and a window of 1,024, one CTA a
-    // pair, 34.8 -> 27.1 us; 64 sequences of up to 2,048 with heads of 256, four CTAs a
-    // sequence, 31.2 -> 28.0; with a window of 512 there, nine pages for eight tiles, 13.2
-    // -> 15.5, and one tile per CTA at 8 sequences 5.5 -> 8.1)
+    // A request by TMA saves its time per tile, and a window that does not start on a page
+    // costs a page more than it has tiles: taken where a CTA may walk four tiles or more
+    // (six with heads of 256, where 8 sequences of a 1B step, four tiles a CTA at most and in
+    // the measured case one, lose 0.9 % of the step to it although the kernel alone is as
+    // fast; two where a window is a ring of its own size, whose pages are its tiles exactly).
+    // Measured alone, 16-byte copies against TMA: 16 sequences with the 27B model's heads
+    // and a window of 1,024, one CTA a pair, 34.8 -> 26.5 us; 64 sequences of up to 2,048
+    // with heads of 256, four CTAs a sequence, 32.3 -> 23.7, and 125 -> 77 at 4,096 to
+    // 8,000 positions; 8 sequences of 256 to 4,096 with four kv heads of 256 32.6 -> 23.6;
+    // 64 sequences with a ring of 512 12.5 -> 11.2; but one tile per CTA (8 sequences with
+    // a ring of 512) 5.7 -> 6.1, which stays with the copies.
     bool tma = can && form == 2;
     if (can && form == 0) {
         const int G = a.nh / a.nkv, groups = a.nkv * ((G + DM_HEADS - 1) / DM_HEADS);
@@ -1178,12 +1217,8 @@ int launch_decode_form(const DecodeArgs& a, int B, cudaStream_t stream, const Fu
         const int most = most_tiles(a, true);
         ctas_per_sequence(decode_sms() * (DmShape<HDP>::NT == 256 ? 2 : 3), groups * B, most, &cs,
                           &clusters);
-        // (with three pages in flight, head sizes up to 128, four tiles are enough: four
-        // sequences with the 27B model's heads and a window of 1,024 13.4 -> 11.5 us.  Where
-        // a window is a ring of its own size, whose pages are its tiles exactly, two tiles a
-        // CTA are enough alone, 64 sequences with heads of 256 and a window of 512 12.5 ->
-        // 11.8 us, but a step shows no gain from it, so the rule is the same there)
-        tma = most >= (DmShape<HDP>::NBUF_TMA == 3 ? 4 : 6) * cs * clusters;
+        const bool ring = a.window > 0 && a.cap == a.window;
+        tma = most >= (ring ? 2 : DmShape<HDP>::NBUF_TMA == 3 ? 4 : 6) * cs * clusters;
     }
     if (tma) return launch_decode_mma<HDP, true>(a, B, stream, fq);
     return launch_decode_mma<HDP, false>(a, B, stream, fq);
